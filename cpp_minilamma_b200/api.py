@@ -1,0 +1,131 @@
+"""The Python entry point: load a model folder (or make random weights) and generate.
+
+    import cpp_minilamma_b200 as ml
+    llm = ml.load("/path/to/model", dtype="bfloat16", max_tokens=8192)
+    outputs = llm.generate([[1, 5, 9], [1, 7]], max_new_tokens=16)          # lists of token ids
+    outputs = llm.generate(prompts, max_new_tokens=16, temperature=0.8, top_k=40, seed=1)
+
+The reference has no Python API (its scripts spawn the `mini-llama` binary); option names
+follow its CLI and sampler: `n_predict` is accepted as an alias of `max_new_tokens`
+(app/backend_cli.cc:96), `temperature`, `top_k`, `seed` are the fields of its
+`SamplerParmas` (include/sampler.h:7-15).
+"""
+from __future__ import annotations
+
+from pathlib import Path
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import models  # noqa: F401  (registers architectures)
+from .config.base import ModelConfig, load_config, lookup_architecture
+from .engine.generate import Backend, Completion, generate
+from .engine.model import Model
+from .engine.step import Engine, StepEntry
+from .sampling.sampler import DeviceSampler, SamplingParams
+from .weights.loader import load_tensors
+from .weights.random_init import random_tensors
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    if dtype not in _DTYPES:
+        raise ValueError(f"dtype {dtype!r} not supported (bfloat16 or float32)")
+    return _DTYPES[dtype]
+
+
+def require_cuda(device) -> torch.device:
+    device = torch.device(device)
+    if device.type != "cuda" or not torch.cuda.is_available():
+        raise RuntimeError("cpp_minilamma_b200 runs on a CUDA device only (there is no CPU path); "
+                           f"asked for {device}, cuda available: {torch.cuda.is_available()}")
+    return device
+
+
+class EngineBackend(Backend):
+    """Connects the generation loop to an engine and a device sampler."""
+
+    def __init__(self, engine: Engine, params: SamplingParams):
+        self.engine = engine
+        self.params = params
+        self.sampler = DeviceSampler(engine.device)
+        self.n_slots = engine.cache.n_slots
+        self.n_pages = engine.cache.n_pages
+        self.max_positions = engine.model.max_positions
+        self.steps = 0
+
+    def acquire(self, count):
+        return self.engine.acquire(count)
+
+    def release(self, slot):
+        self.engine.release(slot)
+
+    def step_and_sample(self, entries, requests, steps):
+        logits = self.engine.step_borrowed(entries)
+        self.steps += 1
+        return self.sampler.sample(logits, self.params, requests, steps)
+
+
+class LLM:
+    def __init__(self, config: ModelConfig, model: Model, max_tokens: int, max_seqs: Optional[int] = None,
+                 max_step_tokens: int = 8192):
+        self.config = config
+        self.model = model
+        self.engine = Engine(model, max_tokens, max_seqs, max_step_tokens)
+
+    @property
+    def stop_token_ids(self) -> List[int]:
+        return list(self.model.spec.stop_token_ids)
+
+    def generate_detailed(self, prompts: Sequence[Sequence[int]], max_new_tokens=None, temperature: float = 0.0,
+                          top_k: int = 0, seed: int = 1, stop_ids: Optional[Sequence[int]] = None,
+                          ignore_eos: bool = False, max_batch: Optional[int] = None, clip: bool = False,
+                          n_predict=None) -> List[Completion]:
+        if max_new_tokens is None:
+            max_new_tokens = 4 if n_predict is None else n_predict  # the reference CLI's default of 4
+        params = SamplingParams(float(temperature), int(top_k), int(seed))
+        params.validate(self.model.spec.vocab_size)
+        stops = set(self.stop_token_ids) | set(stop_ids or ())
+        backend = EngineBackend(self.engine, params)
+        return generate(backend, prompts, max_new_tokens, stops, ignore_eos, max_batch, clip)
+
+    def generate(self, prompts: Sequence[Sequence[int]], **options) -> List[List[int]]:
+        """Token ids generated for each prompt (stop tokens are not included)."""
+        return [c.tokens for c in self.generate_detailed(prompts, **options)]
+
+    def step(self, entries: Sequence[StepEntry]):
+        return self.engine.step(entries)
+
+
+def build_model(config: ModelConfig, dtype, device, max_positions: Optional[int] = None) -> Model:
+    _, builder = lookup_architecture(config.architecture)
+    return Model(builder(config), parse_dtype(dtype), device, max_positions)
+
+
+def load(folder, dtype="bfloat16", device="cuda:0", max_tokens: int = 16384, max_seqs: Optional[int] = None,
+         max_positions: Optional[int] = None, max_step_tokens: int = 8192) -> LLM:
+    """Load `config.json` + safetensors from `folder`; the model class is chosen by
+    `architectures` in config.json."""
+    device = require_cuda(device)
+    config = load_config(folder)
+    model = build_model(config, dtype, device, max_positions)
+    model.bind(load_tensors(Path(folder), model.weight_specs(), parse_dtype(dtype), device))
+    return LLM(config, model, max_tokens, max_seqs, max_step_tokens)
+
+
+def random_model(config: ModelConfig, seed: int = 0, dtype="bfloat16", device="cuda:0", max_tokens: int = 16384,
+                 max_seqs: Optional[int] = None, max_positions: Optional[int] = None, matrix_std: float = 0.02,
+                 norm_std: float = 0.0, max_step_tokens: int = 8192) -> LLM:
+    """A model with seeded random weights drawn on the device (no files)."""
+    device = require_cuda(device)
+    run_dtype = parse_dtype(dtype)
+    model = build_model(config, run_dtype, device, max_positions)
+    tensors = {}
+    specs = model.weight_specs()
+    for index, spec in enumerate(specs):  # one at a time: the float32 draft of a tensor is freed before the next
+        drawn = random_tensors([spec], seed * 4099 + index, torch.float32, device, matrix_std, norm_std)[spec.name]
+        tensors[spec.name] = drawn.to(torch.float32 if spec.kind == "vector" else run_dtype)
+    model.bind(tensors)
+    return LLM(config, model, max_tokens, max_seqs, max_step_tokens)

@@ -1,0 +1,104 @@
+// Shared device helpers of the kernel library (sm_100a).
+//
+// Every exported entry point is `extern "C"`, takes raw device pointers, sizes and
+// a stream, validates its arguments on the host and returns 0 on success.  A refused
+// argument returns a negative code and leaves a message for mll_last_error(); a CUDA
+// launch error returns the positive cudaError_t.  Nothing here allocates memory or
+// synchronises.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define MLL_API extern "C" __attribute__((visibility("default")))
+
+// dtype codes shared with the Python binding
+enum : int { MLL_F32 = 0, MLL_BF16 = 1 };
+
+// number of cache positions in one page
+#define MLL_PAGE 64
+
+void mll_set_error(const char* fmt, ...);
+
+#define MLL_REQUIRE(cond, ...)        \
+  do {                                \
+    if (!(cond)) {                    \
+      mll_set_error(__VA_ARGS__);     \
+      return -1;                      \
+    }                                 \
+  } while (0)
+
+#define MLL_LAUNCH_CHECK()                          \
+  do {                                              \
+    cudaError_t err__ = cudaGetLastError();         \
+    if (err__ != cudaSuccess) {                     \
+      mll_set_error("%s:%d launch failed: %s", __FILE__, __LINE__, cudaGetErrorString(err__)); \
+      return (int)err__;                            \
+    }                                               \
+  } while (0)
+
+namespace mll {
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum with a fixed reduction tree (same result on every run).
+// `scratch` holds at least 32 floats; every thread gets the total.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float total = (lane < nwarps) ? scratch[lane] : 0.f;
+  total = warp_sum(total);
+  return total;
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float total = (lane < nwarps) ? scratch[lane] : -INFINITY;
+  total = warp_max(total);
+  return total;
+}
+
+// 16-byte asynchronous copy global -> shared (both 16-byte aligned)
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+}  // namespace mll

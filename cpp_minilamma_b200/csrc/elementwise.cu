@@ -1,0 +1,149 @@
+// Embedding gather, dtype casts and the SwiGLU activation.
+//
+// Replaces the reference's EmbeddingKernel, SiluKernel and ElementWiseMulKernel
+// (src/cuda_ops.cu:165-192) with batched kernels; SiLU and the product are one pass.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+static thread_local char g_error[512] = "";
+
+void mll_set_error(const char* fmt, ...) {
+  va_list args;
+  va_start(args, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, args);
+  va_end(args);
+}
+
+MLL_API const char* mll_last_error() { return g_error; }
+
+// Identifies the build; the Python side checks it after loading the library.
+MLL_API int mll_abi_version() { return 3; }
+
+namespace mll {
+
+// x[t, :] = float(table[token[t], :]); the residual stream is float32.
+template <typename TableT>
+__global__ void embedding_kernel(const int* __restrict__ tokens, const TableT* __restrict__ table,
+                                 float* __restrict__ x, int width) {
+  const int t = blockIdx.x;
+  const TableT* row = table + (size_t)tokens[t] * width;
+  float* out = x + (size_t)t * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) out[i] = to_float(row[i]);
+}
+
+template <typename In, typename Out>
+__global__ void cast_kernel(const In* __restrict__ in, Out* __restrict__ out, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) out[i] = from_float<Out>(to_float(in[i]));
+}
+
+// out[t, i] = silu(gate) * up.  `gu` rows hold gate and up either as two halves
+// ([gate(0..I) | up(0..I)], block == 0) or interleaved in blocks of `block` columns
+// ([gate(0..b) | up(0..b) | gate(b..2b) | ...]); I is a multiple of `block` then.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int tokens,
+                              int inter, int block) {
+  const size_t total = (size_t)tokens * inter;
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < total; idx += stride) {
+    const int t = (int)(idx / inter), i = (int)(idx % inter);
+    const T* row = gu + (size_t)t * 2 * inter;
+    float g, u;
+    if (block == 0) {
+      g = to_float(row[i]);
+      u = to_float(row[inter + i]);
+    } else {
+      const int b = i / block, r = i % block;
+      g = to_float(row[(size_t)b * 2 * block + r]);
+      u = to_float(row[(size_t)b * 2 * block + block + r]);
+    }
+    const float act = g / (1.f + expf(-g));
+    out[idx] = from_float<T>(act * u);
+  }
+}
+
+// x[t, i] += bias[i] (bias float32, sum in float32)
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ x, const float* __restrict__ bias, size_t total, int width) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < total; idx += stride) x[idx] = from_float<T>(to_float(x[idx]) + bias[idx % width]);
+}
+
+}  // namespace mll
+
+MLL_API int mll_add_bias(void* x, const float* bias, int dtype, int n_rows, int width, cudaStream_t stream) {
+  MLL_REQUIRE(n_rows >= 0 && width > 0, "add_bias: bad sizes rows=%d width=%d", n_rows, width);
+  if (n_rows == 0) return 0;
+  const size_t total = (size_t)n_rows * width;
+  long long blocks = (long long)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == MLL_F32)
+    mll::add_bias_kernel<float><<<(int)blocks, 256, 0, stream>>>((float*)x, bias, total, width);
+  else if (dtype == MLL_BF16)
+    mll::add_bias_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((__nv_bfloat16*)x, bias, total, width);
+  else
+    MLL_REQUIRE(false, "add_bias: unknown dtype %d", dtype);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
+MLL_API int mll_embedding(const int* tokens, const void* table, int table_dtype, float* x,
+                          int n_tokens, int width, cudaStream_t stream) {
+  MLL_REQUIRE(n_tokens >= 0 && width > 0, "embedding: bad sizes tokens=%d width=%d", n_tokens, width);
+  if (n_tokens == 0) return 0;
+  const int threads = width >= 1024 ? 256 : 128;
+  if (table_dtype == MLL_F32)
+    mll::embedding_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, x, width);
+  else if (table_dtype == MLL_BF16)
+    mll::embedding_kernel<__nv_bfloat16>
+        <<<n_tokens, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, x, width);
+  else
+    MLL_REQUIRE(false, "embedding: unknown table dtype %d", table_dtype);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
+MLL_API int mll_cast(const void* in, int in_dtype, void* out, int out_dtype, long long n,
+                     cudaStream_t stream) {
+  MLL_REQUIRE(n >= 0, "cast: negative size");
+  if (n == 0) return 0;
+  const int threads = 256;
+  long long blocks = (n + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (in_dtype == MLL_F32 && out_dtype == MLL_BF16)
+    mll::cast_kernel<float, __nv_bfloat16>
+        <<<(int)blocks, threads, 0, stream>>>((const float*)in, (__nv_bfloat16*)out, (size_t)n);
+  else if (in_dtype == MLL_BF16 && out_dtype == MLL_F32)
+    mll::cast_kernel<__nv_bfloat16, float>
+        <<<(int)blocks, threads, 0, stream>>>((const __nv_bfloat16*)in, (float*)out, (size_t)n);
+  else
+    MLL_REQUIRE(false, "cast: unsupported dtype pair %d -> %d", in_dtype, out_dtype);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
+MLL_API int mll_swiglu(const void* gu, void* out, int dtype, int n_tokens, int inter, int block,
+                       cudaStream_t stream) {
+  MLL_REQUIRE(n_tokens >= 0 && inter > 0, "swiglu: bad sizes tokens=%d inter=%d", n_tokens, inter);
+  MLL_REQUIRE(block >= 0 && (block == 0 || inter % block == 0),
+              "swiglu: intermediate size %d is not a multiple of the interleave block %d", inter, block);
+  if (n_tokens == 0) return 0;
+  const int threads = 256;
+  long long blocks = ((long long)n_tokens * inter + threads - 1) / threads;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (dtype == MLL_F32)
+    mll::swiglu_kernel<float>
+        <<<(int)blocks, threads, 0, stream>>>((const float*)gu, (float*)out, n_tokens, inter, block);
+  else if (dtype == MLL_BF16)
+    mll::swiglu_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>(
+        (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tokens, inter, block);
+  else
+    MLL_REQUIRE(false, "swiglu: unknown dtype %d", dtype);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}

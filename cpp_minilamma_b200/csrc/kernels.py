@@ -1,0 +1,267 @@
+"""Python face of the kernel library: typed wrappers that check tensors on the host
+and launch on the current CUDA stream.
+
+Every function here needs the compiled library and CUDA tensors; there is no other
+implementation behind them.  Argument faults raise `KernelError` before any launch.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .build import KernelBuildError, load_library
+
+PAGE = 64  # cache positions per page; equals MLL_PAGE in common.cuh
+ABI_VERSION = 3
+MAX_TOP_K = 1024
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        handle = load_library()
+        handle.mll_last_error.restype = ctypes.c_char_p
+        handle.mll_attn_decode_scratch_floats.restype = ctypes.c_longlong
+        if handle.mll_abi_version() != ABI_VERSION:
+            raise KernelBuildError(
+                f"kernel library reports ABI {handle.mll_abi_version()}, the package expects {ABI_VERSION}; "
+                "remove csrc/_build and rebuild")
+        _lib = handle
+    return _lib
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        message = lib().mll_last_error().decode("utf-8", "replace")
+        raise KernelError(f"{what}: {message} (code {code})")
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, ndim=None) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{name}: expected a CUDA tensor (the kernels have no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name}: tensor must be contiguous, strides {tuple(t.stride())}")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name}: expected {dtype}, got {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise KernelError(f"{name}: expected {ndim} dimensions, got shape {tuple(t.shape)}")
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype not in _DTYPE_CODE:
+        raise KernelError(f"dtype {dtype} not supported by the kernels (float32, bfloat16)")
+    return _DTYPE_CODE[dtype]
+
+
+# --------------------------------------------------------------------------- #
+def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, :] = float32(table[tokens[t], :]); tokens int32 [T], out float32 [T, D]."""
+    _need(tokens, "embedding tokens", torch.int32, 1)
+    _need(table, "embedding table", None, 2)
+    _need(out, "embedding out", torch.float32, 2)
+    n, width = tokens.shape[0], table.shape[1]
+    if out.shape[0] < n or out.shape[1] != width:
+        raise KernelError(f"embedding: out {tuple(out.shape)} does not fit [{n}, {width}]")
+    _check(lib().mll_embedding(_ptr(tokens), _ptr(table), dtype_code(table.dtype), _ptr(out),
+                               ctypes.c_int(n), ctypes.c_int(width), _stream()), "embedding")
+
+
+def cast(src: torch.Tensor, dst: torch.Tensor) -> None:
+    _need(src, "cast src")
+    _need(dst, "cast dst")
+    if src.numel() != dst.numel():
+        raise KernelError("cast: sizes differ")
+    _check(lib().mll_cast(_ptr(src), dtype_code(src.dtype), _ptr(dst), dtype_code(dst.dtype),
+                          ctypes.c_longlong(src.numel()), _stream()), "cast")
+
+
+def add_bias(x: torch.Tensor, bias: torch.Tensor) -> None:
+    """x[t, :] += bias (float32 bias, in place)."""
+    _need(x, "add_bias x", None, 2)
+    _need(bias, "add_bias bias", torch.float32, 1)
+    if bias.shape[0] != x.shape[1]:
+        raise KernelError("add_bias: bias length differs from the row width")
+    _check(lib().mll_add_bias(_ptr(x), _ptr(bias), dtype_code(x.dtype), ctypes.c_int(x.shape[0]),
+                              ctypes.c_int(x.shape[1]), _stream()), "add_bias")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int) -> None:
+    """out[t, i] = silu(gate) * up; gate_up [T, 2I] holds halves (block 0) or blocks of `block`."""
+    _need(gate_up, "swiglu gate_up", None, 2)
+    _need(out, "swiglu out", gate_up.dtype, 2)
+    tokens, inter = out.shape
+    if gate_up.shape[0] != tokens or gate_up.shape[1] != 2 * inter:
+        raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)} does not match out {tuple(out.shape)}")
+    _check(lib().mll_swiglu(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), ctypes.c_int(tokens),
+                            ctypes.c_int(inter), ctypes.c_int(block), _stream()), "swiglu")
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
+                eps: float, rows: Optional[torch.Tensor] = None) -> None:
+    """x += delta (float32 residual, in place); out = rmsnorm(x) * weight.
+
+    With `rows` (int32 [n]) only those rows of x are normalised into out [n, D] and x is
+    left unchanged."""
+    _need(x, "rmsnorm x", torch.float32, 2)
+    _need(weight, "rmsnorm weight", torch.float32, 1)
+    _need(out, "rmsnorm out", None, 2)
+    width = x.shape[1]
+    if weight.shape[0] != width or out.shape[1] != width:
+        raise KernelError(f"rmsnorm: widths differ: x {width}, weight {weight.shape[0]}, out {out.shape[1]}")
+    if delta is not None:
+        _need(delta, "rmsnorm delta", out.dtype, 2)
+        if delta.shape != x.shape:
+            raise KernelError(f"rmsnorm: delta {tuple(delta.shape)} differs from x {tuple(x.shape)}")
+    if rows is not None:
+        _need(rows, "rmsnorm rows", torch.int32, 1)
+        n_rows = rows.shape[0]
+    else:
+        n_rows = x.shape[0]
+    if out.shape[0] != n_rows:
+        raise KernelError(f"rmsnorm: out has {out.shape[0]} rows, expected {n_rows}")
+    _check(lib().mll_add_rmsnorm(_ptr(x), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows),
+                                 dtype_code(out.dtype), ctypes.c_int(n_rows), ctypes.c_int(width),
+                                 ctypes.c_float(eps), _stream()), "rmsnorm")
+
+
+def rope_cache_write(qkv, bias, cos, sin, tok_pos, tok_seq, seq_slot, block_table, q_out, k_cache, v_cache,
+                     n_heads: int, n_kv_heads: int, head_dim: int, interleaved: bool,
+                     write_kv: bool = True) -> None:
+    """Rotate q and k of qkv [T, (Hq + 2 Hk) d], write q to q_out [T, Hq d] and k, v into the
+    paged cache [n_pages, Hk, PAGE, d] at each token's slot and position."""
+    _need(qkv, "rope qkv", None, 2)
+    _need(q_out, "rope q_out", qkv.dtype, 2)
+    n = qkv.shape[0]
+    for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("seq_slot", seq_slot)):
+        _need(t, f"rope {name}", torch.int32, 1)
+    _need(block_table, "rope block_table", torch.int32, 2)
+    if tok_pos.shape[0] < n or tok_seq.shape[0] < n:
+        raise KernelError("rope: token metadata shorter than the token count")
+    if q_out.shape[0] < n or q_out.shape[1] != n_heads * head_dim:
+        raise KernelError(f"rope: q_out {tuple(q_out.shape)} does not fit [{n}, {n_heads * head_dim}]")
+    if cos is not None:
+        _need(cos, "rope cos", torch.float32, 2)
+        _need(sin, "rope sin", torch.float32, 2)
+        if cos.shape[1] != head_dim // 2 or sin.shape != cos.shape:
+            raise KernelError(f"rope: table {tuple(cos.shape)} does not match head_dim {head_dim}")
+    if bias is not None:
+        _need(bias, "rope bias", torch.float32, 1)
+        if bias.shape[0] != qkv.shape[1]:
+            raise KernelError("rope: bias length differs from the qkv width")
+    if write_kv:
+        _need(k_cache, "rope k_cache", qkv.dtype, 4)
+        _need(v_cache, "rope v_cache", qkv.dtype, 4)
+        want = (n_kv_heads, PAGE, head_dim)
+        if tuple(k_cache.shape[1:]) != want or k_cache.shape != v_cache.shape:
+            raise KernelError(f"rope: cache shape {tuple(k_cache.shape)} is not [pages, {want}]")
+    _check(lib().mll_rope_cache(_ptr(qkv), _ptr(bias), _ptr(cos), _ptr(sin), _ptr(tok_pos), _ptr(tok_seq),
+                                _ptr(seq_slot), _ptr(block_table), _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
+                                dtype_code(qkv.dtype), ctypes.c_int(n), ctypes.c_int(qkv.shape[1]),
+                                ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim),
+                                ctypes.c_int(block_table.shape[1]), ctypes.c_int(int(interleaved)),
+                                ctypes.c_int(int(write_kv)), _stream()), "rope_cache_write")
+
+
+def _check_attention(q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim):
+    _need(q, "attention q", None, 2)
+    _need(out, "attention out", q.dtype, 2)
+    _need(k_cache, "attention k_cache", q.dtype, 4)
+    _need(v_cache, "attention v_cache", q.dtype, 4)
+    if head_dim % 16 != 0 or not 16 <= head_dim <= 256:
+        raise KernelError(f"attention: head_dim {head_dim} is not a multiple of 16 in [16, 256]")
+    if n_heads % n_kv_heads != 0:
+        raise KernelError(f"attention: {n_heads} heads are not a multiple of {n_kv_heads} kv heads")
+    if q.shape[1] != n_heads * head_dim or out.shape[1] != n_heads * head_dim:
+        raise KernelError("attention: q/out width differs from heads * head_dim")
+    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or k_cache.shape != v_cache.shape:
+        raise KernelError(f"attention: cache shape {tuple(k_cache.shape)} is not "
+                          f"[pages, {n_kv_heads}, {PAGE}, {head_dim}]")
+
+
+def attention_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_splits: int) -> int:
+    return int(lib().mll_attn_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits))
+
+
+def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch, out, n_seqs: int,
+                     n_heads: int, n_kv_heads: int, head_dim: int, n_splits: int, window: int,
+                     scale: float) -> None:
+    """One query token per sequence (q row i belongs to sequence i) over the paged cache."""
+    _check_attention(q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim)
+    _need(seq_slot, "attention seq_slot", torch.int32, 1)
+    _need(seq_ctx, "attention seq_ctx", torch.int32, 1)
+    _need(block_table, "attention block_table", torch.int32, 2)
+    if q.shape[0] < n_seqs or out.shape[0] < n_seqs or seq_slot.shape[0] < n_seqs or seq_ctx.shape[0] < n_seqs:
+        raise KernelError("attention decode: an input has fewer rows than sequences")
+    if n_splits > 1:
+        _need(scratch, "attention scratch", torch.float32)
+        if scratch.numel() < attention_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits):
+            raise KernelError("attention decode: scratch too small for the split count")
+    _check(lib().mll_attn_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx),
+                                 _ptr(block_table), _ptr(scratch), _ptr(out), dtype_code(q.dtype),
+                                 ctypes.c_int(n_seqs), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
+                                 ctypes.c_int(head_dim), ctypes.c_int(block_table.shape[1]),
+                                 ctypes.c_int(n_splits), ctypes.c_int(window), ctypes.c_float(scale),
+                                 _stream()), "attention_decode")
+
+
+def attention_prefill(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0,
+                      block_table, out, n_tiles: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                      window: int, scale: float) -> None:
+    """Tiles of up to 64 query tokens of sequences with unequal lengths over the paged cache."""
+    _check_attention(q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim)
+    for name, t in (("seq_slot", seq_slot), ("seq_ctx", seq_ctx), ("seq_qstart", seq_qstart),
+                    ("seq_qlen", seq_qlen), ("tile_seq", tile_seq), ("tile_row0", tile_row0)):
+        _need(t, f"attention {name}", torch.int32, 1)
+    _need(block_table, "attention block_table", torch.int32, 2)
+    if tile_seq.shape[0] < n_tiles or tile_row0.shape[0] < n_tiles:
+        raise KernelError("attention prefill: tile lists shorter than the tile count")
+    _check(lib().mll_attn_prefill(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx),
+                                  _ptr(seq_qstart), _ptr(seq_qlen), _ptr(tile_seq), _ptr(tile_row0),
+                                  _ptr(block_table), _ptr(out), dtype_code(q.dtype), ctypes.c_int(n_tiles),
+                                  ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim),
+                                  ctypes.c_int(block_table.shape[1]), ctypes.c_int(window),
+                                  ctypes.c_float(scale), _stream()), "attention_prefill")
+
+
+def argmax(logits: torch.Tensor, tokens: torch.Tensor, status: torch.Tensor) -> None:
+    """tokens[r] = first index of the maximum of logits[r]; status[r] = 1 if a logit is not finite."""
+    _need(logits, "argmax logits", torch.float32, 2)
+    _need(tokens, "argmax tokens", torch.int32, 1)
+    _need(status, "argmax status", torch.int32, 1)
+    n = logits.shape[0]
+    if tokens.shape[0] < n or status.shape[0] < n:
+        raise KernelError("argmax: outputs shorter than the row count")
+    _check(lib().mll_argmax(_ptr(logits), ctypes.c_int(n), ctypes.c_int(logits.shape[1]), _ptr(tokens),
+                            _ptr(status), _stream()), "argmax")
+
+
+def sample(logits: torch.Tensor, temperature: float, top_k: int, seed: int, request: torch.Tensor,
+           step: torch.Tensor, tokens: torch.Tensor, status: torch.Tensor) -> None:
+    """Temperature (top_k == 0) or top-k sampling with u = f(seed, request[r], step[r])."""
+    _need(logits, "sample logits", torch.float32, 2)
+    for name, t in (("request", request), ("step", step), ("tokens", tokens), ("status", status)):
+        _need(t, f"sample {name}", torch.int32, 1)
+        if t.shape[0] < logits.shape[0]:
+            raise KernelError(f"sample: {name} shorter than the row count")
+    _check(lib().mll_sample(_ptr(logits), ctypes.c_int(logits.shape[0]), ctypes.c_int(logits.shape[1]),
+                            ctypes.c_float(temperature), ctypes.c_int(top_k),
+                            ctypes.c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), _ptr(request), _ptr(step),
+                            _ptr(tokens), _ptr(status), _stream()), "sample")

@@ -1,0 +1,134 @@
+"""Causal grouped-query attention with a paged key/value cache.
+
+One layer's mixer: fused q/k/v projection, rotary encoding of q and k fused with the
+cache write, attention over the cache (prefill tiles or split decode), output
+projection.  The arithmetic is the reference's (src/forward.cc:393-408 for the layer,
+:265-298 for the scores/softmax/values): head h reads kv head h // (Hq / Hk), scores are
+scaled by 1 / sqrt(head_dim) after the dot product, a token attends to itself and all
+earlier positions.  A window (not in the reference) limits that to the last w positions.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+
+from ..csrc import kernels as K
+from .base import (BuildContext, CacheNeed, KVNeed, Mixer, PartSpec, WeightSpec, register_part)
+from .linear import Linear
+from .rope import shared_position_encoding
+
+_TARGET_BLOCKS = 2 * 148  # decode attention aims at two blocks per SM
+
+
+class Attention(Mixer):
+    """params:
+      n_heads, n_kv_heads, head_dim     sizes
+      window                            0 = all earlier positions
+      position                          PartSpec of the position encoding
+      names                             {"q","k","v","o"}: tensor name stems (".weight"/".bias" appended)
+      qkv_bias, o_bias                  whether the projections carry a bias
+      reads_cache_only                  True for an entry that reads another entry's cache:
+                                        it has no k/v projection and writes nothing
+    """
+
+    def __init__(self, params, ctx: BuildContext):
+        super().__init__(params, ctx)
+        self.n_heads = int(params["n_heads"])
+        self.n_kv_heads = int(params["n_kv_heads"])
+        self.head_dim = int(params["head_dim"])
+        self.window = int(params.get("window") or 0)
+        self.names = dict(params["names"])
+        self.qkv_bias = bool(params.get("qkv_bias", False))
+        self.o_bias = bool(params.get("o_bias", False))
+        self.reads_cache_only = bool(params.get("reads_cache_only", False))
+        self.scale = 1.0 / math.sqrt(self.head_dim)
+        if self.head_dim % 16 or not 16 <= self.head_dim <= 256:
+            raise ValueError(f"attention: head_dim {self.head_dim} must be a multiple of 16 in [16, 256] "
+                             "for the attention kernels")
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError(f"attention: {self.n_heads} heads are not a multiple of {self.n_kv_heads} kv heads")
+        self.position = shared_position_encoding(params.get("position") or PartSpec("none"), ctx)
+        self.qkv: Optional[Linear] = None
+        self.o: Optional[Linear] = None
+        self.bias: Optional[torch.Tensor] = None
+        self.o_bias_t: Optional[torch.Tensor] = None
+
+    # ---- weights ---------------------------------------------------------- #
+    def _proj_names(self):
+        return ("q",) if self.reads_cache_only else ("q", "k", "v")
+
+    def weight_specs(self) -> List[WeightSpec]:
+        D, d = self.ctx.hidden_size, self.head_dim
+        rows = {"q": self.n_heads * d, "k": self.n_kv_heads * d, "v": self.n_kv_heads * d}
+        specs = []
+        for p in self._proj_names():
+            specs.append(WeightSpec(self.names[p] + ".weight", (rows[p], D)))
+            if self.qkv_bias:
+                specs.append(WeightSpec(self.names[p] + ".bias", (rows[p],), kind="vector", init="normal"))
+        specs.append(WeightSpec(self.names["o"] + ".weight", (D, self.n_heads * d)))
+        if self.o_bias:
+            specs.append(WeightSpec(self.names["o"] + ".bias", (D,), kind="vector", init="normal"))
+        return specs
+
+    def bind(self, store) -> None:
+        mats = [store.take(self.names[p] + ".weight") for p in self._proj_names()]
+        if len({m.dtype for m in mats}) > 1:  # a 32-bit tensor stays 32-bit: widen its partners
+            mats = [m.float() for m in mats]
+        self.qkv = Linear(torch.cat(mats, dim=0) if len(mats) > 1 else mats[0], self.names["q"] + "+k+v")
+        del mats
+        if self.qkv_bias:
+            self.bias = torch.cat([store.take(self.names[p] + ".bias") for p in self._proj_names()]).contiguous()
+        self.o = Linear(store.take(self.names["o"] + ".weight"), self.names["o"])
+        if self.o_bias:
+            self.o_bias_t = store.take(self.names["o"] + ".bias")
+
+    def parameter_bytes(self) -> int:
+        return self.qkv.parameter_bytes() + self.o.parameter_bytes()
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed(kv=KVNeed(self.n_kv_heads, self.head_dim, self.window))
+
+    # ---- step ------------------------------------------------------------- #
+    def decode_splits(self, n_seqs: int, max_ctx: int) -> int:
+        group = self.n_heads // self.n_kv_heads
+        heads_per_block = max(1, min(group, 2048 // self.head_dim))
+        chunks = -(-group // heads_per_block)
+        blocks = max(1, n_seqs * self.n_kv_heads * chunks)
+        span = max_ctx if self.window <= 0 else min(max_ctx, self.window + K.PAGE)
+        pages = max(1, -(-span // K.PAGE))
+        return max(1, min(-(-_TARGET_BLOCKS // blocks), pages, 64))
+
+    def forward(self, step, h: torch.Tensor, cache) -> torch.Tensor:
+        T = h.shape[0]
+        d, Hq, Hk = self.head_dim, self.n_heads, self.n_kv_heads
+        act = self.ctx.act_dtype
+        if cache.k is None:
+            raise RuntimeError("attention: the cache view has no key/value storage")
+        qkv = self.qkv.forward(step, h, "qkv")
+        q = step.ws.buffer("q", (T, Hq * d), act)
+        cos, sin = self.position.tables()
+        K.rope_cache_write(qkv, self.bias, cos, sin, step.tok_pos, step.tok_seq, step.seq_slot,
+                           cache.block_table, q, cache.k, cache.v, Hq, Hk, d,
+                           self.position.interleaved, write_kv=not self.reads_cache_only)
+        out = step.ws.buffer("attn", (T, Hq * d), act)
+        if step.all_decode:
+            splits = step.decode_splits if step.decode_splits else self.decode_splits(step.n_seqs, step.max_ctx)
+            scratch = None
+            if splits > 1:
+                scratch = step.ws.buffer(
+                    "attn.scratch", (K.attention_decode_scratch_floats(step.n_seqs, Hq, d, splits),), torch.float32)
+            K.attention_decode(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, cache.block_table, scratch, out,
+                               step.n_seqs, Hq, Hk, d, splits, self.window, self.scale)
+        else:
+            K.attention_prefill(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
+                                step.tile_seq, step.tile_row0, cache.block_table, out, step.n_tiles,
+                                Hq, Hk, d, self.window, self.scale)
+        o = self.o.forward(step, out, "o")
+        if self.o_bias_t is not None:
+            K.add_bias(o, self.o_bias_t)
+        return o
+
+
+register_part("mixer", "attention", Attention)

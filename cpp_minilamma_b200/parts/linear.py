@@ -1,0 +1,86 @@
+"""`Linear`: y[T, N] = x[T, K] . W[N, K]^T, the one contraction every part uses.
+
+W is row-major [out, in] as in the reference (src/cuda_matmul.cc:181-186, one
+`cublasSgemm` per call there).  The product runs in the dtype of the weight:
+  * bfloat16 weight, bfloat16 x: tensor-core product with float32 accumulation;
+  * float32 weight: a true float32 product (TF32 must be off; it is refused otherwise);
+    bfloat16 activations are widened first and the result narrowed afterwards.
+Large products go to the library GEMM (as the reference's do); small batches of rows go
+to this package's own weight-streaming kernel when it is available for the shape.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..csrc import kernels as K
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor, name: str = "linear"):
+        if weight.dim() != 2:
+            raise ValueError(f"{name}: weight must be [out, in], got {tuple(weight.shape)}")
+        if weight.dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"{name}: weight dtype {weight.dtype} not supported")
+        self.weight = weight.contiguous()
+        self.name = name
+        self.out_features, self.in_features = weight.shape
+
+    def parameter_bytes(self) -> int:
+        return self.weight.numel() * self.weight.element_size()
+
+    def forward(self, step, x: torch.Tensor, out_name: str, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """x [T, K] in the activation dtype -> [T, N] in `out_dtype` (default: x's dtype)."""
+        rows = x.shape[0]
+        if x.shape[1] != self.in_features:
+            raise ValueError(f"{self.name}: input width {x.shape[1]} != {self.in_features}")
+        out_dtype = out_dtype or x.dtype
+        w = self.weight
+        ws = step.ws
+        if w.dtype == torch.float32:
+            if torch.backends.cuda.matmul.allow_tf32:
+                raise RuntimeError(f"{self.name}: TF32 is enabled; the float32 path needs true 32-bit products")
+            if x.dtype != torch.float32:
+                wide = ws.buffer(out_name + ".x32", (rows, self.in_features), torch.float32)
+                K.cast(x, wide)
+                x = wide
+            if out_dtype == torch.float32:
+                out = ws.buffer(out_name, (rows, self.out_features), torch.float32)
+                torch.mm(x, w.t(), out=out)
+                return out
+            wide_out = ws.buffer(out_name + ".y32", (rows, self.out_features), torch.float32)
+            torch.mm(x, w.t(), out=wide_out)
+            out = ws.buffer(out_name, (rows, self.out_features), out_dtype)
+            K.cast(wide_out, out)
+            return out
+        # bfloat16 weight
+        if x.dtype != torch.bfloat16:
+            raise RuntimeError(f"{self.name}: bfloat16 weight with {x.dtype} activations; "
+                               "a float32 run widens its matrices when it loads them")
+        out = ws.buffer(out_name, (rows, self.out_features), out_dtype)
+        if step.small_linear is not None and step.small_linear(x, w, out):
+            return out
+        if out_dtype == torch.bfloat16:
+            torch.mm(x, w.t(), out=out)
+        else:  # bfloat16 operands, float32 result (the logits)
+            _mm_bf16_to_f32(x, w, out)
+        return out
+
+
+_MM_OUT_DTYPE_WITH_OUT = None
+
+
+def _mm_bf16_to_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    global _MM_OUT_DTYPE_WITH_OUT
+    if _MM_OUT_DTYPE_WITH_OUT is None:
+        try:
+            torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+            _MM_OUT_DTYPE_WITH_OUT = True
+            return
+        except (TypeError, RuntimeError):
+            _MM_OUT_DTYPE_WITH_OUT = False
+    if _MM_OUT_DTYPE_WITH_OUT:
+        torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+    else:
+        out.copy_(torch.mm(x, w.t(), out_dtype=torch.float32))

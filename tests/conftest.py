@@ -1,0 +1,39 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for path in (ROOT, os.path.dirname(os.path.abspath(__file__))):
+    if path not in sys.path:
+        sys.path.insert(0, path)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+def pytest_collection_modifyitems(config, items):
+    import torch
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+@pytest.fixture(scope="session")
+def model_folders(tmp_path_factory):
+    """Folders with seeded random weights for the tiny configurations, made once per run
+    in a temporary directory: {(name, storage dtype): path}."""
+    import tiny_configs
+    made = {}
+
+    def get(name, storage="float32"):
+        key = (name, storage)
+        if key not in made:
+            made[key] = tiny_configs.write_folder(name, storage, tmp_path_factory.mktemp(f"{name}_{storage}"))
+        return made[key]
+
+    return get

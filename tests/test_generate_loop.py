@@ -1,0 +1,121 @@
+"""The generation loop's decisions with a scripted backend (no GPU): batching, stop tokens,
+sequences that end earlier, slot hand-back, token accounting, capacity policy."""
+import pytest
+
+from cpp_minilamma_b200.engine.generate import Backend, GenerationError, generate, plan_batches
+
+
+class Scripted(Backend):
+    """Samples token = script[request][index]; records every step."""
+
+    def __init__(self, scripts, n_slots=4, n_pages=100, max_positions=1000):
+        self.scripts, self.n_slots, self.n_pages, self.max_positions = scripts, n_slots, n_pages, max_positions
+        self.free = list(range(n_slots))
+        self.held = set()
+        self.log = []
+        self.fed = {}
+
+    def acquire(self, count):
+        assert count <= len(self.free)
+        slots = [self.free.pop(0) for _ in range(count)]
+        self.held |= set(slots)
+        for s in slots:
+            self.fed[s] = []
+        return slots
+
+    def release(self, slot):
+        assert slot in self.held, "released twice"
+        self.held.discard(slot)
+        self.free.append(slot)
+
+    def step_and_sample(self, entries, requests, steps):
+        assert len(entries) == len(requests) == len(steps)
+        assert all(e.slot in self.held for e in entries)
+        self.log.append([(r, list(e.tokens), list(e.want), s) for e, r, s in zip(entries, requests, steps)])
+        for e in entries:
+            self.fed[e.slot] += list(e.tokens)
+        return [self.scripts[r][s] for r, s in zip(requests, steps)]
+
+
+def test_prompts_in_one_step_then_one_token_each():
+    scripts = {0: [10, 11, 12], 1: [20, 21, 22], 2: [30, 31, 32]}
+    backend = Scripted(scripts)
+    prompts = [[1, 2, 3, 4, 5], [6] * 9, [7, 8]]
+    out = generate(backend, prompts, 3)
+    assert [c.tokens for c in out] == [[10, 11, 12], [20, 21, 22], [30, 31, 32]]
+    assert all(c.finish_reason == "length" for c in out)
+    first = backend.log[0]
+    assert [(r, t, w) for r, t, w, _ in first] == [(0, prompts[0], [4]), (1, prompts[1], [8]), (2, prompts[2], [1])]
+    # 3 tokens cost the prompt step plus 2 decode steps; the last token is not fed back
+    assert len(backend.log) == 3
+    assert backend.log[1] == [(0, [10], [0], 1), (1, [20], [0], 1), (2, [30], [0], 1)]
+    assert backend.log[2] == [(0, [11], [0], 2), (1, [21], [0], 2), (2, [31], [0], 2)]
+    assert not backend.held
+
+
+def test_stop_token_ends_a_sequence_early_and_is_not_emitted():
+    scripts = {0: [10, 99, 12, 13], 1: [20, 21, 22, 23], 2: [99, 0, 0, 0]}
+    backend = Scripted(scripts)
+    out = generate(backend, [[1], [2, 3], [4]], 4, stop_ids={99})
+    assert [c.tokens for c in out] == [[10], [20, 21, 22, 23], []]
+    assert [c.finish_reason for c in out] == ["stop", "length", "stop"]
+    assert [len(step) for step in backend.log] == [3, 2, 1, 1]   # the batch shrinks
+    assert [r for r, *_ in backend.log[1]] == [0, 1]
+    assert not backend.held
+    again = Scripted(scripts)
+    out = generate(again, [[1], [2, 3], [4]], 4, stop_ids={99}, ignore_eos=True)
+    assert [c.tokens for c in out] == [[10, 99, 12, 13], [20, 21, 22, 23], [99, 0, 0, 0]]
+
+
+def test_unequal_budgets_and_zero():
+    scripts = {i: list(range(100 * i, 100 * i + 10)) for i in range(3)}
+    backend = Scripted(scripts)
+    out = generate(backend, [[1], [2], [3]], [1, 0, 4])
+    assert [c.tokens for c in out] == [[0], [], [200, 201, 202, 203]]
+    assert [c.finish_reason for c in out] == ["length"] * 3
+    assert [r for r, *_ in backend.log[0]] == [0, 2]              # a request that wants nothing never runs
+    assert len(backend.log) == 4
+
+
+def test_more_requests_than_slots_run_in_batches_that_reuse_slots():
+    scripts = {i: [i] * 3 for i in range(7)}
+    backend = Scripted(scripts, n_slots=3)
+    out = generate(backend, [[i + 1] for i in range(7)], 2)
+    assert [c.tokens for c in out] == [[i, i] for i in range(7)]
+    starts = [step for step in backend.log if step[0][3] == 0]
+    assert [[r for r, *_ in step] for step in starts] == [[0, 1, 2], [3, 4, 5], [6]]
+    assert not backend.held and sorted(backend.free) == [0, 1, 2]
+
+
+def test_page_budget_limits_a_batch():
+    assert plan_batches([64, 64, 64], [1, 1, 1], n_slots=8, n_pages=2) == [[0, 1], [2]]
+    assert plan_batches([60, 60], [6, 5], n_slots=8, n_pages=2) == [[0], [1]]   # 65 held tokens: 2 pages; 64: 1
+    assert plan_batches([60, 60], [6, 5], n_slots=8, n_pages=3) == [[0, 1]]
+    assert plan_batches([1] * 5, [1] * 5, n_slots=8, n_pages=100, max_batch=2) == [[0, 1], [2, 3], [4]]
+    with pytest.raises(GenerationError, match="pages"):
+        plan_batches([200], [1], n_slots=8, n_pages=2)
+
+
+def test_capacity_policy():
+    backend = Scripted({0: [1] * 50}, max_positions=20)
+    with pytest.raises(GenerationError, match="exceeds"):
+        generate(backend, [[0] * 15], 10)
+    out = generate(backend, [[0] * 15], 10, clip=True)
+    assert len(out[0].tokens) == 5
+    with pytest.raises(GenerationError, match="empty"):
+        generate(backend, [[]], 1)
+    with pytest.raises(GenerationError, match="one per prompt"):
+        generate(backend, [[1]], [1, 2])
+
+
+def test_slots_go_back_when_the_backend_fails():
+    class Failing(Scripted):
+        def step_and_sample(self, entries, requests, steps):
+            if len(self.log) == 1:
+                raise RuntimeError("boom")
+            return super().step_and_sample(entries, requests, steps)
+
+    backend = Failing({0: [1, 2, 3], 1: [4, 5, 6]})
+    with pytest.raises(RuntimeError, match="boom"):
+        generate(backend, [[1], [2]], 3)
+    assert not backend.held

@@ -1,0 +1,183 @@
+"""The engine against the plain implementation, under every way of cutting the work:
+each request alone and whole; with the last 32 tokens one by one; in batches of unequal
+lengths whose shorter requests end earlier, one batch after another so that slots are
+used again; long decoding; the first tokens of a sequence.  In float32 and bfloat16."""
+import numpy as np
+import pytest
+import torch
+
+import cpp_minilamma_b200 as ml
+import tiny_configs as tc
+from cpp_minilamma_b200 import StepEntry
+from helpers import assert_close, plain_logits
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+CASES = [(name, dtype) for name in "ABC" for dtype in DTYPES]
+
+
+def load(model_folders, name, dtype, storage=None, **kw):
+    storage = storage or dtype  # by default a bfloat16 run reads a bfloat16 folder, a float32 run a float32 one
+    folder = model_folders(name, storage)
+    kw.setdefault("max_tokens", 4096)
+    return folder, ml.load(folder, dtype=dtype, **kw)
+
+
+def request_lengths(name):
+    top = tc.TINY[name]["max_position_embeddings"]
+    return [n for n in (1, 2, 5, 33, 64, 65, 100, 200) if n <= top]
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_whole_requests(model_folders, name, dtype):
+    folder, llm = load(model_folders, name, dtype)
+    for i, length in enumerate(request_lengths(name)):
+        tokens = tc.random_tokens(name, length, 100 + i)
+        slot, = llm.engine.acquire(1)
+        got = llm.engine.step([StepEntry(slot, tokens, list(range(length)))]).cpu().numpy()
+        llm.engine.release(slot)
+        assert_close(got, plain_logits(folder, tokens, dtype), dtype, f"{name} whole len {length}")
+    llm.engine.cache.check()
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_last_32_one_by_one(model_folders, name, dtype):
+    folder, llm = load(model_folders, name, dtype)
+    for i, length in enumerate(request_lengths(name)):
+        tokens = tc.random_tokens(name, length, 200 + i)
+        ref = plain_logits(folder, tokens, dtype)
+        head = max(length - 32, 0)
+        slot, = llm.engine.acquire(1)
+        rows = []
+        if head:
+            rows.append(llm.engine.step([StepEntry(slot, tokens[:head], list(range(head)))]).cpu().numpy())
+        for t in range(head, length):
+            rows.append(llm.engine.step([StepEntry(slot, [tokens[t]], [0])]).cpu().numpy())
+        llm.engine.release(slot)
+        assert_close(np.concatenate(rows), ref, dtype, f"{name} last-32 len {length}")
+
+
+def _batched_replay(llm, requests, prompt_lens, batch_size):
+    """Run requests in consecutive batches: prompts in one step, then one token each until
+    each request's tokens are used up.  Returns per-request logits at every position."""
+    results = [None] * len(requests)
+    for begin in range(0, len(requests), batch_size):
+        group = list(range(begin, min(begin + batch_size, len(requests))))
+        slots = dict(zip(group, llm.engine.acquire(len(group))))
+        fed = {r: prompt_lens[r] for r in group}
+        pieces = {r: [] for r in group}
+        out = llm.engine.step([StepEntry(slots[r], requests[r][:fed[r]], list(range(fed[r]))) for r in group])
+        at = 0
+        for r in group:
+            pieces[r].append(out[at:at + fed[r]].cpu().numpy())
+            at += fed[r]
+        live = [r for r in group if fed[r] < len(requests[r])]
+        for r in group:
+            if r not in live:
+                llm.engine.release(slots[r])
+        while live:
+            out = llm.engine.step([StepEntry(slots[r], [requests[r][fed[r]]], [0]) for r in live])
+            for j, r in enumerate(live):
+                pieces[r].append(out[j:j + 1].cpu().numpy())
+                fed[r] += 1
+            for r in [r for r in live if fed[r] == len(requests[r])]:
+                llm.engine.release(slots[r])
+            live = [r for r in live if fed[r] < len(requests[r])]
+        for r in group:
+            results[r] = np.concatenate(pieces[r])
+        llm.engine.cache.check()
+    return results
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_unequal_batches_reuse_slots(model_folders, name, dtype):
+    # the BASELINE workloads (A: prompts 5/9/2 + 8 steps; B: 17/1/40/6 + 12 steps) and more,
+    # on a cache with fewer slots than requests
+    workloads = {"A": ([5, 9, 2, 1, 30, 7, 3], 8), "B": ([17, 1, 40, 6, 64, 65, 2, 100], 12),
+                 "C": ([3, 130, 64, 1, 257, 20], 20)}
+    prompt_lens, steps = workloads[name]
+    extra = [steps + 3 * (i % 3) for i in range(len(prompt_lens))]  # unequal ends
+    top = tc.TINY[name]["max_position_embeddings"]
+    requests = [tc.random_tokens(name, min(p + e, top), 300 + i) for i, (p, e) in enumerate(zip(prompt_lens, extra))]
+    prompt_lens = [min(p, len(r)) for p, r in zip(prompt_lens, requests)]
+    folder, llm = load(model_folders, name, dtype, max_seqs=4)
+    got = _batched_replay(llm, requests, prompt_lens, batch_size=4 if name != "A" else 3)
+    for i, tokens in enumerate(requests):
+        assert_close(got[i], plain_logits(folder, tokens, dtype), dtype, f"{name} batched request {i}")
+    assert llm.engine.cache.n_free_slots == llm.engine.cache.n_slots
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(model_folders, dtype):
+    # 3 prompt tokens then 600 single-token steps: crosses many pages
+    name = "C"
+    tokens = tc.random_tokens(name, 603, 400)
+    folder, llm = load(model_folders, name, dtype)
+    slot, = llm.engine.acquire(1)
+    rows = [llm.engine.step([StepEntry(slot, tokens[:3], [0, 1, 2])]).cpu().numpy()]
+    for t in range(3, len(tokens)):
+        rows.append(llm.engine.step([StepEntry(slot, [tokens[t]], [0])]).cpu().numpy())
+    llm.engine.release(slot)
+    assert_close(np.concatenate(rows), plain_logits(folder, tokens, dtype), dtype, "long decoding")
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_first_tokens(model_folders, name, dtype):
+    # a sequence's first positions, fed one by one from an empty slot
+    tokens = tc.random_tokens(name, 6, 500)
+    folder, llm = load(model_folders, name, dtype)
+    slot, = llm.engine.acquire(1)
+    rows = [llm.engine.step([StepEntry(slot, [t], [0])]).cpu().numpy() for t in tokens]
+    llm.engine.release(slot)
+    assert_close(np.concatenate(rows), plain_logits(folder, tokens, dtype), dtype, f"{name} first tokens")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_chunked_step_equals_whole(model_folders, dtype):
+    # a step longer than max_step_tokens is cut into chunks inside the engine
+    name = "C"
+    tokens = tc.random_tokens(name, 300, 600)
+    folder, llm = load(model_folders, name, dtype, max_step_tokens=128)
+    slots = llm.engine.acquire(2)
+    other = tc.random_tokens(name, 70, 601)
+    out = llm.engine.step([StepEntry(slots[0], tokens, list(range(300))),
+                           StepEntry(slots[1], other, [69, 0])]).cpu().numpy()
+    assert_close(out[:300], plain_logits(folder, tokens, dtype), dtype, "chunked long")
+    ref_other = plain_logits(folder, other, dtype)
+    assert_close(out[300:], ref_other[[69, 0]], dtype, "chunked short, want out of order")
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_greedy_generation_through_entry_point(model_folders, name, dtype):
+    folder, llm = load(model_folders, name, dtype)
+    prompts = [tc.random_tokens(name, n, 700 + n) for n in (5, 9, 2)]
+    outs = llm.generate(prompts, max_new_tokens=8, ignore_eos=True)
+    for prompt, out in zip(prompts, outs):
+        assert len(out) == 8
+        seq = list(prompt)
+        for token in out:  # each generated token is the argmax of the plain logits, ties aside
+            ref = plain_logits(folder, seq, dtype)[-1]
+            best = int(np.argmax(ref))
+            if token != best:
+                margin = ref[best] - ref[token]
+                assert margin <= (2e-4 if dtype == "float32" else 0.04 * np.abs(ref).max()), \
+                    f"{name} {dtype}: generated {token}, plain argmax {best}, margin {margin}"
+            seq.append(token)
+
+
+@pytest.mark.parametrize("dtype,storage", [("bfloat16", "float32"), ("float32", "bfloat16")])
+def test_run_dtype_differs_from_storage(model_folders, dtype, storage):
+    # tensors stored in 32-bit stay 32-bit in a bfloat16 run (their products run in float32);
+    # a float32 run widens bfloat16 tensors
+    name = "A"
+    folder, llm = load(model_folders, name, dtype, storage=storage)
+    want = torch.float32 if (storage == "float32" or dtype == "float32") else torch.bfloat16
+    assert llm.model.layers[0].mixer.qkv.weight.dtype == want
+    assert llm.model.embedding.table.dtype == want
+    tokens = tc.random_tokens(name, 40, 800)
+    slot, = llm.engine.acquire(1)
+    got = [llm.engine.step([StepEntry(slot, tokens[:30], list(range(30)))]).cpu().numpy()]
+    for t in range(30, 40):
+        got.append(llm.engine.step([StepEntry(slot, [tokens[t]], [0])]).cpu().numpy())
+    assert_close(np.concatenate(got), plain_logits(folder, tokens, dtype), dtype, f"run {dtype} on {storage}")

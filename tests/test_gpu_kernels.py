@@ -1,0 +1,420 @@
+"""Each kernel alone against the plain reference of the same operation, at sizes other
+than the tiny models': head sizes 16..256 in steps of 16, group sizes 1/3/4/5/8, widths
+and vocabularies that are no power of two.  Where random data would hide a fault the
+inputs are made so that it shows: one far key whose score stands out, a window's edge,
+pages scattered over the pool."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as pl
+from cpp_minilamma_b200.csrc import kernels as K
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+PAGE = K.PAGE
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-6) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1e-3)
+
+
+def rnd(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+def as64(t):
+    return t.detach().float().cpu().numpy().astype(np.float64)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding(dtype):
+    table = rnd((1000, 100), dtype, 1)
+    tokens = torch.tensor([0, 999, 5, 5, 731], dtype=torch.int32)
+    out = torch.empty((5, 100), dtype=torch.float32, device=DEV)
+    K.embedding(tokens.to(DEV), table.to(DEV), out)
+    np.testing.assert_array_equal(out.cpu().numpy(), pl.embedding(as64(table), tokens.numpy()).astype(np.float32))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [100, 1000, 4096, 13000])
+def test_add_rmsnorm(dtype, width):
+    rows, eps = 7, 3e-4
+    x = rnd((rows, width), torch.float32, 2, 3.0)
+    delta = rnd((rows, width), dtype, 3)
+    w = 1 + 0.1 * rnd((width,), torch.float32, 4)
+    xd, out = x.to(DEV), torch.empty((rows, width), dtype=dtype, device=DEV)
+    K.add_rmsnorm(xd, delta.to(DEV), w.to(DEV), out, eps)
+    summed = as64(x) + as64(delta)
+    np.testing.assert_allclose(xd.cpu().numpy(), summed, rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(as64(out), pl.rms_norm(summed, as64(w), eps), **tol(dtype))
+    # no delta; gathered rows leave x alone
+    x2 = x.to(DEV)
+    pick = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    out2 = torch.empty((3, width), dtype=dtype, device=DEV)
+    K.add_rmsnorm(x2, delta.to(DEV), w.to(DEV), out2, eps, rows=pick)
+    np.testing.assert_array_equal(x2.cpu().numpy(), x.numpy())
+    np.testing.assert_allclose(as64(out2), pl.rms_norm(summed[[6, 0, 3]], as64(w), eps), **tol(dtype))
+    out3 = torch.empty((rows, width), dtype=dtype, device=DEV)
+    K.add_rmsnorm(x2, None, w.to(DEV), out3, eps)
+    np.testing.assert_allclose(as64(out3), pl.rms_norm(as64(x), as64(w), eps), **tol(dtype))
+
+
+def test_rmsnorm_is_reproducible():
+    x = rnd((5, 5000), torch.float32, 5).to(DEV)
+    w = torch.ones(5000, device=DEV)
+    a, b = torch.empty_like(x), torch.empty_like(x)
+    K.add_rmsnorm(x, None, w, a, 1e-5)
+    K.add_rmsnorm(x, None, w, b, 1e-5)
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inter,block", [(250, 0), (176, 8), (1000, 8)])
+def test_swiglu(dtype, inter, block):
+    rows = 5
+    gate, up = rnd((rows, inter), dtype, 6, 2.0), rnd((rows, inter), dtype, 7)
+    if block:
+        gu = torch.stack([gate.view(rows, inter // block, block), up.view(rows, inter // block, block)], dim=2)
+        gu = gu.reshape(rows, 2 * inter)
+    else:
+        gu = torch.cat([gate, up], dim=1)
+    out = torch.empty((rows, inter), dtype=dtype, device=DEV)
+    K.swiglu(gu.contiguous().to(DEV), out, block)
+    np.testing.assert_allclose(as64(out), pl.swiglu(as64(gate), as64(up)), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_cast_and_bias(dtype):
+    x = rnd((3, 333), torch.float32, 8)
+    y = torch.empty((3, 333), dtype=torch.bfloat16, device=DEV)
+    K.cast(x.to(DEV), y)
+    assert torch.equal(y.cpu(), x.to(torch.bfloat16))
+    z = torch.empty((3, 333), dtype=torch.float32, device=DEV)
+    K.cast(y, z)
+    assert torch.equal(z.cpu(), x.to(torch.bfloat16).float())
+    a = rnd((4, 77), dtype, 9).to(DEV)
+    bias = rnd((77,), torch.float32, 10)
+    before = as64(a)
+    K.add_bias(a, bias.to(DEV))
+    np.testing.assert_allclose(as64(a), before + as64(bias), **tol(dtype))
+
+
+# ------------------------------------------------------------------------------------ #
+class PagedCase:
+    """Sequences of given context lengths with k, v scattered over shuffled pages."""
+
+    def __init__(self, ctx_lens, n_kv_heads, head_dim, dtype, seed, n_slots=None, spare_pages=3):
+        rng = np.random.RandomState(seed)
+        self.ctx_lens = list(ctx_lens)
+        B = len(ctx_lens)
+        n_slots = n_slots or B + 2
+        blocks = [(c + PAGE - 1) // PAGE for c in ctx_lens]
+        n_pages = sum(blocks) + spare_pages
+        self.max_blocks = max(blocks) + 1
+        order = rng.permutation(n_pages)
+        self.slots = rng.permutation(n_slots)[:B]
+        table = np.full((n_slots, self.max_blocks), -1, dtype=np.int32)
+        # unused pages hold NaN so that a read beyond a sequence's length shows
+        self.k_cache = torch.full((n_pages, n_kv_heads, PAGE, head_dim), float("nan"), dtype=dtype)
+        self.v_cache = torch.full((n_pages, n_kv_heads, PAGE, head_dim), float("nan"), dtype=dtype)
+        self.k, self.v = [], []
+        at = 0
+        for b, c in enumerate(ctx_lens):
+            k = rnd((c, n_kv_heads, head_dim), dtype, seed * 100 + b)
+            v = rnd((c, n_kv_heads, head_dim), dtype, seed * 100 + 50 + b)
+            self.k.append(k)
+            self.v.append(v)
+            for blk in range(blocks[b]):
+                page = int(order[at]); at += 1
+                table[self.slots[b], blk] = page
+                n = min(PAGE, c - blk * PAGE)
+                self.k_cache[page, :, :n] = k[blk * PAGE:blk * PAGE + n].transpose(0, 1)
+                self.v_cache[page, :, :n] = v[blk * PAGE:blk * PAGE + n].transpose(0, 1)
+        self.table = torch.from_numpy(table)
+
+    def write(self):
+        """Push (possibly edited) self.k / self.v back into the pages."""
+        table = self.table.numpy()
+        for b, c in enumerate(self.ctx_lens):
+            for blk in range((c + PAGE - 1) // PAGE):
+                page = table[self.slots[b], blk]
+                n = min(PAGE, c - blk * PAGE)
+                self.k_cache[page, :, :n] = self.k[b][blk * PAGE:blk * PAGE + n].transpose(0, 1)
+                self.v_cache[page, :, :n] = self.v[b][blk * PAGE:blk * PAGE + n].transpose(0, 1)
+
+    def dev(self):
+        return (self.k_cache.to(DEV), self.v_cache.to(DEV), torch.tensor(self.slots, dtype=torch.int32, device=DEV),
+                torch.tensor(self.ctx_lens, dtype=torch.int32, device=DEV), self.table.to(DEV))
+
+
+DECODE_SHAPES = [  # heads, kv heads, head_dim
+    (4, 2, 16), (6, 1, 32), (3, 3, 48), (10, 2, 80), (32, 8, 128), (8, 1, 256), (16, 16, 64), (64, 2, 16)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hk,d", DECODE_SHAPES)
+@pytest.mark.parametrize("splits", [1, 3, 8])
+def test_attention_decode(dtype, hq, hk, d, splits):
+    ctx = [1, 63, 64, 65, 300, 129]
+    case = PagedCase(ctx, hk, d, dtype, seed=hq * 7 + d)
+    q = rnd((len(ctx), hq, d), dtype, 11)
+    kc, vc, slots, ctx_t, table = case.dev()
+    out = torch.empty((len(ctx), hq * d), dtype=dtype, device=DEV)
+    scratch = torch.empty(K.attention_decode_scratch_floats(len(ctx), hq, d, splits), dtype=torch.float32, device=DEV)
+    K.attention_decode(q.reshape(len(ctx), hq * d).to(DEV), kc, vc, slots, ctx_t, table, scratch, out,
+                       len(ctx), hq, hk, d, splits, 0, 1.0 / math.sqrt(d))
+    for b, c in enumerate(ctx):
+        ref = pl.causal_attention(as64(q[b:b + 1]), as64(case.k[b]), as64(case.v[b]), q_positions=[c - 1])
+        np.testing.assert_allclose(as64(out[b]).reshape(hq, d), ref[0], **tol(dtype), err_msg=f"seq {b} ctx {c}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("far", [0, 63, 64, 447, 448, 511, 700])
+def test_attention_decode_far_key_stands_out(dtype, far):
+    # one key among 701 gets a score far above the rest: the output must be its value
+    hq, hk, d, c = 8, 2, 64, 701
+    case = PagedCase([c, 5], hk, d, dtype, seed=far + 1)
+    q = rnd((2, hq, d), dtype, 12, 0.1)
+    for g in range(hk):
+        direction = torch.zeros(d)
+        direction[g] = 1.0
+        case.k[0][far, g] = (direction * 40.0).to(dtype)
+        q[0, g * (hq // hk):(g + 1) * (hq // hk)] = (direction * 40.0).to(dtype)
+        case.v[0][far, g] = torch.full((d,), 3.0 + g).to(dtype)
+    case.write()
+    kc, vc, slots, ctx_t, table = case.dev()
+    for splits in (1, 5):
+        out = torch.empty((2, hq * d), dtype=dtype, device=DEV)
+        scratch = torch.empty(K.attention_decode_scratch_floats(2, hq, d, splits), dtype=torch.float32, device=DEV)
+        K.attention_decode(q.reshape(2, hq * d).to(DEV), kc, vc, slots, ctx_t, table, scratch, out,
+                           2, hq, hk, d, splits, 0, 1.0 / math.sqrt(d))
+        got = as64(out[0]).reshape(hq, d)
+        for h in range(hq):
+            np.testing.assert_allclose(got[h], 3.0 + h // (hq // hk), rtol=1e-2, atol=1e-2)
+        ref = pl.causal_attention(as64(q[0:1]), as64(case.k[0]), as64(case.v[0]), q_positions=[c - 1])
+        np.testing.assert_allclose(got, ref[0], **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 5, 64, 100])
+def test_attention_decode_window_edge(dtype, window):
+    # the key just outside the window is made huge: it must not be seen; the one just inside is
+    hq, hk, d = 4, 2, 32
+    ctx = [300, 70, 3]
+    case = PagedCase(ctx, hk, d, dtype, seed=window)
+    q = rnd((3, hq, d), dtype, 13, 0.1)
+    big = torch.zeros(d); big[0] = 30.0
+    for b, c in enumerate(ctx):
+        outside = c - 1 - window
+        if outside >= 0:
+            case.k[b][outside] = big.to(dtype)
+            case.v[b][outside] = torch.full((hk, d), 1000.0).to(dtype)
+    q[:, :, 0] = 30.0
+    case.write()
+    kc, vc, slots, ctx_t, table = case.dev()
+    for splits in (1, 4):
+        out = torch.empty((3, hq * d), dtype=dtype, device=DEV)
+        scratch = torch.empty(K.attention_decode_scratch_floats(3, hq, d, splits), dtype=torch.float32, device=DEV)
+        K.attention_decode(q.reshape(3, hq * d).to(DEV), kc, vc, slots, ctx_t, table, scratch, out,
+                           3, hq, hk, d, splits, window, 1.0 / math.sqrt(d))
+        for b, c in enumerate(ctx):
+            ref = pl.causal_attention(as64(q[b:b + 1]), as64(case.k[b]), as64(case.v[b]), window=window,
+                                      q_positions=[c - 1])
+            np.testing.assert_allclose(as64(out[b]).reshape(hq, d), ref[0], **tol(dtype), err_msg=f"seq {b}")
+
+
+def _prefill_tiles(q_lens):
+    tile_seq, tile_row0 = [], []
+    for i, n in enumerate(q_lens):
+        for r in range(0, n, 64):
+            tile_seq.append(i)
+            tile_row0.append(r)
+    return tile_seq, tile_row0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hk,d", [(4, 2, 16), (6, 1, 32), (3, 3, 48), (10, 2, 80), (8, 2, 128), (4, 1, 256)])
+@pytest.mark.parametrize("window", [0, 70])
+def test_attention_prefill(dtype, hq, hk, d, window):
+    # sequences that start at 0 and sequences that continue an existing context
+    ctx = [200, 1, 65, 130, 64]
+    q_lens = [200, 1, 3, 66, 64]
+    case = PagedCase(ctx, hk, d, dtype, seed=d + hq)
+    total = sum(q_lens)
+    q = rnd((total, hq, d), dtype, 14)
+    kc, vc, slots, ctx_t, table = case.dev()
+    qstart = np.concatenate([[0], np.cumsum(q_lens)[:-1]]).astype(np.int32)
+    tile_seq, tile_row0 = _prefill_tiles(q_lens)
+    out = torch.empty((total, hq * d), dtype=dtype, device=DEV)
+    i32 = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=DEV)
+    K.attention_prefill(q.reshape(total, hq * d).to(DEV), kc, vc, slots, ctx_t, i32(qstart), i32(q_lens),
+                        i32(tile_seq), i32(tile_row0), table, out, len(tile_seq), hq, hk, d, window,
+                        1.0 / math.sqrt(d))
+    got = as64(out).reshape(total, hq, d)
+    for b, (c, n) in enumerate(zip(ctx, q_lens)):
+        rows = slice(qstart[b], qstart[b] + n)
+        ref = pl.causal_attention(as64(q[rows]), as64(case.k[b]), as64(case.v[b]), window=window or None,
+                                  q_positions=list(range(c - n, c)))
+        np.testing.assert_allclose(got[rows], ref, **tol(dtype), err_msg=f"seq {b}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_prefill_far_key_stands_out(dtype):
+    hq, hk, d, c = 4, 2, 64, 520
+    case = PagedCase([c], hk, d, dtype, seed=99)
+    q = rnd((c, hq, d), dtype, 15, 0.1)
+    far = 70
+    direction = torch.zeros(d); direction[3] = 40.0
+    case.k[0][far] = direction.to(dtype)
+    case.v[0][far] = torch.full((hk, d), 7.0).to(dtype)
+    q[:, :, :] = (direction * 1.0).to(dtype)
+    case.write()
+    kc, vc, slots, ctx_t, table = case.dev()
+    tile_seq, tile_row0 = _prefill_tiles([c])
+    i32 = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=DEV)
+    out = torch.empty((c, hq * d), dtype=dtype, device=DEV)
+    K.attention_prefill(q.reshape(c, hq * d).to(DEV), kc, vc, slots, ctx_t, i32([0]), i32([c]), i32(tile_seq),
+                        i32(tile_row0), table, out, len(tile_seq), hq, hk, d, 0, 1.0 / math.sqrt(d))
+    got = as64(out).reshape(c, hq, d)
+    np.testing.assert_allclose(got[far:], 7.0, rtol=1e-2, atol=1e-2)   # every query from `far` on sees it
+    ref = pl.causal_attention(as64(q), as64(case.k[0]), as64(case.v[0]))
+    np.testing.assert_allclose(got, ref, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("interleaved", [True, False])
+@pytest.mark.parametrize("hq,hk,d", [(4, 2, 16), (3, 3, 48), (8, 2, 128)])
+def test_rope_cache_write(dtype, interleaved, hq, hk, d):
+    max_pos = 400
+    inv = pl.rope_inverse_frequencies(d, 10000.0)
+    ang = np.arange(max_pos)[:, None] * inv[None, :]
+    cos, sin = torch.tensor(np.cos(ang), dtype=torch.float32), torch.tensor(np.sin(ang), dtype=torch.float32)
+    starts, lens = [0, 63, 130], [5, 3, 70]   # tokens land on page edges
+    ctx = [s + n for s, n in zip(starts, lens)]
+    case = PagedCase(ctx, hk, d, dtype, seed=3)
+    T = sum(lens)
+    width = (hq + 2 * hk) * d
+    qkv = rnd((T, width), dtype, 16)
+    bias = rnd((width,), torch.float32, 17, 0.5)
+    tok_pos = np.concatenate([np.arange(s, s + n) for s, n in zip(starts, lens)]).astype(np.int32)
+    tok_seq = np.repeat(np.arange(3), lens).astype(np.int32)
+    kc, vc, slots, _, table = case.dev()
+    k_before, v_before = kc.clone(), vc.clone()
+    q_out = torch.empty((T, hq * d), dtype=dtype, device=DEV)
+    i32 = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=DEV)
+    K.rope_cache_write(qkv.to(DEV), bias.to(DEV), cos.to(DEV), sin.to(DEV), i32(tok_pos), i32(tok_seq), slots, table,
+                       q_out, kc, vc, hq, hk, d, interleaved)
+    x = as64(qkv) + as64(bias)
+    q_ref = pl.apply_rope(x[:, :hq * d].reshape(T, hq, d), tok_pos, inv, interleaved)
+    k_ref = pl.apply_rope(x[:, hq * d:(hq + hk) * d].reshape(T, hk, d), tok_pos, inv, interleaved)
+    v_ref = x[:, (hq + hk) * d:].reshape(T, hk, d)
+    np.testing.assert_allclose(as64(q_out).reshape(T, hq, d), q_ref, **tol(dtype))
+    touched = torch.zeros(kc.shape[:1] + kc.shape[2:3], dtype=torch.bool)
+    tab = case.table.numpy()
+    for t in range(T):
+        page, off = tab[case.slots[tok_seq[t]], tok_pos[t] // PAGE], tok_pos[t] % PAGE
+        touched[page, off] = True
+        np.testing.assert_allclose(as64(kc[page, :, off]), k_ref[t], **tol(dtype))
+        np.testing.assert_allclose(as64(vc[page, :, off]), v_ref[t], **tol(dtype))
+    # every other row of the cache is untouched, bit for bit
+    same = lambda a, b: torch.equal(a.view(torch.int16 if dtype == torch.bfloat16 else torch.int32),
+                                    b.view(torch.int16 if dtype == torch.bfloat16 else torch.int32))
+    keep = ~touched.to(DEV)
+    assert same(kc.transpose(1, 2)[keep], k_before.transpose(1, 2)[keep])
+    assert same(vc.transpose(1, 2)[keep], v_before.transpose(1, 2)[keep])
+
+
+# ------------------------------------------------------------------------------------ #
+def test_argmax_first_of_ties_and_status():
+    logits = rnd((6, 50257), torch.float32, 18)
+    logits[0, 100] = logits[0, 40000] = 9.0          # tie: the lower id wins (src/sampler.cc:31-41)
+    logits[1] = 0.0                                   # all equal: id 0
+    logits[2, 50256] = 12.0
+    logits[3, 7] = float("nan")
+    logits[4, 0] = 20.0
+    tokens = torch.empty(6, dtype=torch.int32, device=DEV)
+    status = torch.empty(6, dtype=torch.int32, device=DEV)
+    K.argmax(logits.to(DEV), tokens, status)
+    got = tokens.cpu().tolist()
+    assert got[0] == 100 and got[1] == 0 and got[2] == 50256 and got[4] == 0
+    assert got[5] == pl.greedy(logits[5].numpy())
+    assert status.cpu().tolist() == [0, 0, 0, 1, 0, 0]
+
+
+def _cdf_interval_ok(logits, temperature, top_k, u, token):
+    """The token's slice of the cumulative distribution contains u (with float32 slack)."""
+    logits = logits.astype(np.float64)
+    ids = np.arange(len(logits))
+    if top_k:
+        ids = np.lexsort((ids, -logits))[:top_k]
+    w = np.exp((logits[ids] - logits[ids].max()) / temperature)
+    cdf = np.cumsum(w) / w.sum()
+    where = np.nonzero(ids == token)[0]
+    if len(where) == 0:
+        return False
+    i = int(where[0])
+    lo = cdf[i - 1] if i else 0.0
+    return lo - 1e-4 <= u <= cdf[i] + 1e-4
+
+
+@pytest.mark.parametrize("vocab", [131, 1000, 50257])
+@pytest.mark.parametrize("top_k", [0, 2, 40, 1000])
+def test_sampling_follows_the_plain_rule(vocab, top_k):
+    if top_k > vocab:
+        top_k = vocab
+    rows, temperature, seed = 48, 0.8, 1234
+    logits = rnd((rows, vocab), torch.float32, 19, 3.0)
+    logits[0, :10] = 5.0  # ties inside the kept set
+    request = torch.arange(rows, dtype=torch.int32)
+    step = (torch.arange(rows, dtype=torch.int32) * 7) % 13
+    tokens = torch.empty(rows, dtype=torch.int32, device=DEV)
+    status = torch.empty(rows, dtype=torch.int32, device=DEV)
+    K.sample(logits.to(DEV), temperature, top_k, seed, request.to(DEV), step.to(DEV), tokens, status)
+    again = torch.empty_like(tokens)
+    K.sample(logits.to(DEV), temperature, top_k, seed, request.to(DEV), step.to(DEV), again, status)
+    assert torch.equal(tokens, again)  # seeded: reproducible
+    assert status.cpu().tolist() == [0] * rows
+    exact = 0
+    for r in range(rows):
+        u = float(pl.uniform_from_counter(seed, int(request[r]), int(step[r])))
+        token = int(tokens[r])
+        assert _cdf_interval_ok(logits[r].numpy(), temperature, top_k, u, token), f"row {r}: token {token}, u {u}"
+        exact += token == pl.sample(logits[r].numpy(), temperature, top_k, u)
+    assert exact >= rows - 2  # identical but for float32 summation order at an interval's edge
+
+
+def test_sampling_distribution():
+    # 4 candidates, 4000 draws: frequencies follow softmax(l / T)
+    vocab, rows, temperature = 300, 4000, 1.5
+    base = torch.full((vocab,), -50.0)
+    base[[3, 50, 51, 299]] = torch.tensor([1.0, 2.0, 0.0, 1.5])
+    logits = base.repeat(rows, 1).contiguous()
+    request = torch.arange(rows, dtype=torch.int32, device=DEV)
+    step = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    tokens = torch.empty(rows, dtype=torch.int32, device=DEV)
+    status = torch.empty(rows, dtype=torch.int32, device=DEV)
+    for top_k in (0, 4):
+        K.sample(logits.to(DEV), temperature, top_k, 7, request, step, tokens, status)
+        counts = np.bincount(tokens.cpu().numpy(), minlength=vocab)
+        p = np.exp(np.array([1.0, 2.0, 0.0, 1.5]) / temperature)
+        p /= p.sum()
+        assert counts[[3, 50, 51, 299]].sum() == rows
+        np.testing.assert_allclose(counts[[3, 50, 51, 299]] / rows, p, atol=0.03)
+
+
+def test_kernels_refuse_bad_sizes():
+    q = torch.zeros((1, 4 * 24), dtype=torch.float32, device=DEV)
+    cache = torch.zeros((2, 2, PAGE, 24), dtype=torch.float32, device=DEV)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)
+    with pytest.raises(K.KernelError, match="multiple of 16"):
+        K.attention_decode(q, cache, cache, i32([0]), i32([1]), i32([[0]]), None, torch.empty_like(q), 1, 4, 2, 24,
+                           1, 0, 1.0)
+    with pytest.raises(K.KernelError, match="CUDA tensor"):
+        K.argmax(torch.zeros((1, 8)), i32([0]), i32([0]))
+    with pytest.raises(K.KernelError, match="top_k"):
+        K.sample(torch.zeros((1, 5000), device=DEV), 1.0, 2000, 1, i32([0]), i32([0]), i32([0]), i32([0]))
