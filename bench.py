@@ -1,0 +1,281 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the Llama-3.1-8B shape on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints one JSON line.  A step is one decode step of a batch of 8 sequences with unequal
+prompts (uniform in [128, 2048)) on a cache sized for 4096 tokens each; `value` is decoded
+tokens per second measured with CUDA events around K steps after W warm-up steps.  The
+same line carries: `e2e` (the same metric through `LLM.generate`, token ids in host lists
+in and out), `prefill` (one 2,048-token prompt), `roofline` (bytes a decode step must
+read / its time, against the measured HBM copy bandwidth) and `points` (decode at batch 1
+and 64).  Weights are random (N(0, 0.02)), token ids synthetic; every decode step reads
+about 15 GB of weights, far more than the 126 MB L2, so no L2 flush is needed between
+iterations.  The metric definitions follow the reference's strict bench (timers around
+forwards only, warm-ups first, fresh cache: src/bench_strict.cc:146-176).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+BATCH = 8
+CONTEXT = 4096
+PROMPT_RANGE = (128, 2048)
+PREFILL_TOKENS = 2048
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peaks = dict(FALLBACK_PEAKS)
+    if os.path.isfile(path):
+        try:
+            raw = json.load(open(path))
+            flat = {}
+
+            def walk(node):
+                if isinstance(node, dict):
+                    for k, v in node.items():
+                        if isinstance(v, (int, float)):
+                            flat.setdefault(k, float(v))
+                        else:
+                            walk(v)
+            walk(raw)
+            if "hbm_gbs" in flat:
+                peaks["hbm_gbs"] = flat["hbm_gbs"]
+                peaks["source"] = "measured"
+            if "bf16_tflops" in flat:
+                peaks["bf16_tflops"] = flat["bf16_tflops"]
+            if "bf16_tflops_sustained" in flat:
+                peaks["bf16_tflops_sustained"] = flat["bf16_tflops_sustained"]
+        except (OSError, ValueError):
+            pass
+    return peaks
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.samples = []
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        clocks, reasons, top = [], set(), None
+        for sm, mx, hw, hwt, swt, cap in self.samples:
+            try:
+                clocks.append(int(float(sm)))
+                top = int(float(mx))
+            except ValueError:
+                continue
+            for name, flag in (("hw_slowdown", hw), ("hw_thermal_slowdown", hwt), ("sw_thermal_slowdown", swt),
+                               ("sw_power_cap", cap)):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": top,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def llama31_8b(layers=None):
+    import cpp_minilamma_b200 as ml
+    return ml.config_from_dict({
+        "architectures": ["LlamaForCausalLM"], "vocab_size": 128256, "hidden_size": 4096,
+        "intermediate_size": 14336, "num_hidden_layers": layers or 32, "num_attention_heads": 32,
+        "num_key_value_heads": 8, "head_dim": 128, "max_position_embeddings": 131072, "rope_theta": 500000.0,
+        "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                         "original_max_position_embeddings": 8192},
+        "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "torch_dtype": "bfloat16"})
+
+
+def prompts_for(batch, vocab, seed):
+    import numpy as np
+    rng = np.random.RandomState(seed)
+    lens = rng.randint(PROMPT_RANGE[0], PROMPT_RANGE[1], size=batch)
+    return [[int(t) for t in rng.randint(0, vocab, size=n)] for n in lens]
+
+
+def time_decode(llm, batch, steps, warmup, seed, sampler=None):
+    """Prefill `batch` unequal prompts, then time `steps` decode steps (greedy sampling on
+    the device included) with CUDA events.  Returns (ms per step, live context tokens at
+    the middle of the timed region, launches of this library's kernels per step)."""
+    import torch
+    from cpp_minilamma_b200 import EngineBackend, SamplingParams, StepEntry
+    from cpp_minilamma_b200.csrc import kernels as K
+    engine = llm.engine
+    backend = EngineBackend(engine, SamplingParams())
+    prompts = prompts_for(batch, llm.config.vocab_size, seed)
+    slots = engine.acquire(batch)
+    try:
+        tokens = backend.step_and_sample([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)],
+                                         list(range(batch)), [0] * batch)
+        for i in range(warmup):
+            tokens = backend.step_and_sample([StepEntry(s, [t], [0]) for s, t in zip(slots, tokens)],
+                                             list(range(batch)), [i + 1] * batch)
+        torch.cuda.synchronize()
+        if sampler:
+            sampler.start()
+        launches_before = K.launches
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for i in range(steps):
+            tokens = backend.step_and_sample([StepEntry(s, [t], [0]) for s, t in zip(slots, tokens)],
+                                             list(range(batch)), [warmup + i + 1] * batch)
+        end.record()
+        torch.cuda.synchronize()
+        if sampler:
+            sampler.stop()
+        ms = begin.elapsed_time(end) / steps
+        live = sum(len(p) for p in prompts) + batch * (warmup + steps // 2)
+        return ms, live, (K.launches - launches_before) / steps
+    finally:
+        for s in slots:
+            engine.release(s)
+
+
+def time_e2e(llm, batch, steps, seed):
+    """Decoded tokens per second through LLM.generate: host token lists in, host lists out."""
+    prompts = prompts_for(batch, llm.config.vocab_size, seed)
+    stats = {}
+    llm.generate(prompts, max_new_tokens=steps + 1, ignore_eos=True, stats=stats)
+    return stats
+
+
+def time_prefill(llm, tokens, reps, warmup, seed):
+    import numpy as np
+    import torch
+    from cpp_minilamma_b200 import StepEntry
+    rng = np.random.RandomState(seed)
+    prompt = [int(t) for t in rng.randint(0, llm.config.vocab_size, size=tokens)]
+    times = []
+    for i in range(warmup + reps):
+        slot, = llm.engine.acquire(1)
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        begin.record()
+        llm.engine.step_borrowed([StepEntry(slot, prompt, [tokens - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        llm.engine.release(slot)
+        if i >= warmup:
+            times.append(begin.elapsed_time(end))
+    return sum(times) / len(times)
+
+
+def prefill_flops(cfg, tokens):
+    d, hq, hk = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+    per_layer = 2 * tokens * cfg.hidden_size * ((hq + 2 * hk) * d + hq * d) \
+        + 2 * tokens * cfg.hidden_size * cfg.intermediate_size * 3 \
+        + 2 * hq * tokens * tokens * d  # causal: half of 4 T^2 d per head
+    return cfg.num_hidden_layers * per_layer + 2 * cfg.hidden_size * cfg.vocab_size  # head on one row
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
+    parser.add_argument("--skip-points", action="store_true")
+    args = parser.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "pip cannot install the reference: a CMake C++ project with neither setup.py nor "
+                          "pyproject.toml; it runs one sequence token by token and has no batch decode"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this single-GPU library")
+        return 2
+
+    import torch
+    import cpp_minilamma_b200 as ml
+    warmup = max(args.warmup, 3)
+    steps = max(args.steps, 1)
+    peaks = load_peaks()
+    cfg = llama31_8b(args.layers)
+    budget = 64 * (PROMPT_RANGE[1] + warmup + steps + 64)  # room for the batch-64 point
+    llm = ml.random_model(cfg, seed=0, dtype="bfloat16", max_tokens=max(budget, BATCH * CONTEXT),
+                          max_positions=CONTEXT, max_seqs=64, max_step_tokens=4096)
+    sampler = ClockSampler()
+    ms, live_tokens, launches = time_decode(llm, BATCH, steps, warmup, seed=1, sampler=sampler)
+    value = BATCH * 1000.0 / ms
+    weight_bytes = llm.model.step_weight_bytes()
+    kv_bytes = llm.engine.cache.kv_bytes_per_token() * live_tokens
+    achieved = (weight_bytes + kv_bytes) / (ms * 1e-3) / 1e9
+
+    stats = time_e2e(llm, BATCH, steps, seed=2)
+    e2e_value = BATCH * stats["decode_steps"] / stats["decode_s"]
+    meta_ints = 3 * BATCH + 4 * BATCH + BATCH  # tokens, positions, sequence ids, 4 per-sequence arrays, wanted rows
+
+    prefill_ms = time_prefill(llm, PREFILL_TOKENS, reps=5, warmup=3, seed=3)
+    flops = prefill_flops(cfg, PREFILL_TOKENS)
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            p_ms, _, _ = time_decode(llm, b, max(steps // 2, 8), warmup, seed=10 + b)
+            points[f"decode_b{b}"] = round(b * 1000.0 / p_ms, 1)
+
+    line = {
+        "metric": "decode tok/s at batch 8 (Llama-3.1-8B shape, random bf16 weights)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic token ids, random-init weights", "impl": "ours",
+        "config": {"model": "Llama-3.1-8B shape", "layers": cfg.num_hidden_layers, "layers_full": 32,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "global_batch": BATCH, "seq_len": CONTEXT, "prompt_lens": "uniform[128,2048)",
+                   "parallelism": "1 gpu", "l2": "inputs larger than L2 (15 GB of weights per step)",
+                   "peaks": peaks["source"]},
+        "clocks": sampler.summary(),
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": 4 * meta_ints,
+                "d2h_bytes_per_step": 4 * 2 * 64},
+        "gpu_launches": int(round(launches * steps)),
+        "prefill": {"value": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(prefill_ms, 3),
+                    "frac": round(flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4)},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

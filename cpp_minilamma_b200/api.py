@@ -82,14 +82,14 @@ class LLM:
     def generate_detailed(self, prompts: Sequence[Sequence[int]], max_new_tokens=None, temperature: float = 0.0,
                           top_k: int = 0, seed: int = 1, stop_ids: Optional[Sequence[int]] = None,
                           ignore_eos: bool = False, max_batch: Optional[int] = None, clip: bool = False,
-                          n_predict=None) -> List[Completion]:
+                          n_predict=None, stats: Optional[dict] = None) -> List[Completion]:
         if max_new_tokens is None:
             max_new_tokens = 4 if n_predict is None else n_predict  # the reference CLI's default of 4
         params = SamplingParams(float(temperature), int(top_k), int(seed))
         params.validate(self.model.spec.vocab_size)
         stops = set(self.stop_token_ids) | set(stop_ids or ())
         backend = EngineBackend(self.engine, params)
-        return generate(backend, prompts, max_new_tokens, stops, ignore_eos, max_batch, clip)
+        return generate(backend, prompts, max_new_tokens, stops, ignore_eos, max_batch, clip, stats)
 
     def generate(self, prompts: Sequence[Sequence[int]], **options) -> List[List[int]]:
         """Token ids generated for each prompt (stop tokens are not included)."""

@@ -40,7 +40,12 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
-def _check(code: int, what: str) -> None:
+launches = 0  # kernels of this library launched so far (counted per successful call)
+
+
+def _check(code: int, what: str, kernels: int = 1) -> None:
+    global launches
+    launches += kernels
     if code != 0:
         message = lib().mll_last_error().decode("utf-8", "replace")
         raise KernelError(f"{what}: {message} (code {code})")
@@ -219,7 +224,7 @@ def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratc
                                  ctypes.c_int(n_seqs), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
                                  ctypes.c_int(head_dim), ctypes.c_int(block_table.shape[1]),
                                  ctypes.c_int(n_splits), ctypes.c_int(window), ctypes.c_float(scale),
-                                 _stream()), "attention_decode")
+                                 _stream()), "attention_decode", kernels=2 if n_splits > 1 else 1)
 
 
 def attention_prefill(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0,

@@ -14,6 +14,7 @@ limits), so its decisions can be tested without a device.
 """
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence, Set
 
@@ -80,13 +81,16 @@ def plan_batches(prompt_lens: Sequence[int], max_new: Sequence[int], n_slots: in
 
 
 def generate(backend: Backend, prompts: Sequence[Sequence[int]], max_new_tokens, stop_ids: Set[int] = frozenset(),
-             ignore_eos: bool = False, max_batch: Optional[int] = None, clip: bool = False) -> List[Completion]:
+             ignore_eos: bool = False, max_batch: Optional[int] = None, clip: bool = False,
+             stats: Optional[dict] = None) -> List[Completion]:
     """Generate for every prompt; results come back in request order.
 
     max_new_tokens: one number for all requests or one per request.  A request whose
     prompt plus new tokens exceeds the model's positions is an error (the reference's
     "prompt + n-predict exceeds context window", app/backend_cli.cc:146-148) unless
-    `clip` shortens it (its legacy bench clips, app/main.cc:170).
+    `clip` shortens it (its legacy bench clips, app/main.cc:170).  `stats`, when given,
+    receives wall-clock seconds and counts of the prompt steps and of the decode steps
+    (sampling included, as the caller sees them).
     """
     n_requests = len(prompts)
     if isinstance(max_new_tokens, int):
@@ -118,11 +122,11 @@ def generate(backend: Backend, prompts: Sequence[Sequence[int]], max_new_tokens,
                            backend.n_slots, backend.n_pages, max_batch)
     for batch in batches:
         requests = [active[j] for j in batch]
-        _run_batch(backend, requests, prompts, budgets, stops, results)
+        _run_batch(backend, requests, prompts, budgets, stops, results, stats)
     return results
 
 
-def _run_batch(backend, requests, prompts, budgets, stops, results) -> None:
+def _run_batch(backend, requests, prompts, budgets, stops, results, stats=None) -> None:
     slots = backend.acquire(len(requests))
     live = dict(zip(requests, slots))  # request -> slot, in request order
     try:
@@ -130,7 +134,15 @@ def _run_batch(backend, requests, prompts, budgets, stops, results) -> None:
         produced = 0
         while live:
             order = list(live)
+            began = time.perf_counter()
             sampled = backend.step_and_sample(entries, order, [produced] * len(order))
+            if stats is not None:
+                kind = "prefill" if produced == 0 else "decode"
+                if produced == 0:
+                    decode_began = time.perf_counter()
+                    stats["prefill_s"] = stats.get("prefill_s", 0.0) + decode_began - began
+                stats[kind + "_steps"] = stats.get(kind + "_steps", 0) + 1
+                stats[kind + "_tokens"] = stats.get(kind + "_tokens", 0) + sum(len(e.tokens) for e in entries)
             produced += 1
             entries = []
             for r, token in zip(order, sampled):
@@ -146,6 +158,9 @@ def _run_batch(backend, requests, prompts, budgets, stops, results) -> None:
                     backend.release(live.pop(r))
                 else:
                     entries.append(StepEntry(live[r], [int(token)], [0]))
+        if stats is not None and produced:
+            # everything after the prompt step: decode steps, sampling, host bookkeeping
+            stats["decode_s"] = stats.get("decode_s", 0.0) + time.perf_counter() - decode_began
     finally:
         for slot in live.values():
             backend.release(slot)

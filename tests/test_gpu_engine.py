@@ -181,3 +181,29 @@ def test_run_dtype_differs_from_storage(model_folders, dtype, storage):
     for t in range(30, 40):
         got.append(llm.engine.step([StepEntry(slot, [tokens[t]], [0])]).cpu().numpy())
     assert_close(np.concatenate(got), plain_logits(folder, tokens, dtype), dtype, f"run {dtype} on {storage}")
+
+
+def test_cli_generate_matches_the_api(model_folders, capsys):
+    from cpp_minilamma_b200.cli import main
+    folder, llm = load(model_folders, "B", "float32")
+    prompts = [[5, 17, 3], [9, 9], [200]]
+    expect = llm.generate(prompts, max_new_tokens=5, ignore_eos=True)
+    argv = ["generate", folder, "--dtype", "float32", "-n", "5", "--ignore-eos"]
+    for p in prompts:
+        argv += ["-p", " ".join(map(str, p))]
+    assert main(argv) == 0
+    lines = capsys.readouterr().out.splitlines()
+    assert [[int(t) for t in line.split()] for line in lines[:3]] == expect
+    assert lines[-1].startswith("trace summary: trace_id=") and lines[-1].endswith("status=ok")
+    # sampling with a seed is reproducible and differs between seeds
+    a = llm.generate(prompts, max_new_tokens=12, temperature=1.0, top_k=50, seed=7, ignore_eos=True)
+    b = llm.generate(prompts, max_new_tokens=12, temperature=1.0, top_k=50, seed=7, ignore_eos=True)
+    c = llm.generate(prompts, max_new_tokens=12, temperature=1.0, top_k=50, seed=8, ignore_eos=True)
+    assert a == b and a != c
+    # a request's samples do not depend on its neighbours in the batch
+    alone = llm.generate(prompts[:1], max_new_tokens=12, temperature=1.0, top_k=50, seed=7, ignore_eos=True)
+    assert alone[0] == a[0]
+    # stop tokens end a sequence and are not emitted
+    stops = llm.generate(prompts, max_new_tokens=5, stop_ids=[expect[0][2]])
+    assert stops[0] == expect[0][:2]
+    assert main(["generate", folder, "-p", "1 2 3", "-n", "400", "--dtype", "float32"]) == 2   # over the context

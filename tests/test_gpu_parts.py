@@ -1,0 +1,342 @@
+"""Each part alone against its plain counterpart, and the framework's openness: a toy mixer
+with state of its own, a toy architecture whose layers differ, whose schedule names a
+layer twice and lets an entry read another entry's cache - all defined here, registered
+and stepped without touching the package."""
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+import cpp_minilamma_b200 as ml
+import plain_llama as pl
+from cpp_minilamma_b200 import StepEntry
+from cpp_minilamma_b200.cache import SequenceCache
+from cpp_minilamma_b200.config.base import ModelConfig, take_int
+from cpp_minilamma_b200.engine.step import StepState, Workspace
+from cpp_minilamma_b200.parts import (BuildContext, CacheNeed, LayerSpec, Mixer, ModelSpec, PartSpec, ScheduleEntry,
+                                      StateNeed, WeightSpec, WeightStore, build_part, register_part)
+from cpp_minilamma_b200.parts.rope import inverse_frequencies
+from helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-6) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-3)
+
+
+def as64(t):
+    return t.detach().float().cpu().numpy().astype(np.float64)
+
+
+def rnd(shape, seed, scale=1.0):
+    return torch.randn(shape, generator=torch.Generator().manual_seed(seed)) * scale
+
+
+def make_state(slots, starts, lens, tokens=None):
+    """A StepState for sequences in `slots` that bring `lens` tokens from positions `starts`."""
+    i32 = lambda a: torch.tensor(np.asarray(a, dtype=np.int32), device=DEV)
+    n_tokens = sum(lens)
+    tile_seq, tile_row0 = [], []
+    for i, n in enumerate(lens):
+        for r in range(0, n, 64):
+            tile_seq.append(i)
+            tile_row0.append(r)
+    ctx = [s + n for s, n in zip(starts, lens)]
+    return StepState(
+        ws=Workspace(DEV), n_tokens=n_tokens, n_seqs=len(slots),
+        tokens=i32(tokens if tokens is not None else [0] * n_tokens),
+        tok_pos=i32(np.concatenate([np.arange(s, s + n) for s, n in zip(starts, lens)])),
+        tok_seq=i32(np.repeat(np.arange(len(lens)), lens)), seq_slot=i32(slots), seq_ctx=i32(ctx),
+        seq_qstart=i32(np.concatenate([[0], np.cumsum(lens)[:-1]])), seq_qlen=i32(lens),
+        tile_seq=i32(tile_seq), tile_row0=i32(tile_row0), n_tiles=len(tile_seq), want_rows=None,
+        all_decode=all(n == 1 for n in lens), max_ctx=max(ctx),
+        host={"slots": list(slots), "lens": list(lens), "starts": list(starts)})
+
+
+def ctx_for(dtype, hidden, max_positions=512):
+    return BuildContext(hidden, dtype, DEV, max_positions)
+
+
+def bind(part, dtype, seed):
+    tensors = {}
+    for i, spec in enumerate(part.weight_specs()):
+        t = rnd(spec.shape, seed + i, 0.05)
+        if spec.init == "norm":
+            t = 1 + t
+        tensors[spec.name] = t.to(torch.float32 if spec.kind == "vector" else dtype).to(DEV)
+    host = {k: as64(v) for k, v in tensors.items()}
+    part.bind(WeightStore(tensors))
+    return host
+
+
+# ------------------------------------------------------------------------------------ #
+def test_rotary_tables_match_the_plain_frequencies():
+    scaling = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+               "original_max_position_embeddings": 32}
+    for head_dim, theta, sc in [(16, 10000.0, None), (32, 500000.0, scaling), (128, 500000.0,
+                                {**scaling, "original_max_position_embeddings": 8192})]:
+        ours = inverse_frequencies(head_dim, theta, sc)
+        plain = pl.rope_inverse_frequencies(head_dim, theta, sc)
+        np.testing.assert_allclose(ours, plain, rtol=1e-14)
+        if sc:  # the three regimes are all present for the small original length
+            ratio = plain / pl.rope_inverse_frequencies(head_dim, theta, None)
+            assert ratio.max() == 1.0 and np.isclose(ratio.min(), 1 / 8)
+        part = build_part("position_encoding", PartSpec("rotary", {"head_dim": head_dim, "theta": theta,
+                                                                    "scaling": sc, "interleaved": False}),
+                          ctx_for(torch.float32, 64, 300))
+        cos, sin = part.tables()
+        ang = np.arange(300)[:, None] * plain[None, :]
+        np.testing.assert_allclose(cos.cpu().numpy(), np.cos(ang), atol=1e-7)
+        np.testing.assert_allclose(sin.cpu().numpy(), np.sin(ang), atol=1e-7)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_norm_part(dtype):
+    part = build_part("norm", PartSpec("rms_norm", {"width": 100, "eps": 3e-4, "name": "n.weight"}), ctx_for(dtype, 100))
+    host = bind(part, dtype, 1)
+    x = rnd((9, 100), 2).to(DEV)
+    delta = rnd((9, 100), 3).to(dtype).to(DEV)
+    expect_x = as64(x) + as64(delta)
+    out = part.forward(make_state([0], [0], [9]), x, delta)
+    np.testing.assert_allclose(as64(out), pl.rms_norm(expect_x, host["n.weight"], 3e-4), **tol(dtype))
+    np.testing.assert_allclose(as64(x), expect_x, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inter", [250, 176])
+def test_feed_forward_part(dtype, inter):
+    names = {p: f"mlp.{p}_proj" for p in ("gate", "up", "down")}
+    part = build_part("feed_forward", PartSpec("swiglu", {"intermediate": inter, "names": names}), ctx_for(dtype, 100))
+    host = bind(part, dtype, 10)
+    assert part.block == (8 if inter % 8 == 0 else 0)
+    h = rnd((13, 100), 4).to(dtype).to(DEV)
+    out = part.forward(make_state([0], [0], [13]), h)
+    round_ = pl.round_bf16 if dtype == torch.bfloat16 else (lambda v: v)
+    ref = pl.feed_forward(as64(h), host["mlp.gate_proj.weight"], host["mlp.up_proj.weight"],
+                          host["mlp.down_proj.weight"], round_)
+    np.testing.assert_allclose(as64(out), ref, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_and_head_parts(dtype):
+    ctx = ctx_for(dtype, 100)
+    emb = build_part("embedding", PartSpec("token_embedding", {"vocab": 333, "name": "e.weight"}), ctx)
+    head = build_part("lm_head", PartSpec("linear_head", {"vocab": 333, "name": "h.weight", "tied_to": "e.weight"}), ctx)
+    assert head.weight_specs() == []
+    table = rnd((333, 100), 5, 0.05).to(dtype).to(DEV)
+    store = WeightStore({"e.weight": table})
+    emb.bind(store)
+    head.bind(store)
+    state = make_state([0], [0], [4], tokens=[332, 0, 7, 7])
+    x = emb.forward(state, state.tokens)
+    np.testing.assert_array_equal(x.cpu().numpy(), table.float().cpu().numpy()[[332, 0, 7, 7]])
+    h = rnd((4, 100), 6).to(dtype).to(DEV)
+    logits = head.forward(state, h)
+    assert logits.dtype == torch.float32
+    np.testing.assert_allclose(as64(logits), as64(h) @ as64(table).T, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [0, 40])
+def test_attention_part_prefill_then_decode(dtype, window):
+    hidden, hq, hk, d = 100, 6, 2, 32
+    position = PartSpec("rotary", {"head_dim": d, "theta": 1000.0, "scaling": None, "interleaved": True})
+    names = {p: f"a.{p}_proj" for p in "qkvo"}
+    ctx = ctx_for(dtype, hidden)
+    part = build_part("mixer", PartSpec("attention", {
+        "n_heads": hq, "n_kv_heads": hk, "head_dim": d, "window": window, "position": position,
+        "qkv_bias": True, "o_bias": True, "names": names}), ctx)
+    host = bind(part, dtype, 20)
+    cache = SequenceCache([(0, None, part.cache_need())], 64 * 8, 4, 512, dtype, DEV)
+    slots = cache.acquire(2)
+    lens = [70, 5]
+    h = rnd((sum(lens) + 2, hidden), 7).to(dtype)
+    # prompts of 70 and 5 tokens in one step, then one token each
+    cache.reserve(list(zip(slots, lens)))
+    cache.flush()
+    out1 = part.forward(make_state(slots, [0, 0], lens), h[:75].to(DEV), cache.view(0)).clone()
+    cache.reserve([(s, 1) for s in slots])
+    cache.flush()
+    out2 = part.forward(make_state(slots, lens, [1, 1]), h[75:].to(DEV), cache.view(0)).clone()
+    cfg = {"num_attention_heads": hq, "num_key_value_heads": hk, "head_dim": d, "hidden_size": hidden,
+           "rope_interleaved": True, "sliding_window": window or None}
+    weights = {f"self_attn.{p}_proj.{kind}": host[f"a.{p}_proj.{kind}"] for p in "qkvo" for kind in ("weight", "bias")}
+    inv = pl.rope_inverse_frequencies(d, 1000.0)
+    round_ = pl.round_bf16 if dtype == torch.bfloat16 else (lambda v: v)
+    seq0 = np.concatenate([as64(h[:70]), as64(h[75:76])])
+    seq1 = np.concatenate([as64(h[70:75]), as64(h[76:77])])
+    ref0 = pl.attention_block(seq0, np.arange(71), weights, "", cfg, inv, round_)
+    ref1 = pl.attention_block(seq1, np.arange(6), weights, "", cfg, inv, round_)
+    np.testing.assert_allclose(as64(out1[:70]), ref0[:70], **tol(dtype))
+    np.testing.assert_allclose(as64(out1[70:]), ref1[:5], **tol(dtype))
+    np.testing.assert_allclose(as64(out2[0]), ref0[70], **tol(dtype))
+    np.testing.assert_allclose(as64(out2[1]), ref1[5], **tol(dtype))
+    # what the cache holds is the rotated key and the value of every position
+    k, v = cache.read_kv(0, slots[1])
+    x = seq1 @ weights["self_attn.k_proj.weight"].T + weights["self_attn.k_proj.bias"]
+    k_ref = pl.apply_rope(round_(x).reshape(6, hk, d), np.arange(6), inv, True)
+    np.testing.assert_allclose(as64(k), k_ref, **tol(dtype))
+
+
+# ------------------------------------------------------------------------------------ #
+# a toy mixer with state of its own and a toy architecture, defined here                #
+# ------------------------------------------------------------------------------------ #
+class RunningMeanMixer(Mixer):
+    """out_t = W . mean(h_0 .. h_t): keeps (sum, count) per sequence as fixed-size state."""
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.name = params["name"]
+        self.weight = None
+
+    def weight_specs(self):
+        D = self.ctx.hidden_size
+        return [WeightSpec(self.name, (D, D))]
+
+    def bind(self, store):
+        self.weight = store.take(self.name)
+
+    def cache_need(self):
+        D = self.ctx.hidden_size
+        return CacheNeed(state=StateNeed((("sum", (D,)), ("count", (1,)))))
+
+    def forward(self, step, h, cache):
+        out = step.ws.buffer("toy.out", tuple(h.shape), h.dtype)
+        at = 0
+        for slot, n in zip(step.host["slots"], step.host["lens"]):  # tokens of a sequence in order
+            rows = h[at:at + n].float()
+            sums = cache.state["sum"][slot] + torch.cumsum(rows, dim=0)
+            counts = cache.state["count"][slot] + torch.arange(1, n + 1, device=h.device, dtype=torch.float32)[:, None]
+            mean = (sums / counts).to(self.weight.dtype)
+            out[at:at + n] = (mean @ self.weight.t()).to(h.dtype)
+            cache.state["sum"][slot] = sums[-1]
+            cache.state["count"][slot] = counts[-1]
+            at += n
+        return out
+
+
+@dataclass
+class ToyConfig(ModelConfig):
+    vocab_size: int = 0
+    hidden_size: int = 0
+    torch_dtype: str = "float32"
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(vocab_size=take_int(raw, "vocab_size"), hidden_size=take_int(raw, "hidden_size"),
+                   torch_dtype=raw.get("torch_dtype", "float32"))
+
+    def validate(self):
+        pass
+
+    def to_dict(self):
+        return {"architectures": ["ToyStateLM"], "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
+                "torch_dtype": self.torch_dtype}
+
+
+HQ, HK, HD, INTER = 4, 2, 16, 72
+
+
+def toy_builder(cfg):
+    D = cfg.hidden_size
+
+    def norm(name):
+        return PartSpec("rms_norm", {"width": D, "eps": 1e-5, "name": name})
+
+    def ffn(i):
+        return PartSpec("swiglu", {"intermediate": INTER, "names": {p: f"l{i}.{p}" for p in ("gate", "up", "down")}})
+
+    def attention(i, reads_only=False):
+        return PartSpec("attention", {
+            "n_heads": HQ, "n_kv_heads": HK, "head_dim": HD, "window": 0, "reads_cache_only": reads_only,
+            "position": PartSpec("rotary", {"head_dim": HD, "theta": 100.0, "scaling": None, "interleaved": False}),
+            "names": {p: f"l{i}.{p}" for p in "qkvo"}})
+
+    def layer(i, mixer):
+        return LayerSpec(PartSpec("pre_norm"), mixer, ffn(i), {"input": norm(f"l{i}.n1"), "post_mixer": norm(f"l{i}.n2")})
+
+    layers = [layer(0, attention(0)), layer(1, PartSpec("running_mean", {"name": "l1.mix"})),
+              layer(2, attention(2, reads_only=True))]
+    # layer 0, the state mixer, layer 0 again (a cache of its own), then a layer that reads entry 0's cache,
+    # then the state mixer again (a state of its own)
+    schedule = [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(2, cache_of=0), ScheduleEntry(1)]
+    return ModelSpec(hidden_size=D, vocab_size=cfg.vocab_size, max_positions=256,
+                     embedding=PartSpec("token_embedding", {"vocab": cfg.vocab_size, "name": "emb"}),
+                     layers=layers, schedule=schedule, final_norm=norm("final"),
+                     lm_head=PartSpec("linear_head", {"vocab": cfg.vocab_size, "name": "head", "tied_to": None}))
+
+
+def toy_plain(weights, tokens, D):
+    """Whole-sequence forward of the toy model in NumPy, float64."""
+    T = len(tokens)
+    pos = np.arange(T)
+    inv = pl.rope_inverse_frequencies(HD, 100.0)
+    x = pl.embedding(weights["emb"], tokens)
+    kv = {}
+
+    def attention(i, h, entry, source=None):
+        q = pl.apply_rope(pl.linear(h, weights[f"l{i}.q.weight"]).reshape(T, HQ, HD), pos, inv, False)
+        if source is None:
+            k = pl.apply_rope(pl.linear(h, weights[f"l{i}.k.weight"]).reshape(T, HK, HD), pos, inv, False)
+            v = pl.linear(h, weights[f"l{i}.v.weight"]).reshape(T, HK, HD)
+            kv[entry] = (k, v)
+        else:
+            k, v = kv[source]
+        return pl.linear(pl.causal_attention(q, k, v).reshape(T, HQ * HD), weights[f"l{i}.o.weight"])
+
+    def running_mean(h):
+        mean = np.cumsum(h, axis=0) / np.arange(1, T + 1)[:, None]
+        return pl.linear(mean, weights["l1.mix"])
+
+    for entry, (i, source) in enumerate([(0, None), (1, None), (0, None), (2, 0), (1, None)]):
+        h = pl.rms_norm(x, weights[f"l{i}.n1"], 1e-5)
+        x = x + (running_mean(h) if i == 1 else attention(i, h, entry, source))
+        h = pl.rms_norm(x, weights[f"l{i}.n2"], 1e-5)
+        x = x + pl.feed_forward(h, weights[f"l{i}.gate.weight"], weights[f"l{i}.up.weight"], weights[f"l{i}.down.weight"])
+    return pl.linear(pl.rms_norm(x, weights["final"], 1e-5), weights["head"])
+
+
+def test_toy_architecture_with_a_state_mixer(tmp_path):
+    register_part("mixer", "running_mean", RunningMeanMixer)
+    ml.register_architecture("ToyStateLM", ToyConfig, toy_builder)
+    cfg = ml.config_from_dict({"architectures": ["ToyStateLM"], "vocab_size": 97, "hidden_size": 40})
+    folder = ml.write_random_model(cfg, tmp_path, seed=5)
+    _, weights = pl.read_model_folder(folder)
+    llm = ml.load(folder, dtype="float32", max_tokens=64 * 12, max_seqs=3)
+    assert len(llm.engine.cache.groups) == 1 and llm.engine.cache.groups[0].entries == [0, 2]
+    assert sorted(llm.engine.cache.state) == [1, 4]
+    rng = np.random.RandomState(0)
+    requests = [[int(t) for t in rng.randint(0, 97, size=n)] for n in (70, 3, 20, 9)]
+    refs = [toy_plain(weights, r, 40) for r in requests]
+    # whole
+    for r, ref in zip(requests, refs):
+        slot, = llm.engine.acquire(1)
+        got = llm.engine.step([StepEntry(slot, r, list(range(len(r))))])
+        llm.engine.release(slot)
+        assert_close(got.cpu().numpy(), ref, "float32", "toy whole")
+    # batches of unequal lengths, prompts then one token each, slots reused by the second batch
+    for group in ([0, 1, 2], [3, 1]):
+        slots = dict(zip(group, llm.engine.acquire(len(group))))
+        fed = {g: max(1, len(requests[g]) // 2) for g in group}
+        out = llm.engine.step([StepEntry(slots[g], requests[g][:fed[g]], [fed[g] - 1]) for g in group])
+        for j, g in enumerate(group):
+            assert_close(out[j].cpu().numpy(), refs[g][fed[g] - 1], "float32", "toy prompt")
+        live = list(group)
+        while live:
+            live = [g for g in live if fed[g] < len(requests[g])]
+            if not live:
+                break
+            out = llm.engine.step([StepEntry(slots[g], [requests[g][fed[g]]], [0]) for g in live])
+            for j, g in enumerate(live):
+                assert_close(out[j].cpu().numpy(), refs[g][fed[g]], "float32", f"toy decode request {g}")
+                fed[g] += 1
+        for g in group:
+            llm.engine.release(slots[g])
+    llm.engine.cache.check()
+    # greedy generation runs through the same loop
+    assert len(llm.generate([requests[1]], max_new_tokens=5)[0]) == 5
