@@ -45,15 +45,17 @@ def require_cuda(device) -> torch.device:
 
 
 class EngineBackend(Backend):
-    """Connects the generation loop to an engine and a device sampler."""
+    """Connects the generation loop to an engine and a device sampler.  Steps in which
+    every sequence brings one token run through captured CUDA graphs."""
 
-    def __init__(self, engine: Engine, params: SamplingParams):
+    def __init__(self, engine: Engine, params: SamplingParams, use_graphs: bool = True):
         self.engine = engine
         self.params = params
-        self.sampler = DeviceSampler(engine.device)
         self.n_slots = engine.cache.n_slots
         self.n_pages = engine.cache.n_pages
         self.max_positions = engine.model.max_positions
+        self.sampler = engine.shared_sampler()
+        self.graphs = engine.shared_decode_graphs() if use_graphs else None
         self.steps = 0
 
     def acquire(self, count):
@@ -63,8 +65,11 @@ class EngineBackend(Backend):
         self.engine.release(slot)
 
     def step_and_sample(self, entries, requests, steps):
-        logits = self.engine.step_borrowed(entries)
         self.steps += 1
+        if self.graphs is not None and all(len(e.tokens) == 1 for e in entries):
+            return self.graphs.step([e.slot for e in entries], [e.tokens[0] for e in entries], self.params,
+                                    requests, steps)
+        logits = self.engine.step_borrowed(entries)
         return self.sampler.sample(logits, self.params, requests, steps)
 
 

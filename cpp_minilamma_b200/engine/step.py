@@ -125,6 +125,19 @@ class Engine:
         self.small_linear: Optional[Callable] = None
         self.launch_count = 0  # kernels of this package launched (estimate kept by the parts' callers)
 
+    # ---- helpers shared by everything that generates with this engine -------------------- #
+    def shared_sampler(self):
+        if getattr(self, "_sampler", None) is None:
+            from ..sampling.sampler import DeviceSampler
+            self._sampler = DeviceSampler(self.device, max(self.cache.n_slots, 64))
+        return self._sampler
+
+    def shared_decode_graphs(self):
+        if getattr(self, "_graphs", None) is None:
+            from .decode_graph import DecodeGraphs
+            self._graphs = DecodeGraphs(self, self.shared_sampler())
+        return self._graphs
+
     # ---- slots ---------------------------------------------------------------- #
     def acquire(self, count: int = 1) -> List[int]:
         return self.cache.acquire(count)

@@ -53,23 +53,36 @@ class DeviceSampler:
         self.counters = torch.zeros(2 * rows, dtype=torch.int32, device=self.device)  # request | step
         self.host = torch.zeros(2 * rows, dtype=torch.int32, pin_memory=True)
 
-    def sample(self, logits: torch.Tensor, params: SamplingParams, requests: Sequence[int],
-               steps: Sequence[int]) -> List[int]:
-        """logits float32 [n, vocab] -> n token ids on the host (this call synchronises)."""
+    def launch(self, logits: torch.Tensor, params: SamplingParams, request: torch.Tensor, step: torch.Tensor) -> None:
+        """Enqueue the sampling kernel for logits float32 [n, vocab]; `request` and `step`
+        are int32 device tensors with the random-number counters of each row."""
         from ..csrc import kernels as K
         n = logits.shape[0]
         if n > self.rows:
-            self._alloc(max(n, 2 * self.rows))
+            raise ValueError(f"sampler sized for {self.rows} rows, got {n}")
         tokens, status = self.out[:n], self.out[self.rows:self.rows + n]
         if params.is_greedy:
             K.argmax(logits, tokens, status)
         else:
-            self.counters[:n].copy_(torch.tensor(list(requests), dtype=torch.int32))
-            self.counters[self.rows:self.rows + n].copy_(torch.tensor(list(steps), dtype=torch.int32))
-            K.sample(logits, params.temperature, min(params.top_k, logits.shape[1]), params.seed,
-                     self.counters[:n], self.counters[self.rows:self.rows + n], tokens, status)
+            K.sample(logits, params.temperature, min(params.top_k, logits.shape[1]), params.seed, request, step,
+                     tokens, status)
+
+    def fetch(self, n: int) -> List[int]:
+        """Bring the n sampled token ids to the host (synchronises the stream)."""
         self.host.copy_(self.out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         if int(self.host[self.rows:self.rows + n].max()) != 0:
             raise FloatingPointError("logits are not finite")  # src/sampler.cc:10-19
         return self.host[:n].tolist()
+
+    def sample(self, logits: torch.Tensor, params: SamplingParams, requests: Sequence[int],
+               steps: Sequence[int]) -> List[int]:
+        """logits float32 [n, vocab] -> n token ids on the host (this call synchronises)."""
+        n = logits.shape[0]
+        if n > self.rows:
+            self._alloc(max(n, 2 * self.rows))
+        if not params.is_greedy:
+            self.counters[:n].copy_(torch.tensor(list(requests), dtype=torch.int32))
+            self.counters[self.rows:self.rows + n].copy_(torch.tensor(list(steps), dtype=torch.int32))
+        self.launch(logits, params, self.counters[:n], self.counters[self.rows:self.rows + n])
+        return self.fetch(n)

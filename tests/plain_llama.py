@@ -217,9 +217,13 @@ def attention_block(h, positions, weights, prefix, cfg, inv_freq, act_round=_ide
     d = cfg.get("head_dim") or cfg["hidden_size"] // Hq
     T = h.shape[0]
     name = prefix + "self_attn."
-    q = act_round(linear(h, weights[name + "q_proj.weight"], weights.get(name + "q_proj.bias")))
-    k = act_round(linear(h, weights[name + "k_proj.weight"], weights.get(name + "k_proj.bias")))
-    v = act_round(linear(h, weights[name + "v_proj.weight"], weights.get(name + "v_proj.bias")))
+    def project(which):
+        # a bfloat16 engine stores the product, then adds the bias in float32
+        y = act_round(linear(h, weights[name + which + "_proj.weight"]))
+        bias = weights.get(name + which + "_proj.bias")
+        return y if bias is None else y + bias.astype(np.float64)
+
+    q, k, v = project("q"), project("k"), act_round(project("v"))
     q = q.reshape(T, Hq, d)
     k = k.reshape(T, Hk, d)
     v = v.reshape(T, Hk, d)
@@ -227,8 +231,9 @@ def attention_block(h, positions, weights, prefix, cfg, inv_freq, act_round=_ide
     q = act_round(apply_rope(q, positions, inv_freq, interleaved))
     k = act_round(apply_rope(k, positions, inv_freq, interleaved))
     a = act_round(causal_attention(q, k, v, cfg.get("sliding_window")))
-    return act_round(linear(a.reshape(T, Hq * d), weights[name + "o_proj.weight"],
-                            weights.get(name + "o_proj.bias")))
+    out = act_round(linear(a.reshape(T, Hq * d), weights[name + "o_proj.weight"]))
+    bias = weights.get(name + "o_proj.bias")
+    return out if bias is None else act_round(out + bias.astype(np.float64))
 
 
 def forward_sequence(cfg, weights, tokens, act_round=_identity, return_hidden=False):

@@ -207,3 +207,22 @@ def test_cli_generate_matches_the_api(model_folders, capsys):
     stops = llm.generate(prompts, max_new_tokens=5, stop_ids=[expect[0][2]])
     assert stops[0] == expect[0][:2]
     assert main(["generate", folder, "-p", "1 2 3", "-n", "400", "--dtype", "float32"]) == 2   # over the context
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16"), ("C", "bfloat16")])
+def test_graph_replay_equals_eager_steps(model_folders, name, dtype):
+    # the same generation with captured decode graphs and with eager launches; budgets differ so
+    # the batch shrinks and other graph sizes come into play; a second round reuses the graphs
+    from cpp_minilamma_b200 import EngineBackend, SamplingParams
+    from cpp_minilamma_b200.engine.generate import generate
+    folder, llm = load(model_folders, name, dtype)
+    prompts = [tc.random_tokens(name, n, 950 + n) for n in (5, 30, 2, 9)]
+    budgets = [20, 7, 12, 20]
+    for params in (SamplingParams(), SamplingParams(temperature=0.9, top_k=20, seed=3)):
+        eager = generate(EngineBackend(llm.engine, params, use_graphs=False), prompts, budgets)
+        for _ in range(2):
+            backend = EngineBackend(llm.engine, params, use_graphs=True)
+            replayed = generate(backend, prompts, budgets)
+            assert [c.tokens for c in replayed] == [c.tokens for c in eager]
+        assert backend.graphs.replays > 0
+    llm.engine.cache.check()
