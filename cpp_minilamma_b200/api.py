@@ -55,7 +55,7 @@ class EngineBackend(Backend):
         self.n_pages = engine.cache.n_pages
         self.max_positions = engine.model.max_positions
         self.sampler = engine.shared_sampler()
-        self.graphs = engine.shared_decode_graphs() if use_graphs else None
+        self.graphs = engine.shared_decode_graphs() if use_graphs and engine.model.capturable() else None
         self.steps = 0
 
     def acquire(self, count):

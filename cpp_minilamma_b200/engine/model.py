@@ -98,6 +98,10 @@ class Model:
             total += sum(p.parameter_bytes() for p in self.layers[entry.layer].parts())
         return total
 
+    def capturable(self) -> bool:
+        """Whether a decode step of this model can be captured in a CUDA graph."""
+        return all(part.capturable for part in self.all_parts()) and all(l.block.capturable for l in self.layers)
+
     # ---- cache needs ---------------------------------------------------------- #
     def cache_needs(self) -> List[Tuple[int, Optional[int], CacheNeed]]:
         return [(i, entry.cache_of, self.layers[entry.layer].mixer.cache_need())

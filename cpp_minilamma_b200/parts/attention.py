@@ -33,6 +33,8 @@ class Attention(Mixer):
                                         it has no k/v projection and writes nothing
     """
 
+    capturable = True
+
     def __init__(self, params, ctx: BuildContext):
         super().__init__(params, ctx)
         self.n_heads = int(params["n_heads"])

@@ -143,6 +143,10 @@ class WeightStore:
 
 class Part:
     role = "part"
+    # True when `forward` only enqueues work whose arguments live in device memory at fixed
+    # addresses, so that a decode step can be captured in a CUDA graph and replayed.  A part
+    # that reads host-side step information (step.host) or allocates must leave it False.
+    capturable = False
 
     def __init__(self, params: Dict[str, Any], ctx: BuildContext):
         self.params = params

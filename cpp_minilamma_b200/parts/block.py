@@ -13,6 +13,8 @@ from .base import Block, register_part
 
 
 class PreNormBlock(Block):
+    capturable = True
+
     def norm_names(self) -> List[str]:
         return ["input", "post_mixer"]
 

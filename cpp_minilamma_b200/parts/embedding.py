@@ -19,6 +19,8 @@ from .linear import Linear
 class TokenEmbedding(Part):
     """params: vocab, name."""
 
+    capturable = True
+
     role = "embedding"
 
     def __init__(self, params, ctx: BuildContext):
@@ -41,6 +43,8 @@ class TokenEmbedding(Part):
 
 class LMHead(Part):
     """params: vocab, name, tied_to (name of the embedding tensor, or None)."""
+
+    capturable = True
 
     role = "lm_head"
 

@@ -35,6 +35,8 @@ def fuse_gate_up(gate: torch.Tensor, up: torch.Tensor):
 class SwiGLUFeedForward(FeedForward):
     """params: intermediate, names {"gate","up","down"} (tensor name stems)."""
 
+    capturable = True
+
     def __init__(self, params, ctx: BuildContext):
         super().__init__(params, ctx)
         self.inter = int(params["intermediate"])

@@ -17,6 +17,8 @@ from .base import BuildContext, Norm, WeightSpec, register_part
 class RMSNorm(Norm):
     """params: width, eps, name (tensor name of the weight)."""
 
+    capturable = True
+
     def __init__(self, params, ctx: BuildContext):
         super().__init__(params, ctx)
         self.width = int(params["width"])
