@@ -14,7 +14,7 @@ import torch
 from .build import KernelBuildError, load_library
 
 PAGE = 64  # cache positions per page; equals MLL_PAGE in common.cuh
-ABI_VERSION = 3
+ABI_VERSION = 4
 MAX_TOP_K = 1024
 
 
@@ -106,6 +106,38 @@ def add_bias(x: torch.Tensor, bias: torch.Tensor) -> None:
         raise KernelError("add_bias: bias length differs from the row width")
     _check(lib().mll_add_bias(_ptr(x), _ptr(bias), dtype_code(x.dtype), ctypes.c_int(x.shape[0]),
                               ctypes.c_int(x.shape[1]), _stream()), "add_bias")
+
+
+EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
+
+
+def linear_small_supported(rows: int, out_features: int, in_features: int, epilogue: int = EPI_BF16) -> bool:
+    return bool(lib().mll_linear_small_supported(rows, out_features, in_features, epilogue))
+
+
+def linear_small(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                 epilogue: int = EPI_BF16, ranks: int = 0) -> None:
+    """out = x . w^T for at most 64 rows of bfloat16 x [M, K] and bfloat16 w [N, K], read once.
+
+    epilogue EPI_BF16 / EPI_F32: out [M, N] in that dtype (+ float32 bias [N]);
+    EPI_SWIGLU: w holds gate and up rows interleaved in blocks of 8, out [M, N / 2] = silu(gate) * up."""
+    _need(x, "linear_small x", torch.bfloat16, 2)
+    _need(w, "linear_small w", torch.bfloat16, 2)
+    rows, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise KernelError(f"linear_small: x width {k} differs from w width {w.shape[1]}")
+    want = (rows, n // 2) if epilogue == EPI_SWIGLU else (rows, n)
+    _need(out, "linear_small out", torch.float32 if epilogue == EPI_F32 else torch.bfloat16, 2)
+    if tuple(out.shape) != want:
+        raise KernelError(f"linear_small: out {tuple(out.shape)}, expected {want}")
+    if bias is not None:
+        _need(bias, "linear_small bias", torch.float32, 1)
+        if bias.shape[0] != n:
+            raise KernelError("linear_small: bias length differs from the output width")
+    _check(lib().mll_linear_small(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), ctypes.c_int(rows), ctypes.c_int(n),
+                                  ctypes.c_int(k), ctypes.c_int(epilogue), ctypes.c_int(ranks), _stream()),
+           "linear_small")
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int) -> None:

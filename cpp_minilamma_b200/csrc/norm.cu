@@ -40,9 +40,104 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const DeltaT* __restri
     o[i] = from_float<OutT>(row_buf[i] * scale * weight[i]);
 }
 
+// Rows whose width is a multiple of 4 and at most 4 * NV * blockDim: every thread keeps
+// its share of the row in registers and issues all its loads before the first use, so the
+// kernel costs one memory latency instead of one per loop trip (decode has very few rows).
+template <typename T>
+__device__ __forceinline__ float4 load4(const T* p);
+template <>
+__device__ __forceinline__ float4 load4<float>(const float* p) {
+  return *reinterpret_cast<const float4*>(p);
+}
+template <>
+__device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<unsigned*>(&lo);
+  raw.y = *reinterpret_cast<unsigned*>(&hi);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename DeltaT, typename OutT, int NV>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_vec_kernel(float* __restrict__ x, const DeltaT* __restrict__ delta,
+                       const float* __restrict__ weight, OutT* __restrict__ out,
+                       const int* __restrict__ rows, int width, float eps) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* xr = x + (size_t)src * width;
+  const DeltaT* dr = delta ? delta + (size_t)src * width : nullptr;
+  const int groups = width >> 2;
+  float4 v[NV], w[NV];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int g = threadIdx.x + k * 256;
+    if (g < groups) {
+      v[k] = load4<float>(xr + 4 * g);
+      w[k] = load4<float>(weight + 4 * g);
+    }
+  }
+  if (dr) {
+    float4 dl[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int g = threadIdx.x + k * 256;
+      if (g < groups) dl[k] = load4<DeltaT>(dr + 4 * g);
+    }
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int g = threadIdx.x + k * 256;
+      if (g < groups) {
+        v[k].x += dl[k].x; v[k].y += dl[k].y; v[k].z += dl[k].z; v[k].w += dl[k].w;
+        if (!rows) store4(xr + 4 * g, v[k]);
+      }
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int g = threadIdx.x + k * 256;
+    if (g < groups) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.f / sqrtf(ss / (float)width + eps);
+  OutT* o = out + (size_t)r * width;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int g = threadIdx.x + k * 256;
+    if (g < groups)
+      store4(o + 4 * g, make_float4(v[k].x * scale * w[k].x, v[k].y * scale * w[k].y, v[k].z * scale * w[k].z,
+                                    v[k].w * scale * w[k].w));
+  }
+}
+
 template <typename DeltaT, typename OutT>
 int launch_add_rmsnorm(float* x, const void* delta, const float* weight, void* out, const int* rows,
                        int n_rows, int width, float eps, cudaStream_t stream) {
+  const bool aligned = width % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)weight % 16 == 0) &&
+                       ((uintptr_t)out % 8 == 0) && (!delta || (uintptr_t)delta % 8 == 0);
+  if (aligned && width <= 4 * 256 * 8) {
+    const int groups = width / 4;
+    if (groups <= 256 * 2)
+      add_rmsnorm_vec_kernel<DeltaT, OutT, 2><<<n_rows, 256, 0, stream>>>(x, (const DeltaT*)delta, weight,
+                                                                          (OutT*)out, rows, width, eps);
+    else if (groups <= 256 * 4)
+      add_rmsnorm_vec_kernel<DeltaT, OutT, 4><<<n_rows, 256, 0, stream>>>(x, (const DeltaT*)delta, weight,
+                                                                          (OutT*)out, rows, width, eps);
+    else
+      add_rmsnorm_vec_kernel<DeltaT, OutT, 8><<<n_rows, 256, 0, stream>>>(x, (const DeltaT*)delta, weight,
+                                                                          (OutT*)out, rows, width, eps);
+    MLL_LAUNCH_CHECK();
+    return 0;
+  }
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
   const size_t smem = (size_t)width * sizeof(float);
   auto kernel = add_rmsnorm_kernel<DeltaT, OutT>;

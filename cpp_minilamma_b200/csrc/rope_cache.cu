@@ -27,59 +27,50 @@ struct RopeArgs {
   int ld, n_heads, n_kv_heads, head_dim, max_blocks, interleaved, write_kv;
 };
 
+// grid (tokens, Hq + 2 Hk): one block per head of one token, one thread per pair, so that
+// no thread waits for more than one round of loads.
 template <typename T>
 __global__ void rope_cache_kernel(RopeArgs a) {
   const int t = blockIdx.x;
+  const int hb = blockIdx.y;  // q heads, then k heads, then v heads
   const int d = a.head_dim, half = d >> 1;
+  const bool is_q = hb < a.n_heads;
+  const bool is_k = !is_q && hb < a.n_heads + a.n_kv_heads;
+  if (!is_q && !a.write_kv) return;
   const int pos = a.tok_pos[t];
-  const T* row = (const T*)a.qkv + (size_t)t * a.ld;
-  // no table: positions are not encoded and q, k pass through unrotated
-  const float* cs = a.cos_table ? a.cos_table + (size_t)pos * half : nullptr;
-  const float* sn = a.cos_table ? a.sin_table + (size_t)pos * half : nullptr;
-
-  // where this token's k and v rows live
-  const int slot = a.seq_slot[a.tok_seq[t]];
-  const int page = a.block_table[(size_t)slot * a.max_blocks + pos / MLL_PAGE];
-  const int in_page = pos % MLL_PAGE;
-
-  const int q_pairs = a.n_heads * half;
-  const int k_pairs = a.write_kv ? a.n_kv_heads * half : 0;
-  const int v_pairs = k_pairs;
-  const int q_cols = a.n_heads * d, kv_cols = a.n_kv_heads * d;
-  T* q_out = (T*)a.q_out + (size_t)t * q_cols;
-
-  for (int w = threadIdx.x; w < q_pairs + k_pairs + v_pairs; w += blockDim.x) {
-    if (w < q_pairs + k_pairs) {
-      const bool is_q = w < q_pairs;
-      const int p = is_q ? w : w - q_pairs;
-      const int head = p / half, i = p % half;
-      const int e0 = a.interleaved ? 2 * i : i;
-      const int e1 = a.interleaved ? 2 * i + 1 : i + half;
-      const int col = (is_q ? 0 : q_cols) + head * d;
-      float x0 = to_float(row[col + e0]), x1 = to_float(row[col + e1]);
-      if (a.bias) {
-        x0 += a.bias[col + e0];
-        x1 += a.bias[col + e1];
-      }
-      const float c = cs ? cs[i] : 1.f, s = cs ? sn[i] : 0.f;
-      const float y0 = x0 * c - x1 * s, y1 = x0 * s + x1 * c;
-      T* dst = is_q ? q_out + head * d
-                    : (T*)a.k_cache + (((size_t)page * a.n_kv_heads + head) * MLL_PAGE + in_page) * d;
-      dst[e0] = from_float<T>(y0);
-      dst[e1] = from_float<T>(y1);
-    } else {
-      const int p = w - q_pairs - k_pairs;
-      const int head = p / half, i = p % half;
-      const int col = q_cols + kv_cols + head * d;
-      float x0 = to_float(row[col + 2 * i]), x1 = to_float(row[col + 2 * i + 1]);
-      if (a.bias) {
-        x0 += a.bias[col + 2 * i];
-        x1 += a.bias[col + 2 * i + 1];
-      }
-      T* dst = (T*)a.v_cache + (((size_t)page * a.n_kv_heads + head) * MLL_PAGE + in_page) * d;
-      dst[2 * i] = from_float<T>(x0);
-      dst[2 * i + 1] = from_float<T>(x1);
+  const T* row = (const T*)a.qkv + (size_t)t * a.ld + (size_t)hb * d;
+  const float* bias = a.bias ? a.bias + (size_t)hb * d : nullptr;
+  T* dst;
+  if (is_q) {
+    dst = (T*)a.q_out + (size_t)t * a.n_heads * d + (size_t)hb * d;
+  } else {
+    // where this token's k and v rows live
+    const int slot = a.seq_slot[a.tok_seq[t]];
+    const int page = a.block_table[(size_t)slot * a.max_blocks + pos / MLL_PAGE];
+    const int head = is_k ? hb - a.n_heads : hb - a.n_heads - a.n_kv_heads;
+    T* base = (T*)(is_k ? a.k_cache : a.v_cache);
+    dst = base + (((size_t)page * a.n_kv_heads + head) * MLL_PAGE + pos % MLL_PAGE) * d;
+  }
+  const bool rotate = (is_q || is_k) && a.cos_table != nullptr;  // no table: positions are not encoded
+  const float* cs = a.cos_table + (size_t)pos * half;
+  const float* sn = a.sin_table + (size_t)pos * half;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const bool split = (is_q || is_k) && !a.interleaved;
+    const int e0 = split ? i : 2 * i;
+    const int e1 = split ? i + half : 2 * i + 1;
+    float x0 = to_float(row[e0]), x1 = to_float(row[e1]);
+    if (bias) {
+      x0 += bias[e0];
+      x1 += bias[e1];
     }
+    float y0 = x0, y1 = x1;
+    if (rotate) {
+      const float c = cs[i], s = sn[i];
+      y0 = x0 * c - x1 * s;
+      y1 = x0 * s + x1 * c;
+    }
+    dst[e0] = from_float<T>(y0);
+    dst[e1] = from_float<T>(y1);
   }
 }
 
@@ -98,12 +89,14 @@ MLL_API int mll_rope_cache(const void* qkv, const float* bias, const float* cos_
   if (n_tokens == 0) return 0;
   mll::RopeArgs a{qkv, bias, cos_table, sin_table, tok_pos, tok_seq, seq_slot, block_table, q_out,
                   k_cache, v_cache, ld, n_heads, n_kv_heads, head_dim, max_blocks, interleaved, write_kv};
-  const int work = (n_heads + 2 * n_kv_heads) * head_dim / 2;
-  const int threads = work >= 2048 ? 256 : 128;
+  const int half = head_dim / 2;
+  const int threads = half >= 128 ? 128 : (half >= 64 ? 64 : 32);
+  MLL_REQUIRE(n_heads + 2 * n_kv_heads <= 65535, "rope: too many heads for one launch");
+  const dim3 grid(n_tokens, n_heads + (write_kv ? 2 * n_kv_heads : 0));
   if (dtype == MLL_F32)
-    mll::rope_cache_kernel<float><<<n_tokens, threads, 0, stream>>>(a);
+    mll::rope_cache_kernel<float><<<grid, threads, 0, stream>>>(a);
   else if (dtype == MLL_BF16)
-    mll::rope_cache_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(a);
+    mll::rope_cache_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(a);
   else
     MLL_REQUIRE(false, "rope: unknown dtype %d", dtype);
   MLL_LAUNCH_CHECK();

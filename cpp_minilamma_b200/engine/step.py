@@ -85,7 +85,7 @@ class StepState:
     all_decode: bool
     max_ctx: int
     decode_splits: int = 0                      # fixed split count (graph replay), 0 = choose per step
-    small_linear: Optional[Callable] = None     # this package's small-batch product, if enabled
+    small_rows: int = 0                         # steps with at most this many rows use the weight-streaming product
     host: Dict[str, list] = field(default_factory=dict)  # host copies for parts written in Python
 
 
@@ -122,7 +122,7 @@ class Engine:
         self._meta_host: Optional[torch.Tensor] = None
         self._meta_dev: Optional[torch.Tensor] = None
         self._meta_copied = None
-        self.small_linear: Optional[Callable] = None
+        self.small_rows = 16  # rows up to which linears use this package's weight-streaming kernel
         self.launch_count = 0  # kernels of this package launched (estimate kept by the parts' callers)
 
     # ---- helpers shared by everything that generates with this engine -------------------- #
@@ -297,7 +297,7 @@ class Engine:
                           tok_seq=tok_seq, seq_slot=seq_slot, seq_ctx=seq_ctx, seq_qstart=seq_qstart,
                           seq_qlen=seq_qlen, tile_seq=tile_seq, tile_row0=tile_row0, n_tiles=n_tiles,
                           want_rows=want, all_decode=all_decode, max_ctx=max(ctx), decode_splits=decode_splits,
-                          small_linear=self.small_linear,
+                          small_rows=self.small_rows,
                           host={"slots": [s.slot for s in seqs], "lens": lens, "starts": [s.start for s in seqs]})
         return state, out_rows
 

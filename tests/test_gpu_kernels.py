@@ -418,3 +418,49 @@ def test_kernels_refuse_bad_sizes():
         K.argmax(torch.zeros((1, 8)), i32([0]), i32([0]))
     with pytest.raises(K.KernelError, match="top_k"):
         K.sample(torch.zeros((1, 5000), device=DEV), 1.0, 2000, 1, i32([0]), i32([0]), i32([0]), i32([0]))
+
+
+# ------------------------------------------------------------------------------------ #
+@pytest.mark.parametrize("rows", [1, 3, 8, 9, 16, 33, 64])
+@pytest.mark.parametrize("n,k,ranks", [(16, 32, 1), (40, 64, 2), (4104, 4096, 0), (512, 14336, 8), (128, 4096, 4),
+                                        (100, 224, 1)])
+def test_linear_small(rows, n, k, ranks):
+    x = rnd((rows, k), torch.bfloat16, 30)
+    w = rnd((n, k), torch.bfloat16, 31, 0.05)
+    bias = rnd((n,), torch.float32, 32)
+    ref = as64(x) @ as64(w).T
+    assert K.linear_small_supported(rows, n, k)
+    for epilogue, dtype, b in ((K.EPI_BF16, torch.bfloat16, None), (K.EPI_F32, torch.float32, bias)):
+        out = torch.full((rows, n), float("nan"), dtype=dtype, device=DEV)
+        K.linear_small(x.to(DEV), w.to(DEV), None if b is None else b.to(DEV), out, epilogue, ranks)
+        want = ref if b is None else ref + as64(b)
+        if dtype == torch.float32:  # float32 accumulation of exact bfloat16 products
+            np.testing.assert_allclose(as64(out), want, rtol=2e-5, atol=2e-5 * np.abs(want).max())
+        else:
+            np.testing.assert_allclose(as64(out), want, rtol=8e-3, atol=8e-3 * np.abs(want).max())
+        again = torch.empty_like(out)
+        K.linear_small(x.to(DEV), w.to(DEV), None if b is None else b.to(DEV), again, epilogue, ranks)
+        assert torch.equal(out, again)  # fixed summation order
+
+
+@pytest.mark.parametrize("rows", [1, 8, 13, 64])
+@pytest.mark.parametrize("inter,k,ranks", [(176, 64, 1), (1000, 4096, 0), (64, 14336, 8)])
+def test_linear_small_swiglu(rows, inter, k, ranks):
+    gate = rnd((inter, k), torch.bfloat16, 33, 0.05)
+    up = rnd((inter, k), torch.bfloat16, 34, 0.05)
+    x = rnd((rows, k), torch.bfloat16, 35)
+    fused = torch.stack([gate.view(inter // 8, 8, k), up.view(inter // 8, 8, k)], dim=1).reshape(2 * inter, k)
+    out = torch.full((rows, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    K.linear_small(x.to(DEV), fused.contiguous().to(DEV), None, out, K.EPI_SWIGLU, ranks)
+    want = pl.swiglu(as64(x) @ as64(gate).T, as64(x) @ as64(up).T)
+    np.testing.assert_allclose(as64(out), want, rtol=8e-3, atol=8e-3 * np.abs(want).max())
+
+
+def test_linear_small_refuses():
+    assert not K.linear_small_supported(65, 4096, 4096)
+    assert not K.linear_small_supported(8, 4096, 100)
+    assert not K.linear_small_supported(8, 8, 64)
+    with pytest.raises(K.KernelError, match="unsupported sizes"):
+        K.linear_small(torch.zeros((2, 48), dtype=torch.bfloat16, device=DEV),
+                       torch.zeros((16, 48), dtype=torch.bfloat16, device=DEV), None,
+                       torch.zeros((2, 16), dtype=torch.bfloat16, device=DEV))
