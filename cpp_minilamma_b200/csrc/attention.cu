@@ -539,6 +539,26 @@ MLL_API int mll_attn_decode(const void* q, const void* k_cache, const void* v_ca
   return -1;
 }
 
+// Merges the partial results of a split decode (scratch layout as written by the decode kernels).
+MLL_API int mll_attn_combine(float* scratch, void* out, int dtype, int n_seqs, int n_heads, int head_dim,
+                             int n_splits, cudaStream_t stream) {
+  MLL_REQUIRE(n_seqs >= 0 && n_heads > 0 && head_dim > 0 && n_splits >= 1, "attention combine: bad sizes");
+  if (n_seqs == 0) return 0;
+  mll::AttnArgs a{};
+  a.part_o = scratch;
+  a.part_ml = scratch + (size_t)n_seqs * n_heads * n_splits * head_dim;
+  a.out = out;
+  a.n_heads = n_heads; a.head_dim = head_dim; a.n_splits = n_splits;
+  if (dtype == MLL_F32)
+    mll::attn_combine_kernel<float><<<n_seqs * n_heads, 128, 0, stream>>>(a);
+  else if (dtype == MLL_BF16)
+    mll::attn_combine_kernel<__nv_bfloat16><<<n_seqs * n_heads, 128, 0, stream>>>(a);
+  else
+    MLL_REQUIRE(false, "attention combine: unknown dtype %d", dtype);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
 MLL_API int mll_attn_prefill(const void* q, const void* k_cache, const void* v_cache, const int* seq_slot,
                              const int* seq_ctx, const int* seq_qstart, const int* seq_qlen,
                              const int* tile_seq, const int* tile_row0, const int* block_table, void* out,

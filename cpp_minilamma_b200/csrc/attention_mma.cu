@@ -1,0 +1,321 @@
+// Decode attention on tensor cores (bfloat16, head_dim 64 / 128 / 256).
+//
+// One block of four warps per (sequence, kv head [, chunk of 16 query heads], split of the
+// context).  The block walks its pages together: key and value pages arrive in shared
+// memory through a cp.async pipeline; every warp scores the query heads against its 16 of
+// the page's 64 keys (mma.sync m16n8k16, heads padded to the 16 rows of the tile), the warps
+// exchange row maxima and sums through shared memory (online softmax in float32), the
+// probabilities go to shared memory as bfloat16, and every warp multiplies them with its
+// quarter of the value columns.  The arithmetic is that of the general kernel in
+// attention.cu (the reference's src/forward.cc:265-298); only the order of the sums differs.
+// The output format (direct, or partial results + (max, sum) per split for the combine
+// kernel) is the same as the general kernel's, which remains the path for other head sizes
+// and for float32.
+#include "common.cuh"
+
+namespace mll {
+
+struct DecodeMmaArgs {
+  const __nv_bfloat16* q;        // [B, Hq * d]
+  const __nv_bfloat16* k_cache;  // [n_pages, Hk, PAGE, d]
+  const __nv_bfloat16* v_cache;
+  const int* seq_slot;
+  const int* seq_ctx;
+  const int* block_table;
+  float* part_o;                 // [B, Hq, S, d]
+  float* part_ml;                // [B, Hq, S, 2]
+  __nv_bfloat16* out;            // [B, Hq * d]
+  int n_heads, n_kv_heads, max_blocks, n_splits, window;
+  float scale;
+};
+
+__device__ __forceinline__ void cp_async16_zfill(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;  // fewer source bytes than 16: the rest is written as zero
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int D, int STAGES>
+struct DecodeMmaSmem {
+  static constexpr int STRIDE = D + 8;                       // bf16 elements per key row (16 bytes of padding)
+  static constexpr int TILE = MLL_PAGE * STRIDE;             // elements of one K or V page
+  static constexpr int P_STRIDE = MLL_PAGE + 8;
+  static constexpr size_t BYTES = (size_t)STAGES * 2 * TILE * 2 + 16 * P_STRIDE * 2 + 2 * 4 * 16 * sizeof(float);
+};
+
+// grid (B, Hk * head_chunks, n_splits); 128 threads.
+template <int D, int STAGES>
+__global__ void __launch_bounds__(128)
+attn_decode_mma_kernel(DecodeMmaArgs a) {
+  using L = DecodeMmaSmem<D, STAGES>;
+  constexpr int KSTEPS = D / 16;       // k-steps of the score product
+  constexpr int NT_OUT = D / 32;       // value n-tiles (8 columns) per warp
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* kv_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);         // [STAGES][2][PAGE][STRIDE]
+  __nv_bfloat16* p_s = kv_s + (size_t)STAGES * 2 * L::TILE;                 // [16][P_STRIDE]
+  float* wmax = reinterpret_cast<float*>(p_s + 16 * L::P_STRIDE);           // [4][16]
+  float* wsum = wmax + 4 * 16;                                              // [4][16]
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int group = a.n_heads / a.n_kv_heads;
+  const int chunks = (group + 15) / 16;
+  const int b = blockIdx.x;
+  const int kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks;
+  const int split = blockIdx.z;
+  const int ng = min(16, group - chunk * 16);
+  const int h0 = kvh * group + chunk * 16;
+
+  const int ctx = a.seq_ctx[b];
+  const int first_key = a.window > 0 ? max(0, ctx - a.window) : 0;
+  const int pages_total = (ctx + MLL_PAGE - 1) / MLL_PAGE;
+  const int first_page = first_key / MLL_PAGE;
+  const int per_split = (pages_total - first_page + a.n_splits - 1) / a.n_splits;
+  const int p_begin = first_page + split * per_split;
+  const int p_end = min(pages_total, p_begin + per_split);
+  const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_blocks;
+
+  // query fragments (A operand), rows = heads of this chunk, zero beyond ng
+  unsigned qf[KSTEPS][4];
+  {
+    const __nv_bfloat16* q0 = a.q + ((size_t)b * a.n_heads + h0) * D;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      const int col = ks * 16 + 2 * t;
+      qf[ks][0] = g < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + col) : 0u;
+      qf[ks][1] = g + 8 < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + col) : 0u;
+      qf[ks][2] = g < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + col + 8) : 0u;
+      qf[ks][3] = g + 8 < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + col + 8) : 0u;
+    }
+  }
+
+  constexpr int CPR = D / 8;  // 16-byte chunks per key row
+  auto load_page = [&](int page_index, int stage) {
+    const int page = table[page_index];
+    const size_t base = ((size_t)page * a.n_kv_heads + kvh) * MLL_PAGE * D;
+    __nv_bfloat16* kd = kv_s + (size_t)stage * 2 * L::TILE;
+    __nv_bfloat16* vd = kd + L::TILE;
+    const int valid_rows = ctx - page_index * MLL_PAGE;  // rows past the sequence hold no data
+    for (int c = tid; c < MLL_PAGE * CPR; c += 128) {
+      const int r = c / CPR, cc = c % CPR;
+      cp_async16(kd + r * L::STRIDE + cc * 8, a.k_cache + base + (size_t)r * D + cc * 8);
+      cp_async16_zfill(vd + r * L::STRIDE + cc * 8, a.v_cache + base + (size_t)r * D + cc * 8, r < valid_rows);
+    }
+  };
+
+  float o[NT_OUT][4];
+#pragma unroll
+  for (int n = 0; n < NT_OUT; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // rows g and g + 8
+
+  const int n_pages = max(0, p_end - p_begin);
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < n_pages) load_page(p_begin + s, s);
+    cp_async_commit();
+  }
+
+  for (int it = 0; it < n_pages; ++it) {
+    const int p = p_begin + it;
+    cp_async_wait<STAGES - 2>();  // page `it` has landed (one group per iteration, committed even when empty)
+    __syncthreads();              // ... for every thread's copies; and all warps are done with page it - 1
+    if (it + STAGES - 1 < n_pages) load_page(p + STAGES - 1, (it + STAGES - 1) % STAGES);
+    cp_async_commit();
+
+    const __nv_bfloat16* kt = kv_s + (size_t)(it % STAGES) * 2 * L::TILE;
+    const __nv_bfloat16* vt = kt + L::TILE;
+
+    // scores of the 16 heads against this warp's 16 keys: two n-tiles of 8 keys
+    float s_acc[2][4];
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s_acc[n][i] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      // matrices: (keys 0-7, dims 0-7), (keys 0-7, dims 8-15), (keys 8-15, dims 0-7), (keys 8-15, dims 8-15)
+      unsigned kb[4];
+      const int key = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
+      const int dim = ks * 16 + (((lane >> 3) & 1) << 3);
+      ldmatrix_x4(kb, kt + key * L::STRIDE + dim);
+      mma_16816(s_acc[0], qf[ks], kb[0], kb[1]);
+      mma_16816(s_acc[1], qf[ks], kb[2], kb[3]);
+    }
+    // scale, mask, row maxima over this warp's keys
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int kpos = p * MLL_PAGE + warp * 16 + n * 8 + 2 * t + (i & 1);
+        const bool ok = kpos < ctx && kpos >= first_key;
+        const float v = ok ? s_acc[n][i] * a.scale : -INFINITY;
+        s_acc[n][i] = v;
+        tile_max[i >> 1] = fmaxf(tile_max[i >> 1], v);
+      }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+      tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+    }
+    if (t == 0) {
+      wmax[warp * 16 + g] = tile_max[0];
+      wmax[warp * 16 + g + 8] = tile_max[1];
+    }
+    __syncthreads();
+    float alpha[2], row_sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = g + 8 * r;
+      const float m_tile = fmaxf(fmaxf(wmax[row], wmax[16 + row]), fmaxf(wmax[32 + row], wmax[48 + row]));
+      const float m_new = fmaxf(m_run[r], m_tile);
+      alpha[r] = m_new > -INFINITY ? __expf(m_run[r] - m_new) : 1.f;
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const float pv = m_new > -INFINITY ? __expf(s_acc[n][2 * r + i] - m_new) : 0.f;
+          s_acc[n][2 * r + i] = pv;
+          row_sum[r] += pv;
+        }
+      m_run[r] = m_new;
+    }
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+      const int col = warp * 16 + n * 8 + 2 * t;
+      *reinterpret_cast<__nv_bfloat162*>(p_s + g * L::P_STRIDE + col) = __floats2bfloat162_rn(s_acc[n][0], s_acc[n][1]);
+      *reinterpret_cast<__nv_bfloat162*>(p_s + (g + 8) * L::P_STRIDE + col) =
+          __floats2bfloat162_rn(s_acc[n][2], s_acc[n][3]);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
+      row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
+    }
+    if (t == 0) {
+      wsum[warp * 16 + g] = row_sum[0];
+      wsum[warp * 16 + g + 8] = row_sum[1];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = g + 8 * r;
+      l_run[r] = l_run[r] * alpha[r] + ((wsum[row] + wsum[16 + row]) + (wsum[32 + row] + wsum[48 + row]));
+    }
+    // out[:, this warp's columns] = alpha * out + P[16 x 64] . V[64 x columns]
+#pragma unroll
+    for (int n = 0; n < NT_OUT; ++n) {
+      o[n][0] *= alpha[0];
+      o[n][1] *= alpha[0];
+      o[n][2] *= alpha[1];
+      o[n][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int ks = 0; ks < MLL_PAGE / 16; ++ks) {
+      unsigned pa[4];
+      // matrices: (rows 0-7, keys 0-7), (rows 8-15, keys 0-7), (rows 0-7, keys 8-15), (rows 8-15, keys 8-15)
+      ldmatrix_x4(pa, p_s + ((lane & 7) + (((lane >> 3) & 1) << 3)) * L::P_STRIDE + ks * 16 + ((lane >> 4) << 3));
+#pragma unroll
+      for (int n = 0; n < NT_OUT; n += 2) {
+        // transposed 8x8 tiles of V: (keys 0-7, cols n), (keys 8-15, cols n), (keys 0-7, cols n+1), (keys 8-15, cols n+1)
+        unsigned vb[4];
+        const int key = ks * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+        const int col = warp * (D / 4) + (n + (lane >> 4)) * 8;
+        ldmatrix_x4_trans(vb, vt + key * L::STRIDE + col);
+        mma_16816(o[n], pa, vb[0], vb[1]);
+        if (n + 1 < NT_OUT) mma_16816(o[n + 1], pa, vb[2], vb[3]);
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+  // rows g and g + 8 of the tile are heads h0 + g and h0 + g + 8; this thread holds columns
+  // warp * D/4 + n * 8 + 2 t + {0, 1}
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = g + 8 * r;
+    if (row >= ng) continue;
+    const size_t head = (size_t)b * a.n_heads + h0 + row;
+    if (a.n_splits == 1) {
+      const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+#pragma unroll
+      for (int n = 0; n < NT_OUT; ++n) {
+        const int col = warp * (D / 4) + n * 8 + 2 * t;
+        *reinterpret_cast<__nv_bfloat162*>(a.out + head * D + col) =
+            __floats2bfloat162_rn(o[n][2 * r] * inv, o[n][2 * r + 1] * inv);
+      }
+    } else {
+      float* po = a.part_o + (head * a.n_splits + split) * D;
+#pragma unroll
+      for (int n = 0; n < NT_OUT; ++n) {
+        const int col = warp * (D / 4) + n * 8 + 2 * t;
+        *reinterpret_cast<float2*>(po + col) = make_float2(o[n][2 * r], o[n][2 * r + 1]);
+      }
+      if (warp == 0 && t == 0) {
+        float* ml = a.part_ml + (head * a.n_splits + split) * 2;
+        ml[0] = m_run[r];
+        ml[1] = l_run[r];
+      }
+    }
+  }
+}
+
+template <int D, int STAGES>
+int launch_decode_mma(const DecodeMmaArgs& a, int n_seqs, cudaStream_t stream) {
+  const size_t smem = DecodeMmaSmem<D, STAGES>::BYTES;
+  auto kernel = attn_decode_mma_kernel<D, STAGES>;
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (err != cudaSuccess) {
+    mll_set_error("attention decode (mma): cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
+    return (int)err;
+  }
+  const int group = a.n_heads / a.n_kv_heads;
+  dim3 grid(n_seqs, a.n_kv_heads * ((group + 15) / 16), a.n_splits);
+  kernel<<<grid, 128, smem, stream>>>(a);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace mll
+
+MLL_API int mll_attn_decode_mma_supported(int dtype, int head_dim) {
+  return dtype == MLL_BF16 && (head_dim == 64 || head_dim == 128 || head_dim == 256);
+}
+
+// Same contract as mll_attn_decode without the combine step: with n_splits > 1 the caller
+// merges the partial results (scratch layout: partial outputs, then (max, sum) pairs).
+MLL_API int mll_attn_decode_mma(const void* q, const void* k_cache, const void* v_cache, const int* seq_slot,
+                                const int* seq_ctx, const int* block_table, float* scratch, void* out, int n_seqs,
+                                int n_heads, int n_kv_heads, int head_dim, int max_blocks, int n_splits, int window,
+                                float scale, cudaStream_t stream) {
+  MLL_REQUIRE(mll_attn_decode_mma_supported(MLL_BF16, head_dim), "attention decode (mma): head_dim %d", head_dim);
+  MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention decode (mma): bad head counts");
+  MLL_REQUIRE(n_seqs >= 0 && n_splits >= 1 && n_splits <= 65535, "attention decode (mma): bad batch or split count");
+  MLL_REQUIRE(n_splits == 1 || scratch != nullptr, "attention decode (mma): %d splits need scratch memory", n_splits);
+  if (n_seqs == 0) return 0;
+  mll::DecodeMmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
+                       seq_slot, seq_ctx, block_table, scratch,
+                       scratch ? scratch + (size_t)n_seqs * n_heads * n_splits * head_dim : nullptr,
+                       (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, n_splits, window, scale};
+  if (head_dim == 64) return mll::launch_decode_mma<64, 3>(a, n_seqs, stream);
+  if (head_dim == 128) return mll::launch_decode_mma<128, 3>(a, n_seqs, stream);
+  return mll::launch_decode_mma<256, 2>(a, n_seqs, stream);
+}

@@ -14,7 +14,7 @@ import torch
 from .build import KernelBuildError, load_library
 
 PAGE = 64  # cache positions per page; equals MLL_PAGE in common.cuh
-ABI_VERSION = 4
+ABI_VERSION = 5
 MAX_TOP_K = 1024
 
 
@@ -237,10 +237,14 @@ def attention_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_
     return int(lib().mll_attn_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits))
 
 
+USE_TENSOR_CORE_DECODE = True  # tests switch this off to reach the general kernel at every size
+
+
 def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch, out, n_seqs: int,
                      n_heads: int, n_kv_heads: int, head_dim: int, n_splits: int, window: int,
                      scale: float) -> None:
-    """One query token per sequence (q row i belongs to sequence i) over the paged cache."""
+    """One query token per sequence (q row i belongs to sequence i) over the paged cache.
+    bfloat16 with head_dim 64/128/256 runs on tensor cores, everything else on the general kernel."""
     _check_attention(q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim)
     _need(seq_slot, "attention seq_slot", torch.int32, 1)
     _need(seq_ctx, "attention seq_ctx", torch.int32, 1)
@@ -251,8 +255,21 @@ def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratc
         _need(scratch, "attention scratch", torch.float32)
         if scratch.numel() < attention_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits):
             raise KernelError("attention decode: scratch too small for the split count")
+    code = dtype_code(q.dtype)
+    if USE_TENSOR_CORE_DECODE and lib().mll_attn_decode_mma_supported(code, head_dim):
+        _check(lib().mll_attn_decode_mma(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx),
+                                         _ptr(block_table), _ptr(scratch), _ptr(out), ctypes.c_int(n_seqs),
+                                         ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim),
+                                         ctypes.c_int(block_table.shape[1]), ctypes.c_int(n_splits),
+                                         ctypes.c_int(window), ctypes.c_float(scale), _stream()),
+               "attention_decode (tensor cores)")
+        if n_splits > 1:
+            _check(lib().mll_attn_combine(_ptr(scratch), _ptr(out), code, ctypes.c_int(n_seqs), ctypes.c_int(n_heads),
+                                          ctypes.c_int(head_dim), ctypes.c_int(n_splits), _stream()),
+                   "attention_combine")
+        return
     _check(lib().mll_attn_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx),
-                                 _ptr(block_table), _ptr(scratch), _ptr(out), dtype_code(q.dtype),
+                                 _ptr(block_table), _ptr(scratch), _ptr(out), code,
                                  ctypes.c_int(n_seqs), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
                                  ctypes.c_int(head_dim), ctypes.c_int(block_table.shape[1]),
                                  ctypes.c_int(n_splits), ctypes.c_int(window), ctypes.c_float(scale),

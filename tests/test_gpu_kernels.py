@@ -152,14 +152,24 @@ class PagedCase:
                 torch.tensor(self.ctx_lens, dtype=torch.int32, device=DEV), self.table.to(DEV))
 
 
+@pytest.fixture(params=["tensor_core", "general"])
+def decode_impl(request):
+    """bfloat16 decode attention has a tensor-core kernel for head sizes 64/128/256; the
+    general kernel must stay right at those sizes too."""
+    K.USE_TENSOR_CORE_DECODE = request.param == "tensor_core"
+    yield request.param
+    K.USE_TENSOR_CORE_DECODE = True
+
+
 DECODE_SHAPES = [  # heads, kv heads, head_dim
-    (4, 2, 16), (6, 1, 32), (3, 3, 48), (10, 2, 80), (32, 8, 128), (8, 1, 256), (16, 16, 64), (64, 2, 16)]
+    (4, 2, 16), (6, 1, 32), (3, 3, 48), (10, 2, 80), (32, 8, 128), (8, 1, 256), (16, 16, 64), (64, 2, 16),
+    (40, 2, 64), (5, 5, 128)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("hq,hk,d", DECODE_SHAPES)
 @pytest.mark.parametrize("splits", [1, 3, 8])
-def test_attention_decode(dtype, hq, hk, d, splits):
+def test_attention_decode(dtype, hq, hk, d, splits, decode_impl):
     ctx = [1, 63, 64, 65, 300, 129]
     case = PagedCase(ctx, hk, d, dtype, seed=hq * 7 + d)
     q = rnd((len(ctx), hq, d), dtype, 11)
@@ -175,7 +185,7 @@ def test_attention_decode(dtype, hq, hk, d, splits):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("far", [0, 63, 64, 447, 448, 511, 700])
-def test_attention_decode_far_key_stands_out(dtype, far):
+def test_attention_decode_far_key_stands_out(dtype, far, decode_impl):
     # one key among 701 gets a score far above the rest: the output must be its value
     hq, hk, d, c = 8, 2, 64, 701
     case = PagedCase([c, 5], hk, d, dtype, seed=far + 1)
@@ -202,9 +212,9 @@ def test_attention_decode_far_key_stands_out(dtype, far):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [1, 5, 64, 100])
-def test_attention_decode_window_edge(dtype, window):
+def test_attention_decode_window_edge(dtype, window, decode_impl):
     # the key just outside the window is made huge: it must not be seen; the one just inside is
-    hq, hk, d = 4, 2, 32
+    hq, hk, d = 4, 2, 64
     ctx = [300, 70, 3]
     case = PagedCase(ctx, hk, d, dtype, seed=window)
     q = rnd((3, hq, d), dtype, 13, 0.1)
