@@ -19,7 +19,7 @@ void mll_set_error(const char* fmt, ...) {
 MLL_API const char* mll_last_error() { return g_error; }
 
 // Identifies the build; the Python side checks it after loading the library.
-MLL_API int mll_abi_version() { return 5; }
+MLL_API int mll_abi_version() { return 6; }
 
 namespace mll {
 

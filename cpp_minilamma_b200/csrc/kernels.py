@@ -14,7 +14,7 @@ import torch
 from .build import KernelBuildError, load_library
 
 PAGE = 64  # cache positions per page; equals MLL_PAGE in common.cuh
-ABI_VERSION = 5
+ABI_VERSION = 6
 MAX_TOP_K = 1024
 
 
@@ -138,6 +138,59 @@ def linear_small(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
     _check(lib().mll_linear_small(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), ctypes.c_int(rows), ctypes.c_int(n),
                                   ctypes.c_int(k), ctypes.c_int(epilogue), ctypes.c_int(ranks), _stream()),
            "linear_small")
+
+
+def linear_tma_supported(rows: int, out_features: int, in_features: int, epilogue: int = EPI_BF16) -> bool:
+    return bool(lib().mll_linear_tma_supported(rows, out_features, in_features, epilogue))
+
+
+def linear_tma(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+               epilogue: int = EPI_BF16, ranks: int = 0) -> None:
+    """As `linear_small`, with the weights streamed through a TMA + mbarrier pipeline.  Takes
+    any N, any K that is a multiple of 8, at most 64 rows."""
+    _need(x, "linear_tma x", torch.bfloat16, 2)
+    _need(w, "linear_tma w", torch.bfloat16, 2)
+    rows, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise KernelError(f"linear_tma: x width {k} differs from w width {w.shape[1]}")
+    want = (rows, n // 2) if epilogue == EPI_SWIGLU else (rows, n)
+    _need(out, "linear_tma out", torch.float32 if epilogue == EPI_F32 else torch.bfloat16, 2)
+    if tuple(out.shape) != want:
+        raise KernelError(f"linear_tma: out {tuple(out.shape)}, expected {want}")
+    if bias is not None:
+        _need(bias, "linear_tma bias", torch.float32, 1)
+        if bias.shape[0] != n:
+            raise KernelError("linear_tma: bias length differs from the output width")
+    _check(lib().mll_linear_tma(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), ctypes.c_int(rows), ctypes.c_int(n),
+                                ctypes.c_int(k), ctypes.c_int(epilogue), ctypes.c_int(ranks), _stream()),
+           "linear_tma")
+
+
+def take_device_error() -> int:
+    """1 when a kernel's bounded wait ran out since the last call (then cleared); synchronises."""
+    return int(lib().mll_take_device_error())
+
+
+def small_linear_kind(rows: int, out_features: int, in_features: int, epilogue: int = EPI_BF16) -> str:
+    """Which of this library's weight-streaming kernels takes the problem: "tma", "direct" or ""."""
+    if SMALL_LINEAR in ("tma", "auto") and linear_tma_supported(rows, out_features, in_features, epilogue):
+        return "tma"
+    if SMALL_LINEAR in ("direct", "auto") and linear_small_supported(rows, out_features, in_features, epilogue):
+        return "direct"
+    return ""
+
+
+def small_linear(x, w, bias, out, epilogue: int = EPI_BF16) -> bool:
+    kind = small_linear_kind(x.shape[0], w.shape[0], w.shape[1], epilogue)
+    if kind == "tma":
+        linear_tma(x, w, bias, out, epilogue)
+    elif kind == "direct":
+        linear_small(x, w, bias, out, epilogue)
+    return bool(kind)
+
+
+SMALL_LINEAR = "auto"  # "tma", "direct", "auto" (tma where it applies), or "none"
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int) -> None:

@@ -51,10 +51,9 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
 }
 
 constexpr int LS_WARPS = 4;
-constexpr int LS_UNROLL = 4;  // 32-element chunks in flight per warp
 
 // grid: (row tiles * cluster size); block: 128 threads.  NT: n-tiles of 8 batch rows.
-template <int NT, bool CLUSTER>
+template <int NT, bool CLUSTER, int LS_UNROLL>  // LS_UNROLL: 32-element chunks in flight per warp
 __global__ void __launch_bounds__(LS_WARPS * 32)
 linear_small_kernel(LinearArgs a) {
   __shared__ float red[LS_WARPS][16][8 * NT];
@@ -180,7 +179,7 @@ linear_small_kernel(LinearArgs a) {
   }
 }
 
-template <int NT>
+template <int NT, int U>
 int launch_linear_small(const LinearArgs& a, int tiles, int ranks, cudaStream_t stream) {
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(tiles * ranks);
@@ -196,9 +195,9 @@ int launch_linear_small(const LinearArgs& a, int tiles, int ranks, cudaStream_t 
     attr[0].val.clusterDim.z = 1;
     config.attrs = attr;
     config.numAttrs = 1;
-    err = cudaLaunchKernelEx(&config, linear_small_kernel<NT, true>, a);
+    err = cudaLaunchKernelEx(&config, linear_small_kernel<NT, true, U>, a);
   } else {
-    err = cudaLaunchKernelEx(&config, linear_small_kernel<NT, false>, a);
+    err = cudaLaunchKernelEx(&config, linear_small_kernel<NT, false, U>, a);
   }
   if (err != cudaSuccess) {
     mll_set_error("linear_small: launch failed: %s", cudaGetErrorString(err));
@@ -208,6 +207,9 @@ int launch_linear_small(const LinearArgs& a, int tiles, int ranks, cudaStream_t 
 }
 
 }  // namespace mll
+
+// tuning knob for experiments: chunks in flight per warp for M <= 8 (2, 4 or 8)
+extern "C" __attribute__((visibility("default"))) int mll_linear_small_unroll = 4;
 
 // Whether mll_linear_small takes this problem (the caller uses the library GEMM otherwise).
 MLL_API int mll_linear_small_supported(int M, int N, int K, int epilogue) {
@@ -237,8 +239,12 @@ MLL_API int mll_linear_small(const void* x, const void* w, const float* bias, vo
   mll::LinearArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, out, M, N, K, epilogue, 0};
   const int splits = mll::LS_WARPS * ranks;
   a.chunks_per_warp = (chunks + splits - 1) / splits;
-  if (M <= 8) return mll::launch_linear_small<1>(a, tiles, ranks, stream);
-  if (M <= 16) return mll::launch_linear_small<2>(a, tiles, ranks, stream);
-  if (M <= 32) return mll::launch_linear_small<4>(a, tiles, ranks, stream);
-  return mll::launch_linear_small<8>(a, tiles, ranks, stream);
+  if (M <= 8) {
+    if (mll_linear_small_unroll == 2) return mll::launch_linear_small<1, 2>(a, tiles, ranks, stream);
+    if (mll_linear_small_unroll == 8) return mll::launch_linear_small<1, 8>(a, tiles, ranks, stream);
+    return mll::launch_linear_small<1, 4>(a, tiles, ranks, stream);
+  }
+  if (M <= 16) return mll::launch_linear_small<2, 4>(a, tiles, ranks, stream);
+  if (M <= 32) return mll::launch_linear_small<4, 2>(a, tiles, ranks, stream);
+  return mll::launch_linear_small<8, 2>(a, tiles, ranks, stream);
 }

@@ -59,8 +59,8 @@ class Linear:
             raise RuntimeError(f"{self.name}: bfloat16 weight with {x.dtype} activations; "
                                "a float32 run widens its matrices when it loads them")
         out = ws.buffer(out_name, (rows, self.out_features), out_dtype)
-        if rows <= step.small_rows and K.linear_small_supported(rows, self.out_features, self.in_features):
-            K.linear_small(x, w, None, out, K.EPI_F32 if out_dtype == torch.float32 else K.EPI_BF16)
+        if rows <= step.small_rows and K.small_linear(x, w, None, out,
+                                                       K.EPI_F32 if out_dtype == torch.float32 else K.EPI_BF16):
             return out
         if out_dtype == torch.bfloat16:
             torch.mm(x, w.t(), out=out)

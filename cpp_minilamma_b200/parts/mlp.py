@@ -63,12 +63,13 @@ class SwiGLUFeedForward(FeedForward):
     def forward(self, step, h: torch.Tensor) -> torch.Tensor:
         rows = h.shape[0]
         w = self.gate_up.weight
-        if (rows <= step.small_rows and self.block == INTERLEAVE and w.dtype == torch.bfloat16
-                and h.dtype == torch.bfloat16 and K.linear_small_supported(rows, 2 * self.inter, w.shape[1],
-                                                                           K.EPI_SWIGLU)):
+        fused = (rows <= step.small_rows and self.block == INTERLEAVE and w.dtype == torch.bfloat16
+                 and h.dtype == torch.bfloat16
+                 and bool(K.small_linear_kind(rows, 2 * self.inter, w.shape[1], K.EPI_SWIGLU)))
+        if fused:
             # few rows: one weight-streaming kernel whose epilogue applies the activation
             act = step.ws.buffer("act", (rows, self.inter), torch.bfloat16)
-            K.linear_small(h, w, None, act, K.EPI_SWIGLU)
+            K.small_linear(h, w, None, act, K.EPI_SWIGLU)
         else:
             gu = self.gate_up.forward(step, h, "gu")
             act = step.ws.buffer("act", (rows, self.inter), gu.dtype)

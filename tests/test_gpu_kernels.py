@@ -474,3 +474,51 @@ def test_linear_small_refuses():
         K.linear_small(torch.zeros((2, 48), dtype=torch.bfloat16, device=DEV),
                        torch.zeros((16, 48), dtype=torch.bfloat16, device=DEV), None,
                        torch.zeros((2, 16), dtype=torch.bfloat16, device=DEV))
+
+
+@pytest.mark.parametrize("rows", [1, 3, 8, 9, 16, 33, 64])
+@pytest.mark.parametrize("n,k,ranks", [(16, 32, 1), (40, 64, 2), (4104, 4096, 0), (512, 14336, 8), (128, 4096, 4),
+                                        (100, 224, 1), (7, 8, 1), (257, 200, 2), (1000, 1096, 0)])
+def test_linear_tma(rows, n, k, ranks):
+    # N that is no multiple of the 64-row tile, K that is no multiple of the 64-column stage:
+    # the TMA unit fills what lies outside with zeros
+    x = rnd((rows, k), torch.bfloat16, 40)
+    w = rnd((n, k), torch.bfloat16, 41, 0.05)
+    bias = rnd((n,), torch.float32, 42)
+    ref = as64(x) @ as64(w).T
+    assert K.linear_tma_supported(rows, n, k)
+    for epilogue, dtype, b in ((K.EPI_BF16, torch.bfloat16, None), (K.EPI_F32, torch.float32, bias)):
+        out = torch.full((rows, n), float("nan"), dtype=dtype, device=DEV)
+        K.linear_tma(x.to(DEV), w.to(DEV), None if b is None else b.to(DEV), out, epilogue, ranks)
+        want = ref if b is None else ref + as64(b)
+        if dtype == torch.float32:
+            np.testing.assert_allclose(as64(out), want, rtol=2e-5, atol=2e-5 * np.abs(want).max())
+        else:
+            np.testing.assert_allclose(as64(out), want, rtol=8e-3, atol=8e-3 * np.abs(want).max())
+        again = torch.empty_like(out)
+        K.linear_tma(x.to(DEV), w.to(DEV), None if b is None else b.to(DEV), again, epilogue, ranks)
+        assert torch.equal(out, again)
+    assert K.take_device_error() == 0
+
+
+@pytest.mark.parametrize("rows", [1, 8, 13, 64])
+@pytest.mark.parametrize("inter,k,ranks", [(176, 64, 1), (1000, 4096, 0), (64, 14336, 8), (40, 72, 1)])
+def test_linear_tma_swiglu(rows, inter, k, ranks):
+    gate = rnd((inter, k), torch.bfloat16, 43, 0.05)
+    up = rnd((inter, k), torch.bfloat16, 44, 0.05)
+    x = rnd((rows, k), torch.bfloat16, 45)
+    fused = torch.stack([gate.view(inter // 8, 8, k), up.view(inter // 8, 8, k)], dim=1).reshape(2 * inter, k)
+    out = torch.full((rows, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    K.linear_tma(x.to(DEV), fused.contiguous().to(DEV), None, out, K.EPI_SWIGLU, ranks)
+    want = pl.swiglu(as64(x) @ as64(gate).T, as64(x) @ as64(up).T)
+    np.testing.assert_allclose(as64(out), want, rtol=8e-3, atol=8e-3 * np.abs(want).max())
+    assert K.take_device_error() == 0
+
+
+def test_linear_tma_refuses():
+    assert not K.linear_tma_supported(65, 4096, 4096)
+    assert not K.linear_tma_supported(8, 4096, 100)   # rows of 200 bytes: TMA needs multiples of 16
+    with pytest.raises(K.KernelError, match="unsupported sizes"):
+        K.linear_tma(torch.zeros((2, 12), dtype=torch.bfloat16, device=DEV),
+                     torch.zeros((16, 12), dtype=torch.bfloat16, device=DEV), None,
+                     torch.zeros((2, 16), dtype=torch.bfloat16, device=DEV))
