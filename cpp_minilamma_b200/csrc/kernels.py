@@ -173,18 +173,27 @@ def take_device_error() -> int:
 
 
 def small_linear_kind(rows: int, out_features: int, in_features: int, epilogue: int = EPI_BF16) -> str:
-    """Which of this library's weight-streaming kernels takes the problem: "tma", "direct" or ""."""
-    if SMALL_LINEAR in ("tma", "auto") and linear_tma_supported(rows, out_features, in_features, epilogue):
-        return "tma"
-    if SMALL_LINEAR in ("direct", "auto") and linear_small_supported(rows, out_features, in_features, epilogue):
-        return "direct"
-    return ""
+    """Which of this library's weight-streaming kernels takes the problem: "tma", "direct" or "".
+
+    Measured on the 8B shapes (CUDA-graph timing, B200): the TMA pipeline wins on tall
+    matrices (gate/up, lm_head), where its deep queue of loads counts; the direct kernel
+    wins on the 4096-row projections, where a launch is short and its finer split over the
+    machine counts.  Above 8 rows both fall behind the library GEMM, except that the fused
+    SwiGLU epilogue still pays up to 16 rows."""
+    limit = 16 if epilogue == EPI_SWIGLU else 8
+    if rows > limit or SMALL_LINEAR == "none":
+        return ""
+    tma = SMALL_LINEAR in ("tma", "auto") and linear_tma_supported(rows, out_features, in_features, epilogue)
+    direct = SMALL_LINEAR in ("direct", "auto") and linear_small_supported(rows, out_features, in_features, epilogue)
+    if tma and direct and SMALL_LINEAR == "auto":
+        return "tma" if out_features >= 16384 else "direct"
+    return "tma" if tma else ("direct" if direct else "")
 
 
 def small_linear(x, w, bias, out, epilogue: int = EPI_BF16) -> bool:
     kind = small_linear_kind(x.shape[0], w.shape[0], w.shape[1], epilogue)
     if kind == "tma":
-        linear_tma(x, w, bias, out, epilogue)
+        linear_tma(x, w, bias, out, epilogue, 1 if x.shape[0] > 8 else 0)
     elif kind == "direct":
         linear_small(x, w, bias, out, epilogue)
     return bool(kind)

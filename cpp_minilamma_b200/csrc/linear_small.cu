@@ -231,9 +231,10 @@ MLL_API int mll_linear_small(const void* x, const void* w, const float* bias, vo
   const int tiles = (N + 15) / 16;
   const int chunks = K / 32;
   if (ranks <= 0) {
-    // enough blocks to fill the machine a few times over, while a warp keeps >= 8 chunks
+    // split K while every block still fits on the machine at once (10 blocks per multiprocessor)
+    // and a warp keeps at least 4 chunks
     ranks = 1;
-    while (ranks < 8 && tiles * ranks < 148 * 6 && chunks / (mll::LS_WARPS * ranks * 2) >= 8) ranks *= 2;
+    while (ranks < 8 && tiles * ranks * 2 <= 148 * 10 && chunks / (mll::LS_WARPS * ranks * 2) >= 4) ranks *= 2;
   }
   MLL_REQUIRE(ranks == 1 || ranks == 2 || ranks == 4 || ranks == 8, "linear_small: cluster size %d", ranks);
   mll::LinearArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, out, M, N, K, epilogue, 0};
