@@ -578,3 +578,66 @@ MLL_API int mll_attn_prefill(const void* q, const void* k_cache, const void* v_c
   MLL_REQUIRE(false, "attention prefill: unknown dtype %d", dtype);
   return -1;
 }
+
+// ---------------------------------------------------------------------------------- //
+// decode without allocation (declared and explained in no_alloc.h)                    //
+// ---------------------------------------------------------------------------------- //
+#include <mutex>
+
+#include "no_alloc.h"
+
+// Partial results of the context splits live here instead of in caller-provided scratch.
+// In host code this name is only a handle for the runtime; the device address comes from
+// cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_no_alloc_scratch[MLL_NO_ALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_no_alloc_address[kMaxDevices] = {};
+std::mutex g_no_alloc_lock;
+
+// Device address of the scratch array on the current device, looked up once per device.
+int no_alloc_scratch(float** address) {
+  int device = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) {
+    mll_set_error("attention decode (no alloc): cudaGetDevice failed: %s", cudaGetErrorString(err));
+    return (int)err;
+  }
+  if (device < 0 || device >= kMaxDevices) {
+    mll_set_error("attention decode (no alloc): device %d is beyond the %d devices this table holds", device, kMaxDevices);
+    return -1;
+  }
+  std::lock_guard<std::mutex> guard(g_no_alloc_lock);
+  if (g_no_alloc_address[device] == nullptr) {
+    void* ptr = nullptr;
+    err = cudaGetSymbolAddress(&ptr, g_no_alloc_scratch);
+    if (err != cudaSuccess || ptr == nullptr) {
+      mll_set_error("attention decode (no alloc): cudaGetSymbolAddress failed: %s", cudaGetErrorString(err));
+      return err != cudaSuccess ? (int)err : -1;
+    }
+    g_no_alloc_address[device] = static_cast<float*>(ptr);
+  }
+  *address = g_no_alloc_address[device];
+  return 0;
+}
+}  // namespace
+
+MLL_API int mll_attn_decode_no_alloc(const void* q, const void* k_cache, const void* v_cache, const int* seq_slot,
+                                     const int* seq_ctx, const int* block_table, void* out, int dtype, int n_seqs,
+                                     int n_heads, int n_kv_heads, int head_dim, int max_blocks, int n_splits,
+                                     int window, float scale, cudaStream_t stream) {
+  MLL_REQUIRE(n_seqs >= 0 && n_heads > 0 && head_dim > 0 && n_splits >= 1,
+              "attention decode (no alloc): bad sizes seqs=%d heads=%d head_dim=%d splits=%d", n_seqs, n_heads,
+              head_dim, n_splits);
+  const long long need = mll_attn_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits);
+  MLL_REQUIRE(need <= (long long)MLL_NO_ALLOC_SCRATCH_FLOATS,
+              "attention decode (no alloc): %d sequences x %d heads x %d splits x (head_dim %d + 2) = %lld floats of "
+              "scratch exceed the built-in %d; use fewer splits or the entry point that takes scratch from the caller",
+              n_seqs, n_heads, n_splits, head_dim, need, MLL_NO_ALLOC_SCRATCH_FLOATS);
+  float* scratch = nullptr;
+  const int rc = no_alloc_scratch(&scratch);
+  if (rc != 0) return rc;
+  return mll_attn_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch, out, dtype, n_seqs, n_heads,
+                         n_kv_heads, head_dim, max_blocks, n_splits, window, scale, stream);
+}
