@@ -204,6 +204,40 @@ def prefill_flops(cfg, tokens):
     return cfg.num_hidden_layers * per_layer + 2 * cfg.hidden_size * cfg.vocab_size  # head on one row
 
 
+def profile_region(args):
+    """One eager step inside cudaProfilerStart/Stop, after warm-up steps of the same kind."""
+    import numpy as np
+    import torch
+    import cpp_minilamma_b200 as ml
+    from cpp_minilamma_b200 import StepEntry
+    cfg = llama31_8b(args.layers or 4)
+    llm = ml.random_model(cfg, seed=0, dtype="bfloat16", max_tokens=(args.batch + 1) * 4096, max_positions=4096,
+                          max_seqs=args.batch + 2, max_step_tokens=4096)
+    rng = np.random.RandomState(0)
+    engine = llm.engine
+    draw = lambda n: [int(t) for t in rng.randint(0, cfg.vocab_size, size=n)]
+    if args.profile == "decode":
+        slots = engine.acquire(args.batch)
+        engine.step_borrowed([StepEntry(s, draw(args.context), [args.context - 1]) for s in slots])
+        for _ in range(2):
+            engine.step_borrowed([StepEntry(s, [5], [0]) for s in slots])
+        step = lambda: engine.step_borrowed([StepEntry(s, [7], [0]) for s in slots])
+    else:
+        prompt = draw(PREFILL_TOKENS)
+        slot, = engine.acquire(1)
+        engine.step_borrowed([StepEntry(slot, prompt, [PREFILL_TOKENS - 1])])
+        engine.release(slot)
+        slot, = engine.acquire(1)
+        step = lambda: engine.step_borrowed([StepEntry(slot, prompt, [PREFILL_TOKENS - 1])])
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print(f"profiled one {args.profile} step: {cfg.num_hidden_layers} layers, batch {args.batch}")
+    return 0
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -212,6 +246,11 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
     parser.add_argument("--skip-points", action="store_true")
+    parser.add_argument("--profile", choices=["decode", "prefill"], default=None,
+                        help="run one step of that kind between cudaProfilerStart/Stop (for ncu "
+                             "--profile-from-start off) on a small case and exit; use with --layers")
+    parser.add_argument("--batch", type=int, default=BATCH, help="batch of the --profile decode step")
+    parser.add_argument("--context", type=int, default=1024, help="prompt length of the --profile decode step")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -225,6 +264,8 @@ def main():
 
     import torch
     import cpp_minilamma_b200 as ml
+    if args.profile:
+        return profile_region(args)
     warmup = max(args.warmup, 3)
     steps = max(args.steps, 1)
     peaks = load_peaks()
