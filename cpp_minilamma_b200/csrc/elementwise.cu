@@ -19,7 +19,7 @@ void mll_set_error(const char* fmt, ...) {
 MLL_API const char* mll_last_error() { return g_error; }
 
 // Identifies the build; the Python side checks it after loading the library.
-MLL_API int mll_abi_version() { return 6; }
+MLL_API int mll_abi_version() { return 7; }
 
 namespace mll {
 
@@ -63,6 +63,62 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     }
     const float act = g / (1.f + expf(-g));
     out[idx] = from_float<T>(act * u);
+  }
+}
+
+// The same over groups of 8 consecutive outputs (inter % 8 == 0, block 0 or 8): 16- or
+// 32-byte loads of a gate group and its up group, one vector store.
+template <typename T>
+struct Pack8;
+template <>
+struct Pack8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+    uint4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+  }
+};
+template <>
+struct Pack8<float> {
+  static __device__ __forceinline__ void load(const float* p, float* v) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+
+template <typename T>
+__global__ void swiglu_vec8_kernel(const T* __restrict__ gu, T* __restrict__ out, int tokens, int inter, int block) {
+  const int groups = inter >> 3;
+  const size_t total = (size_t)tokens * groups;
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < total; idx += stride) {
+    const int t = (int)(idx / groups), b = (int)(idx % groups);
+    const T* row = gu + (size_t)t * 2 * inter;
+    const T* gp = block ? row + (size_t)b * 16 : row + (size_t)b * 8;
+    const T* up = block ? gp + 8 : row + inter + (size_t)b * 8;
+    float g[8], u[8], r[8];
+    Pack8<T>::load(gp, g);
+    Pack8<T>::load(up, u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r[i] = g[i] / (1.f + expf(-g[i])) * u[i];
+    Pack8<T>::store(out + (size_t)t * inter + (size_t)b * 8, r);
   }
 }
 
@@ -134,6 +190,22 @@ MLL_API int mll_swiglu(const void* gu, void* out, int dtype, int n_tokens, int i
               "swiglu: intermediate size %d is not a multiple of the interleave block %d", inter, block);
   if (n_tokens == 0) return 0;
   const int threads = 256;
+  const bool vec = inter % 8 == 0 && (block == 0 || block == 8) && ((uintptr_t)gu % 16 == 0) &&
+                   ((uintptr_t)out % 16 == 0);
+  if (vec) {
+    long long groups = ((long long)n_tokens * (inter / 8) + threads - 1) / threads;
+    if (groups > 148 * 32) groups = 148 * 32;
+    if (dtype == MLL_F32)
+      mll::swiglu_vec8_kernel<float><<<(int)groups, threads, 0, stream>>>((const float*)gu, (float*)out, n_tokens,
+                                                                       inter, block);
+    else if (dtype == MLL_BF16)
+      mll::swiglu_vec8_kernel<__nv_bfloat16><<<(int)groups, threads, 0, stream>>>(
+          (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tokens, inter, block);
+    else
+      MLL_REQUIRE(false, "swiglu: unknown dtype %d", dtype);
+    MLL_LAUNCH_CHECK();
+    return 0;
+  }
   long long blocks = ((long long)n_tokens * inter + threads - 1) / threads;
   if (blocks > 148 * 32) blocks = 148 * 32;
   if (dtype == MLL_F32)

@@ -14,7 +14,7 @@ import torch
 from .build import KernelBuildError, load_library
 
 PAGE = 64  # cache positions per page; equals MLL_PAGE in common.cuh
-ABI_VERSION = 6
+ABI_VERSION = 7
 MAX_TOP_K = 1024
 
 
@@ -299,7 +299,8 @@ def attention_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_
     return int(lib().mll_attn_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits))
 
 
-USE_TENSOR_CORE_DECODE = True  # tests switch this off to reach the general kernel at every size
+USE_TENSOR_CORE_DECODE = True  # tests switch these off to reach the general kernels at every size
+USE_TENSOR_CORE_PREFILL = True
 
 
 def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch, out, n_seqs: int,
@@ -349,6 +350,14 @@ def attention_prefill(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_ql
     _need(block_table, "attention block_table", torch.int32, 2)
     if tile_seq.shape[0] < n_tiles or tile_row0.shape[0] < n_tiles:
         raise KernelError("attention prefill: tile lists shorter than the tile count")
+    if USE_TENSOR_CORE_PREFILL and lib().mll_attn_prefill_mma_supported(dtype_code(q.dtype), head_dim):
+        _check(lib().mll_attn_prefill_mma(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx),
+                                          _ptr(seq_qstart), _ptr(seq_qlen), _ptr(tile_seq), _ptr(tile_row0),
+                                          _ptr(block_table), _ptr(out), ctypes.c_int(n_tiles), ctypes.c_int(n_heads),
+                                          ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim),
+                                          ctypes.c_int(block_table.shape[1]), ctypes.c_int(window),
+                                          ctypes.c_float(scale), _stream()), "attention_prefill (tensor cores)")
+        return
     _check(lib().mll_attn_prefill(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx),
                                   _ptr(seq_qstart), _ptr(seq_qlen), _ptr(tile_seq), _ptr(tile_row0),
                                   _ptr(block_table), _ptr(out), dtype_code(q.dtype), ctypes.c_int(n_tiles),

@@ -238,6 +238,13 @@ def test_attention_decode_window_edge(dtype, window, decode_impl):
             np.testing.assert_allclose(as64(out[b]).reshape(hq, d), ref[0], **tol(dtype), err_msg=f"seq {b}")
 
 
+@pytest.fixture(params=["tensor_core", "general"])
+def prefill_impl(request):
+    K.USE_TENSOR_CORE_PREFILL = request.param == "tensor_core"
+    yield request.param
+    K.USE_TENSOR_CORE_PREFILL = True
+
+
 def _prefill_tiles(q_lens):
     tile_seq, tile_row0 = [], []
     for i, n in enumerate(q_lens):
@@ -248,9 +255,10 @@ def _prefill_tiles(q_lens):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hq,hk,d", [(4, 2, 16), (6, 1, 32), (3, 3, 48), (10, 2, 80), (8, 2, 128), (4, 1, 256)])
+@pytest.mark.parametrize("hq,hk,d", [(4, 2, 16), (6, 1, 32), (3, 3, 48), (10, 2, 80), (8, 2, 128), (4, 1, 256),
+                                      (6, 3, 64)])
 @pytest.mark.parametrize("window", [0, 70])
-def test_attention_prefill(dtype, hq, hk, d, window):
+def test_attention_prefill(dtype, hq, hk, d, window, prefill_impl):
     # sequences that start at 0 and sequences that continue an existing context
     ctx = [200, 1, 65, 130, 64]
     q_lens = [200, 1, 3, 66, 64]
@@ -274,7 +282,7 @@ def test_attention_prefill(dtype, hq, hk, d, window):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_attention_prefill_far_key_stands_out(dtype):
+def test_attention_prefill_far_key_stands_out(dtype, prefill_impl):
     hq, hk, d, c = 4, 2, 64, 520
     case = PagedCase([c], hk, d, dtype, seed=99)
     q = rnd((c, hq, d), dtype, 15, 0.1)
