@@ -69,6 +69,7 @@ struct Vec16<__nv_bfloat16> {
 template <typename T, int NACC>
 __global__ void __launch_bounds__(128)
 attn_decode_kernel(AttnArgs a, int two_stage) {
+  mll::pdl_begin();
   constexpr int PAD = 16 / sizeof(T);
   constexpr int VN = Vec16<T>::N;
   const int d = a.head_dim;
@@ -241,6 +242,7 @@ attn_decode_kernel(AttnArgs a, int two_stage) {
 // grid (B * Hq), merges the splits of one (sequence, head) in a fixed order.
 template <typename T>
 __global__ void attn_combine_kernel(AttnArgs a) {
+  mll::pdl_begin();
   const int bh = blockIdx.x;
   const int d = a.head_dim, S = a.n_splits;
   const float* ml = a.part_ml + (size_t)bh * S * 2;
@@ -268,6 +270,7 @@ __global__ void attn_combine_kernel(AttnArgs a) {
 template <typename T, int DT>
 __global__ void __launch_bounds__(256)
 attn_prefill_kernel(AttnArgs a) {
+  mll::pdl_begin();
   constexpr int BM = 64, BN = MLL_PAGE;
   const int d = a.head_dim;
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
@@ -439,7 +442,7 @@ int launch_decode(const AttnArgs& a, int n_seqs, int chunks, size_t smem, int tw
     }
   }
   dim3 grid(n_seqs, a.n_kv_heads * chunks, a.n_splits);
-  kernel<<<grid, 128, smem, stream>>>(a, two_stage);
+  MLL_LAUNCH((kernel), grid, 128, smem, stream, a, two_stage);
   MLL_LAUNCH_CHECK();
   return 0;
 }
@@ -470,7 +473,7 @@ int decode_dispatch(AttnArgs a, int n_seqs, cudaStream_t stream) {
   else rc = launch_decode<T, 16>(a, n_seqs, chunks, smem, two_stage, stream);
   if (rc != 0) return rc;
   if (a.n_splits > 1) {
-    attn_combine_kernel<T><<<n_seqs * a.n_heads, 128, 0, stream>>>(a);
+    MLL_LAUNCH((attn_combine_kernel<T>), n_seqs * a.n_heads, 128, 0, stream, a);
     MLL_LAUNCH_CHECK();
   }
   return 0;
@@ -490,7 +493,7 @@ int launch_prefill(const AttnArgs& a, int n_tiles, cudaStream_t stream) {
     }
   }
   dim3 grid(n_tiles, a.n_heads);
-  kernel<<<grid, 256, smem, stream>>>(a);
+  MLL_LAUNCH((kernel), grid, 256, smem, stream, a);
   MLL_LAUNCH_CHECK();
   return 0;
 }
@@ -550,9 +553,9 @@ MLL_API int mll_attn_combine(float* scratch, void* out, int dtype, int n_seqs, i
   a.out = out;
   a.n_heads = n_heads; a.head_dim = head_dim; a.n_splits = n_splits;
   if (dtype == MLL_F32)
-    mll::attn_combine_kernel<float><<<n_seqs * n_heads, 128, 0, stream>>>(a);
+    MLL_LAUNCH((mll::attn_combine_kernel<float>), n_seqs * n_heads, 128, 0, stream, a);
   else if (dtype == MLL_BF16)
-    mll::attn_combine_kernel<__nv_bfloat16><<<n_seqs * n_heads, 128, 0, stream>>>(a);
+    MLL_LAUNCH((mll::attn_combine_kernel<__nv_bfloat16>), n_seqs * n_heads, 128, 0, stream, a);
   else
     MLL_REQUIRE(false, "attention combine: unknown dtype %d", dtype);
   MLL_LAUNCH_CHECK();

@@ -63,6 +63,7 @@ struct DecodeMmaSmem {
 template <int D, int STAGES>
 __global__ void __launch_bounds__(128)
 attn_decode_mma_kernel(DecodeMmaArgs a) {
+  mll::pdl_begin();
   using L = DecodeMmaSmem<D, STAGES>;
   constexpr int KSTEPS = D / 16;       // k-steps of the score product
   constexpr int NT_OUT = D / 32;       // value n-tiles (8 columns) per warp
@@ -289,7 +290,7 @@ int launch_decode_mma(const DecodeMmaArgs& a, int n_seqs, cudaStream_t stream) {
   }
   const int group = a.n_heads / a.n_kv_heads;
   dim3 grid(n_seqs, a.n_kv_heads * ((group + 15) / 16), a.n_splits);
-  kernel<<<grid, 128, smem, stream>>>(a);
+  MLL_LAUNCH((kernel), grid, 128, smem, stream, a);
   MLL_LAUNCH_CHECK();
   return 0;
 }
@@ -328,6 +329,7 @@ struct PrefillMmaSmem {
 template <int D>
 __global__ void __launch_bounds__(128)
 attn_prefill_mma_kernel(PrefillMmaArgs a) {
+  mll::pdl_begin();
   using L = PrefillMmaSmem<D>;
   constexpr int KSTEPS = D / 16;
   constexpr int NT_OUT = D / 8;
@@ -506,7 +508,7 @@ int launch_prefill_mma(const PrefillMmaArgs& a, int n_tiles, cudaStream_t stream
     mll_set_error("attention prefill (mma): cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
     return (int)err;
   }
-  kernel<<<dim3(n_tiles, a.n_heads), 128, smem, stream>>>(a);
+  MLL_LAUNCH((kernel), dim3(n_tiles, a.n_heads), 128, smem, stream, a);
   MLL_LAUNCH_CHECK();
   return 0;
 }

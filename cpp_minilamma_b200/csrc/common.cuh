@@ -29,16 +29,56 @@ void mll_set_error(const char* fmt, ...);
     }                                 \
   } while (0)
 
+// Launches `kernel` on `stream`; with programmatic dependent launch switched on
+// (mll_set_pdl) the launch may begin while the previous kernel of the stream is still
+// draining: every kernel of this library calls pdl_wait() before it touches anything that
+// an earlier kernel wrote or still reads.  The outcome is picked up by MLL_LAUNCH_CHECK.
+#define MLL_LAUNCH(kernel, grid, block, smem, stream, ...) \
+  mll_launch_status = mll::launch_kernel(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, ##__VA_ARGS__)
+
 #define MLL_LAUNCH_CHECK()                          \
   do {                                              \
-    cudaError_t err__ = cudaGetLastError();         \
+    cudaError_t err__ = mll_launch_status;          \
+    mll_launch_status = cudaSuccess;                \
+    if (err__ == cudaSuccess) err__ = cudaGetLastError(); \
     if (err__ != cudaSuccess) {                     \
       mll_set_error("%s:%d launch failed: %s", __FILE__, __LINE__, cudaGetErrorString(err__)); \
       return (int)err__;                            \
     }                                               \
   } while (0)
 
+extern thread_local cudaError_t mll_launch_status;
+extern int mll_pdl_enabled;
+
 namespace mll {
+
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (mll_pdl_enabled) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
+// Programmatic dependent launch: let the next kernel of the stream start its prologue now,
+// and wait until everything earlier kernels wrote is complete and visible.  Both are
+// no-ops for a kernel that was launched without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_begin() {
+  pdl_launch_dependents();
+  pdl_wait();
+}
 
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -18,8 +18,14 @@ void mll_set_error(const char* fmt, ...) {
 
 MLL_API const char* mll_last_error() { return g_error; }
 
+thread_local cudaError_t mll_launch_status = cudaSuccess;
+int mll_pdl_enabled = 0;
+
+// Switches programmatic dependent launch on (1) or off (0) for every later launch of this library.
+MLL_API void mll_set_pdl(int enabled) { mll_pdl_enabled = enabled ? 1 : 0; }
+
 // Identifies the build; the Python side checks it after loading the library.
-MLL_API int mll_abi_version() { return 7; }
+MLL_API int mll_abi_version() { return 8; }
 
 namespace mll {
 
@@ -27,6 +33,7 @@ namespace mll {
 template <typename TableT>
 __global__ void embedding_kernel(const int* __restrict__ tokens, const TableT* __restrict__ table,
                                  float* __restrict__ x, int width) {
+  mll::pdl_begin();
   const int t = blockIdx.x;
   const TableT* row = table + (size_t)tokens[t] * width;
   float* out = x + (size_t)t * width;
@@ -35,6 +42,7 @@ __global__ void embedding_kernel(const int* __restrict__ tokens, const TableT* _
 
 template <typename In, typename Out>
 __global__ void cast_kernel(const In* __restrict__ in, Out* __restrict__ out, size_t n) {
+  mll::pdl_begin();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; i < n; i += stride) out[i] = from_float<Out>(to_float(in[i]));
@@ -46,6 +54,7 @@ __global__ void cast_kernel(const In* __restrict__ in, Out* __restrict__ out, si
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int tokens,
                               int inter, int block) {
+  mll::pdl_begin();
   const size_t total = (size_t)tokens * inter;
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -104,6 +113,7 @@ struct Pack8<float> {
 
 template <typename T>
 __global__ void swiglu_vec8_kernel(const T* __restrict__ gu, T* __restrict__ out, int tokens, int inter, int block) {
+  mll::pdl_begin();
   const int groups = inter >> 3;
   const size_t total = (size_t)tokens * groups;
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -125,6 +135,7 @@ __global__ void swiglu_vec8_kernel(const T* __restrict__ gu, T* __restrict__ out
 // x[t, i] += bias[i] (bias float32, sum in float32)
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ x, const float* __restrict__ bias, size_t total, int width) {
+  mll::pdl_begin();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; idx < total; idx += stride) x[idx] = from_float<T>(to_float(x[idx]) + bias[idx % width]);
@@ -139,9 +150,9 @@ MLL_API int mll_add_bias(void* x, const float* bias, int dtype, int n_rows, int 
   long long blocks = (long long)((total + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (dtype == MLL_F32)
-    mll::add_bias_kernel<float><<<(int)blocks, 256, 0, stream>>>((float*)x, bias, total, width);
+    MLL_LAUNCH((mll::add_bias_kernel<float>), (int)blocks, 256, 0, stream, (float*)x, bias, total, width);
   else if (dtype == MLL_BF16)
-    mll::add_bias_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((__nv_bfloat16*)x, bias, total, width);
+    MLL_LAUNCH((mll::add_bias_kernel<__nv_bfloat16>), (int)blocks, 256, 0, stream, (__nv_bfloat16*)x, bias, total, width);
   else
     MLL_REQUIRE(false, "add_bias: unknown dtype %d", dtype);
   MLL_LAUNCH_CHECK();
@@ -154,10 +165,9 @@ MLL_API int mll_embedding(const int* tokens, const void* table, int table_dtype,
   if (n_tokens == 0) return 0;
   const int threads = width >= 1024 ? 256 : 128;
   if (table_dtype == MLL_F32)
-    mll::embedding_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, x, width);
+    MLL_LAUNCH((mll::embedding_kernel<float>), n_tokens, threads, 0, stream, tokens, (const float*)table, x, width);
   else if (table_dtype == MLL_BF16)
-    mll::embedding_kernel<__nv_bfloat16>
-        <<<n_tokens, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, x, width);
+    MLL_LAUNCH((mll::embedding_kernel<__nv_bfloat16>), n_tokens, threads, 0, stream, tokens, (const __nv_bfloat16*)table, x, width);
   else
     MLL_REQUIRE(false, "embedding: unknown table dtype %d", table_dtype);
   MLL_LAUNCH_CHECK();
@@ -172,11 +182,9 @@ MLL_API int mll_cast(const void* in, int in_dtype, void* out, int out_dtype, lon
   long long blocks = (n + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (in_dtype == MLL_F32 && out_dtype == MLL_BF16)
-    mll::cast_kernel<float, __nv_bfloat16>
-        <<<(int)blocks, threads, 0, stream>>>((const float*)in, (__nv_bfloat16*)out, (size_t)n);
+    MLL_LAUNCH((mll::cast_kernel<float, __nv_bfloat16>), (int)blocks, threads, 0, stream, (const float*)in, (__nv_bfloat16*)out, (size_t)n);
   else if (in_dtype == MLL_BF16 && out_dtype == MLL_F32)
-    mll::cast_kernel<__nv_bfloat16, float>
-        <<<(int)blocks, threads, 0, stream>>>((const __nv_bfloat16*)in, (float*)out, (size_t)n);
+    MLL_LAUNCH((mll::cast_kernel<__nv_bfloat16, float>), (int)blocks, threads, 0, stream, (const __nv_bfloat16*)in, (float*)out, (size_t)n);
   else
     MLL_REQUIRE(false, "cast: unsupported dtype pair %d -> %d", in_dtype, out_dtype);
   MLL_LAUNCH_CHECK();
@@ -196,11 +204,10 @@ MLL_API int mll_swiglu(const void* gu, void* out, int dtype, int n_tokens, int i
     long long groups = ((long long)n_tokens * (inter / 8) + threads - 1) / threads;
     if (groups > 148 * 32) groups = 148 * 32;
     if (dtype == MLL_F32)
-      mll::swiglu_vec8_kernel<float><<<(int)groups, threads, 0, stream>>>((const float*)gu, (float*)out, n_tokens,
+      MLL_LAUNCH((mll::swiglu_vec8_kernel<float>), (int)groups, threads, 0, stream, (const float*)gu, (float*)out, n_tokens,
                                                                        inter, block);
     else if (dtype == MLL_BF16)
-      mll::swiglu_vec8_kernel<__nv_bfloat16><<<(int)groups, threads, 0, stream>>>(
-          (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tokens, inter, block);
+      MLL_LAUNCH((mll::swiglu_vec8_kernel<__nv_bfloat16>), (int)groups, threads, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tokens, inter, block);
     else
       MLL_REQUIRE(false, "swiglu: unknown dtype %d", dtype);
     MLL_LAUNCH_CHECK();
@@ -209,11 +216,9 @@ MLL_API int mll_swiglu(const void* gu, void* out, int dtype, int n_tokens, int i
   long long blocks = ((long long)n_tokens * inter + threads - 1) / threads;
   if (blocks > 148 * 32) blocks = 148 * 32;
   if (dtype == MLL_F32)
-    mll::swiglu_kernel<float>
-        <<<(int)blocks, threads, 0, stream>>>((const float*)gu, (float*)out, n_tokens, inter, block);
+    MLL_LAUNCH((mll::swiglu_kernel<float>), (int)blocks, threads, 0, stream, (const float*)gu, (float*)out, n_tokens, inter, block);
   else if (dtype == MLL_BF16)
-    mll::swiglu_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>(
-        (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tokens, inter, block);
+    MLL_LAUNCH((mll::swiglu_kernel<__nv_bfloat16>), (int)blocks, threads, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tokens, inter, block);
   else
     MLL_REQUIRE(false, "swiglu: unknown dtype %d", dtype);
   MLL_LAUNCH_CHECK();

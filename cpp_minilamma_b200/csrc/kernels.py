@@ -7,6 +7,7 @@ implementation behind them.  Argument faults raise `KernelError` before any laun
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -14,7 +15,7 @@ import torch
 from .build import KernelBuildError, load_library
 
 PAGE = 64  # cache positions per page; equals MLL_PAGE in common.cuh
-ABI_VERSION = 7
+ABI_VERSION = 8
 MAX_TOP_K = 1024
 
 
@@ -37,7 +38,14 @@ def lib() -> ctypes.CDLL:
                 f"kernel library reports ABI {handle.mll_abi_version()}, the package expects {ABI_VERSION}; "
                 "remove csrc/_build and rebuild")
         _lib = handle
+        # kernels of a stream overlap their prologue with the previous kernel's tail unless MLL_PDL=0
+        handle.mll_set_pdl(0 if os.environ.get("MLL_PDL", "1") == "0" else 1)
     return _lib
+
+
+def set_pdl(enabled: bool) -> None:
+    """Programmatic dependent launch for every later launch of this library (default on)."""
+    lib().mll_set_pdl(1 if enabled else 0)
 
 
 launches = 0  # kernels of this library launched so far (counted per successful call)

@@ -57,6 +57,7 @@ template <int NT, bool CLUSTER, int LS_UNROLL>  // LS_UNROLL: 32-element chunks 
 __global__ void __launch_bounds__(LS_WARPS * 32)
 linear_small_kernel(LinearArgs a) {
   __shared__ float red[LS_WARPS][16][8 * NT];
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   int rank = 0, ranks = 1;
@@ -90,12 +91,25 @@ linear_small_kernel(LinearArgs a) {
     for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
 
   int c = first;
-  for (; c + LS_UNROLL <= last; c += LS_UNROLL) {
-    uint4 fa[LS_UNROLL], fb[LS_UNROLL];
+  // The weights do not depend on earlier kernels: the first group of loads is issued before
+  // waiting for them (the activations are read only after the wait).
+  uint4 fa[LS_UNROLL], fb[LS_UNROLL];
+  const bool primed = c + LS_UNROLL <= last;
+  if (primed) {
 #pragma unroll
     for (int u = 0; u < LS_UNROLL; ++u) {
       fa[u] = ldg_stream(wa + (size_t)(c + u) * 32);
       fb[u] = ldg_stream(wb + (size_t)(c + u) * 32);
+    }
+  }
+  pdl_wait();
+  for (; c + LS_UNROLL <= last; c += LS_UNROLL) {
+    if (!(primed && c == first)) {
+#pragma unroll
+      for (int u = 0; u < LS_UNROLL; ++u) {
+        fa[u] = ldg_stream(wa + (size_t)(c + u) * 32);
+        fb[u] = ldg_stream(wb + (size_t)(c + u) * 32);
+      }
     }
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
@@ -111,12 +125,12 @@ linear_small_kernel(LinearArgs a) {
     }
   }
   for (; c < last; ++c) {
-    const uint4 fa = ldg_stream(wa + (size_t)c * 32), fb = ldg_stream(wb + (size_t)c * 32);
+    const uint4 ta = ldg_stream(wa + (size_t)c * 32), tb = ldg_stream(wb + (size_t)c * 32);
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
       const uint4 fx = x_ok[n] ? ldg_keep(xr[n] + (size_t)c * 32) : make_uint4(0u, 0u, 0u, 0u);
-      mma_bf16(acc[n], fa.x, fb.x, fa.y, fb.y, fx.x, fx.y);
-      mma_bf16(acc[n], fa.z, fb.z, fa.w, fb.w, fx.z, fx.w);
+      mma_bf16(acc[n], ta.x, tb.x, ta.y, tb.y, fx.x, fx.y);
+      mma_bf16(acc[n], ta.z, tb.z, ta.w, tb.w, fx.z, fx.w);
     }
   }
 
@@ -186,15 +200,21 @@ int launch_linear_small(const LinearArgs& a, int tiles, int ranks, cudaStream_t 
   config.blockDim = dim3(LS_WARPS * 32);
   config.dynamicSmemBytes = 0;
   config.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   cudaError_t err;
+  config.attrs = attr;
+  config.numAttrs = 0;
+  if (mll_pdl_enabled) {
+    attr[config.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[config.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+    ++config.numAttrs;
+  }
   if (ranks > 1) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = ranks;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    config.attrs = attr;
-    config.numAttrs = 1;
+    attr[config.numAttrs].id = cudaLaunchAttributeClusterDimension;
+    attr[config.numAttrs].val.clusterDim.x = ranks;
+    attr[config.numAttrs].val.clusterDim.y = 1;
+    attr[config.numAttrs].val.clusterDim.z = 1;
+    ++config.numAttrs;
     err = cudaLaunchKernelEx(&config, linear_small_kernel<NT, true, U>, a);
   } else {
     err = cudaLaunchKernelEx(&config, linear_small_kernel<NT, false, U>, a);

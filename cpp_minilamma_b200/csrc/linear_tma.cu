@@ -112,6 +112,7 @@ linear_tma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
   float* red = reinterpret_cast<float*>(base + (size_t)T_STAGES * L::STAGE);          // [64][8 NT]
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(red + L::RED_FLOATS);  // full[S], empty[S]
 
+  pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int rank = 0, ranks = 1;
   if (CLUSTER) {
@@ -142,9 +143,21 @@ linear_tma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
 
   if (warp == 4) {
     if (lane == 0) {
-      for (int i = 0; i < count; ++i) {
+      // The weights do not depend on earlier kernels: the ring is filled with weight boxes
+      // before waiting for them; the activation boxes follow after the wait.
+      const int primed = min(count, T_STAGES);
+      for (int i = 0; i < primed; ++i) {
+        const unsigned full = smem_u32(bars + i);
+        mbar_expect_tx(full, L::STAGE);
+        tma_load_2d(smem_u32(base + (size_t)i * L::STAGE), &wmap, (first + i) * T_KB, n0, full);
+      }
+      pdl_wait();
+      for (int i = 0; i < primed; ++i)
+        tma_load_2d(smem_u32(base + (size_t)i * L::STAGE) + L::W_BYTES, &xmap, (first + i) * T_KB, 0,
+                    smem_u32(bars + i));
+      for (int i = primed; i < count; ++i) {
         const int s = i % T_STAGES;
-        if (i >= T_STAGES && !mbar_wait(smem_u32(bars + T_STAGES + s), ((i / T_STAGES) & 1) ^ 1)) break;
+        if (!mbar_wait(smem_u32(bars + T_STAGES + s), ((i / T_STAGES) & 1) ^ 1)) break;
         const unsigned full = smem_u32(bars + s);
         const unsigned dst = smem_u32(base + (size_t)s * L::STAGE);
         mbar_expect_tx(full, L::STAGE);
@@ -193,6 +206,7 @@ linear_tma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
       r1[1] = acc[n][3];
     }
   }
+  pdl_wait();  // no global write before the earlier kernels are complete (the producer thread already waited)
   if (CLUSTER) {
     cg::cluster_group cluster = cg::this_cluster();
     cluster.sync();  // every block's partial tile is complete and visible
@@ -324,14 +338,20 @@ int launch_linear_tma(const CUtensorMap& wmap, const CUtensorMap& xmap, const Tm
   config.blockDim = dim3(T_THREADS);
   config.dynamicSmemBytes = smem;
   config.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  config.attrs = attr;
+  config.numAttrs = 0;
+  if (mll_pdl_enabled) {
+    attr[config.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[config.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+    ++config.numAttrs;
+  }
   if (ranks > 1) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = ranks;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    config.attrs = attr;
-    config.numAttrs = 1;
+    attr[config.numAttrs].id = cudaLaunchAttributeClusterDimension;
+    attr[config.numAttrs].val.clusterDim.x = ranks;
+    attr[config.numAttrs].val.clusterDim.y = 1;
+    attr[config.numAttrs].val.clusterDim.z = 1;
+    ++config.numAttrs;
     err = cudaLaunchKernelEx(&config, linear_tma_kernel<NT, true>, wmap, xmap, a);
   } else {
     err = cudaLaunchKernelEx(&config, linear_tma_kernel<NT, false>, wmap, xmap, a);

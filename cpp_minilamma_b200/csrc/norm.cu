@@ -17,6 +17,7 @@ template <typename DeltaT, typename OutT>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const DeltaT* __restrict__ delta,
                                    const float* __restrict__ weight, OutT* __restrict__ out,
                                    const int* __restrict__ rows, int width, float eps) {
+  mll::pdl_begin();
   extern __shared__ float row_buf[];
   __shared__ float scratch[32];
   const int r = blockIdx.x;
@@ -70,6 +71,7 @@ __global__ void __launch_bounds__(256)
 add_rmsnorm_vec_kernel(float* __restrict__ x, const DeltaT* __restrict__ delta,
                        const float* __restrict__ weight, OutT* __restrict__ out,
                        const int* __restrict__ rows, int width, float eps) {
+  mll::pdl_begin();
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
@@ -127,13 +129,13 @@ int launch_add_rmsnorm(float* x, const void* delta, const float* weight, void* o
   if (aligned && width <= 4 * 256 * 8) {
     const int groups = width / 4;
     if (groups <= 256 * 2)
-      add_rmsnorm_vec_kernel<DeltaT, OutT, 2><<<n_rows, 256, 0, stream>>>(x, (const DeltaT*)delta, weight,
+      MLL_LAUNCH((add_rmsnorm_vec_kernel<DeltaT, OutT, 2>), n_rows, 256, 0, stream, x, (const DeltaT*)delta, weight,
                                                                           (OutT*)out, rows, width, eps);
     else if (groups <= 256 * 4)
-      add_rmsnorm_vec_kernel<DeltaT, OutT, 4><<<n_rows, 256, 0, stream>>>(x, (const DeltaT*)delta, weight,
+      MLL_LAUNCH((add_rmsnorm_vec_kernel<DeltaT, OutT, 4>), n_rows, 256, 0, stream, x, (const DeltaT*)delta, weight,
                                                                           (OutT*)out, rows, width, eps);
     else
-      add_rmsnorm_vec_kernel<DeltaT, OutT, 8><<<n_rows, 256, 0, stream>>>(x, (const DeltaT*)delta, weight,
+      MLL_LAUNCH((add_rmsnorm_vec_kernel<DeltaT, OutT, 8>), n_rows, 256, 0, stream, x, (const DeltaT*)delta, weight,
                                                                           (OutT*)out, rows, width, eps);
     MLL_LAUNCH_CHECK();
     return 0;
@@ -148,7 +150,7 @@ int launch_add_rmsnorm(float* x, const void* delta, const float* weight, void* o
       return (int)err;
     }
   }
-  kernel<<<n_rows, threads, smem, stream>>>(x, (const DeltaT*)delta, weight, (OutT*)out, rows, width, eps);
+  MLL_LAUNCH((kernel), n_rows, threads, smem, stream, x, (const DeltaT*)delta, weight, (OutT*)out, rows, width, eps);
   MLL_LAUNCH_CHECK();
   return 0;
 }

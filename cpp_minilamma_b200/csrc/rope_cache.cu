@@ -31,6 +31,7 @@ struct RopeArgs {
 // no thread waits for more than one round of loads.
 template <typename T>
 __global__ void rope_cache_kernel(RopeArgs a) {
+  mll::pdl_begin();
   const int t = blockIdx.x;
   const int hb = blockIdx.y;  // q heads, then k heads, then v heads
   const int d = a.head_dim, half = d >> 1;
@@ -94,9 +95,9 @@ MLL_API int mll_rope_cache(const void* qkv, const float* bias, const float* cos_
   MLL_REQUIRE(n_heads + 2 * n_kv_heads <= 65535, "rope: too many heads for one launch");
   const dim3 grid(n_tokens, n_heads + (write_kv ? 2 * n_kv_heads : 0));
   if (dtype == MLL_F32)
-    mll::rope_cache_kernel<float><<<grid, threads, 0, stream>>>(a);
+    MLL_LAUNCH((mll::rope_cache_kernel<float>), grid, threads, 0, stream, a);
   else if (dtype == MLL_BF16)
-    mll::rope_cache_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(a);
+    MLL_LAUNCH((mll::rope_cache_kernel<__nv_bfloat16>), grid, threads, 0, stream, a);
   else
     MLL_REQUIRE(false, "rope: unknown dtype %d", dtype);
   MLL_LAUNCH_CHECK();

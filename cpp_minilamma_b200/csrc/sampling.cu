@@ -83,6 +83,7 @@ __device__ __forceinline__ int block_min_int(int v, int* scratch) {
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ tokens, int* __restrict__ status) {
+  mll::pdl_begin();
   __shared__ Best warp_best[32];
   __shared__ int bad;
   const float* row = logits + (size_t)blockIdx.x * vocab;
@@ -122,6 +123,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_temperature_kernel(const float* __restrict__ logits, int vocab, float temperature,
                           unsigned long long seed, const int* __restrict__ request,
                           const int* __restrict__ step, int* __restrict__ tokens, int* __restrict__ status) {
+  mll::pdl_begin();
   __shared__ float fscratch[33];
   __shared__ int iscratch[32];
   __shared__ int bad;
@@ -179,6 +181,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_top_k_kernel(const float* __restrict__ logits, int vocab, int top_k, float temperature,
                     unsigned long long seed, const int* __restrict__ request, const int* __restrict__ step,
                     int* __restrict__ tokens, int* __restrict__ status) {
+  mll::pdl_begin();
   __shared__ unsigned long long cand[SAMPLE_THREADS];
   __shared__ int hist[256];
   __shared__ float fscratch[33];
@@ -308,7 +311,7 @@ MLL_API int mll_argmax(const float* logits, int n_rows, int vocab, int* tokens, 
                        cudaStream_t stream) {
   MLL_REQUIRE(n_rows >= 0 && vocab > 0, "argmax: bad sizes rows=%d vocab=%d", n_rows, vocab);
   if (n_rows == 0) return 0;
-  mll::argmax_kernel<<<n_rows, mll::SAMPLE_THREADS, 0, stream>>>(logits, vocab, tokens, status);
+  MLL_LAUNCH((mll::argmax_kernel), n_rows, mll::SAMPLE_THREADS, 0, stream, logits, vocab, tokens, status);
   MLL_LAUNCH_CHECK();
   return 0;
 }
@@ -326,11 +329,9 @@ MLL_API int mll_sample(const float* logits, int n_rows, int vocab, float tempera
               "sample: top_k %d above the supported maximum of %d", top_k, mll::SAMPLE_THREADS);
   if (n_rows == 0) return 0;
   if (top_k == 0)
-    mll::sample_temperature_kernel<<<n_rows, mll::SAMPLE_THREADS, 0, stream>>>(
-        logits, vocab, temperature, seed, request, step, tokens, status);
+    MLL_LAUNCH((mll::sample_temperature_kernel), n_rows, mll::SAMPLE_THREADS, 0, stream, logits, vocab, temperature, seed, request, step, tokens, status);
   else
-    mll::sample_top_k_kernel<<<n_rows, mll::SAMPLE_THREADS, 0, stream>>>(
-        logits, vocab, top_k, temperature, seed, request, step, tokens, status);
+    MLL_LAUNCH((mll::sample_top_k_kernel), n_rows, mll::SAMPLE_THREADS, 0, stream, logits, vocab, top_k, temperature, seed, request, step, tokens, status);
   MLL_LAUNCH_CHECK();
   return 0;
 }

@@ -22,6 +22,15 @@ def tol(dtype):
     return dict(rtol=2e-5, atol=2e-6) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1e-3)
 
 
+def attention_tol(dtype, impl, values):
+    """The tensor-core attention kernels round the probabilities to bfloat16 before the P.V
+    product (2^-9 relative each), so their output error is bounded by 2^-9 * sum_j p_j |v_j|
+    <= 2^-9 * max|v|; the bound used is twice that.  The general kernels keep P in float32."""
+    if dtype == torch.bfloat16 and impl == "tensor_core":
+        return dict(rtol=1.6e-2, atol=2.0 ** -8 * float(np.abs(values).max()))
+    return tol(dtype)
+
+
 def rnd(shape, dtype, seed, scale=1.0):
     g = torch.Generator().manual_seed(seed)
     return (torch.randn(shape, generator=g) * scale).to(dtype)
@@ -180,7 +189,8 @@ def test_attention_decode(dtype, hq, hk, d, splits, decode_impl):
                        len(ctx), hq, hk, d, splits, 0, 1.0 / math.sqrt(d))
     for b, c in enumerate(ctx):
         ref = pl.causal_attention(as64(q[b:b + 1]), as64(case.k[b]), as64(case.v[b]), q_positions=[c - 1])
-        np.testing.assert_allclose(as64(out[b]).reshape(hq, d), ref[0], **tol(dtype), err_msg=f"seq {b} ctx {c}")
+        np.testing.assert_allclose(as64(out[b]).reshape(hq, d), ref[0],
+                                   **attention_tol(dtype, decode_impl, as64(case.v[b])), err_msg=f"seq {b} ctx {c}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -207,7 +217,7 @@ def test_attention_decode_far_key_stands_out(dtype, far, decode_impl):
         for h in range(hq):
             np.testing.assert_allclose(got[h], 3.0 + h // (hq // hk), rtol=1e-2, atol=1e-2)
         ref = pl.causal_attention(as64(q[0:1]), as64(case.k[0]), as64(case.v[0]), q_positions=[c - 1])
-        np.testing.assert_allclose(got, ref[0], **tol(dtype))
+        np.testing.assert_allclose(got, ref[0], **attention_tol(dtype, decode_impl, as64(case.v[0])))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -235,7 +245,9 @@ def test_attention_decode_window_edge(dtype, window, decode_impl):
         for b, c in enumerate(ctx):
             ref = pl.causal_attention(as64(q[b:b + 1]), as64(case.k[b]), as64(case.v[b]), window=window,
                                       q_positions=[c - 1])
-            np.testing.assert_allclose(as64(out[b]).reshape(hq, d), ref[0], **tol(dtype), err_msg=f"seq {b}")
+            np.testing.assert_allclose(as64(out[b]).reshape(hq, d), ref[0],
+                                       **attention_tol(dtype, decode_impl, as64(case.v[b][max(0, c - window):])),
+                                       err_msg=f"seq {b}")
 
 
 @pytest.fixture(params=["tensor_core", "general"])
@@ -278,7 +290,8 @@ def test_attention_prefill(dtype, hq, hk, d, window, prefill_impl):
         rows = slice(qstart[b], qstart[b] + n)
         ref = pl.causal_attention(as64(q[rows]), as64(case.k[b]), as64(case.v[b]), window=window or None,
                                   q_positions=list(range(c - n, c)))
-        np.testing.assert_allclose(got[rows], ref, **tol(dtype), err_msg=f"seq {b}")
+        np.testing.assert_allclose(got[rows], ref, **attention_tol(dtype, prefill_impl, as64(case.v[b])),
+                                   err_msg=f"seq {b}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -301,7 +314,7 @@ def test_attention_prefill_far_key_stands_out(dtype, prefill_impl):
     got = as64(out).reshape(c, hq, d)
     np.testing.assert_allclose(got[far:], 7.0, rtol=1e-2, atol=1e-2)   # every query from `far` on sees it
     ref = pl.causal_attention(as64(q), as64(case.k[0]), as64(case.v[0]))
-    np.testing.assert_allclose(got, ref, **tol(dtype))
+    np.testing.assert_allclose(got, ref, **attention_tol(dtype, prefill_impl, as64(case.v[0])))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
