@@ -90,26 +90,14 @@ linear_small_kernel(LinearArgs a) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
 
+  pdl_wait();
   int c = first;
-  // The weights do not depend on earlier kernels: the first group of loads is issued before
-  // waiting for them (the activations are read only after the wait).
-  uint4 fa[LS_UNROLL], fb[LS_UNROLL];
-  const bool primed = c + LS_UNROLL <= last;
-  if (primed) {
+  for (; c + LS_UNROLL <= last; c += LS_UNROLL) {
+    uint4 fa[LS_UNROLL], fb[LS_UNROLL];
 #pragma unroll
     for (int u = 0; u < LS_UNROLL; ++u) {
       fa[u] = ldg_stream(wa + (size_t)(c + u) * 32);
       fb[u] = ldg_stream(wb + (size_t)(c + u) * 32);
-    }
-  }
-  pdl_wait();
-  for (; c + LS_UNROLL <= last; c += LS_UNROLL) {
-    if (!(primed && c == first)) {
-#pragma unroll
-      for (int u = 0; u < LS_UNROLL; ++u) {
-        fa[u] = ldg_stream(wa + (size_t)(c + u) * 32);
-        fb[u] = ldg_stream(wb + (size_t)(c + u) * 32);
-      }
     }
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
