@@ -15,7 +15,7 @@ import torch
 from .build import KernelBuildError, load_library
 
 PAGE = 64  # cache positions per page; equals MLL_PAGE in common.cuh
-ABI_VERSION = 8
+ABI_VERSION = 9
 MAX_TOP_K = 1024
 
 
@@ -174,6 +174,33 @@ def linear_tma(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], o
     _check(lib().mll_linear_tma(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), ctypes.c_int(rows), ctypes.c_int(n),
                                 ctypes.c_int(k), ctypes.c_int(epilogue), ctypes.c_int(ranks), _stream()),
            "linear_tma")
+
+
+def linear_tc5_supported(rows: int, out_features: int, in_features: int, epilogue: int = EPI_BF16) -> bool:
+    return bool(lib().mll_linear_tc5_supported(rows, out_features, in_features, epilogue))
+
+
+def linear_tc5(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+               epilogue: int = EPI_BF16, ranks: int = 0) -> None:
+    """As `linear_tma`, with the product on the fifth-generation tensor cores: tcgen05.mma reads
+    the TMA-filled stages from shared memory and accumulates in tensor memory."""
+    _need(x, "linear_tc5 x", torch.bfloat16, 2)
+    _need(w, "linear_tc5 w", torch.bfloat16, 2)
+    rows, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise KernelError(f"linear_tc5: x width {k} differs from w width {w.shape[1]}")
+    want = (rows, n // 2) if epilogue == EPI_SWIGLU else (rows, n)
+    _need(out, "linear_tc5 out", torch.float32 if epilogue == EPI_F32 else torch.bfloat16, 2)
+    if tuple(out.shape) != want:
+        raise KernelError(f"linear_tc5: out {tuple(out.shape)}, expected {want}")
+    if bias is not None:
+        _need(bias, "linear_tc5 bias", torch.float32, 1)
+        if bias.shape[0] != n:
+            raise KernelError("linear_tc5: bias length differs from the output width")
+    _check(lib().mll_linear_tc5(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), ctypes.c_int(rows), ctypes.c_int(n),
+                                ctypes.c_int(k), ctypes.c_int(epilogue), ctypes.c_int(ranks), _stream()),
+           "linear_tc5")
 
 
 def take_device_error() -> int:

@@ -1,0 +1,362 @@
+// y[M, N] = x[M, K] . W[N, K]^T for at most 64 rows: TMA -> shared memory -> tcgen05.mma -> TMEM.
+//
+// The fifth-generation tensor cores read both operands straight from shared memory and keep
+// the accumulator in tensor memory, so the block needs no fragment loads at all:
+//   * warp 4, one thread: TMA producer.  Per k-block of 64 it loads a [128 weight rows x 64]
+//     box and the [16..64 activation rows x 64] box (128-byte swizzle, K-major) into a ring
+//     of stages guarded by full/empty mbarriers;
+//   * warp 5, one thread: issues four tcgen05.mma (M = 128 weight rows, N = batch rows padded
+//     to 16/32/64, K = 16) per stage from shared-memory descriptors and releases the stage
+//     with tcgen05.commit; the same warp allocates and frees the block's TMEM columns;
+//   * warps 0-3: after the last commit they read the 128 x N float32 accumulator from TMEM
+//     (tcgen05.ld, one row per thread) into shared memory.
+// "Swap-AB": the weights are the M operand, the batch is N, so a decode step with 1..64
+// sequences fills the 128-row MMA.  K is split over the blocks of a cluster; partial tiles
+// are summed in rank order through distributed shared memory (reproducible); the epilogue
+// (bias, SwiGLU on gate/up rows interleaved in blocks of 8, bfloat16 or float32 output) runs
+// on the full sum.  Rows and columns outside the matrices are zero-filled by TMA, so any N,
+// any M <= 64 and any K % 8 == 0 are taken.  No load uses cluster multicast.
+//
+// Every mbarrier wait is bounded; on a timeout the thread raises an error flag (read with
+// mll_take_device_error) and leaves its loop, the block still reaches its barriers, frees its TMEM and exits.
+//
+// The reference calls cublasSgemm with rows = 1 for every linear (src/cuda_matmul.cc:181-186).
+#include <cooperative_groups.h>
+#include <cuda.h>
+
+#include "common.cuh"
+#include "tensor_map.h"
+
+namespace cg = cooperative_groups;
+
+// raised by a bounded wait that ran out; read and cleared through mll_take_device_error()
+__device__ int mll_tc5_error_flag = 0;
+
+namespace mll {
+
+enum : int { CEPI_BF16 = 0, CEPI_F32 = 1, CEPI_SWIGLU = 2 };
+constexpr int C_ROWS = 128;     // weight rows per block (the MMA's M)
+constexpr int C_KB = 64;        // k elements per stage: one 128-byte swizzle span
+constexpr int C_STAGES = 4;
+constexpr int C_THREADS = 192;  // 4 epilogue warps, 1 producer warp, 1 MMA warp
+constexpr unsigned C_SPIN_LIMIT = 4u << 20;
+
+struct Tc5Args {
+  const float* bias;
+  void* out;
+  int M, N, K, epilogue, blocks_per_rank;
+};
+
+__device__ __forceinline__ unsigned c_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void c_mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void c_mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool c_mbar_test(unsigned bar, unsigned parity) {
+  unsigned done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done != 0;
+}
+__device__ __forceinline__ bool c_mbar_wait(unsigned bar, unsigned parity) {
+  for (unsigned spin = 0; spin < C_SPIN_LIMIT; ++spin) {
+    if (c_mbar_test(bar, parity)) return true;
+    if (spin > 64) __nanosleep(40);
+  }
+  atomicExch(&mll_tc5_error_flag, 1);
+  return false;
+}
+__device__ __forceinline__ void c_tma_load_2d(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16)
+// with the 128-byte swizzle: groups of 8 rows are 1024 bytes apart (stride byte offset), the
+// leading byte offset is not used by swizzled K-major layouts, descriptor version 1,
+// layout type 2 (SWIZZLE_128B).  `addr` is the shared-memory byte address of the first row,
+// advanced by 32 bytes per K = 16 step inside the swizzle span.
+__device__ __forceinline__ unsigned long long umma_desc_sw128(unsigned addr) {
+  return (unsigned long long)((addr >> 4) & 0x3FFFu) | (1ull << 16) | ((unsigned long long)(1024 >> 4) << 32) |
+         (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor, kind::f16: float32 accumulator, bfloat16 A and B, both K-major.
+__host__ __device__ constexpr unsigned umma_idesc_bf16(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long desc_a, unsigned long long desc_b,
+                                          unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+template <int NB>  // batch columns of the MMA: 16, 32 or 64
+struct Tc5Smem {
+  static constexpr int W_BYTES = C_ROWS * C_KB * 2;  // 16384
+  static constexpr int X_BYTES = NB * C_KB * 2;      // 2048 .. 8192
+  static constexpr int STAGE = W_BYTES + X_BYTES;    // a multiple of 1024
+  static constexpr int RED_FLOATS = C_ROWS * NB;
+  static constexpr int TMEM_COLS = NB < 32 ? 32 : NB;
+  static constexpr size_t BYTES = 1024 + (size_t)C_STAGES * STAGE + RED_FLOATS * 4 + 128;
+};
+
+template <int NB, bool CLUSTER>
+__global__ void __launch_bounds__(C_THREADS)
+linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap, Tc5Args a) {
+  using L = Tc5Smem<NB>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  float* red = reinterpret_cast<float*>(base + (size_t)C_STAGES * L::STAGE);  // [128][NB]
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(red + L::RED_FLOATS);  // full[S], empty[S], done
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * C_STAGES + 1);
+
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int rank = 0, ranks = 1;
+  if (CLUSTER) {
+    cg::cluster_group cluster = cg::this_cluster();
+    rank = (int)cluster.block_rank();
+    ranks = (int)cluster.num_blocks();
+  }
+  const int tile = blockIdx.x / ranks;
+  const int n0 = tile * C_ROWS;
+  const int k_blocks = (a.K + C_KB - 1) / C_KB;
+  const int first = rank * a.blocks_per_rank;
+  const int count = max(0, min(k_blocks, first + a.blocks_per_rank) - first);
+  const unsigned done_bar = c_smem(bars + 2 * C_STAGES);
+
+  if (tid == 0) {
+    for (int s = 0; s < C_STAGES; ++s) {
+      c_mbar_init(c_smem(bars + s), 1);             // full: the producer's expect_tx arrival
+      c_mbar_init(c_smem(bars + C_STAGES + s), 1);  // empty: one tcgen05.commit per use
+    }
+    c_mbar_init(done_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {  // this warp owns the block's tensor memory
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(c_smem(tmem_slot)),
+                 "r"((unsigned)L::TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      // weights first (they do not depend on earlier kernels), activations after the wait
+      const int primed = min(count, C_STAGES);
+      for (int i = 0; i < primed; ++i) {
+        const unsigned full = c_smem(bars + i);
+        c_mbar_expect_tx(full, L::STAGE);
+        c_tma_load_2d(c_smem(base + (size_t)i * L::STAGE), &wmap, (first + i) * C_KB, n0, full);
+      }
+      pdl_wait();
+      for (int i = 0; i < primed; ++i)
+        c_tma_load_2d(c_smem(base + (size_t)i * L::STAGE) + L::W_BYTES, &xmap, (first + i) * C_KB, 0, c_smem(bars + i));
+      for (int i = primed; i < count; ++i) {
+        const int s = i % C_STAGES;
+        if (!c_mbar_wait(c_smem(bars + C_STAGES + s), ((i / C_STAGES) & 1) ^ 1)) break;
+        const unsigned full = c_smem(bars + s);
+        const unsigned dst = c_smem(base + (size_t)s * L::STAGE);
+        c_mbar_expect_tx(full, L::STAGE);
+        c_tma_load_2d(dst, &wmap, (first + i) * C_KB, n0, full);
+        c_tma_load_2d(dst + L::W_BYTES, &xmap, (first + i) * C_KB, 0, full);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr unsigned idesc = umma_idesc_bf16(C_ROWS, NB);
+      bool ok = true;
+      for (int i = 0; i < count && ok; ++i) {
+        const int s = i % C_STAGES;
+        ok = c_mbar_wait(c_smem(bars + s), (i / C_STAGES) & 1);
+        if (!ok) break;
+        tc_fence_after();
+        const unsigned wt = c_smem(base + (size_t)s * L::STAGE);
+        const unsigned xt = wt + L::W_BYTES;
+#pragma unroll
+        for (int k = 0; k < C_KB / 16; ++k)
+          umma_bf16(tmem_base, umma_desc_sw128(wt + k * 32), umma_desc_sw128(xt + k * 32), idesc,
+                    (i > 0 || k > 0) ? 1u : 0u);
+        umma_commit(c_smem(bars + C_STAGES + s));  // the stage is free once these MMAs have read it
+      }
+      umma_commit(done_bar);  // arrives when every MMA issued above is complete
+    }
+  }
+
+  // epilogue warps: accumulator row (weight row) = TMEM lane, one row per thread
+  if (warp < 4) {
+    const bool ok = c_mbar_wait(done_bar, 0);
+    tc_fence_after();
+    float* row = red + (warp * 32 + lane) * NB;
+    if (ok && count > 0) {
+#pragma unroll
+      for (int c = 0; c < NB; c += 16) {
+        unsigned v[16];
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+              "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+            : "r"(tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)c));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 16; ++j) row[c + j] = __uint_as_float(v[j]);
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < NB; ++c) row[c] = 0.f;  // no k-block for this rank (or a timeout)
+    }
+  }
+  tc_fence_before();
+  pdl_wait();  // no global write before the earlier kernels are complete
+  __syncthreads();
+  if (warp == 5) {  // every read of the accumulator is done
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)L::TMEM_COLS));
+  }
+  if (CLUSTER) {
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    if (rank == 0) {
+      for (int i = tid; i < L::RED_FLOATS; i += C_THREADS) {
+        float s = red[i];
+        for (int r = 1; r < ranks; ++r) s += *cluster.map_shared_rank(red + i, r);
+        red[i] = s;
+      }
+    }
+    cluster.sync();
+    if (rank != 0) return;
+    __syncthreads();
+  }
+
+  // red[row][m] is y[m][n0 + row]
+  if (a.epilogue == CEPI_SWIGLU) {
+    __nv_bfloat16* out = (__nv_bfloat16*)a.out;
+    const int half = a.N >> 1;
+    for (int i = tid; i < (C_ROWS / 2) * NB; i += C_THREADS) {
+      const int m = i / (C_ROWS / 2), j = i % (C_ROWS / 2);
+      const int row = (j >> 3) * 16 + (j & 7);  // gate row; its up row is 8 further
+      if (m < a.M && n0 + row + 8 < a.N) {
+        const float gate = red[row * NB + m], up = red[(row + 8) * NB + m];
+        out[(size_t)m * half + (n0 >> 1) + j] = __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+      }
+    }
+  } else {
+    for (int i = tid; i < C_ROWS * NB; i += C_THREADS) {
+      const int m = i / C_ROWS, row = i % C_ROWS;
+      if (m < a.M && n0 + row < a.N) {
+        float v = red[row * NB + m];
+        if (a.bias) v += a.bias[n0 + row];
+        if (a.epilogue == CEPI_F32)
+          ((float*)a.out)[(size_t)m * a.N + n0 + row] = v;
+        else
+          ((__nv_bfloat16*)a.out)[(size_t)m * a.N + n0 + row] = __float2bfloat16_rn(v);
+      }
+    }
+  }
+  if (*(volatile int*)&mll_tc5_error_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+}
+
+template <int NB>
+int launch_linear_tc5(const CUtensorMap& wmap, const CUtensorMap& xmap, const Tc5Args& a, int tiles, int ranks,
+                      cudaStream_t stream) {
+  const size_t smem = Tc5Smem<NB>::BYTES;
+  cudaError_t err;
+  if (ranks > 1)
+    err = cudaFuncSetAttribute(linear_tc5_kernel<NB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  else
+    err = cudaFuncSetAttribute(linear_tc5_kernel<NB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (err != cudaSuccess) {
+    mll_set_error("linear_tc5: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
+    return (int)err;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(tiles * ranks);
+  config.blockDim = dim3(C_THREADS);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[2];
+  config.attrs = attr;
+  config.numAttrs = 0;
+  if (mll_pdl_enabled) {
+    attr[config.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[config.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+    ++config.numAttrs;
+  }
+  if (ranks > 1) {
+    attr[config.numAttrs].id = cudaLaunchAttributeClusterDimension;
+    attr[config.numAttrs].val.clusterDim.x = ranks;
+    attr[config.numAttrs].val.clusterDim.y = 1;
+    attr[config.numAttrs].val.clusterDim.z = 1;
+    ++config.numAttrs;
+    err = cudaLaunchKernelEx(&config, linear_tc5_kernel<NB, true>, wmap, xmap, a);
+  } else {
+    err = cudaLaunchKernelEx(&config, linear_tc5_kernel<NB, false>, wmap, xmap, a);
+  }
+  if (err != cudaSuccess) {
+    mll_set_error("linear_tc5: launch failed: %s", cudaGetErrorString(err));
+    return (int)err;
+  }
+  return 0;
+}
+
+}  // namespace mll
+
+// Used by mll_take_device_error(): this file's flag, read and cleared.
+extern "C" int mll_tc5_take_error() {
+  int flag = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&flag, mll_tc5_error_flag, sizeof(int)) != cudaSuccess) return -1;
+  if (flag) cudaMemcpyToSymbol(mll_tc5_error_flag, &zero, sizeof(int));
+  return flag;
+}
+
+MLL_API int mll_linear_tc5_supported(int M, int N, int K, int epilogue) {
+  if (M < 1 || M > 64 || N < 1 || K < 8 || K % 8 != 0) return 0;
+  if (epilogue == mll::CEPI_SWIGLU && N % 16 != 0) return 0;
+  return 1;
+}
+
+// Same contract as mll_linear_tma.  ranks: cluster size along K (1, 2, 4 or 8), 0 = choose.
+MLL_API int mll_linear_tc5(const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
+                           int epilogue, int ranks, cudaStream_t stream) {
+  MLL_REQUIRE(mll_linear_tc5_supported(M, N, K, epilogue), "linear_tc5: unsupported sizes M=%d N=%d K=%d", M, N, K);
+  MLL_REQUIRE(epilogue >= 0 && epilogue <= 2, "linear_tc5: unknown epilogue %d", epilogue);
+  MLL_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "linear_tc5: operands must be 16-byte aligned");
+  MLL_REQUIRE(epilogue != mll::CEPI_SWIGLU || bias == nullptr, "linear_tc5: the SwiGLU epilogue takes no bias");
+  const int tiles = (N + mll::C_ROWS - 1) / mll::C_ROWS;
+  const int k_blocks = (K + mll::C_KB - 1) / mll::C_KB;
+  if (ranks <= 0) {
+    // split K while all blocks can be resident together (2-3 per multiprocessor) and keep >= 8 k-blocks each
+    ranks = 1;
+    while (ranks < 8 && tiles * ranks * 2 <= 148 * 2 && k_blocks / (ranks * 2) >= 8) ranks *= 2;
+  }
+  MLL_REQUIRE(ranks == 1 || ranks == 2 || ranks == 4 || ranks == 8, "linear_tc5: cluster size %d", ranks);
+  const int nb = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  CUtensorMap wmap, xmap;
+  if (mll::tensor_map_bf16(w, N, K, mll::C_ROWS, &wmap) != 0) return -1;
+  if (mll::tensor_map_bf16(x, M, K, nb, &xmap) != 0) return -1;
+  mll::Tc5Args a{bias, out, M, N, K, epilogue, (k_blocks + ranks - 1) / ranks};
+  if (nb == 16) return mll::launch_linear_tc5<16>(wmap, xmap, a, tiles, ranks, stream);
+  if (nb == 32) return mll::launch_linear_tc5<32>(wmap, xmap, a, tiles, ranks, stream);
+  return mll::launch_linear_tc5<64>(wmap, xmap, a, tiles, ranks, stream);
+}

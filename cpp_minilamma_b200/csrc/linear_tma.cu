@@ -27,6 +27,7 @@
 #include <unordered_map>
 
 #include "common.cuh"
+#include "tensor_map.h"
 
 namespace cg = cooperative_groups;
 
@@ -286,8 +287,7 @@ struct MapKeyHash {
   }
 };
 
-// A [rows, cols] bfloat16 row-major matrix read in boxes of [box_rows x 64] with the 128-byte swizzle.
-static int tensor_map(const void* ptr, long long rows, long long cols, int box_rows, CUtensorMap* out) {
+int tensor_map_bf16(const void* ptr, long long rows, long long cols, int box_rows, CUtensorMap* out) {
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   static std::mutex lock;
   std::lock_guard<std::mutex> guard(lock);
@@ -367,11 +367,15 @@ int launch_linear_tma(const CUtensorMap& wmap, const CUtensorMap& xmap, const Tm
 
 // Reads and clears the flag that device code raises when a bounded wait runs out
 // (synchronises with the device).
+extern "C" int mll_tc5_take_error();
+
 MLL_API int mll_take_device_error() {
   int flag = 0, zero = 0;
   if (cudaMemcpyFromSymbol(&flag, mll_device_error_flag, sizeof(int)) != cudaSuccess) return -1;
   if (flag) cudaMemcpyToSymbol(mll_device_error_flag, &zero, sizeof(int));
-  return flag;
+  const int other = mll_tc5_take_error();
+  if (other < 0) return -1;
+  return flag | (other ? 2 : 0);
 }
 
 MLL_API int mll_linear_tma_supported(int M, int N, int K, int epilogue) {
@@ -398,8 +402,8 @@ MLL_API int mll_linear_tma(const void* x, const void* w, const float* bias, void
   MLL_REQUIRE(ranks == 1 || ranks == 2 || ranks == 4 || ranks == 8, "linear_tma: cluster size %d", ranks);
   const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
   CUtensorMap wmap, xmap;
-  if (mll::tensor_map(w, N, K, mll::T_ROWS, &wmap) != 0) return -1;
-  if (mll::tensor_map(x, M, K, 8 * nt, &xmap) != 0) return -1;
+  if (mll::tensor_map_bf16(w, N, K, mll::T_ROWS, &wmap) != 0) return -1;
+  if (mll::tensor_map_bf16(x, M, K, 8 * nt, &xmap) != 0) return -1;
   mll::TmaLinearArgs a{bias, out, M, N, K, epilogue, (k_blocks + ranks - 1) / ranks};
   if (nt == 1) return mll::launch_linear_tma<1>(wmap, xmap, a, tiles, ranks, stream);
   if (nt == 2) return mll::launch_linear_tma<2>(wmap, xmap, a, tiles, ranks, stream);

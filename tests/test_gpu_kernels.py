@@ -543,3 +543,41 @@ def test_linear_tma_refuses():
         K.linear_tma(torch.zeros((2, 12), dtype=torch.bfloat16, device=DEV),
                      torch.zeros((16, 12), dtype=torch.bfloat16, device=DEV), None,
                      torch.zeros((2, 16), dtype=torch.bfloat16, device=DEV))
+
+
+@pytest.mark.parametrize("rows", [1, 3, 8, 16, 17, 33, 64])
+@pytest.mark.parametrize("n,k,ranks", [(16, 32, 1), (40, 64, 2), (4104, 4096, 0), (512, 14336, 8), (128, 4096, 4),
+                                        (100, 224, 1), (7, 8, 1), (257, 200, 2), (1000, 1096, 0)])
+def test_linear_tc5(rows, n, k, ranks):
+    # the tcgen05 / TMEM kernel: same contract as the TMA kernel
+    x = rnd((rows, k), torch.bfloat16, 50)
+    w = rnd((n, k), torch.bfloat16, 51, 0.05)
+    bias = rnd((n,), torch.float32, 52)
+    ref = as64(x) @ as64(w).T
+    assert K.linear_tc5_supported(rows, n, k)
+    for epilogue, dtype, b in ((K.EPI_BF16, torch.bfloat16, None), (K.EPI_F32, torch.float32, bias)):
+        out = torch.full((rows, n), float("nan"), dtype=dtype, device=DEV)
+        K.linear_tc5(x.to(DEV), w.to(DEV), None if b is None else b.to(DEV), out, epilogue, ranks)
+        want = ref if b is None else ref + as64(b)
+        if dtype == torch.float32:
+            np.testing.assert_allclose(as64(out), want, rtol=2e-5, atol=2e-5 * np.abs(want).max())
+        else:
+            np.testing.assert_allclose(as64(out), want, rtol=8e-3, atol=8e-3 * np.abs(want).max())
+        again = torch.empty_like(out)
+        K.linear_tc5(x.to(DEV), w.to(DEV), None if b is None else b.to(DEV), again, epilogue, ranks)
+        assert torch.equal(out, again)
+    assert K.take_device_error() == 0
+
+
+@pytest.mark.parametrize("rows", [1, 8, 13, 64])
+@pytest.mark.parametrize("inter,k,ranks", [(176, 64, 1), (1000, 4096, 0), (64, 14336, 8), (40, 72, 1)])
+def test_linear_tc5_swiglu(rows, inter, k, ranks):
+    gate = rnd((inter, k), torch.bfloat16, 53, 0.05)
+    up = rnd((inter, k), torch.bfloat16, 54, 0.05)
+    x = rnd((rows, k), torch.bfloat16, 55)
+    fused = torch.stack([gate.view(inter // 8, 8, k), up.view(inter // 8, 8, k)], dim=1).reshape(2 * inter, k)
+    out = torch.full((rows, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    K.linear_tc5(x.to(DEV), fused.contiguous().to(DEV), None, out, K.EPI_SWIGLU, ranks)
+    want = pl.swiglu(as64(x) @ as64(gate).T, as64(x) @ as64(up).T)
+    np.testing.assert_allclose(as64(out), want, rtol=8e-3, atol=8e-3 * np.abs(want).max())
+    assert K.take_device_error() == 0
