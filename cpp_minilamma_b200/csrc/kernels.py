@@ -208,34 +208,46 @@ def take_device_error() -> int:
     return int(lib().mll_take_device_error())
 
 
-def small_linear_kind(rows: int, out_features: int, in_features: int, epilogue: int = EPI_BF16) -> str:
-    """Which of this library's weight-streaming kernels takes the problem: "tma", "direct" or "".
+TC5_MAX_ROWS = 64     # rows up to which tall matrices go to the tcgen05 kernel
+DIRECT_MAX_ROWS = 8   # rows up to which the other matrices go to the direct kernel
+TALL = 16384          # output features from which a matrix counts as tall
 
-    Measured on the 8B shapes (CUDA-graph timing, B200): the TMA pipeline wins on tall
-    matrices (gate/up, lm_head), where its deep queue of loads counts; the direct kernel
-    wins on the 4096-row projections, where a launch is short and its finer split over the
-    machine counts.  Above 8 rows both fall behind the library GEMM, except that the fused
-    SwiGLU epilogue still pays up to 16 rows."""
-    limit = 16 if epilogue == EPI_SWIGLU else 8
-    if rows > limit or SMALL_LINEAR == "none":
+
+def small_linear_kind(rows: int, out_features: int, in_features: int, epilogue: int = EPI_BF16) -> str:
+    """Which of this library's weight-streaming kernels takes the problem: "tc5", "tma", "direct" or "".
+
+    Measured on the 8B shapes (CUDA-graph timing, B200): the TMA-fed kernels (tcgen05 or
+    mma.sync consumers) win on tall matrices (gate/up, lm_head), where a deep queue of loads
+    counts; the direct kernel wins on the 4096-row projections, where a launch is short and
+    its finer split over the machine counts; beyond that the library GEMM is used."""
+    if SMALL_LINEAR == "none":
         return ""
-    tma = SMALL_LINEAR in ("tma", "auto") and linear_tma_supported(rows, out_features, in_features, epilogue)
-    direct = SMALL_LINEAR in ("direct", "auto") and linear_small_supported(rows, out_features, in_features, epilogue)
-    if tma and direct and SMALL_LINEAR == "auto":
-        return "tma" if out_features >= 16384 else "direct"
-    return "tma" if tma else ("direct" if direct else "")
+    if SMALL_LINEAR != "auto":  # a forced kind (tests, experiments)
+        supported = {"tc5": linear_tc5_supported, "tma": linear_tma_supported, "direct": linear_small_supported}
+        return SMALL_LINEAR if rows <= 64 and supported[SMALL_LINEAR](rows, out_features, in_features, epilogue) else ""
+    if out_features >= TALL and rows <= TC5_MAX_ROWS and linear_tc5_supported(rows, out_features, in_features,
+                                                                               epilogue):
+        return "tc5"
+    if rows <= DIRECT_MAX_ROWS:
+        if linear_small_supported(rows, out_features, in_features, epilogue):
+            return "direct"
+        if linear_tc5_supported(rows, out_features, in_features, epilogue):
+            return "tc5"
+    return ""
 
 
 def small_linear(x, w, bias, out, epilogue: int = EPI_BF16) -> bool:
     kind = small_linear_kind(x.shape[0], w.shape[0], w.shape[1], epilogue)
-    if kind == "tma":
+    if kind == "tc5":
+        linear_tc5(x, w, bias, out, epilogue)
+    elif kind == "tma":
         linear_tma(x, w, bias, out, epilogue, 1 if x.shape[0] > 8 else 0)
     elif kind == "direct":
         linear_small(x, w, bias, out, epilogue)
     return bool(kind)
 
 
-SMALL_LINEAR = "auto"  # "tma", "direct", "auto" (tma where it applies), or "none"
+SMALL_LINEAR = "auto"  # "auto", a forced kind ("tc5", "tma", "direct"), or "none" (library GEMM only)
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int) -> None:

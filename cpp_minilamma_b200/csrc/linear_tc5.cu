@@ -112,7 +112,9 @@ struct Tc5Smem {
   static constexpr int STAGE = W_BYTES + X_BYTES;    // a multiple of 1024
   static constexpr int RED_FLOATS = C_ROWS * NB;
   static constexpr int TMEM_COLS = NB < 32 ? 32 : NB;
-  static constexpr size_t BYTES = 1024 + (size_t)C_STAGES * STAGE + RED_FLOATS * 4 + 128;
+  // the float32 tile that the epilogue works on reuses the ring once the last MMA is done
+  static constexpr int RING = C_STAGES * STAGE > RED_FLOATS * 4 ? C_STAGES * STAGE : RED_FLOATS * 4;
+  static constexpr size_t BYTES = 1024 + (size_t)RING + 128;
 };
 
 template <int NB, bool CLUSTER>
@@ -121,8 +123,8 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
   using L = Tc5Smem<NB>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  float* red = reinterpret_cast<float*>(base + (size_t)C_STAGES * L::STAGE);  // [128][NB]
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(red + L::RED_FLOATS);  // full[S], empty[S], done
+  float* red = reinterpret_cast<float*>(base);  // [128][NB], over the ring: written only after the last MMA
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(base + L::RING);  // full[S], empty[S], done
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * C_STAGES + 1);
 
   pdl_launch_dependents();
@@ -346,9 +348,11 @@ MLL_API int mll_linear_tc5(const void* x, const void* w, const float* bias, void
   const int tiles = (N + mll::C_ROWS - 1) / mll::C_ROWS;
   const int k_blocks = (K + mll::C_KB - 1) / mll::C_KB;
   if (ranks <= 0) {
-    // split K while all blocks can be resident together (2-3 per multiprocessor) and keep >= 8 k-blocks each
+    // split K while all blocks can be resident together (3 per multiprocessor up to 16 rows, 2 above)
+    // and each keeps >= 8 k-blocks
+    const int resident = 148 * (M <= 16 ? 3 : 2);
     ranks = 1;
-    while (ranks < 8 && tiles * ranks * 2 <= 148 * 2 && k_blocks / (ranks * 2) >= 8) ranks *= 2;
+    while (ranks < 8 && tiles * ranks * 2 <= resident && k_blocks / (ranks * 2) >= 8) ranks *= 2;
   }
   MLL_REQUIRE(ranks == 1 || ranks == 2 || ranks == 4 || ranks == 8, "linear_tc5: cluster size %d", ranks);
   const int nb = M <= 16 ? 16 : (M <= 32 ? 32 : 64);

@@ -122,7 +122,7 @@ class Engine:
         self._meta_host: Optional[torch.Tensor] = None
         self._meta_dev: Optional[torch.Tensor] = None
         self._meta_copied = None
-        self.small_rows = 16  # rows up to which linears use this package's weight-streaming kernel
+        self.small_rows = 64  # rows up to which linears may use this package's weight-streaming kernels
         self.launch_count = 0  # kernels of this package launched (estimate kept by the parts' callers)
 
     # ---- helpers shared by everything that generates with this engine -------------------- #
