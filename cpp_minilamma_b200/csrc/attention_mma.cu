@@ -27,6 +27,7 @@ struct DecodeMmaArgs {
   __nv_bfloat16* out;            // [B, Hq * d]
   int n_heads, n_kv_heads, max_blocks, n_splits, window;
   float scale;
+  Prefetch pf;
 };
 
 __device__ __forceinline__ void cp_async16_zfill(void* smem, const void* gmem, bool valid) {
@@ -64,6 +65,7 @@ template <int D, int STAGES>
 __global__ void __launch_bounds__(128)
 attn_decode_mma_kernel(DecodeMmaArgs a) {
   mll::pdl_begin();
+  l2_prefetch_by_grid(a.pf);
   using L = DecodeMmaSmem<D, STAGES>;
   constexpr int KSTEPS = D / 16;       // k-steps of the score product
   constexpr int NT_OUT = D / 32;       // value n-tiles (8 columns) per warp
@@ -319,7 +321,7 @@ template <int D>
 struct PrefillMmaSmem {
   static constexpr int STRIDE = D + 8;
   static constexpr int TILE = 64 * STRIDE;  // elements of the Q tile or of one K or V page
-  static constexpr size_t BYTES = (size_t)(1 + 2 * 2) * TILE * 2;  // Q + two stages of (K, V)
+  static constexpr size_t BYTES = (size_t)(2 * 2) * TILE * 2;  // two stages of (K, V); Q passes through stage 1
 };
 
 // Flash-style attention for tiles of 64 query tokens: grid (n_tiles, Hq), four warps, each
@@ -327,15 +329,15 @@ struct PrefillMmaSmem {
 // registers (float32, base 2), P re-used from the accumulator registers as the A operand of
 // O += P V.  Pages arrive through a two-stage cp.async ring shared by the four warps.
 template <int D>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 3)
 attn_prefill_mma_kernel(PrefillMmaArgs a) {
   mll::pdl_begin();
   using L = PrefillMmaSmem<D>;
   constexpr int KSTEPS = D / 16;
   constexpr int NT_OUT = D / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-  __nv_bfloat16* kv_s = q_s + L::TILE;  // [2 stages][K, V][64][STRIDE]
+  __nv_bfloat16* kv_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [2 stages][K, V][64][STRIDE]
+  __nv_bfloat16* q_s = kv_s + 2 * L::TILE;  // the query tile lands in stage 1 and moves to registers before page 1
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -385,14 +387,15 @@ attn_prefill_mma_kernel(PrefillMmaArgs a) {
     const int stage = (p - p_first) & 1;
     cp_async_wait<0>();
     __syncthreads();  // page p (and, the first time, Q) landed; every warp is done with page p - 1
-    if (p < p_last) load_page(p + 1, stage ^ 1);
-    cp_async_commit();
     if (p == p_first) {
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks)
         ldmatrix_x4(qf[ks], q_s + (warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3)) * L::STRIDE + ks * 16 +
                                 ((lane >> 4) << 3));
+      __syncthreads();  // every warp holds its query fragments: stage 1 may be overwritten
     }
+    if (p < p_last) load_page(p + 1, stage ^ 1);
+    cp_async_commit();
     const __nv_bfloat16* kt = kv_s + (size_t)stage * 2 * L::TILE;
     const __nv_bfloat16* vt = kt + L::TILE;
 
@@ -524,7 +527,8 @@ MLL_API int mll_attn_decode_mma_supported(int dtype, int head_dim) {
 MLL_API int mll_attn_decode_mma(const void* q, const void* k_cache, const void* v_cache, const int* seq_slot,
                                 const int* seq_ctx, const int* block_table, float* scratch, void* out, int n_seqs,
                                 int n_heads, int n_kv_heads, int head_dim, int max_blocks, int n_splits, int window,
-                                float scale, cudaStream_t stream) {
+                                float scale, const void* prefetch_ptr, long long prefetch_bytes,
+                                cudaStream_t stream) {
   MLL_REQUIRE(mll_attn_decode_mma_supported(MLL_BF16, head_dim), "attention decode (mma): head_dim %d", head_dim);
   MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention decode (mma): bad head counts");
   MLL_REQUIRE(n_seqs >= 0 && n_splits >= 1 && n_splits <= 65535, "attention decode (mma): bad batch or split count");
@@ -533,7 +537,8 @@ MLL_API int mll_attn_decode_mma(const void* q, const void* k_cache, const void* 
   mll::DecodeMmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
                        seq_slot, seq_ctx, block_table, scratch,
                        scratch ? scratch + (size_t)n_seqs * n_heads * n_splits * head_dim : nullptr,
-                       (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, n_splits, window, scale};
+                       (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, n_splits, window, scale,
+                       mll::Prefetch{prefetch_ptr, prefetch_ptr ? (unsigned long long)prefetch_bytes : 0ull}};
   if (head_dim == 64) return mll::launch_decode_mma<64, 3>(a, n_seqs, stream);
   if (head_dim == 128) return mll::launch_decode_mma<128, 3>(a, n_seqs, stream);
   return mll::launch_decode_mma<256, 2>(a, n_seqs, stream);

@@ -80,6 +80,32 @@ __device__ __forceinline__ void pdl_begin() {
   pdl_wait();
 }
 
+// A range of global memory (weights that a later kernel of the step will stream) that the
+// blocks of a latency-bound kernel ask the L2 cache to fetch while they do their own work.
+// Decode steps alternate kernels that wait on latencies with kernels that wait on HBM; the
+// hints keep HBM busy during the former.  ptr is 16-byte aligned, bytes a multiple of 16.
+struct Prefetch {
+  const void* ptr;
+  unsigned long long bytes;
+};
+
+// Called by one thread per block: block `block` of `blocks` requests every blocks-th 16 KB chunk.
+__device__ __forceinline__ void l2_prefetch_chunks(const Prefetch& pf, unsigned block, unsigned blocks) {
+  constexpr unsigned long long kChunk = 16384;
+  const unsigned long long chunks = (pf.bytes + kChunk - 1) / kChunk;
+  for (unsigned long long c = block; c < chunks; c += blocks) {
+    const unsigned long long off = c * kChunk;
+    const unsigned size = (unsigned)(pf.bytes - off < kChunk ? pf.bytes - off : kChunk);
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"((const char*)pf.ptr + off), "r"(size) : "memory");
+  }
+}
+__device__ __forceinline__ void l2_prefetch_by_grid(const Prefetch& pf) {
+  if (pf.bytes == 0 || threadIdx.x != 0 || threadIdx.y != 0 || threadIdx.z != 0) return;
+  const unsigned blocks = gridDim.x * gridDim.y * gridDim.z;
+  const unsigned block = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  l2_prefetch_chunks(pf, block, blocks);
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -28,6 +28,7 @@ struct LinearArgs {
   const float* bias;       // optional [N]
   void* out;               // [M, N] (EPI_SWIGLU: [M, N / 2])
   int M, N, K, epilogue, chunks_per_warp;
+  Prefetch pf;
 };
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
@@ -58,6 +59,7 @@ __global__ void __launch_bounds__(LS_WARPS * 32)
 linear_small_kernel(LinearArgs a) {
   __shared__ float red[LS_WARPS][16][8 * NT];
   pdl_launch_dependents();
+  l2_prefetch_by_grid(a.pf);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   int rank = 0, ranks = 1;
@@ -231,7 +233,8 @@ MLL_API int mll_linear_small_supported(int M, int N, int K, int epilogue) {
 // with gate and up rows of w interleaved in blocks of 8 (2).  ranks: cluster size along K
 // (1, 2, 4 or 8), 0 = choose.
 MLL_API int mll_linear_small(const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
-                             int epilogue, int ranks, cudaStream_t stream) {
+                             int epilogue, int ranks, const void* prefetch_ptr, long long prefetch_bytes,
+                             cudaStream_t stream) {
   MLL_REQUIRE(mll_linear_small_supported(M, N, K, epilogue), "linear_small: unsupported sizes M=%d N=%d K=%d", M, N, K);
   MLL_REQUIRE(epilogue >= 0 && epilogue <= 2, "linear_small: unknown epilogue %d", epilogue);
   MLL_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "linear_small: operands must be 16-byte aligned");
@@ -245,7 +248,8 @@ MLL_API int mll_linear_small(const void* x, const void* w, const float* bias, vo
     while (ranks < 8 && tiles * ranks * 2 <= 148 * 10 && chunks / (mll::LS_WARPS * ranks * 2) >= 4) ranks *= 2;
   }
   MLL_REQUIRE(ranks == 1 || ranks == 2 || ranks == 4 || ranks == 8, "linear_small: cluster size %d", ranks);
-  mll::LinearArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, out, M, N, K, epilogue, 0};
+  mll::LinearArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, out, M, N, K, epilogue, 0,
+                    mll::Prefetch{prefetch_ptr, prefetch_ptr ? (unsigned long long)prefetch_bytes : 0ull}};
   const int splits = mll::LS_WARPS * ranks;
   a.chunks_per_warp = (chunks + splits - 1) / splits;
   if (M <= 8) {

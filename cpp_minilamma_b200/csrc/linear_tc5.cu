@@ -37,7 +37,6 @@ namespace mll {
 enum : int { CEPI_BF16 = 0, CEPI_F32 = 1, CEPI_SWIGLU = 2 };
 constexpr int C_ROWS = 128;     // weight rows per block (the MMA's M)
 constexpr int C_KB = 64;        // k elements per stage: one 128-byte swizzle span
-constexpr int C_STAGES = 4;
 constexpr int C_THREADS = 192;  // 4 epilogue warps, 1 producer warp, 1 MMA warp
 constexpr unsigned C_SPIN_LIMIT = 4u << 20;
 
@@ -110,10 +109,11 @@ struct Tc5Smem {
   static constexpr int W_BYTES = C_ROWS * C_KB * 2;  // 16384
   static constexpr int X_BYTES = NB * C_KB * 2;      // 2048 .. 8192
   static constexpr int STAGE = W_BYTES + X_BYTES;    // a multiple of 1024
+  static constexpr int STAGES = NB <= 16 ? 6 : (NB <= 32 ? 5 : 4);  // about 100 KB of ring: two blocks per multiprocessor
   static constexpr int RED_FLOATS = C_ROWS * NB;
   static constexpr int TMEM_COLS = NB < 32 ? 32 : NB;
   // the float32 tile that the epilogue works on reuses the ring once the last MMA is done
-  static constexpr int RING = C_STAGES * STAGE > RED_FLOATS * 4 ? C_STAGES * STAGE : RED_FLOATS * 4;
+  static constexpr int RING = STAGES * STAGE > RED_FLOATS * 4 ? STAGES * STAGE : RED_FLOATS * 4;
   static constexpr size_t BYTES = 1024 + (size_t)RING + 128;
 };
 
@@ -125,7 +125,7 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   float* red = reinterpret_cast<float*>(base);  // [128][NB], over the ring: written only after the last MMA
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(base + L::RING);  // full[S], empty[S], done
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * C_STAGES + 1);
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * L::STAGES + 1);
 
   pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -140,12 +140,12 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
   const int k_blocks = (a.K + C_KB - 1) / C_KB;
   const int first = rank * a.blocks_per_rank;
   const int count = max(0, min(k_blocks, first + a.blocks_per_rank) - first);
-  const unsigned done_bar = c_smem(bars + 2 * C_STAGES);
+  const unsigned done_bar = c_smem(bars + 2 * L::STAGES);
 
   if (tid == 0) {
-    for (int s = 0; s < C_STAGES; ++s) {
+    for (int s = 0; s < L::STAGES; ++s) {
       c_mbar_init(c_smem(bars + s), 1);             // full: the producer's expect_tx arrival
-      c_mbar_init(c_smem(bars + C_STAGES + s), 1);  // empty: one tcgen05.commit per use
+      c_mbar_init(c_smem(bars + L::STAGES + s), 1);  // empty: one tcgen05.commit per use
     }
     c_mbar_init(done_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -163,7 +163,7 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
   if (warp == 4) {
     if (lane == 0) {
       // weights first (they do not depend on earlier kernels), activations after the wait
-      const int primed = min(count, C_STAGES);
+      const int primed = min(count, L::STAGES);
       for (int i = 0; i < primed; ++i) {
         const unsigned full = c_smem(bars + i);
         c_mbar_expect_tx(full, L::STAGE);
@@ -173,8 +173,8 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
       for (int i = 0; i < primed; ++i)
         c_tma_load_2d(c_smem(base + (size_t)i * L::STAGE) + L::W_BYTES, &xmap, (first + i) * C_KB, 0, c_smem(bars + i));
       for (int i = primed; i < count; ++i) {
-        const int s = i % C_STAGES;
-        if (!c_mbar_wait(c_smem(bars + C_STAGES + s), ((i / C_STAGES) & 1) ^ 1)) break;
+        const int s = i % L::STAGES;
+        if (!c_mbar_wait(c_smem(bars + L::STAGES + s), ((i / L::STAGES) & 1) ^ 1)) break;
         const unsigned full = c_smem(bars + s);
         const unsigned dst = c_smem(base + (size_t)s * L::STAGE);
         c_mbar_expect_tx(full, L::STAGE);
@@ -187,8 +187,8 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
       constexpr unsigned idesc = umma_idesc_bf16(C_ROWS, NB);
       bool ok = true;
       for (int i = 0; i < count && ok; ++i) {
-        const int s = i % C_STAGES;
-        ok = c_mbar_wait(c_smem(bars + s), (i / C_STAGES) & 1);
+        const int s = i % L::STAGES;
+        ok = c_mbar_wait(c_smem(bars + s), (i / L::STAGES) & 1);
         if (!ok) break;
         tc_fence_after();
         const unsigned wt = c_smem(base + (size_t)s * L::STAGE);
@@ -197,7 +197,7 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
         for (int k = 0; k < C_KB / 16; ++k)
           umma_bf16(tmem_base, umma_desc_sw128(wt + k * 32), umma_desc_sw128(xt + k * 32), idesc,
                     (i > 0 || k > 0) ? 1u : 0u);
-        umma_commit(c_smem(bars + C_STAGES + s));  // the stage is free once these MMAs have read it
+        umma_commit(c_smem(bars + L::STAGES + s));  // the stage is free once these MMAs have read it
       }
       umma_commit(done_bar);  // arrives when every MMA issued above is complete
     }
@@ -348,9 +348,9 @@ MLL_API int mll_linear_tc5(const void* x, const void* w, const float* bias, void
   const int tiles = (N + mll::C_ROWS - 1) / mll::C_ROWS;
   const int k_blocks = (K + mll::C_KB - 1) / mll::C_KB;
   if (ranks <= 0) {
-    // split K while all blocks can be resident together (3 per multiprocessor up to 16 rows, 2 above)
+    // split K while all blocks can be resident together (2 per multiprocessor)
     // and each keeps >= 8 k-blocks
-    const int resident = 148 * (M <= 16 ? 3 : 2);
+    const int resident = 148 * 2;
     ranks = 1;
     while (ranks < 8 && tiles * ranks * 2 <= resident && k_blocks / (ranks * 2) >= 8) ranks *= 2;
   }

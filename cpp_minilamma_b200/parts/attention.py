@@ -89,6 +89,9 @@ class Attention(Mixer):
     def parameter_bytes(self) -> int:
         return self.qkv.parameter_bytes() + self.o.parameter_bytes()
 
+    def first_weight(self):
+        return self.qkv.weight
+
     def cache_need(self) -> CacheNeed:
         return CacheNeed(kv=KVNeed(self.n_kv_heads, self.head_dim, self.window))
 
@@ -100,7 +103,9 @@ class Attention(Mixer):
         blocks = max(1, n_seqs * self.n_kv_heads * chunks)
         span = max_ctx if self.window <= 0 else min(max_ctx, self.window + K.PAGE)
         pages = max(1, -(-span // K.PAGE))
-        return max(1, min(-(-_TARGET_BLOCKS // blocks), pages, 64))
+        # as many splits as keep every block resident at once (two per multiprocessor): a second,
+        # nearly empty wave costs more than slightly coarser splits
+        return max(1, min(_TARGET_BLOCKS // blocks, pages, 64))
 
     def forward(self, step, h: torch.Tensor, cache) -> torch.Tensor:
         T = h.shape[0]
@@ -108,12 +113,16 @@ class Attention(Mixer):
         act = self.ctx.act_dtype
         if cache.k is None:
             raise RuntimeError("attention: the cache view has no key/value storage")
-        qkv = self.qkv.forward(step, h, "qkv")
+        # decode steps: while the latency-bound kernels run, the L2 fetches what the next products stream
+        hints = step.prefetch
+        after = step.next_weight if hints else None
+        qkv = self.qkv.forward(step, h, "qkv", prefetch=K.hint(self.o.weight, 0, 40) if hints else None)
         q = step.ws.buffer("q", (T, Hq * d), act)
         cos, sin = self.position.tables()
         K.rope_cache_write(qkv, self.bias, cos, sin, step.tok_pos, step.tok_seq, step.seq_slot,
                            cache.block_table, q, cache.k, cache.v, Hq, Hk, d,
-                           self.position.interleaved, write_kv=not self.reads_cache_only)
+                           self.position.interleaved, write_kv=not self.reads_cache_only,
+                           prefetch=K.hint(after, 0, 32))
         out = step.ws.buffer("attn", (T, Hq * d), act)
         if step.all_decode:
             splits = step.decode_splits if step.decode_splits else self.decode_splits(step.n_seqs, step.max_ctx)
@@ -122,7 +131,8 @@ class Attention(Mixer):
                 scratch = step.ws.buffer(
                     "attn.scratch", (K.attention_decode_scratch_floats(step.n_seqs, Hq, d, splits),), torch.float32)
             K.attention_decode(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, cache.block_table, scratch, out,
-                               step.n_seqs, Hq, Hk, d, splits, self.window, self.scale)
+                               step.n_seqs, Hq, Hk, d, splits, self.window, self.scale,
+                               prefetch=K.hint(after, 32, 32))
         else:
             K.attention_prefill(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
                                 step.tile_seq, step.tile_row0, cache.block_table, out, step.n_tiles,
