@@ -141,7 +141,23 @@ __global__ void add_bias_kernel(T* __restrict__ x, const float* __restrict__ bia
   for (; idx < total; idx += stride) x[idx] = from_float<T>(to_float(x[idx]) + bias[idx % width]);
 }
 
+// Only asks the L2 cache to fetch a range (see Prefetch in common.cuh).
+__global__ void l2_prefetch_kernel(Prefetch pf) {
+  mll::pdl_begin();
+  l2_prefetch_by_grid(pf);
+}
+
 }  // namespace mll
+
+// Asks the L2 cache to fetch `bytes` from `ptr` (16-byte aligned, multiple of 16) with `blocks` blocks.
+MLL_API int mll_l2_prefetch(const void* ptr, long long bytes, int blocks, cudaStream_t stream) {
+  MLL_REQUIRE(ptr != nullptr && bytes >= 0 && blocks > 0, "l2_prefetch: bad arguments");
+  MLL_REQUIRE(((uintptr_t)ptr % 16 == 0) && bytes % 16 == 0, "l2_prefetch: range must be 16-byte aligned");
+  if (bytes == 0) return 0;
+  MLL_LAUNCH((mll::l2_prefetch_kernel), blocks, 32, 0, stream, mll::Prefetch{ptr, (unsigned long long)bytes});
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
 
 MLL_API int mll_add_bias(void* x, const float* bias, int dtype, int n_rows, int width, cudaStream_t stream) {
   MLL_REQUIRE(n_rows >= 0 && width > 0, "add_bias: bad sizes rows=%d width=%d", n_rows, width);
