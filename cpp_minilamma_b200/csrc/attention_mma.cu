@@ -64,7 +64,7 @@ struct DecodeMmaSmem {
 template <int D, int STAGES>
 __global__ void __launch_bounds__(128)
 attn_decode_mma_kernel(DecodeMmaArgs a) {
-  mll::pdl_begin();
+  mll::pdl_begin_long();
   l2_prefetch_by_grid(a.pf);
   using L = DecodeMmaSmem<D, STAGES>;
   constexpr int KSTEPS = D / 16;       // k-steps of the score product
@@ -249,6 +249,7 @@ attn_decode_mma_kernel(DecodeMmaArgs a) {
     }
   }
   cp_async_wait<0>();
+  pdl_launch_dependents();
 
   // rows g and g + 8 of the tile are heads h0 + g and h0 + g + 8; this thread holds columns
   // warp * D/4 + n * 8 + 2 t + {0, 1}

@@ -75,10 +75,14 @@ inline cudaError_t launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 
 // no-ops for a kernel that was launched without the attribute.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Start of a short kernel: nothing to overlap, so it lets the next kernel launch right away
+// and waits for its own inputs.  Longer kernels call pdl_launch_dependents() after their main
+// loop instead, so that the next kernel's prologue overlaps their tail and not their body.
 __device__ __forceinline__ void pdl_begin() {
   pdl_launch_dependents();
   pdl_wait();
 }
+__device__ __forceinline__ void pdl_begin_long() { pdl_wait(); }
 
 // A range of global memory (weights that a later kernel of the step will stream) that the
 // blocks of a latency-bound kernel ask the L2 cache to fetch while they do their own work.

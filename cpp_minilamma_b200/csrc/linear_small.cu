@@ -51,14 +51,13 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-constexpr int LS_WARPS = 4;
 
 // grid: (row tiles * cluster size); block: 128 threads.  NT: n-tiles of 8 batch rows.
-template <int NT, bool CLUSTER, int LS_UNROLL>  // LS_UNROLL: 32-element chunks in flight per warp
+// LS_UNROLL: 32-element chunks in flight per warp; LS_WARPS: warps per block (K is split over them)
+template <int NT, bool CLUSTER, int LS_UNROLL, int LS_WARPS>
 __global__ void __launch_bounds__(LS_WARPS * 32)
 linear_small_kernel(LinearArgs a) {
   __shared__ float red[LS_WARPS][16][8 * NT];
-  pdl_launch_dependents();
   l2_prefetch_by_grid(a.pf);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -124,6 +123,7 @@ linear_small_kernel(LinearArgs a) {
     }
   }
 
+  pdl_launch_dependents();  // the stream of weights is over: the next kernel may set itself up
   // this warp's 16 x (8 NT) partial tile: rows g and g + 8, batch columns n * 8 + 2 t + {0, 1}
 #pragma unroll
   for (int n = 0; n < NT; ++n) {
@@ -183,7 +183,7 @@ linear_small_kernel(LinearArgs a) {
   }
 }
 
-template <int NT, int U>
+template <int NT, int U, int LS_WARPS>
 int launch_linear_small(const LinearArgs& a, int tiles, int ranks, cudaStream_t stream) {
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(tiles * ranks);
@@ -205,9 +205,9 @@ int launch_linear_small(const LinearArgs& a, int tiles, int ranks, cudaStream_t 
     attr[config.numAttrs].val.clusterDim.y = 1;
     attr[config.numAttrs].val.clusterDim.z = 1;
     ++config.numAttrs;
-    err = cudaLaunchKernelEx(&config, linear_small_kernel<NT, true, U>, a);
+    err = cudaLaunchKernelEx(&config, linear_small_kernel<NT, true, U, LS_WARPS>, a);
   } else {
-    err = cudaLaunchKernelEx(&config, linear_small_kernel<NT, false, U>, a);
+    err = cudaLaunchKernelEx(&config, linear_small_kernel<NT, false, U, LS_WARPS>, a);
   }
   if (err != cudaSuccess) {
     mll_set_error("linear_small: launch failed: %s", cudaGetErrorString(err));
@@ -220,6 +220,8 @@ int launch_linear_small(const LinearArgs& a, int tiles, int ranks, cudaStream_t 
 
 // tuning knob for experiments: chunks in flight per warp for M <= 8 (2, 4 or 8)
 extern "C" __attribute__((visibility("default"))) int mll_linear_small_unroll = 4;
+// tuning knob for experiments: warps per block for M <= 8 (4 or 8)
+extern "C" __attribute__((visibility("default"))) int mll_linear_small_warps = 4;
 
 // Whether mll_linear_small takes this problem (the caller uses the library GEMM otherwise).
 MLL_API int mll_linear_small_supported(int M, int N, int K, int epilogue) {
@@ -241,23 +243,25 @@ MLL_API int mll_linear_small(const void* x, const void* w, const float* bias, vo
   MLL_REQUIRE(epilogue != mll::EPI_SWIGLU || bias == nullptr, "linear_small: the SwiGLU epilogue takes no bias");
   const int tiles = (N + 15) / 16;
   const int chunks = K / 32;
+  const int warps = mll_linear_small_warps == 8 && M <= 8 ? 8 : 4;
   if (ranks <= 0) {
-    // split K while every block still fits on the machine at once (10 blocks per multiprocessor)
-    // and a warp keeps at least 4 chunks
+    // split K while every block still fits on the machine at once and a warp keeps at least 4 chunks
+    const int resident = 148 * (warps == 8 ? 5 : 10);
     ranks = 1;
-    while (ranks < 8 && tiles * ranks * 2 <= 148 * 10 && chunks / (mll::LS_WARPS * ranks * 2) >= 4) ranks *= 2;
+    while (ranks < 8 && tiles * ranks * 2 <= resident && chunks / (warps * ranks * 2) >= 4) ranks *= 2;
   }
   MLL_REQUIRE(ranks == 1 || ranks == 2 || ranks == 4 || ranks == 8, "linear_small: cluster size %d", ranks);
   mll::LinearArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, out, M, N, K, epilogue, 0,
                     mll::Prefetch{prefetch_ptr, prefetch_ptr ? (unsigned long long)prefetch_bytes : 0ull}};
-  const int splits = mll::LS_WARPS * ranks;
+  const int splits = warps * ranks;
   a.chunks_per_warp = (chunks + splits - 1) / splits;
   if (M <= 8) {
-    if (mll_linear_small_unroll == 2) return mll::launch_linear_small<1, 2>(a, tiles, ranks, stream);
-    if (mll_linear_small_unroll == 8) return mll::launch_linear_small<1, 8>(a, tiles, ranks, stream);
-    return mll::launch_linear_small<1, 4>(a, tiles, ranks, stream);
+    if (warps == 8) return mll::launch_linear_small<1, 4, 8>(a, tiles, ranks, stream);
+    if (mll_linear_small_unroll == 2) return mll::launch_linear_small<1, 2, 4>(a, tiles, ranks, stream);
+    if (mll_linear_small_unroll == 8) return mll::launch_linear_small<1, 8, 4>(a, tiles, ranks, stream);
+    return mll::launch_linear_small<1, 4, 4>(a, tiles, ranks, stream);
   }
-  if (M <= 16) return mll::launch_linear_small<2, 4>(a, tiles, ranks, stream);
-  if (M <= 32) return mll::launch_linear_small<4, 2>(a, tiles, ranks, stream);
-  return mll::launch_linear_small<8, 2>(a, tiles, ranks, stream);
+  if (M <= 16) return mll::launch_linear_small<2, 4, 4>(a, tiles, ranks, stream);
+  if (M <= 32) return mll::launch_linear_small<4, 2, 4>(a, tiles, ranks, stream);
+  return mll::launch_linear_small<8, 2, 4>(a, tiles, ranks, stream);
 }

@@ -127,7 +127,6 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(base + L::RING);  // full[S], empty[S], done
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * L::STAGES + 1);
 
-  pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int rank = 0, ranks = 1;
   if (CLUSTER) {
@@ -200,6 +199,7 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
         umma_commit(c_smem(bars + L::STAGES + s));  // the stage is free once these MMAs have read it
       }
       umma_commit(done_bar);  // arrives when every MMA issued above is complete
+      pdl_launch_dependents();  // the stream of weights is over: the next kernel may set itself up
     }
   }
 

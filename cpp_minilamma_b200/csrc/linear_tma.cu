@@ -113,7 +113,6 @@ linear_tma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
   float* red = reinterpret_cast<float*>(base + (size_t)T_STAGES * L::STAGE);          // [64][8 NT]
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(red + L::RED_FLOATS);  // full[S], empty[S]
 
-  pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int rank = 0, ranks = 1;
   if (CLUSTER) {
@@ -195,6 +194,7 @@ linear_tma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(bars + T_STAGES + s));
     }
+    if (warp == 0 && lane == 0) pdl_launch_dependents();  // the stream of weights is over
     // this warp's 16 x (8 NT) partial tile
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll
