@@ -28,6 +28,7 @@ struct DecodeMmaArgs {
   int n_heads, n_kv_heads, max_blocks, n_splits, window;
   float scale;
   Prefetch pf;
+  int* counters;                 // optional [B, gridDim.y], zero between launches: the last split merges
 };
 
 __device__ __forceinline__ void cp_async16_zfill(void* smem, const void* gmem, bool valid) {
@@ -280,6 +281,39 @@ attn_decode_mma_kernel(DecodeMmaArgs a) {
       }
     }
   }
+  if (a.n_splits == 1 || a.counters == nullptr) return;
+
+  // The block that finishes last for this (sequence, kv head, head chunk) merges all splits.
+  __shared__ int is_last;
+  __threadfence();  // this block's partial results are visible before its arrival is counted
+  __syncthreads();
+  if (tid == 0) {
+    int* counter = a.counters + (size_t)b * gridDim.y + blockIdx.y;
+    const int arrived = atomicAdd(counter, 1);
+    is_last = arrived == a.n_splits - 1;
+    if (is_last) *counter = 0;  // ready for the next launch
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const int S = a.n_splits;
+  for (int idx = tid; idx < ng * D; idx += 128) {
+    const int row = idx / D, col = idx % D;
+    const size_t head = (size_t)b * a.n_heads + h0 + row;
+    const float* ml = a.part_ml + head * S * 2;
+    float m = -INFINITY;
+    for (int sp = 0; sp < S; ++sp) m = fmaxf(m, __ldcg(ml + 2 * sp));
+    float l = 0.f, acc = 0.f;
+    for (int sp = 0; sp < S; ++sp) {
+      const float ms = __ldcg(ml + 2 * sp);
+      if (ms > -INFINITY) {
+        const float w = __expf(ms - m);
+        l += __ldcg(ml + 2 * sp + 1) * w;
+        acc += __ldcg(a.part_o + (head * S + sp) * D + col) * w;
+      }
+    }
+    a.out[head * D + col] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+  }
 }
 
 template <int D, int STAGES>
@@ -523,12 +557,14 @@ MLL_API int mll_attn_decode_mma_supported(int dtype, int head_dim) {
   return dtype == MLL_BF16 && (head_dim == 64 || head_dim == 128 || head_dim == 256);
 }
 
-// Same contract as mll_attn_decode without the combine step: with n_splits > 1 the caller
-// merges the partial results (scratch layout: partial outputs, then (max, sum) pairs).
+// Same contract as mll_attn_decode.  With n_splits > 1 and `counters` (int32, one per
+// (sequence, kv head x head chunk), zero before the first launch; the kernel leaves them zero)
+// the last block of each group merges the partial results; without counters the caller runs
+// mll_attn_combine (scratch layout: partial outputs, then (max, sum) pairs).
 MLL_API int mll_attn_decode_mma(const void* q, const void* k_cache, const void* v_cache, const int* seq_slot,
                                 const int* seq_ctx, const int* block_table, float* scratch, void* out, int n_seqs,
                                 int n_heads, int n_kv_heads, int head_dim, int max_blocks, int n_splits, int window,
-                                float scale, const void* prefetch_ptr, long long prefetch_bytes,
+                                float scale, const void* prefetch_ptr, long long prefetch_bytes, int* counters,
                                 cudaStream_t stream) {
   MLL_REQUIRE(mll_attn_decode_mma_supported(MLL_BF16, head_dim), "attention decode (mma): head_dim %d", head_dim);
   MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention decode (mma): bad head counts");
@@ -539,7 +575,7 @@ MLL_API int mll_attn_decode_mma(const void* q, const void* k_cache, const void* 
                        seq_slot, seq_ctx, block_table, scratch,
                        scratch ? scratch + (size_t)n_seqs * n_heads * n_splits * head_dim : nullptr,
                        (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, n_splits, window, scale,
-                       mll::Prefetch{prefetch_ptr, prefetch_ptr ? (unsigned long long)prefetch_bytes : 0ull}};
+                       mll::Prefetch{prefetch_ptr, prefetch_ptr ? (unsigned long long)prefetch_bytes : 0ull}, counters};
   if (head_dim == 64) return mll::launch_decode_mma<64, 3>(a, n_seqs, stream);
   if (head_dim == 128) return mll::launch_decode_mma<128, 3>(a, n_seqs, stream);
   return mll::launch_decode_mma<256, 2>(a, n_seqs, stream);

@@ -15,7 +15,7 @@ import torch
 from .build import KernelBuildError, load_library
 
 PAGE = 64  # cache positions per page; equals MLL_PAGE in common.cuh
-ABI_VERSION = 10
+ABI_VERSION = 11
 MAX_TOP_K = 1024
 
 
@@ -372,7 +372,7 @@ USE_TENSOR_CORE_PREFILL = True
 
 def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch, out, n_seqs: int,
                      n_heads: int, n_kv_heads: int, head_dim: int, n_splits: int, window: int,
-                     scale: float, prefetch=None) -> None:
+                     scale: float, prefetch=None, counters: Optional[torch.Tensor] = None) -> None:
     """One query token per sequence (q row i belongs to sequence i) over the paged cache.
     bfloat16 with head_dim 64/128/256 runs on tensor cores, everything else on the general kernel."""
     _check_attention(q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim)
@@ -386,14 +386,20 @@ def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratc
         if scratch.numel() < attention_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits):
             raise KernelError("attention decode: scratch too small for the split count")
     code = dtype_code(q.dtype)
+    if counters is not None:
+        _need(counters, "attention counters", torch.int32, 1)
+        group = n_heads // n_kv_heads
+        if counters.shape[0] < n_seqs * n_kv_heads * ((group + 15) // 16):
+            raise KernelError("attention decode: counters shorter than sequences x kv heads x head chunks")
     if USE_TENSOR_CORE_DECODE and lib().mll_attn_decode_mma_supported(code, head_dim):
         _check(lib().mll_attn_decode_mma(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx),
                                          _ptr(block_table), _ptr(scratch), _ptr(out), ctypes.c_int(n_seqs),
                                          ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim),
                                          ctypes.c_int(block_table.shape[1]), ctypes.c_int(n_splits),
-                                         ctypes.c_int(window), ctypes.c_float(scale), *_hint_args(prefetch), _stream()),
+                                         ctypes.c_int(window), ctypes.c_float(scale), *_hint_args(prefetch),
+                                         _ptr(counters if n_splits > 1 else None), _stream()),
                "attention_decode (tensor cores)")
-        if n_splits > 1:
+        if n_splits > 1 and counters is None:
             _check(lib().mll_attn_combine(_ptr(scratch), _ptr(out), code, ctypes.c_int(n_seqs), ctypes.c_int(n_heads),
                                           ctypes.c_int(head_dim), ctypes.c_int(n_splits), _stream()),
                    "attention_combine")

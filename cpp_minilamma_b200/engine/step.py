@@ -61,6 +61,18 @@ class Workspace:
             self.generation += 1
         return flat[:count].view(shape)
 
+    def zeros(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        """As `buffer`, but zero-filled when it is (re)allocated - for counters that the
+        kernels using them leave at zero."""
+        count = 1
+        for dim in shape:
+            count *= dim
+        flat = self._flat.get(name)
+        if flat is None or flat.dtype != dtype or flat.numel() < count:
+            self._flat[name] = torch.zeros(max(count, 64), dtype=dtype, device=self.device)
+            self.generation += 1
+        return self._flat[name][:count].view(shape)
+
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self._flat.values())
 

@@ -126,13 +126,15 @@ class Attention(Mixer):
         out = step.ws.buffer("attn", (T, Hq * d), act)
         if step.all_decode:
             splits = step.decode_splits if step.decode_splits else self.decode_splits(step.n_seqs, step.max_ctx)
-            scratch = None
+            scratch = counters = None
             if splits > 1:
                 scratch = step.ws.buffer(
                     "attn.scratch", (K.attention_decode_scratch_floats(step.n_seqs, Hq, d, splits),), torch.float32)
+                # one arrival counter per (sequence, kv head, chunk of 16 heads): the last split merges
+                counters = step.ws.zeros("attn.counters", (step.n_seqs * Hk * (-(-(Hq // Hk) // 16)),), torch.int32)
             K.attention_decode(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, cache.block_table, scratch, out,
                                step.n_seqs, Hq, Hk, d, splits, self.window, self.scale,
-                               prefetch=K.hint(after, 32, 32))
+                               prefetch=K.hint(after, 32, 32), counters=counters)
         else:
             K.attention_prefill(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
                                 step.tile_seq, step.tile_row0, cache.block_table, out, step.n_tiles,

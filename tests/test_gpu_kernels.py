@@ -191,6 +191,16 @@ def test_attention_decode(dtype, hq, hk, d, splits, decode_impl):
         ref = pl.causal_attention(as64(q[b:b + 1]), as64(case.k[b]), as64(case.v[b]), q_positions=[c - 1])
         np.testing.assert_allclose(as64(out[b]).reshape(hq, d), ref[0],
                                    **attention_tol(dtype, decode_impl, as64(case.v[b])), err_msg=f"seq {b} ctx {c}")
+    # with arrival counters the last block of each group merges the splits itself; the counters
+    # come back as zeros, so the same buffer serves the next launch
+    counters = torch.zeros(len(ctx) * hk * (-(-(hq // hk) // 16)), dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        merged = torch.full_like(out, float("nan"))
+        K.attention_decode(q.reshape(len(ctx), hq * d).to(DEV), kc, vc, slots, ctx_t, table, scratch, merged,
+                           len(ctx), hq, hk, d, splits, 0, 1.0 / math.sqrt(d), counters=counters)
+        np.testing.assert_allclose(as64(merged), as64(out), rtol=1e-2 if dtype == torch.bfloat16 else 1e-5,
+                                   atol=1e-3 if dtype == torch.bfloat16 else 1e-6)
+        assert int(counters.abs().sum()) == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
