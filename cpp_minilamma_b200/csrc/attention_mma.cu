@@ -296,23 +296,48 @@ attn_decode_mma_kernel(DecodeMmaArgs a) {
   __syncthreads();
   if (!is_last) return;
   __threadfence();
+  // weights of the splits per head, once: w_s = exp(m_s - max m) (zero for an empty split)
   const int S = a.n_splits;
+  float* w_s = reinterpret_cast<float*>(smem_raw);  // [ng][S] and [ng] sums, over the (finished) page ring
+  float* l_s = w_s + 16 * S;
+  for (int row = warp; row < ng; row += 4) {
+    const float* ml = a.part_ml + ((size_t)b * a.n_heads + h0 + row) * S * 2;
+    float m = -INFINITY;
+    for (int sp = lane; sp < S; sp += 32) m = fmaxf(m, __ldcg(ml + 2 * sp));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    float l = 0.f;
+    for (int sp = lane; sp < S; sp += 32) {
+      const float ms = __ldcg(ml + 2 * sp);
+      const float w = ms > -INFINITY ? __expf(ms - m) : 0.f;
+      w_s[row * S + sp] = w;
+      l += __ldcg(ml + 2 * sp + 1) * w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (lane == 0) l_s[row] = l;
+  }
+  __syncthreads();
   for (int idx = tid; idx < ng * D; idx += 128) {
     const int row = idx / D, col = idx % D;
     const size_t head = (size_t)b * a.n_heads + h0 + row;
-    const float* ml = a.part_ml + head * S * 2;
-    float m = -INFINITY;
-    for (int sp = 0; sp < S; ++sp) m = fmaxf(m, __ldcg(ml + 2 * sp));
-    float l = 0.f, acc = 0.f;
-    for (int sp = 0; sp < S; ++sp) {
-      const float ms = __ldcg(ml + 2 * sp);
-      if (ms > -INFINITY) {
-        const float w = __expf(ms - m);
-        l += __ldcg(ml + 2 * sp + 1) * w;
-        acc += __ldcg(a.part_o + (head * S + sp) * D + col) * w;
-      }
+    const float* po = a.part_o + head * S * D + col;
+    float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+    int sp = 0;
+    for (; sp + 4 <= S; sp += 4) {  // four independent loads in flight
+      const float v0 = __ldcg(po + (size_t)sp * D), v1 = __ldcg(po + (size_t)(sp + 1) * D);
+      const float v2 = __ldcg(po + (size_t)(sp + 2) * D), v3 = __ldcg(po + (size_t)(sp + 3) * D);
+      acc0 = fmaf(v0, w_s[row * S + sp], acc0);
+      acc1 = fmaf(v1, w_s[row * S + sp + 1], acc1);
+      acc2 = fmaf(v2, w_s[row * S + sp + 2], acc2);
+      acc3 = fmaf(v3, w_s[row * S + sp + 3], acc3);
     }
-    a.out[head * D + col] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    for (; sp < S; ++sp) acc0 = fmaf(__ldcg(po + (size_t)sp * D), w_s[row * S + sp], acc0);
+    const float l = l_s[row];
+    a.out[head * D + col] = __float2bfloat16_rn(l > 0.f ? ((acc0 + acc1) + (acc2 + acc3)) / l : 0.f);
   }
 }
 

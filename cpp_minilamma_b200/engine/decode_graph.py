@@ -56,15 +56,23 @@ class DecodeGraphs:
         self._generation = engine.ws.generation
         self.replays = 0
 
-    def _splits(self, batch: int) -> int:
-        """One split count for all attention layers of a captured step: chosen from the batch
-        size alone, since the graph must serve every context length."""
+    def _splits(self, batch: int, context: int) -> int:
+        """One split count for all attention layers of a captured step, chosen for the batch
+        size and the context bucket that the graph serves."""
         best = 1
         for layer in self.engine.model.layers:
             chooser = getattr(layer.mixer, "decode_splits", None)
             if chooser is not None:
-                best = max(best, chooser(batch, self.engine.model.max_positions))
+                best = max(best, chooser(batch, context))
         return best
+
+    @staticmethod
+    def _bucket(context: int) -> int:
+        """Contexts share a graph per power of two (from 256 on): the split count depends on it."""
+        bucket = 256
+        while bucket < context:
+            bucket *= 2
+        return bucket
 
     def step(self, slots: Sequence[int], tokens: Sequence[int], params: SamplingParams,
              requests: Sequence[int], steps: Sequence[int]) -> List[int]:
@@ -83,12 +91,13 @@ class DecodeGraphs:
         if self._generation != engine.ws.generation:  # a workspace buffer moved: old graphs point at freed memory
             self._captured.clear()
             self._generation = engine.ws.generation
-        key = (batch, params.is_greedy, params.temperature, params.top_k, params.seed)
+        bucket = self._bucket(max(starts) + 1)
+        key = (batch, bucket, params.is_greedy, params.temperature, params.top_k, params.seed)
         cap = self._captured.get(key)
         fresh = cap is None
         if fresh:
             cap = self._captured[key] = _Captured(engine, batch)
-            cap.state.decode_splits = self._splits(batch)
+            cap.state.decode_splits = self._splits(batch, bucket)
         else:
             cap.copied.synchronize()  # the previous replay's copy has read the pinned buffer
         f = cap.fields

@@ -103,9 +103,9 @@ class Attention(Mixer):
         blocks = max(1, n_seqs * self.n_kv_heads * chunks)
         span = max_ctx if self.window <= 0 else min(max_ctx, self.window + K.PAGE)
         pages = max(1, -(-span // K.PAGE))
-        # as many splits as keep every block resident at once (two per multiprocessor): a second,
-        # nearly empty wave costs more than slightly coarser splits
-        return max(1, min(_TARGET_BLOCKS // blocks, pages, 64))
+        # as many splits as keep every block resident at once (two per multiprocessor) - a second,
+        # nearly empty wave costs more than coarser splits - and at least two pages per split
+        return max(1, min(_TARGET_BLOCKS // blocks, pages // 2, 64))
 
     def forward(self, step, h: torch.Tensor, cache) -> torch.Tensor:
         T = h.shape[0]
