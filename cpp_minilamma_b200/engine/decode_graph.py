@@ -32,6 +32,7 @@ class _Captured:
         self.dev = torch.zeros(_FIELDS * batch, dtype=torch.int32, device=engine.device)
         self.copied = torch.cuda.Event()
         self.graph = None
+        self.failures = 0  # captures that did not go through (the step then ran eagerly)
         self.launches = 0
         h = self.host.numpy().reshape(_FIELDS, batch)
         h[2] = np.arange(batch)   # sequence of each token
@@ -56,23 +57,15 @@ class DecodeGraphs:
         self._generation = engine.ws.generation
         self.replays = 0
 
-    def _splits(self, batch: int, context: int) -> int:
-        """One split count for all attention layers of a captured step, chosen for the batch
-        size and the context bucket that the graph serves."""
+    def _splits(self, batch: int) -> int:
+        """One split count for all attention layers of a captured step: chosen from the batch
+        size alone, since the graph must serve every context length."""
         best = 1
         for layer in self.engine.model.layers:
             chooser = getattr(layer.mixer, "decode_splits", None)
             if chooser is not None:
-                best = max(best, chooser(batch, context))
+                best = max(best, chooser(batch, self.engine.model.max_positions))
         return best
-
-    @staticmethod
-    def _bucket(context: int) -> int:
-        """Contexts share a graph per power of two (from 256 on): the split count depends on it."""
-        bucket = 256
-        while bucket < context:
-            bucket *= 2
-        return bucket
 
     def step(self, slots: Sequence[int], tokens: Sequence[int], params: SamplingParams,
              requests: Sequence[int], steps: Sequence[int]) -> List[int]:
@@ -91,13 +84,12 @@ class DecodeGraphs:
         if self._generation != engine.ws.generation:  # a workspace buffer moved: old graphs point at freed memory
             self._captured.clear()
             self._generation = engine.ws.generation
-        bucket = self._bucket(max(starts) + 1)
-        key = (batch, bucket, params.is_greedy, params.temperature, params.top_k, params.seed)
+        key = (batch, params.is_greedy, params.temperature, params.top_k, params.seed)
         cap = self._captured.get(key)
         fresh = cap is None
         if fresh:
             cap = self._captured[key] = _Captured(engine, batch)
-            cap.state.decode_splits = self._splits(batch, bucket)
+            cap.state.decode_splits = self._splits(batch)
         else:
             cap.copied.synchronize()  # the previous replay's copy has read the pinned buffer
         f = cap.fields
@@ -106,11 +98,22 @@ class DecodeGraphs:
         f[8], f[9] = requests, steps
         cap.dev.copy_(cap.host, non_blocking=True)
         cap.copied.record()
-        if cap.graph is None and not fresh:
+        if cap.graph is None and not fresh and cap.failures < 3:
             before = K.launches
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            try:
+                # relaxed: a driver call made elsewhere in the process while this stream captures
+                # (a tensor or an older graph being released, a lazily loaded module) must not
+                # invalidate the capture
+                with torch.cuda.graph(graph, capture_error_mode="relaxed"):
+                    self._body(cap, params)
+            except Exception:
+                # the capture ran nothing: do this step eagerly and try again on a later one
+                cap.failures += 1
+                K.launches = before
+                torch.cuda.synchronize()
                 self._body(cap, params)
+                return self.sampler.fetch(batch)
             cap.launches = K.launches - before
             K.launches = before
             if self._generation != engine.ws.generation:

@@ -104,8 +104,9 @@ class Attention(Mixer):
         span = max_ctx if self.window <= 0 else min(max_ctx, self.window + K.PAGE)
         pages = max(1, -(-span // K.PAGE))
         # as many splits as keep every block resident at once (two per multiprocessor) - a second,
-        # nearly empty wave costs more than coarser splits - and at least two pages per split
-        return max(1, min(_TARGET_BLOCKS // blocks, pages // 2, 64))
+        # nearly empty wave costs more than coarser splits - at least two pages per split, and at
+        # most 16: the merge of the splits grows with their number
+        return max(1, min(_TARGET_BLOCKS // blocks, pages // 2, 16))
 
     def forward(self, step, h: torch.Tensor, cache) -> torch.Tensor:
         T = h.shape[0]
