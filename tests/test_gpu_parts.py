@@ -345,3 +345,155 @@ def test_toy_architecture_with_a_state_mixer(tmp_path):
     llm.engine.cache.check()
     # greedy generation runs through the same loop
     assert len(llm.generate([requests[1]], max_new_tokens=5)[0]) == 5
+
+
+# ------------------------------------------------------------------------------------ #
+# a second toy architecture: windowed attention without position encoding next to full  #
+# attention with rotary encoding, a feed-forward with routing, another position encoding #
+# ------------------------------------------------------------------------------------ #
+from cpp_minilamma_b200.parts import FeedForward, PositionEncoding  # noqa: E402
+
+
+class Top1Experts(FeedForward):
+    """Routed feed-forward: router logits in float32, the best expert's SwiGLU output scaled by
+    its softmax weight.  Written with torch ops: the interface is what is under test."""
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.n, self.inter, self.prefix = params["experts"], params["intermediate"], params["prefix"]
+
+    def weight_specs(self):
+        D = self.ctx.hidden_size
+        specs = [WeightSpec(self.prefix + "router", (self.n, D))]
+        for e in range(self.n):
+            specs += [WeightSpec(f"{self.prefix}e{e}.gate", (self.inter, D)), WeightSpec(f"{self.prefix}e{e}.up", (self.inter, D)),
+                      WeightSpec(f"{self.prefix}e{e}.down", (D, self.inter))]
+        return specs
+
+    def bind(self, store):
+        self.router = store.take(self.prefix + "router").float()
+        self.experts = [(store.take(f"{self.prefix}e{e}.gate").float(), store.take(f"{self.prefix}e{e}.up").float(),
+                         store.take(f"{self.prefix}e{e}.down").float()) for e in range(self.n)]
+
+    def forward(self, step, h):
+        x = h.float()
+        probs = torch.softmax(x @ self.router.t(), dim=-1)
+        best = probs.argmax(dim=-1)
+        out = torch.zeros_like(x)
+        for e, (g, u, d) in enumerate(self.experts):
+            y = (torch.nn.functional.silu(x @ g.t()) * (x @ u.t())) @ d.t()
+            out += torch.where((best == e)[:, None], y * probs[:, e:e + 1], torch.zeros_like(y))
+        return out.to(h.dtype)
+
+
+class HalfSpeedRotary(PositionEncoding):
+    """Another position encoding: rotary tables whose angles advance half a step per position."""
+
+    interleaved = True
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        freqs = pl.rope_inverse_frequencies(params["head_dim"], params["theta"]) * 0.5
+        ang = np.arange(ctx.max_positions)[:, None] * freqs[None, :]
+        self.cos = torch.tensor(np.cos(ang), dtype=torch.float32, device=ctx.device)
+        self.sin = torch.tensor(np.sin(ang), dtype=torch.float32, device=ctx.device)
+
+    def tables(self):
+        return self.cos, self.sin
+
+
+@dataclass
+class MixConfig(ToyConfig):
+    def to_dict(self):
+        return {**super().to_dict(), "architectures": ["ToyMixLM"]}
+
+
+WINDOW = 70
+
+
+def mix_builder(cfg):
+    D = cfg.hidden_size
+
+    def norm(name):
+        return PartSpec("rms_norm", {"width": D, "eps": 1e-6, "name": name})
+
+    def attention(i, window, position):
+        return PartSpec("attention", {"n_heads": HQ, "n_kv_heads": HK, "head_dim": HD, "window": window,
+                                      "position": position, "names": {p: f"l{i}.{p}" for p in "qkvo"}})
+
+    layers = [
+        LayerSpec(PartSpec("pre_norm"), attention(0, 0, PartSpec("half_speed_rotary", {"head_dim": HD, "theta": 50.0})),
+                  PartSpec("top1_experts", {"experts": 3, "intermediate": 24, "prefix": "l0.moe."}),
+                  {"input": norm("l0.n1"), "post_mixer": norm("l0.n2")}),
+        LayerSpec(PartSpec("pre_norm"), attention(1, WINDOW, PartSpec("none")),
+                  PartSpec("swiglu", {"intermediate": INTER, "names": {p: f"l1.{p}" for p in ("gate", "up", "down")}}),
+                  {"input": norm("l1.n1"), "post_mixer": norm("l1.n2")}),
+    ]
+    return ModelSpec(hidden_size=D, vocab_size=cfg.vocab_size, max_positions=512,
+                     embedding=PartSpec("token_embedding", {"vocab": cfg.vocab_size, "name": "emb"}),
+                     layers=layers, schedule=[ScheduleEntry(0), ScheduleEntry(1)], final_norm=norm("final"),
+                     lm_head=PartSpec("linear_head", {"vocab": cfg.vocab_size, "name": "head", "tied_to": "emb"}))
+
+
+def mix_plain(weights, tokens):
+    T = len(tokens)
+    pos = np.arange(T)
+    x = pl.embedding(weights["emb"], tokens)
+    # layer 0: full attention, half-speed interleaved rotary, routed feed-forward
+    h = pl.rms_norm(x, weights["l0.n1"], 1e-6)
+    inv = pl.rope_inverse_frequencies(HD, 50.0) * 0.5
+    q = pl.apply_rope(pl.linear(h, weights["l0.q.weight"]).reshape(T, HQ, HD), pos, inv, True)
+    k = pl.apply_rope(pl.linear(h, weights["l0.k.weight"]).reshape(T, HK, HD), pos, inv, True)
+    v = pl.linear(h, weights["l0.v.weight"]).reshape(T, HK, HD)
+    x = x + pl.linear(pl.causal_attention(q, k, v).reshape(T, HQ * HD), weights["l0.o.weight"])
+    h = pl.rms_norm(x, weights["l0.n2"], 1e-6)
+    logits = pl.linear(h, weights["l0.moe.router"])
+    probs = np.exp(logits - logits.max(axis=-1, keepdims=True))
+    probs /= probs.sum(axis=-1, keepdims=True)
+    best = probs.argmax(axis=-1)
+    moe = np.zeros_like(x)
+    for t in range(T):
+        e = int(best[t])
+        moe[t] = probs[t, e] * pl.feed_forward(h[t:t + 1], weights[f"l0.moe.e{e}.gate"], weights[f"l0.moe.e{e}.up"],
+                                               weights[f"l0.moe.e{e}.down"])[0]
+    x = x + moe
+    # layer 1: the last WINDOW keys only, no position encoding, dense feed-forward
+    h = pl.rms_norm(x, weights["l1.n1"], 1e-6)
+    q = pl.linear(h, weights["l1.q.weight"]).reshape(T, HQ, HD)
+    k = pl.linear(h, weights["l1.k.weight"]).reshape(T, HK, HD)
+    v = pl.linear(h, weights["l1.v.weight"]).reshape(T, HK, HD)
+    x = x + pl.linear(pl.causal_attention(q, k, v, window=WINDOW).reshape(T, HQ * HD), weights["l1.o.weight"])
+    h = pl.rms_norm(x, weights["l1.n2"], 1e-6)
+    x = x + pl.feed_forward(h, weights["l1.gate.weight"], weights["l1.up.weight"], weights["l1.down.weight"])
+    return pl.linear(pl.rms_norm(x, weights["final"], 1e-6), weights["emb"])
+
+
+def test_toy_architecture_with_window_group_routing_and_other_encoding(tmp_path):
+    register_part("feed_forward", "top1_experts", Top1Experts)
+    register_part("position_encoding", "half_speed_rotary", HalfSpeedRotary)
+    ml.register_architecture("ToyMixLM", MixConfig, mix_builder)
+    cfg = ml.config_from_dict({"architectures": ["ToyMixLM"], "vocab_size": 61, "hidden_size": 48})
+    folder = ml.write_random_model(cfg, tmp_path, seed=9, matrix_std=0.08)
+    _, weights = pl.read_model_folder(folder)
+    llm = ml.load(folder, dtype="float32", max_tokens=64 * 10, max_seqs=2)
+    cache = llm.engine.cache
+    # the two attention layers differ in their need: storage and block table of their own
+    assert len(cache.groups) == 2 and {g.need.window for g in cache.groups} == {0, WINDOW}
+    rng = np.random.RandomState(1)
+    tokens = [int(t) for t in rng.randint(0, 61, size=300)]
+    ref = mix_plain(weights, tokens)
+    slot, = llm.engine.acquire(1)
+    rows = [llm.engine.step([StepEntry(slot, tokens[:150], list(range(150)))]).cpu().numpy()]
+    for t in range(150, 300):   # decoding far beyond the window: the windowed group gives pages back
+        rows.append(llm.engine.step([StepEntry(slot, [tokens[t]], [0])]).cpu().numpy())
+    assert_close(np.concatenate(rows), ref, "float32", "toy mix: prompt then decode")
+    full, windowed = sorted(cache.groups, key=lambda g: g.need.window)
+    assert sum(p is not None for p in full.pages[slot]) == 5           # 300 tokens: 5 pages
+    assert sum(p is not None for p in windowed.pages[slot]) <= 3       # about WINDOW tokens stay
+    cache.check()
+    llm.engine.release(slot)
+    # whole, in one step, next to a second sequence
+    a, b = llm.engine.acquire(2)
+    out = llm.engine.step([StepEntry(a, tokens, list(range(300))), StepEntry(b, tokens[:7], [6])]).cpu().numpy()
+    assert_close(out[:300], ref, "float32", "toy mix: whole")
+    assert_close(out[300], mix_plain(weights, tokens[:7])[6], "float32", "toy mix: short neighbour")
