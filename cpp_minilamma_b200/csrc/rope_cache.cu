@@ -77,6 +77,99 @@ __global__ void rope_cache_kernel(RopeArgs a) {
   }
 }
 
+// bfloat16 with head_dim a multiple of 16: one thread per 16 elements of a head (8 pairs), moved as
+// 16-byte words.  A step of thousands of tokens is bound by memory traffic, which scalar
+// 2-byte accesses cannot saturate.  Same arithmetic, element by element, as the kernel above.
+__device__ __forceinline__ void unpack8(const uint4& w, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 v = __bfloat1622float2(h[i]);
+    f[2 * i] = v.x;
+    f[2 * i + 1] = v.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 w;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return w;
+}
+
+__global__ void __launch_bounds__(256) rope_cache_vec_kernel(RopeArgs a, long long n_items) {
+  mll::pdl_begin();
+  l2_prefetch_by_grid(a.pf);
+  const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (item >= n_items) return;
+  const int d = a.head_dim, half = d >> 1;
+  const int chunks = d >> 4;                       // 16 elements each
+  const int heads = a.n_heads + (a.write_kv ? 2 * a.n_kv_heads : 0);
+  const int c = (int)(item % chunks);
+  const int hb = (int)((item / chunks) % heads);
+  const int t = (int)(item / ((long long)chunks * heads));
+  const bool is_q = hb < a.n_heads;
+  const bool is_k = !is_q && hb < a.n_heads + a.n_kv_heads;
+  const int pos = a.tok_pos[t];
+  const __nv_bfloat16* row = (const __nv_bfloat16*)a.qkv + (size_t)t * a.ld + (size_t)hb * d;
+  const float* bias = a.bias ? a.bias + (size_t)hb * d : nullptr;
+  __nv_bfloat16* dst;
+  if (is_q) {
+    dst = (__nv_bfloat16*)a.q_out + (size_t)t * a.n_heads * d + (size_t)hb * d;
+  } else {
+    const int slot = a.seq_slot[a.tok_seq[t]];
+    const int page = a.block_table[(size_t)slot * a.max_blocks + pos / MLL_PAGE];
+    const int head = is_k ? hb - a.n_heads : hb - a.n_heads - a.n_kv_heads;
+    __nv_bfloat16* base = (__nv_bfloat16*)(is_k ? a.k_cache : a.v_cache);
+    dst = base + (((size_t)page * a.n_kv_heads + head) * MLL_PAGE + pos % MLL_PAGE) * d;
+  }
+  const bool rotate = (is_q || is_k) && a.cos_table != nullptr;
+  const bool split = rotate && !a.interleaved;
+  // the two 8-element words of this thread: the halves' matching parts, or 16 neighbours
+  const int e0 = split ? 8 * c : 16 * c;
+  const int e1 = split ? half + 8 * c : 16 * c + 8;
+  float x0[8], x1[8];
+  unpack8(*reinterpret_cast<const uint4*>(row + e0), x0);
+  unpack8(*reinterpret_cast<const uint4*>(row + e1), x1);
+  if (bias) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      x0[i] += bias[e0 + i];
+      x1[i] += bias[e1 + i];
+    }
+  }
+  if (rotate) {
+    // pairs 8c .. 8c+7 of the head
+    const float4* cs = reinterpret_cast<const float4*>(a.cos_table + (size_t)pos * half + 8 * c);
+    const float4* sn = reinterpret_cast<const float4*>(a.sin_table + (size_t)pos * half + 8 * c);
+    float cv[8], sv[8];
+    *reinterpret_cast<float4*>(cv) = cs[0];
+    *reinterpret_cast<float4*>(cv + 4) = cs[1];
+    *reinterpret_cast<float4*>(sv) = sn[0];
+    *reinterpret_cast<float4*>(sv + 4) = sn[1];
+    if (split) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float p = x0[i], q = x1[i];
+        x0[i] = p * cv[i] - q * sv[i];
+        x1[i] = p * sv[i] + q * cv[i];
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float p = x0[2 * i], q = x0[2 * i + 1];
+        x0[2 * i] = p * cv[i] - q * sv[i];
+        x0[2 * i + 1] = p * sv[i] + q * cv[i];
+        p = x1[2 * i], q = x1[2 * i + 1];
+        x1[2 * i] = p * cv[4 + i] - q * sv[4 + i];
+        x1[2 * i + 1] = p * sv[4 + i] + q * cv[4 + i];
+      }
+    }
+  }
+  *reinterpret_cast<uint4*>(dst + e0) = pack8(x0);
+  *reinterpret_cast<uint4*>(dst + e1) = pack8(x1);
+}
+
 }  // namespace mll
 
 MLL_API int mll_rope_cache(const void* qkv, const float* bias, const float* cos_table,
@@ -97,7 +190,13 @@ MLL_API int mll_rope_cache(const void* qkv, const float* bias, const float* cos_
   const int threads = half >= 128 ? 128 : (half >= 64 ? 64 : 32);
   MLL_REQUIRE(n_heads + 2 * n_kv_heads <= 65535, "rope: too many heads for one launch");
   const dim3 grid(n_tokens, n_heads + (write_kv ? 2 * n_kv_heads : 0));
-  if (dtype == MLL_F32)
+  const bool aligned16 = ((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache |
+                          (uintptr_t)cos_table | (uintptr_t)sin_table) % 16 == 0;
+  if (dtype == MLL_BF16 && head_dim % 16 == 0 && ld % 8 == 0 && aligned16) {
+    const long long items = (long long)n_tokens * grid.y * (head_dim / 16);
+    MLL_REQUIRE((items + 255) / 256 <= 0x7fffffffLL, "rope: too many tokens for one launch");
+    MLL_LAUNCH(mll::rope_cache_vec_kernel, (unsigned)((items + 255) / 256), 256, 0, stream, a, items);
+  } else if (dtype == MLL_F32)
     MLL_LAUNCH((mll::rope_cache_kernel<float>), grid, threads, 0, stream, a);
   else if (dtype == MLL_BF16)
     MLL_LAUNCH((mll::rope_cache_kernel<__nv_bfloat16>), grid, threads, 0, stream, a);
