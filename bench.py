@@ -67,14 +67,27 @@ class ClockSampler:
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index=0):
-        self.samples = []
+        self.samples = []      # (time of arrival, fields)
         self.proc = None
         self.index = index
+        self.window = [None, None]
+
+    def wait_for_first_line(self, limit=3.0):
+        deadline = time.monotonic() + limit
+        while self.proc is not None and not self.samples and time.monotonic() < deadline:
+            time.sleep(0.01)
+
+    def begin(self):
+        """The timed region starts now: earlier samples are dropped."""
+        self.window[0] = time.monotonic()
+
+    def end(self):
+        self.window[1] = time.monotonic()
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -84,7 +97,7 @@ class ClockSampler:
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) == 6:
-                self.samples.append(parts)
+                self.samples.append((time.monotonic(), parts))
 
     def stop(self):
         if self.proc is not None:
@@ -96,7 +109,11 @@ class ClockSampler:
 
     def summary(self):
         clocks, reasons, top = [], set(), None
-        for sm, mx, hw, hwt, swt, cap in self.samples:
+        lo, hi = self.window
+        for at, (sm, mx, hw, hwt, swt, cap) in self.samples:
+            # a line arrives up to one period after its reading
+            if (lo is not None and at < lo + 0.05) or (hi is not None and at > hi + 0.05):
+                continue
             try:
                 clocks.append(int(float(sm)))
                 top = int(float(mx))
@@ -141,6 +158,8 @@ def time_decode(llm, batch, steps, warmup, seed, sampler=None):
     prompts = prompts_for(batch, llm.config.vocab_size, seed)
     slots = engine.acquire(batch)
     try:
+        if sampler:
+            sampler.start()    # nvidia-smi needs a moment before its first line: it runs through the warm-up
         tokens = backend.step_and_sample([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)],
                                          list(range(batch)), [0] * batch)
         for i in range(warmup):
@@ -148,7 +167,8 @@ def time_decode(llm, batch, steps, warmup, seed, sampler=None):
                                              list(range(batch)), [i + 1] * batch)
         torch.cuda.synchronize()
         if sampler:
-            sampler.start()
+            sampler.wait_for_first_line()
+            sampler.begin()
         launches_before = K.launches
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         begin.record()
@@ -158,6 +178,7 @@ def time_decode(llm, batch, steps, warmup, seed, sampler=None):
         end.record()
         torch.cuda.synchronize()
         if sampler:
+            sampler.end()
             sampler.stop()
         ms = begin.elapsed_time(end) / steps
         live = sum(len(p) for p in prompts) + batch * (warmup + steps // 2)
@@ -241,7 +262,7 @@ def profile_region(args):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")

@@ -15,7 +15,7 @@ import torch
 from .build import KernelBuildError, load_library
 
 PAGE = 64  # cache positions per page; equals MLL_PAGE in common.cuh
-ABI_VERSION = 11
+ABI_VERSION = 12
 MAX_TOP_K = 1024
 
 
@@ -223,7 +223,8 @@ def linear_tc5(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], o
 
 
 def take_device_error() -> int:
-    """1 when a kernel's bounded wait ran out since the last call (then cleared); synchronises."""
+    """Non-zero when a kernel's bounded wait ran out since the last call (then cleared): bit 0 the TMA
+    linear kernel, bit 1 the tcgen05 linear kernel, bit 2 the tcgen05 attention kernel; synchronises."""
     return int(lib().mll_take_device_error())
 
 
@@ -368,6 +369,7 @@ def attention_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_
 
 USE_TENSOR_CORE_DECODE = True  # tests switch these off to reach the general kernels at every size
 USE_TENSOR_CORE_PREFILL = True
+USE_TCGEN05_PREFILL = True      # off: the mma.sync kernel takes the tensor-core prefill
 
 
 def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch, out, n_seqs: int,
@@ -423,6 +425,16 @@ def attention_prefill(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_ql
     _need(block_table, "attention block_table", torch.int32, 2)
     if tile_seq.shape[0] < n_tiles or tile_row0.shape[0] < n_tiles:
         raise KernelError("attention prefill: tile lists shorter than the tile count")
+    if (USE_TENSOR_CORE_PREFILL and USE_TCGEN05_PREFILL
+            and lib().mll_attn_prefill_tc5_supported(dtype_code(q.dtype), head_dim)):
+        _check(lib().mll_attn_prefill_tc5(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx),
+                                          _ptr(seq_qstart), _ptr(seq_qlen), _ptr(tile_seq), _ptr(tile_row0),
+                                          _ptr(block_table), _ptr(out), ctypes.c_int(q.shape[0]),
+                                          ctypes.c_longlong(k_cache.shape[0]), ctypes.c_int(n_tiles),
+                                          ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim),
+                                          ctypes.c_int(block_table.shape[1]), ctypes.c_int(window),
+                                          ctypes.c_float(scale), _stream()), "attention_prefill (tcgen05)")
+        return
     if USE_TENSOR_CORE_PREFILL and lib().mll_attn_prefill_mma_supported(dtype_code(q.dtype), head_dim):
         _check(lib().mll_attn_prefill_mma(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx),
                                           _ptr(seq_qstart), _ptr(seq_qlen), _ptr(tile_seq), _ptr(tile_row0),

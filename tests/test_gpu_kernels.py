@@ -260,11 +260,15 @@ def test_attention_decode_window_edge(dtype, window, decode_impl):
                                        err_msg=f"seq {b}")
 
 
-@pytest.fixture(params=["tensor_core", "general"])
+@pytest.fixture(params=["tcgen05", "tensor_core", "general"])
 def prefill_impl(request):
-    K.USE_TENSOR_CORE_PREFILL = request.param == "tensor_core"
-    yield request.param
+    """tcgen05: the TMA/tensor-memory kernel (head sizes 64 and 128, else the next one);
+    tensor_core: the mma.sync kernel; general: the kernel for every size and dtype."""
+    K.USE_TENSOR_CORE_PREFILL = request.param != "general"
+    K.USE_TCGEN05_PREFILL = request.param == "tcgen05"
+    yield "general" if request.param == "general" else "tensor_core"
     K.USE_TENSOR_CORE_PREFILL = True
+    K.USE_TCGEN05_PREFILL = True
 
 
 def _prefill_tiles(q_lens):
