@@ -141,8 +141,11 @@ struct PrefillTc5Smem {
   static constexpr int P_BYTES = A_ROWS * MLL_PAGE * 2;
   static constexpr int Q_OFF = 0, K_OFF = Q_BYTES, V_OFF = K_OFF + 2 * KV_BYTES, P_OFF = V_OFF + 2 * KV_BYTES;
   static constexpr int BAR_OFF = P_OFF + P_BYTES;
-  // never three blocks per multiprocessor: their tensor memory would not fit
-  static constexpr size_t USED = 1024 + (size_t)BAR_OFF + 128;
+  // Two blocks per multiprocessor: 2 x (BYTES + 1 KB that the system keeps per block) must stay
+  // within 227 KB, which leaves no room for alignment slack: the kernel checks that its dynamic
+  // shared memory starts on a 1024-byte boundary (the swizzle's period) and refuses otherwise.
+  // Never three blocks: their tensor memory would not fit.
+  static constexpr size_t USED = (size_t)BAR_OFF + 128;
   static constexpr size_t BYTES = USED > 80 * 1024 ? USED : 80 * 1024;
   static constexpr int TMEM_COLS = 256;                // S: 2 x 64, O: up to 128
   static constexpr int O_COL = 128;
@@ -155,11 +158,17 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
   using L = PrefillTc5Smem<D>;
   constexpr int DB = D / 64;  // 64-column boxes per row of Q, K or V
   mll::pdl_begin();
-  const int row0 = a.tile_row0[blockIdx.x];
+  // later tiles of a sequence see more keys: they go first, so that the short ones fill the tail
+  const int tile = (gridDim.x - 1 - blockIdx.x) / a.n_heads;   // all heads of a tile are neighbours
+  const int row0 = a.tile_row0[tile];
   if (row0 % A_ROWS != 0) return;  // the second half of a 128-row tile
 
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* base = smem_raw;
+  if (a_smem(base) & 1023u) {  // cannot hold swizzled tiles: report and leave (uniform for the block)
+    if (threadIdx.x == 0) atomicExch(&mll_attn_tc5_error_flag, 2);
+    return;
+  }
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(base + L::BAR_OFF);
   // barriers: 0 query, 1-2 keys of stage 0/1, 3-4 values, 5-6 S buffers, 7 O
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 8);
@@ -169,8 +178,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
   const unsigned bar_o = a_smem(bars + 7);
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int seq = a.tile_seq[blockIdx.x];
-  const int h = blockIdx.y;
+  const int seq = a.tile_seq[tile];
+  const int h = blockIdx.x % a.n_heads;
   const int kvh = h / (a.n_heads / a.n_kv_heads);
   const int ctx = a.seq_ctx[seq], qlen = a.seq_qlen[seq], qstart = a.seq_qstart[seq];
   const int rows = min(A_ROWS, qlen - row0);
@@ -262,22 +271,28 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
         s[c] = keep ? s[c] : -INFINITY;
       }
     }
-    float mx = -INFINITY;
+    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains instead of one
 #pragma unroll
-    for (int c = 0; c < MLL_PAGE; ++c) mx = fmaxf(mx, s[c]);
+    for (int c = 0; c < MLL_PAGE; c += 4) {
+      mx4[0] = fmaxf(mx4[0], s[c]);
+      mx4[1] = fmaxf(mx4[1], s[c + 1]);
+      mx4[2] = fmaxf(mx4[2], s[c + 2]);
+      mx4[3] = fmaxf(mx4[3], s[c + 3]);
+    }
+    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
     const float m_new = fmaxf(m_run, mx * a.scale_log2);
     const float shift = m_new > -INFINITY ? m_new : 0.f;  // a fully masked row stays at zero weight
     const float alpha = a_exp2(m_run - shift);
-    float sum = 0.f;
+    float sum4[4] = {0.f, 0.f, 0.f, 0.f};
     unsigned packed[MLL_PAGE / 2];
 #pragma unroll
     for (int c = 0; c < MLL_PAGE; c += 2) {
       const float p0 = a_exp2(fmaf(s[c], a.scale_log2, -shift)), p1 = a_exp2(fmaf(s[c + 1], a.scale_log2, -shift));
-      sum += p0 + p1;
+      sum4[(c >> 1) & 3] += p0 + p1;
       __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
       packed[c >> 1] = *reinterpret_cast<unsigned*>(&pair);
     }
-    l_run = l_run * alpha + sum;
+    l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
     m_run = m_new;
     {  // row tid of P: eight 16-byte chunks, chunk index xor (row % 8)
       const unsigned row_addr = p_s + (tid >> 3) * 1024 + (tid & 7) * 128;
@@ -362,7 +377,7 @@ int launch_prefill_tc5(const CUtensorMap& qmap, const CUtensorMap& kmap, const C
                   cudaGetErrorString(err));
     return (int)err;
   }
-  MLL_LAUNCH((kernel), dim3(n_tiles, a.n_heads), A_ROWS, smem, stream, qmap, kmap, vmap, a);
+  MLL_LAUNCH((kernel), dim3((unsigned)(n_tiles * a.n_heads)), A_ROWS, smem, stream, qmap, kmap, vmap, a);
   MLL_LAUNCH_CHECK();
   return 0;
 }
@@ -390,7 +405,8 @@ MLL_API int mll_attn_prefill_tc5(const void* q, const void* k_cache, const void*
                                  int max_blocks, int window, float scale, cudaStream_t stream) {
   MLL_REQUIRE(mll_attn_prefill_tc5_supported(MLL_BF16, head_dim), "attention prefill (tcgen05): head_dim %d", head_dim);
   MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention prefill (tcgen05): bad head counts");
-  MLL_REQUIRE(n_tiles >= 0 && n_heads <= 65535 && n_tokens >= 0, "attention prefill (tcgen05): bad tile or head count");
+  MLL_REQUIRE(n_tiles >= 0 && n_tokens >= 0 && (long long)n_tiles * n_heads < (1ll << 31),
+              "attention prefill (tcgen05): bad tile or head count");
   MLL_REQUIRE(n_pages > 0 && n_pages * n_kv_heads * MLL_PAGE < (1ll << 31),
               "attention prefill (tcgen05): %lld pages are more than the row coordinate holds", n_pages);
   MLL_REQUIRE(((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) % 16 == 0,
