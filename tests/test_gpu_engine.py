@@ -14,7 +14,7 @@ from helpers import assert_close, plain_logits
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
-CASES = [(name, dtype) for name in "ABC" for dtype in DTYPES]
+CASES = [(name, dtype) for name in "ABCD" for dtype in DTYPES]
 
 
 def load(model_folders, name, dtype, storage=None, **kw):
@@ -95,7 +95,7 @@ def test_unequal_batches_reuse_slots(model_folders, name, dtype):
     # the BASELINE workloads (A: prompts 5/9/2 + 8 steps; B: 17/1/40/6 + 12 steps) and more,
     # on a cache with fewer slots than requests
     workloads = {"A": ([5, 9, 2, 1, 30, 7, 3], 8), "B": ([17, 1, 40, 6, 64, 65, 2, 100], 12),
-                 "C": ([3, 130, 64, 1, 257, 20], 20)}
+                 "C": ([3, 130, 64, 1, 257, 20], 20), "D": ([70, 1, 128, 5, 200, 64, 129], 40)}
     prompt_lens, steps = workloads[name]
     extra = [steps + 3 * (i % 3) for i in range(len(prompt_lens))]  # unequal ends
     top = tc.TINY[name]["max_position_embeddings"]
@@ -108,11 +108,11 @@ def test_unequal_batches_reuse_slots(model_folders, name, dtype):
     assert llm.engine.cache.n_free_slots == llm.engine.cache.n_slots
 
 
+@pytest.mark.parametrize("name", ["C", "D"])
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_long_decoding(model_folders, dtype):
-    # 3 prompt tokens then 600 single-token steps: crosses many pages
-    name = "C"
-    tokens = tc.random_tokens(name, 603, 400)
+def test_long_decoding(model_folders, name, dtype):
+    # 3 prompt tokens, then single-token steps up to 600: crosses many pages
+    tokens = tc.random_tokens(name, min(603, tc.TINY[name]["max_position_embeddings"]), 400)
     folder, llm = load(model_folders, name, dtype)
     slot, = llm.engine.acquire(1)
     rows = [llm.engine.step([StepEntry(slot, tokens[:3], [0, 1, 2])]).cpu().numpy()]
@@ -209,7 +209,7 @@ def test_cli_generate_matches_the_api(model_folders, capsys):
     assert main(["generate", folder, "-p", "1 2 3", "-n", "400", "--dtype", "float32"]) == 2   # over the context
 
 
-@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16"), ("C", "bfloat16")])
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16"), ("C", "bfloat16"), ("D", "bfloat16")])
 def test_graph_replay_equals_eager_steps(model_folders, name, dtype):
     # the same generation with captured decode graphs and with eager launches; budgets differ so
     # the batch shrinks and other graph sizes come into play; a second round reuses the graphs

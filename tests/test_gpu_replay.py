@@ -59,7 +59,7 @@ def build_trace(requests):
     return steps, expect
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run(model_folders, tmp_path, name, dtype):
     folder = model_folders(name, dtype)

@@ -1,6 +1,7 @@
 """Tiny Llama configurations for the tests.  They differ in every size and option: head
 counts and groups (GQA, MQA, MHA), head sizes, widths that are no power of two, layer
-counts, vocabulary, eps, rope base, rope scaling, pairing, tied head, biases."""
+counts, vocabulary, eps, rope base, rope scaling, pairing, tied head, biases.  "D" has the head
+size and widths at which the bfloat16 engine runs its tensor-core and TMA kernels."""
 import numpy as np
 
 import cpp_minilamma_b200 as ml
@@ -23,8 +24,14 @@ TINY = {
               num_attention_heads=3, num_key_value_heads=3, head_dim=48, max_position_embeddings=1024,
               rope_theta=1000.0, rope_scaling=None, rope_interleaved=False, rms_norm_eps=3e-4,
               tie_word_embeddings=False, attention_bias=True, eos_token_id=None),
+    # 2 layers, GQA 4/2, head 64: the head size that the tensor-core attention kernels take; widths that
+    # the TMA-fed linear kernels take (multiples of 8), interleaved pairs, tied
+    "D": dict(vocab_size=300, hidden_size=256, intermediate_size=328, num_hidden_layers=2,
+              num_attention_heads=4, num_key_value_heads=2, head_dim=64, max_position_embeddings=512,
+              rope_theta=20000.0, rope_scaling=None, rope_interleaved=True, rms_norm_eps=2e-5,
+              tie_word_embeddings=True, eos_token_id=7),
 }
-SEEDS = {"A": 0, "B": 1, "C": 2}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
 
 
 def config(name, storage="float32"):
