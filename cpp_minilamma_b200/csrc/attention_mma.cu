@@ -29,7 +29,23 @@ struct DecodeMmaArgs {
   float scale;
   Prefetch pf;
   int* counters;                 // optional [B, gridDim.y], zero between launches: the last split merges
+  // fused variant: q, k and v of the step's token come straight from the projection's output;
+  // the kernel rotates them and writes the new key and value row into the cache itself
+  const __nv_bfloat16* qkv;      // [B, ld]: q heads, k heads, v heads
+  const float* cos_table;        // [max_pos, d/2] or null (positions not encoded)
+  const float* sin_table;
+  __nv_bfloat16* k_write;        // the caches again, writable (null: this layer reads another layer's cache)
+  __nv_bfloat16* v_write;
+  int qkv_ld, interleaved;
 };
+
+__device__ __forceinline__ float2 unpack_bf162(unsigned r) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r));
+}
+__device__ __forceinline__ unsigned pack_bf162(float x, float y) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(x, y);
+  return *reinterpret_cast<unsigned*>(&v);
+}
 
 __device__ __forceinline__ void cp_async16_zfill(void* smem, const void* gmem, bool valid) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -61,8 +77,12 @@ struct DecodeMmaSmem {
   static constexpr size_t BYTES = (size_t)STAGES * 2 * TILE * 2 + 16 * P_STRIDE * 2 + 2 * 4 * 16 * sizeof(float);
 };
 
-// grid (B, Hk * head_chunks, n_splits); 128 threads.
-template <int D, int STAGES>
+// grid (B, Hk * head_chunks, n_splits); 128 threads.  FUSED: the rotary encoding and the cache
+// write of the step's token happen here instead of in a kernel of their own (one launch less
+// per layer): every block rotates its query heads in registers; the block whose pages include
+// the sequence's last one rotates the new key, puts it and the new value into its shared-memory
+// copy of that page and into the cache.
+template <int D, int STAGES, bool FUSED>
 __global__ void __launch_bounds__(128)
 attn_decode_mma_kernel(DecodeMmaArgs a) {
   mll::pdl_begin_long();
@@ -95,20 +115,6 @@ attn_decode_mma_kernel(DecodeMmaArgs a) {
   const int p_end = min(pages_total, p_begin + per_split);
   const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_blocks;
 
-  // query fragments (A operand), rows = heads of this chunk, zero beyond ng
-  unsigned qf[KSTEPS][4];
-  {
-    const __nv_bfloat16* q0 = a.q + ((size_t)b * a.n_heads + h0) * D;
-#pragma unroll
-    for (int ks = 0; ks < KSTEPS; ++ks) {
-      const int col = ks * 16 + 2 * t;
-      qf[ks][0] = g < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + col) : 0u;
-      qf[ks][1] = g + 8 < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + col) : 0u;
-      qf[ks][2] = g < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + col + 8) : 0u;
-      qf[ks][3] = g + 8 < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + col + 8) : 0u;
-    }
-  }
-
   constexpr int CPR = D / 8;  // 16-byte chunks per key row
   auto load_page = [&](int page_index, int stage) {
     const int page = table[page_index];
@@ -136,6 +142,77 @@ attn_decode_mma_kernel(DecodeMmaArgs a) {
     if (s < n_pages) load_page(p_begin + s, s);
     cp_async_commit();
   }
+  // FUSED: the block whose pages include the sequence's last one fetches the new key pair and
+  // value pair of its kv head now (one pair per thread), long before the page comes up
+  const bool owns_new_row = FUSED && a.k_write != nullptr && ctx > 0 && p_begin <= pages_total - 1 &&
+                            pages_total - 1 < p_end;
+  __nv_bfloat16 new_k0 = __float2bfloat16_rn(0.f), new_k1 = new_k0;
+  unsigned new_v = 0;
+  if (owns_new_row && tid < D / 2) {
+    const __nv_bfloat16* k_in = a.qkv + (size_t)b * a.qkv_ld + (size_t)(a.n_heads + kvh) * D;
+    const __nv_bfloat16* v_in = k_in + (size_t)a.n_kv_heads * D;
+    const int e0 = a.interleaved ? 2 * tid : tid, e1 = a.interleaved ? 2 * tid + 1 : tid + D / 2;
+    const float x0 = __bfloat162float(k_in[e0]), x1 = __bfloat162float(k_in[e1]);
+    new_v = *reinterpret_cast<const unsigned*>(v_in + 2 * tid);
+    float y0 = x0, y1 = x1;
+    if (a.cos_table != nullptr) {
+      const float c = a.cos_table[(size_t)(ctx - 1) * (D / 2) + tid], sv = a.sin_table[(size_t)(ctx - 1) * (D / 2) + tid];
+      y0 = x0 * c - x1 * sv;
+      y1 = x0 * sv + x1 * c;
+    }
+    new_k0 = __float2bfloat16_rn(y0);
+    new_k1 = __float2bfloat16_rn(y1);
+  }
+
+  // the first pages are on their way: the queries' latency hides behind theirs
+  // query fragments (A operand), rows = heads of this chunk, zero beyond ng
+  unsigned qf[KSTEPS][4];
+  {
+    const __nv_bfloat16* q0 = FUSED ? a.qkv + (size_t)b * a.qkv_ld + (size_t)h0 * D
+                                    : a.q + ((size_t)b * a.n_heads + h0) * D;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      const int col = ks * 16 + 2 * t;
+      qf[ks][0] = g < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + col) : 0u;
+      qf[ks][1] = g + 8 < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + col) : 0u;
+      qf[ks][2] = g < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + col + 8) : 0u;
+      qf[ks][3] = g + 8 < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + col + 8) : 0u;
+    }
+    if (FUSED && a.cos_table != nullptr && ctx > 0) {
+      // the token's position is ctx - 1 for every head; registers [2j] and [2j + 1] hold rows g and
+      // g + 8 at columns col + 8 j, col + 8 j + 1
+      const float* cs = a.cos_table + (size_t)(ctx - 1) * (D / 2);
+      const float* sn = a.sin_table + (size_t)(ctx - 1) * (D / 2);
+      if (a.interleaved) {  // pairs (2i, 2i + 1): both halves of a pair sit in one register
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks)
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int pair = ks * 8 + t + 4 * j;
+            const float c = cs[pair], sv = sn[pair];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+              const float2 x = unpack_bf162(qf[ks][2 * j + r]);
+              qf[ks][2 * j + r] = pack_bf162(x.x * c - x.y * sv, x.x * sv + x.y * c);
+            }
+          }
+      } else {  // pairs (i, i + d/2): the partner sits in the same place of k-step ks + KSTEPS / 2
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS / 2; ++ks)
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int i0 = ks * 16 + 2 * t + 8 * j;
+            const float c0 = cs[i0], s0 = sn[i0], c1 = cs[i0 + 1], s1 = sn[i0 + 1];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+              const float2 lo = unpack_bf162(qf[ks][2 * j + r]), hi = unpack_bf162(qf[ks + KSTEPS / 2][2 * j + r]);
+              qf[ks][2 * j + r] = pack_bf162(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);
+              qf[ks + KSTEPS / 2][2 * j + r] = pack_bf162(lo.x * s0 + hi.x * c0, lo.y * s1 + hi.y * c1);
+            }
+          }
+      }
+    }
+  }
 
   for (int it = 0; it < n_pages; ++it) {
     const int p = p_begin + it;
@@ -146,6 +223,23 @@ attn_decode_mma_kernel(DecodeMmaArgs a) {
 
     const __nv_bfloat16* kt = kv_s + (size_t)(it % STAGES) * 2 * L::TILE;
     const __nv_bfloat16* vt = kt + L::TILE;
+    if (FUSED && owns_new_row && p == pages_total - 1) {
+      // the step's token lies in this page: its key (rotated) and value replace whatever the cache held
+      const int row = (ctx - 1) % MLL_PAGE;
+      if (tid < D / 2) {
+        __nv_bfloat16* k_row = kv_s + (size_t)(it % STAGES) * 2 * L::TILE + row * L::STRIDE;
+        __nv_bfloat16* v_row = k_row + L::TILE;
+        const size_t cache_row = (((size_t)table[p] * a.n_kv_heads + kvh) * MLL_PAGE + row) * D;
+        const int e0 = a.interleaved ? 2 * tid : tid, e1 = a.interleaved ? 2 * tid + 1 : tid + D / 2;
+        k_row[e0] = new_k0;
+        k_row[e1] = new_k1;
+        a.k_write[cache_row + e0] = new_k0;
+        a.k_write[cache_row + e1] = new_k1;
+        *reinterpret_cast<unsigned*>(v_row + 2 * tid) = new_v;
+        *reinterpret_cast<unsigned*>(a.v_write + cache_row + 2 * tid) = new_v;
+      }
+      __syncthreads();
+    }
 
     // scores of the 16 heads against this warp's 16 keys: two n-tiles of 8 keys
     float s_acc[2][4];
@@ -341,10 +435,10 @@ attn_decode_mma_kernel(DecodeMmaArgs a) {
   }
 }
 
-template <int D, int STAGES>
+template <int D, int STAGES, bool FUSED>
 int launch_decode_mma(const DecodeMmaArgs& a, int n_seqs, cudaStream_t stream) {
   const size_t smem = DecodeMmaSmem<D, STAGES>::BYTES;
-  auto kernel = attn_decode_mma_kernel<D, STAGES>;
+  auto kernel = attn_decode_mma_kernel<D, STAGES, FUSED>;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (err != cudaSuccess) {
     mll_set_error("attention decode (mma): cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
@@ -600,10 +694,42 @@ MLL_API int mll_attn_decode_mma(const void* q, const void* k_cache, const void* 
                        seq_slot, seq_ctx, block_table, scratch,
                        scratch ? scratch + (size_t)n_seqs * n_heads * n_splits * head_dim : nullptr,
                        (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, n_splits, window, scale,
-                       mll::Prefetch{prefetch_ptr, prefetch_ptr ? (unsigned long long)prefetch_bytes : 0ull}, counters};
-  if (head_dim == 64) return mll::launch_decode_mma<64, 3>(a, n_seqs, stream);
-  if (head_dim == 128) return mll::launch_decode_mma<128, 3>(a, n_seqs, stream);
-  return mll::launch_decode_mma<256, 2>(a, n_seqs, stream);
+                       mll::Prefetch{prefetch_ptr, prefetch_ptr ? (unsigned long long)prefetch_bytes : 0ull}, counters,
+                       nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0};
+  if (head_dim == 64) return mll::launch_decode_mma<64, 3, false>(a, n_seqs, stream);
+  if (head_dim == 128) return mll::launch_decode_mma<128, 3, false>(a, n_seqs, stream);
+  return mll::launch_decode_mma<256, 2, false>(a, n_seqs, stream);
+}
+
+// The decode step's rotary encoding, cache write and attention in one launch: qkv [B, ld] holds
+// the projection's output (q heads, then k heads, then v heads; no bias pending), row i
+// belongs to sequence i, whose new token has position seq_ctx[i] - 1.  cos/sin: float32
+// [max_pos, head_dim / 2] or null; write_kv = 0 for a layer that reads another layer's cache.
+// Otherwise the contract of mll_attn_decode_mma.
+MLL_API int mll_attn_decode_mma_fused(const void* qkv, int qkv_ld, const float* cos_table, const float* sin_table,
+                                      int interleaved, int write_kv, void* k_cache, void* v_cache,
+                                      const int* seq_slot, const int* seq_ctx, const int* block_table, float* scratch,
+                                      void* out, int n_seqs, int n_heads, int n_kv_heads, int head_dim, int max_blocks,
+                                      int n_splits, int window, float scale, int* counters, cudaStream_t stream) {
+  MLL_REQUIRE(mll_attn_decode_mma_supported(MLL_BF16, head_dim), "attention decode (fused): head_dim %d", head_dim);
+  MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention decode (fused): bad head counts");
+  MLL_REQUIRE(n_seqs >= 0 && n_splits >= 1 && n_splits <= 65535, "attention decode (fused): bad batch or split count");
+  MLL_REQUIRE(n_splits == 1 || scratch != nullptr, "attention decode (fused): %d splits need scratch memory", n_splits);
+  MLL_REQUIRE(qkv_ld >= (n_heads + (write_kv ? 2 * n_kv_heads : 0)) * head_dim && qkv_ld % 2 == 0,
+              "attention decode (fused): row stride %d shorter than the q/k/v columns", qkv_ld);
+  MLL_REQUIRE((cos_table == nullptr) == (sin_table == nullptr), "attention decode (fused): one rotary table is missing");
+  if (n_seqs == 0) return 0;
+  mll::DecodeMmaArgs a{nullptr, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
+                       seq_slot, seq_ctx, block_table, scratch,
+                       scratch ? scratch + (size_t)n_seqs * n_heads * n_splits * head_dim : nullptr,
+                       (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, n_splits, window, scale,
+                       mll::Prefetch{nullptr, 0ull}, counters,
+                       (const __nv_bfloat16*)qkv, cos_table, sin_table,
+                       write_kv ? (__nv_bfloat16*)k_cache : nullptr, write_kv ? (__nv_bfloat16*)v_cache : nullptr,
+                       qkv_ld, interleaved};
+  if (head_dim == 64) return mll::launch_decode_mma<64, 3, true>(a, n_seqs, stream);
+  if (head_dim == 128) return mll::launch_decode_mma<128, 3, true>(a, n_seqs, stream);
+  return mll::launch_decode_mma<256, 2, true>(a, n_seqs, stream);
 }
 
 MLL_API int mll_attn_prefill_mma_supported(int dtype, int head_dim) {

@@ -25,7 +25,7 @@ int mll_pdl_enabled = 0;
 MLL_API void mll_set_pdl(int enabled) { mll_pdl_enabled = enabled ? 1 : 0; }
 
 // Identifies the build; the Python side checks it after loading the library.
-MLL_API int mll_abi_version() { return 12; }
+MLL_API int mll_abi_version() { return 13; }
 
 namespace mll {
 

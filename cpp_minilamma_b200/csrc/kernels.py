@@ -15,7 +15,7 @@ import torch
 from .build import KernelBuildError, load_library
 
 PAGE = 64  # cache positions per page; equals MLL_PAGE in common.cuh
-ABI_VERSION = 12
+ABI_VERSION = 13
 MAX_TOP_K = 1024
 
 
@@ -412,6 +412,59 @@ def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratc
                                  ctypes.c_int(head_dim), ctypes.c_int(block_table.shape[1]),
                                  ctypes.c_int(n_splits), ctypes.c_int(window), ctypes.c_float(scale),
                                  _stream()), "attention_decode", kernels=2 if n_splits > 1 else 1)
+
+
+USE_FUSED_DECODE = True  # off: rotary encoding and cache write stay a kernel of their own in decode steps
+
+
+def attention_decode_fused_supported(dtype: torch.dtype, head_dim: int) -> bool:
+    """Whether a decode step's rotary encoding, cache write and attention can be one launch."""
+    return bool(USE_FUSED_DECODE and USE_TENSOR_CORE_DECODE
+                and lib().mll_attn_decode_mma_supported(dtype_code(dtype), head_dim))
+
+
+def attention_decode_fused(qkv, cos, sin, interleaved: bool, write_kv: bool, k_cache, v_cache, seq_slot, seq_ctx,
+                           block_table, scratch, out, n_seqs: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                           n_splits: int, window: int, scale: float, counters: Optional[torch.Tensor] = None) -> None:
+    """Decode step: row i of qkv [B, (Hq + 2 Hk) d] is sequence i's new token at position seq_ctx[i] - 1.
+    Rotates q and k (tables as for rope_cache_write, or None), writes k and v into the paged cache and
+    attends over it, in one launch (bfloat16, head_dim 64/128/256)."""
+    _need(qkv, "attention qkv", torch.bfloat16, 2)
+    _need(out, "attention out", torch.bfloat16, 2)
+    _need(k_cache, "attention k_cache", torch.bfloat16, 4)
+    _need(v_cache, "attention v_cache", torch.bfloat16, 4)
+    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or k_cache.shape != v_cache.shape:
+        raise KernelError(f"attention: cache shape {tuple(k_cache.shape)} is not [pages, {n_kv_heads}, {PAGE}, {head_dim}]")
+    if out.shape[1] != n_heads * head_dim or qkv.shape[1] < (n_heads + (2 * n_kv_heads if write_kv else 0)) * head_dim:
+        raise KernelError("attention decode (fused): qkv/out width differs from the heads")
+    for name, t in (("seq_slot", seq_slot), ("seq_ctx", seq_ctx)):
+        _need(t, f"attention {name}", torch.int32, 1)
+    _need(block_table, "attention block_table", torch.int32, 2)
+    if min(qkv.shape[0], out.shape[0], seq_slot.shape[0], seq_ctx.shape[0]) < n_seqs:
+        raise KernelError("attention decode (fused): an input has fewer rows than sequences")
+    if cos is not None:
+        _need(cos, "rope cos", torch.float32, 2)
+        _need(sin, "rope sin", torch.float32, 2)
+        if cos.shape[1] != head_dim // 2 or sin.shape != cos.shape:
+            raise KernelError(f"rope: table {tuple(cos.shape)} does not match head_dim {head_dim}")
+    if n_splits > 1:
+        _need(scratch, "attention scratch", torch.float32)
+        if scratch.numel() < attention_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits):
+            raise KernelError("attention decode: scratch too small for the split count")
+        if counters is None:
+            raise KernelError("attention decode (fused): splits need arrival counters")
+        _need(counters, "attention counters", torch.int32, 1)
+        if counters.shape[0] < n_seqs * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16):
+            raise KernelError("attention decode: counters shorter than sequences x kv heads x head chunks")
+    _check(lib().mll_attn_decode_mma_fused(_ptr(qkv), ctypes.c_int(qkv.shape[1]), _ptr(cos), _ptr(sin),
+                                           ctypes.c_int(int(interleaved)), ctypes.c_int(int(write_kv)), _ptr(k_cache),
+                                           _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx), _ptr(block_table),
+                                           _ptr(scratch), _ptr(out), ctypes.c_int(n_seqs), ctypes.c_int(n_heads),
+                                           ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim),
+                                           ctypes.c_int(block_table.shape[1]), ctypes.c_int(n_splits),
+                                           ctypes.c_int(window), ctypes.c_float(scale),
+                                           _ptr(counters if n_splits > 1 else None), _stream()),
+           "attention_decode (fused)")
 
 
 def attention_prefill(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0,

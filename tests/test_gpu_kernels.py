@@ -260,6 +260,62 @@ def test_attention_decode_window_edge(dtype, window, decode_impl):
                                        err_msg=f"seq {b}")
 
 
+@pytest.mark.parametrize("hq,hk,d", [(32, 8, 128), (8, 1, 256), (16, 16, 64), (40, 2, 64), (5, 5, 128)])
+@pytest.mark.parametrize("interleaved", [True, False])
+@pytest.mark.parametrize("splits,window", [(1, 0), (3, 0), (2, 70)])
+@pytest.mark.parametrize("encoded", [True, False])
+def test_attention_decode_fused_with_rope_and_cache_write(hq, hk, d, interleaved, splits, window, encoded):
+    """One launch (rotate q and k, write k and v, attend) against the separate kernels and the plain
+    reference.  The slot of the new token holds NaN before the call, here and in the separate path."""
+    dtype = torch.bfloat16
+    ctx = [1, 63, 64, 65, 300, 129]
+    B = len(ctx)
+    case = PagedCase(ctx, hk, d, dtype, seed=hq + d)
+    width = (hq + 2 * hk) * d
+    qkv = rnd((B, width), dtype, 21)
+    inv = pl.rope_inverse_frequencies(d, 10000.0)
+    ang = np.arange(400)[:, None] * inv[None, :]
+    cos = torch.tensor(np.cos(ang), dtype=torch.float32, device=DEV) if encoded else None
+    sin = torch.tensor(np.sin(ang), dtype=torch.float32, device=DEV) if encoded else None
+    pos = np.array([c - 1 for c in ctx], dtype=np.int32)
+    # the plain reference: the new token's k (rotated) and v replace the last cached position
+    x = as64(qkv)
+    rot = (lambda t: pl.apply_rope(t, pos, inv, interleaved)) if encoded else (lambda t: t)
+    q_ref = as64(torch.tensor(rot(x[:, :hq * d].reshape(B, hq, d))).to(dtype))
+    k_new = as64(torch.tensor(rot(x[:, hq * d:(hq + hk) * d].reshape(B, hk, d))).to(dtype))
+    v_new = x[:, (hq + hk) * d:].reshape(B, hk, d)
+    table = case.table.numpy()
+    for b, c in enumerate(ctx):   # poison the new token's place
+        page, off = table[case.slots[b], (c - 1) // PAGE], (c - 1) % PAGE
+        case.k_cache[page, :, off] = float("nan")
+        case.v_cache[page, :, off] = float("nan")
+    kc, vc, slots, ctx_t, table_d = case.dev()
+    scratch = torch.empty(K.attention_decode_scratch_floats(B, hq, d, splits), dtype=torch.float32, device=DEV)
+    counters = torch.zeros(B * hk * (-(-(hq // hk) // 16)), dtype=torch.int32, device=DEV)
+    out = torch.full((B, hq * d), float("nan"), dtype=dtype, device=DEV)
+    K.attention_decode_fused(qkv.to(DEV), cos, sin, interleaved, True, kc, vc, slots, ctx_t, table_d, scratch, out,
+                             B, hq, hk, d, splits, window, 1.0 / math.sqrt(d), counters=counters)
+    assert int(counters.abs().sum()) == 0
+    # separate kernels on a second copy of the cache
+    kc2, vc2, _, _, _ = case.dev()
+    i32 = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=DEV)
+    q2 = torch.empty((B, hq * d), dtype=dtype, device=DEV)
+    K.rope_cache_write(qkv.to(DEV), None, cos, sin, i32(pos), i32(np.arange(B)), slots, table_d, q2, kc2, vc2, hq, hk, d,
+                       interleaved)
+    out2 = torch.empty_like(out)
+    K.attention_decode(q2, kc2, vc2, slots, ctx_t, table_d, scratch, out2, B, hq, hk, d, splits, window,
+                       1.0 / math.sqrt(d), counters=counters)
+    same = lambda a, b: torch.equal(a.view(torch.int16), b.view(torch.int16))
+    assert same(kc, kc2) and same(vc, vc2)          # the cache, bit for bit (NaN places included)
+    for b, c in enumerate(ctx):
+        k_all = np.concatenate([as64(case.k[b])[:c - 1], k_new[b:b + 1]])
+        v_all = np.concatenate([as64(case.v[b])[:c - 1], v_new[b:b + 1]])
+        ref = pl.causal_attention(q_ref[b:b + 1], k_all, v_all, q_positions=[c - 1], window=window or None)
+        np.testing.assert_allclose(as64(out[b]).reshape(hq, d), ref[0], **attention_tol(dtype, "tensor_core", v_all),
+                                   err_msg=f"seq {b} ctx {c}")
+    np.testing.assert_allclose(as64(out), as64(out2), rtol=1.6e-2, atol=2.0 ** -8 * float(np.abs(v_new).max() + 4))
+
+
 @pytest.fixture(params=["tcgen05", "tensor_core", "general"])
 def prefill_impl(request):
     """tcgen05: the TMA/tensor-memory kernel (head sizes 64 and 128, else the next one);
