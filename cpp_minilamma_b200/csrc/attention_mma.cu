@@ -115,9 +115,15 @@ attn_decode_mma_kernel(DecodeMmaArgs a) {
   const int p_end = min(pages_total, p_begin + per_split);
   const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_blocks;
 
+  // The block's page numbers, fetched ahead into a ring of 256 entries: a lookup in global
+  // memory right before each page's copies would put one more memory latency into every iteration.
+  __shared__ int page_ids[256];
+  for (int j = tid; j < min(p_end - p_begin, 256); j += 128) page_ids[j] = table[p_begin + j];
+  __syncthreads();
+
   constexpr int CPR = D / 8;  // 16-byte chunks per key row
   auto load_page = [&](int page_index, int stage) {
-    const int page = table[page_index];
+    const int page = page_ids[(page_index - p_begin) & 255];
     const size_t base = ((size_t)page * a.n_kv_heads + kvh) * MLL_PAGE * D;
     __nv_bfloat16* kd = kv_s + (size_t)stage * 2 * L::TILE;
     __nv_bfloat16* vd = kd + L::TILE;
@@ -220,6 +226,10 @@ attn_decode_mma_kernel(DecodeMmaArgs a) {
     __syncthreads();              // ... for every thread's copies; and all warps are done with page it - 1
     if (it + STAGES - 1 < n_pages) load_page(p + STAGES - 1, (it + STAGES - 1) % STAGES);
     cp_async_commit();
+    if ((it & 127) == 0 && it > 0) {  // entries it + 128 .. it + 255 take the places of pages long done
+      const int j = it + 128 + tid;
+      if (j < n_pages) page_ids[j & 255] = table[p_begin + j];
+    }
 
     const __nv_bfloat16* kt = kv_s + (size_t)(it % STAGES) * 2 * L::TILE;
     const __nv_bfloat16* vt = kt + L::TILE;
@@ -229,7 +239,7 @@ attn_decode_mma_kernel(DecodeMmaArgs a) {
       if (tid < D / 2) {
         __nv_bfloat16* k_row = kv_s + (size_t)(it % STAGES) * 2 * L::TILE + row * L::STRIDE;
         __nv_bfloat16* v_row = k_row + L::TILE;
-        const size_t cache_row = (((size_t)table[p] * a.n_kv_heads + kvh) * MLL_PAGE + row) * D;
+        const size_t cache_row = (((size_t)page_ids[it & 255] * a.n_kv_heads + kvh) * MLL_PAGE + row) * D;
         const int e0 = a.interleaved ? 2 * tid : tid, e1 = a.interleaved ? 2 * tid + 1 : tid + D / 2;
         k_row[e0] = new_k0;
         k_row[e1] = new_k1;

@@ -204,9 +204,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
   const unsigned tmem_base = *tmem_slot;
   const unsigned tmem_row = tmem_base + ((unsigned)(warp * 32) << 16);
 
-  auto load_page = [&](int i) {  // thread 0: keys and values of the block's i-th page into stage i % 2
+  auto load_page = [&](int i, int page) {  // thread 0: keys and values of the block's i-th page into stage i % 2
     const int st = i & 1;
-    const int page = table[p_first + i];
     const int row = (page * a.n_kv_heads + kvh) * MLL_PAGE;
     a_mbar_expect_tx(bar_k + 8 * st, L::KV_BYTES);
     a_mbar_expect_tx(bar_v + 8 * st, L::KV_BYTES);
@@ -229,12 +228,14 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
   };
 
   bool ok = true;
+  int next_page = 0;
   if (tid == 0) {
     a_mbar_expect_tx(bar_q, L::Q_BYTES);
 #pragma unroll
     for (int b = 0; b < DB; ++b) a_tma_load_2d(q_s + b * (A_ROWS * 128), &qmap, h * D + b * 64, qstart + row0, bar_q);
-    load_page(0);
-    if (n_pages > 1) load_page(1);
+    load_page(0, table[p_first]);
+    if (n_pages > 1) load_page(1, table[p_first + 1]);
+    if (n_pages > 2) next_page = table[p_first + 2];  // looked up one iteration before its loads are issued
     ok = a_mbar_wait(bar_q, 0) && a_mbar_wait(bar_k, 0);
     a_fence_after();
     if (ok) issue_s(0);
@@ -338,7 +339,10 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
 #pragma unroll
       for (int j = 0; j < 32; ++j) o[c + j] = fmaf(o[c + j], alpha, t[j]);
     }
-    if (tid == 0 && ok && i + 2 < n_pages) load_page(i + 2);  // both products of page i are complete
+    if (tid == 0 && ok && i + 2 < n_pages) {  // both products of page i are complete
+      load_page(i + 2, next_page);
+      if (i + 3 < n_pages) next_page = table[p_first + i + 3];
+    }
     __syncwarp();
   }
   a_fence_before();
