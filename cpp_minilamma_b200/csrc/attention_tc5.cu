@@ -134,25 +134,58 @@ __device__ __forceinline__ float a_exp2(float x) {
   return y;
 }
 
+// 32 consecutive 32-bit columns of this thread's lane, written from registers
+__device__ __forceinline__ void a_tmem_st32(unsigned addr, const unsigned* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void a_tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D[tmem] (+)= A[tmem] . B[smem]: the A operand (M = 128 rows in the 128 lanes, 16 bfloat16 of K
+// packed in 8 columns) comes from tensor memory
+__device__ __forceinline__ void a_umma_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long desc_b, unsigned idesc,
+                                          unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void a_mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+constexpr int A_THREADS = 192;       // warps 0-3: one query row per thread; warp 4: TMA loads; warp 5: MMAs
+constexpr float A_RESCALE_STEP = 8.f;  // the output is rescaled only when a row's maximum grows by more than 2^8
+
 template <int D>
 struct PrefillTc5Smem {
   static constexpr int Q_BYTES = A_ROWS * D * 2;       // D / 64 boxes of [128 rows x 128 bytes]
   static constexpr int KV_BYTES = MLL_PAGE * D * 2;    // D / 64 boxes of [64 rows x 128 bytes]
-  static constexpr int P_BYTES = A_ROWS * MLL_PAGE * 2;
-  static constexpr int Q_OFF = 0, K_OFF = Q_BYTES, V_OFF = K_OFF + 2 * KV_BYTES, P_OFF = V_OFF + 2 * KV_BYTES;
-  static constexpr int BAR_OFF = P_OFF + P_BYTES;
-  // Two blocks per multiprocessor: 2 x (BYTES + 1 KB that the system keeps per block) must stay
-  // within 227 KB, which leaves no room for alignment slack: the kernel checks that its dynamic
-  // shared memory starts on a 1024-byte boundary (the swizzle's period) and refuses otherwise.
-  // Never three blocks: their tensor memory would not fit.
-  static constexpr size_t USED = (size_t)BAR_OFF + 128;
+  static constexpr int Q_OFF = 0, K_OFF = Q_BYTES, V_OFF = K_OFF + 2 * KV_BYTES;
+  static constexpr int BAR_OFF = V_OFF + 2 * KV_BYTES;
+  // Two blocks per multiprocessor (their tensor memory: 2 x 256 columns); never three: the request
+  // is padded above a third of the shared memory.  The kernel checks that its dynamic shared
+  // memory starts on a 1024-byte boundary (the swizzle's period) and refuses otherwise.
+  static constexpr size_t USED = (size_t)BAR_OFF + 256;
   static constexpr size_t BYTES = USED > 80 * 1024 ? USED : 80 * 1024;
-  static constexpr int TMEM_COLS = 256;                // S: 2 x 64, O: up to 128
+  static constexpr int TMEM_COLS = 256;                // S / P: 2 x 64, O: up to 128
   static constexpr int O_COL = 128;
 };
 
+// barrier slots
+enum : int { AB_Q = 0, AB_K_FULL = 1, AB_V_FULL = 3, AB_K_EMPTY = 5, AB_V_EMPTY = 7, AB_S_FULL = 9, AB_P_READY = 11,
+             AB_PV_DONE = 13, AB_COUNT = 15 };
+
 template <int D>
-__global__ void __launch_bounds__(A_ROWS, 2)
+__global__ void __launch_bounds__(A_THREADS, 2)
 attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                         const __grid_constant__ CUtensorMap vmap, PrefillTc5Args a) {
   using L = PrefillTc5Smem<D>;
@@ -170,14 +203,17 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
     return;
   }
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(base + L::BAR_OFF);
-  // barriers: 0 query, 1-2 keys of stage 0/1, 3-4 values, 5-6 S buffers, 7 O
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 8);
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + AB_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + AB_COUNT) + 1;
   const unsigned q_s = a_smem(base + L::Q_OFF), k_s = a_smem(base + L::K_OFF), v_s = a_smem(base + L::V_OFF);
-  const unsigned p_s = a_smem(base + L::P_OFF);
-  const unsigned bar_q = a_smem(bars), bar_k = a_smem(bars + 1), bar_v = a_smem(bars + 3), bar_s = a_smem(bars + 5);
-  const unsigned bar_o = a_smem(bars + 7);
+  auto bar = [&](int slot, int index) { return a_smem(bars + slot + index); };
+  // a wait that gives up makes every later wait of the block return at once
+  auto wait = [&](unsigned barrier, unsigned parity) {
+    if (*abort_flag) return;
+    if (!a_mbar_wait(barrier, parity)) *abort_flag = 1;
+  };
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int seq = a.tile_seq[tile];
   const int h = blockIdx.x % a.n_heads;
   const int kvh = h / (a.n_heads / a.n_kv_heads);
@@ -190,10 +226,12 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
   const int n_pages = p_last - p_first + 1;
 
   if (tid == 0) {
-    for (int i = 0; i < 8; ++i) a_mbar_init(a_smem(bars + i), 1);
+    for (int i = 0; i < AB_COUNT; ++i)
+      a_mbar_init(a_smem(bars + i), (i == AB_P_READY || i == AB_P_READY + 1) ? A_ROWS : 1);
+    *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 0) {
+  if (warp == 5) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(a_smem(tmem_slot)),
                  "r"((unsigned)L::TMEM_COLS));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
@@ -202,169 +240,182 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
   __syncthreads();
   a_fence_after();
   const unsigned tmem_base = *tmem_slot;
-  const unsigned tmem_row = tmem_base + ((unsigned)(warp * 32) << 16);
 
-  auto load_page = [&](int i, int page) {  // thread 0: keys and values of the block's i-th page into stage i % 2
-    const int st = i & 1;
-    const int row = (page * a.n_kv_heads + kvh) * MLL_PAGE;
-    a_mbar_expect_tx(bar_k + 8 * st, L::KV_BYTES);
-    a_mbar_expect_tx(bar_v + 8 * st, L::KV_BYTES);
+  if (warp == 4) {
+    // ---- loads: the query tile once, then key and value pages into a two-stage ring -------- //
+    if (lane == 0) {
+      a_mbar_expect_tx(bar(AB_Q, 0), L::Q_BYTES);
 #pragma unroll
-    for (int b = 0; b < DB; ++b) {
-      a_tma_load_2d(k_s + st * L::KV_BYTES + b * (MLL_PAGE * 128), &kmap, b * 64, row, bar_k + 8 * st);
-      a_tma_load_2d(v_s + st * L::KV_BYTES + b * (MLL_PAGE * 128), &vmap, b * 64, row, bar_v + 8 * st);
-    }
-  };
-  auto issue_s = [&](int i) {  // thread 0: S[i % 2] = Q K_i^T
-    constexpr unsigned idesc = a_idesc(A_ROWS, MLL_PAGE, false);
-    const unsigned kt = k_s + (i & 1) * L::KV_BYTES;
+      for (int b = 0; b < DB; ++b)
+        a_tma_load_2d(q_s + b * (A_ROWS * 128), &qmap, h * D + b * 64, qstart + row0, bar(AB_Q, 0));
+      int page = table[p_first];
+      for (int i = 0; i < n_pages && !*abort_flag; ++i) {
+        const int st = i & 1;
+        const unsigned parity = ((i >> 1) & 1) ^ 1;  // the stage's previous use (none for the first two pages)
+        const int row = (page * a.n_kv_heads + kvh) * MLL_PAGE;
+        if (i + 1 < n_pages) page = table[p_first + i + 1];  // looked up while this page's loads fly
+        wait(bar(AB_K_EMPTY, st), parity);
+        a_mbar_expect_tx(bar(AB_K_FULL, st), L::KV_BYTES);
 #pragma unroll
-    for (int b = 0; b < DB; ++b)
+        for (int b = 0; b < DB; ++b)
+          a_tma_load_2d(k_s + st * L::KV_BYTES + b * (MLL_PAGE * 128), &kmap, b * 64, row, bar(AB_K_FULL, st));
+        wait(bar(AB_V_EMPTY, st), parity);
+        a_mbar_expect_tx(bar(AB_V_FULL, st), L::KV_BYTES);
 #pragma unroll
-      for (int k = 0; k < 4; ++k)
-        a_umma(tmem_base + (i & 1) * MLL_PAGE, a_desc(q_s + b * (A_ROWS * 128) + k * 32, 16),
-               a_desc(kt + b * (MLL_PAGE * 128) + k * 32, 16), idesc, (b > 0 || k > 0) ? 1u : 0u);
-    a_commit(bar_s + 8 * (i & 1));
-  };
-
-  bool ok = true;
-  int next_page = 0;
-  if (tid == 0) {
-    a_mbar_expect_tx(bar_q, L::Q_BYTES);
-#pragma unroll
-    for (int b = 0; b < DB; ++b) a_tma_load_2d(q_s + b * (A_ROWS * 128), &qmap, h * D + b * 64, qstart + row0, bar_q);
-    load_page(0, table[p_first]);
-    if (n_pages > 1) load_page(1, table[p_first + 1]);
-    if (n_pages > 2) next_page = table[p_first + 2];  // looked up one iteration before its loads are issued
-    ok = a_mbar_wait(bar_q, 0) && a_mbar_wait(bar_k, 0);
-    a_fence_after();
-    if (ok) issue_s(0);
-  }
-
-  float o[D];
-#pragma unroll
-  for (int c = 0; c < D; ++c) o[c] = 0.f;
-  float m_run = -INFINITY, l_run = 0.f;
-  const int qpos = pos0 + tid;
-  bool failed = false;
-
-  for (int i = 0; i < n_pages; ++i) {
-    const int st = i & 1;
-    ok = a_mbar_wait(bar_s + 8 * st, (i >> 1) & 1) && ok;
-    a_fence_after();
-    if (tid == 0 && i + 1 < n_pages) {  // the next page's product runs under this page's softmax
-      ok = a_mbar_wait(bar_k + 8 * (st ^ 1), ((i + 1) >> 1) & 1) && ok;
-      a_fence_after();
-      if (ok) issue_s(i + 1);
-    }
-    __syncwarp();
-
-    float s[MLL_PAGE];
-    a_tmem_ld32(tmem_row + st * MLL_PAGE, s);
-    a_tmem_ld32(tmem_row + st * MLL_PAGE + 32, s + 32);
-    const int k0 = (p_first + i) * MLL_PAGE;
-    const bool needs_mask = (k0 + MLL_PAGE - 1 > pos0) || a.window > 0 || rows < A_ROWS;
-    if (needs_mask) {
-#pragma unroll
-      for (int c = 0; c < MLL_PAGE; ++c) {
-        const int kpos = k0 + c;
-        const bool keep = tid < rows && kpos <= qpos && (a.window <= 0 || kpos > qpos - a.window);
-        s[c] = keep ? s[c] : -INFINITY;
+        for (int b = 0; b < DB; ++b)
+          a_tma_load_2d(v_s + st * L::KV_BYTES + b * (MLL_PAGE * 128), &vmap, b * 64, row, bar(AB_V_FULL, st));
       }
     }
-    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains instead of one
+  } else if (warp == 5) {
+    // ---- MMAs: S_{i+1} = Q K_{i+1}^T is issued before O += P_i V_i, so it runs under softmax i //
+    if (lane == 0) {
+      constexpr unsigned idesc_s = a_idesc(A_ROWS, MLL_PAGE, false), idesc_o = a_idesc(A_ROWS, D, true);
+      auto issue_s = [&](int i) {
+        const unsigned kt = k_s + (i & 1) * L::KV_BYTES;
 #pragma unroll
-    for (int c = 0; c < MLL_PAGE; c += 4) {
-      mx4[0] = fmaxf(mx4[0], s[c]);
-      mx4[1] = fmaxf(mx4[1], s[c + 1]);
-      mx4[2] = fmaxf(mx4[2], s[c + 2]);
-      mx4[3] = fmaxf(mx4[3], s[c + 3]);
-    }
-    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-    const float m_new = fmaxf(m_run, mx * a.scale_log2);
-    const float shift = m_new > -INFINITY ? m_new : 0.f;  // a fully masked row stays at zero weight
-    const float alpha = a_exp2(m_run - shift);
-    float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-    unsigned packed[MLL_PAGE / 2];
+        for (int b = 0; b < DB; ++b)
 #pragma unroll
-    for (int c = 0; c < MLL_PAGE; c += 2) {
-      const float p0 = a_exp2(fmaf(s[c], a.scale_log2, -shift)), p1 = a_exp2(fmaf(s[c + 1], a.scale_log2, -shift));
-      sum4[(c >> 1) & 3] += p0 + p1;
-      __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
-      packed[c >> 1] = *reinterpret_cast<unsigned*>(&pair);
-    }
-    l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-    m_run = m_new;
-    {  // row tid of P: eight 16-byte chunks, chunk index xor (row % 8)
-      const unsigned row_addr = p_s + (tid >> 3) * 1024 + (tid & 7) * 128;
-#pragma unroll
-      for (int c = 0; c < 8; ++c)
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + ((c ^ (tid & 7)) << 4)),
-                     "r"(packed[4 * c]), "r"(packed[4 * c + 1]), "r"(packed[4 * c + 2]), "r"(packed[4 * c + 3])
-                     : "memory");
-    }
-    const int valid = ctx - k0;  // positions of this page that the sequence has
-    if (valid < MLL_PAGE) {      // only the sequence's last page: the rest of it may hold anything
-      ok = a_mbar_wait(bar_v + 8 * st, (i >> 1) & 1) && ok;
-      unsigned char* vt = base + L::V_OFF + st * L::KV_BYTES;
-      const int n_chunks = (MLL_PAGE - valid) * 8;  // 16-byte chunks per box
-      for (int b = 0; b < DB; ++b)
-        for (int c = tid; c < n_chunks; c += A_ROWS)
-          *reinterpret_cast<uint4*>(vt + b * (MLL_PAGE * 128) + valid * 128 + c * 16) = make_uint4(0, 0, 0, 0);
-    }
-    a_fence_async_smem();
-    a_fence_before();
-    failed = __syncthreads_or(!ok);
-    if (failed) break;
-    if (tid == 0) {
-      ok = a_mbar_wait(bar_v + 8 * st, (i >> 1) & 1);
+          for (int k = 0; k < 4; ++k)
+            a_umma(tmem_base + (i & 1) * MLL_PAGE, a_desc(q_s + b * (A_ROWS * 128) + k * 32, 16),
+                   a_desc(kt + b * (MLL_PAGE * 128) + k * 32, 16), idesc_s, (b > 0 || k > 0) ? 1u : 0u);
+        a_commit(bar(AB_S_FULL, i & 1));
+        a_commit(bar(AB_K_EMPTY, i & 1));
+      };
+      wait(bar(AB_Q, 0), 0);
+      wait(bar(AB_K_FULL, 0), 0);
       a_fence_after();
-      if (ok) {
-        constexpr unsigned idesc = a_idesc(A_ROWS, D, true);
+      if (!*abort_flag) issue_s(0);
+      for (int i = 0; i < n_pages && !*abort_flag; ++i) {
+        const int st = i & 1;
+        if (i + 1 < n_pages) {
+          // S[(i + 1) % 2] held P of page i - 1: the MMAs of one thread run in order, and that
+          // page's P V was issued before
+          wait(bar(AB_K_FULL, st ^ 1), ((i + 1) >> 1) & 1);
+          a_fence_after();
+          if (!*abort_flag) issue_s(i + 1);
+        }
+        wait(bar(AB_P_READY, st), (i >> 1) & 1);
+        wait(bar(AB_V_FULL, st), (i >> 1) & 1);
+        a_fence_after();
+        if (*abort_flag) break;
         const unsigned vt = v_s + st * L::KV_BYTES;
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          a_umma(tmem_base + L::O_COL, a_desc(p_s + k * 32, 16), a_desc(vt + k * (16 * 128), MLL_PAGE * 128), idesc,
-                 k > 0 ? 1u : 0u);
-        a_commit(bar_o);
+        for (int k = 0; k < 4; ++k)  // P: 16 keys = 8 packed columns per step
+          a_umma_ts(tmem_base + L::O_COL, tmem_base + st * MLL_PAGE + k * 8, a_desc(vt + k * (16 * 128), MLL_PAGE * 128),
+                    idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+        a_commit(bar(AB_PV_DONE, st));
+        a_commit(bar(AB_V_EMPTY, st));
       }
     }
-    __syncwarp();
-    ok = a_mbar_wait(bar_o, i & 1) && ok;
+  } else {
+    // ---- softmax: thread tid owns query row tid = lane tid of tensor memory ---------------- //
+    const unsigned tmem_row = tmem_base + ((unsigned)(warp * 32) << 16);
+    const int qpos = pos0 + tid;
+    float m_used = -INFINITY, l_run = 0.f;  // the maximum that P and O are scaled by; the sum
+    for (int i = 0; i < n_pages; ++i) {
+      const int st = i & 1;
+      wait(bar(AB_S_FULL, st), (i >> 1) & 1);
+      a_fence_after();
+      float s[MLL_PAGE];
+      a_tmem_ld32(tmem_row + st * MLL_PAGE, s);
+      a_tmem_ld32(tmem_row + st * MLL_PAGE + 32, s + 32);
+      const int k0 = (p_first + i) * MLL_PAGE;
+      const bool needs_mask = (k0 + MLL_PAGE - 1 > pos0) || a.window > 0 || rows < A_ROWS;
+      if (needs_mask) {
+#pragma unroll
+        for (int c = 0; c < MLL_PAGE; ++c) {
+          const int kpos = k0 + c;
+          const bool keep = tid < rows && kpos <= qpos && (a.window <= 0 || kpos > qpos - a.window);
+          s[c] = keep ? s[c] : -INFINITY;
+        }
+      }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < MLL_PAGE; c += 4) {
+        mx4[0] = fmaxf(mx4[0], s[c]);
+        mx4[1] = fmaxf(mx4[1], s[c + 1]);
+        mx4[2] = fmaxf(mx4[2], s[c + 2]);
+        mx4[3] = fmaxf(mx4[3], s[c + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;
+      // P and O stay scaled by m_used while the row's maximum is within 2^8 of it: exact all the
+      // same (O / l does not depend on the scale), and O in tensor memory is touched only rarely
+      const bool moved = mx > m_used + A_RESCALE_STEP || (m_used == -INFINITY && mx > -INFINITY);
+      if (i > 0 && __any_sync(0xffffffffu, moved)) {
+        const float alpha = moved ? a_exp2(m_used - mx) : 1.f;
+        wait(bar(AB_PV_DONE, st ^ 1), ((i - 1) >> 1) & 1);  // O holds every page before this one
+        a_fence_after();
+#pragma unroll
+        for (int c = 0; c < D; c += 32) {
+          float t[32];
+          a_tmem_ld32(tmem_row + L::O_COL + c, t);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) t[j] *= alpha;
+          a_tmem_st32(tmem_row + L::O_COL + c, reinterpret_cast<const unsigned*>(t));
+        }
+        l_run *= alpha;
+      }
+      if (moved) m_used = mx;
+      const float shift = m_used > -INFINITY ? m_used : 0.f;  // a fully masked row stays at zero weight
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      unsigned packed[MLL_PAGE / 2];
+#pragma unroll
+      for (int c = 0; c < MLL_PAGE; c += 2) {
+        const float p0 = a_exp2(fmaf(s[c], a.scale_log2, -shift)), p1 = a_exp2(fmaf(s[c + 1], a.scale_log2, -shift));
+        sum4[(c >> 1) & 3] += p0 + p1;
+        __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
+        packed[c >> 1] = *reinterpret_cast<unsigned*>(&pair);
+      }
+      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      a_tmem_st32(tmem_row + st * MLL_PAGE, packed);  // P over the first half of S
+      const int valid = ctx - k0;  // positions of this page that the sequence has
+      if (valid < MLL_PAGE) {      // only the sequence's last page: the rest of it may hold anything
+        wait(bar(AB_V_FULL, st), (i >> 1) & 1);
+        unsigned char* vt = base + L::V_OFF + st * L::KV_BYTES;
+        const int n_chunks = (MLL_PAGE - valid) * 8;  // 16-byte chunks per box
+        for (int b = 0; b < DB; ++b)
+          for (int c = tid; c < n_chunks; c += A_ROWS)
+            *reinterpret_cast<uint4*>(vt + b * (MLL_PAGE * 128) + valid * 128 + c * 16) = make_uint4(0, 0, 0, 0);
+        a_fence_async_smem();
+      }
+      a_tmem_wait_st();
+      a_fence_before();
+      a_mbar_arrive(bar(AB_P_READY, st));
+    }
+    // the output row: O / l
+    wait(bar(AB_PV_DONE, (n_pages - 1) & 1), ((n_pages - 1) >> 1) & 1);
     a_fence_after();
+    {
+      // tcgen05.ld is a warp-wide instruction: every thread of the warp reads its lane, and only the
+      // threads that own a row of the sequence store
+      const bool store = !*abort_flag && tid < rows;
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* dst = a.out + ((size_t)qstart + row0 + (store ? tid : 0)) * a.n_heads * D + (size_t)h * D;
 #pragma unroll
-    for (int c = 0; c < D; c += 32) {
-      float t[32];
-      a_tmem_ld32(tmem_row + L::O_COL + c, t);
+      for (int c = 0; c < D; c += 32) {
+        float t[32];
+        a_tmem_ld32(tmem_row + L::O_COL + c, t);
+        if (store) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) o[c + j] = fmaf(o[c + j], alpha, t[j]);
+          for (int j = 0; j < 32; j += 8) {
+            uint4 w;
+            __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) hp[e] = __floats2bfloat162_rn(t[j + 2 * e] * inv, t[j + 2 * e + 1] * inv);
+            *reinterpret_cast<uint4*>(dst + c + j) = w;
+          }
+        }
+      }
     }
-    if (tid == 0 && ok && i + 2 < n_pages) {  // both products of page i are complete
-      load_page(i + 2, next_page);
-      if (i + 3 < n_pages) next_page = table[p_first + i + 3];
-    }
-    __syncwarp();
   }
-  a_fence_before();
-  if (!failed) failed = __syncthreads_or(!ok);
 
-  if (!failed && tid < rows) {
-    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-    __nv_bfloat16* dst = a.out + ((size_t)qstart + row0 + tid) * a.n_heads * D + (size_t)h * D;
-#pragma unroll
-    for (int c = 0; c < D; c += 8) {
-      uint4 w;
-      __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&w);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) hp[j] = __floats2bfloat162_rn(o[c + 2 * j] * inv, o[c + 2 * j + 1] * inv);
-      *reinterpret_cast<uint4*>(dst + c) = w;
-    }
-  }
-  if (failed) {  // loads may still be in flight: give them time before the shared memory is given up
+  a_fence_before();
+  __syncthreads();
+  if (*abort_flag && tid == 0) {  // loads may still be in flight: give them time before the shared memory goes
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
   }
   __syncthreads();
-  if (warp == 0) {
+  if (warp == 5) {
     a_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)L::TMEM_COLS));
   }
@@ -381,7 +432,7 @@ int launch_prefill_tc5(const CUtensorMap& qmap, const CUtensorMap& kmap, const C
                   cudaGetErrorString(err));
     return (int)err;
   }
-  MLL_LAUNCH((kernel), dim3((unsigned)(n_tiles * a.n_heads)), A_ROWS, smem, stream, qmap, kmap, vmap, a);
+  MLL_LAUNCH((kernel), dim3((unsigned)(n_tiles * a.n_heads)), A_THREADS, smem, stream, qmap, kmap, vmap, a);
   MLL_LAUNCH_CHECK();
   return 0;
 }
