@@ -2,6 +2,8 @@
 each request alone and whole; with the last 32 tokens one by one; in batches of unequal
 lengths whose shorter requests end earlier, one batch after another so that slots are
 used again; long decoding; the first tokens of a sequence.  In float32 and bfloat16."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -226,3 +228,51 @@ def test_graph_replay_equals_eager_steps(model_folders, name, dtype):
             assert [c.tokens for c in replayed] == [c.tokens for c in eager]
         assert backend.graphs.replays > 0
     llm.engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_context_chunked_prefill_then_decode(tmp_path, dtype):
+    """5,000 prompt tokens (80 pages) in chunks of 2,048 that continue from the cache, then
+    single-token steps whose attention is split 16 ways over the context; head size 128.  Random
+    weights spread attention evenly, which would hide a wrong page or a lost split, so one early
+    position gets a key that every later query prefers (one token id that stands at position 70 only)."""
+    import plain_llama as pl
+    raw = dict(vocab_size=160, hidden_size=128, intermediate_size=200, num_hidden_layers=2, num_attention_heads=2,
+               num_key_value_heads=1, head_dim=128, max_position_embeddings=8192, rope_theta=1.0e6,
+               rope_interleaved=False, rms_norm_eps=1e-5, tie_word_embeddings=False, architectures=["LlamaForCausalLM"],
+               torch_dtype=dtype)
+    cfg = ml.config_from_dict(raw)
+    folder = str(tmp_path / "long")
+    ml.write_random_model(cfg, folder, seed=11, matrix_std=0.05, norm_std=0.1)
+    rng = np.random.RandomState(5)
+    marked = 159
+    tokens = [int(t) for t in rng.randint(0, marked, size=5040)]   # the marked id appears once
+    tokens[70] = marked
+    # Plant the key (the file is rewritten; the engine and the plain implementation read it afterwards).
+    # RMSNorm removes an embedding's length, so the mark is a direction: every token gets a
+    # common component on hidden dim 0, the marked token one on dim 1; layer 0's query rows for
+    # head dim 63 read dim 0, its key row for dim 63 reads dim 1.  Dim 63 pairs with 127 at the
+    # lowest rotary frequency (1e6 ** (-63/64) per position): the product survives 5,000 positions.
+    from cpp_minilamma_b200.weights.safetensors_io import write_safetensors
+    _, weights = pl.read_model_folder(folder)
+    storage = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+    tensors = {name: torch.tensor(np.asarray(w, dtype=np.float32)) for name, w in weights.items()}
+    tensors["model.embed_tokens.weight"][:, 0] += 3.0
+    tensors["model.embed_tokens.weight"][marked, 1] += 8.0
+    for head in range(2):
+        tensors["model.layers.0.self_attn.q_proj.weight"][head * 128 + 63, 0] += 4.0
+    tensors["model.layers.0.self_attn.k_proj.weight"][63, 1] += 4.0
+    write_safetensors(os.path.join(folder, "model.safetensors"), {n: t.to(storage) for n, t in tensors.items()},
+                      {"format": "pt"})
+    ref = plain_logits(folder, tokens, dtype)
+    llm = ml.load(folder, dtype=dtype, max_tokens=64 * 90, max_seqs=2, max_step_tokens=2048)
+    slot, = llm.engine.acquire(1)
+    want = [0, 69, 70, 71, 2047, 2048, 4095, 4096, 4999]
+    rows = [llm.engine.step([StepEntry(slot, tokens[:5000], want)]).cpu().numpy()]
+    for t in range(5000, 5040):
+        rows.append(llm.engine.step([StepEntry(slot, [tokens[t]], [0])]).cpu().numpy())
+    llm.engine.release(slot)
+    assert_close(np.concatenate(rows), ref[want + list(range(5000, 5040))], dtype, "long context")
+    # the planted key does carry weight: without position 70 the last logits differ visibly
+    cut = plain_logits(folder, tokens[:70] + tokens[71:], dtype)
+    assert np.abs(cut[-1] - ref[-1]).max() > 0.02 * np.abs(ref[-1]).max()
