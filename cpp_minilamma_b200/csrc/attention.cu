@@ -69,7 +69,6 @@ struct Vec16<__nv_bfloat16> {
 template <typename T, int NACC>
 __global__ void __launch_bounds__(128)
 attn_decode_kernel(AttnArgs a, int two_stage) {
-  mll::pdl_begin();
   constexpr int PAD = 16 / sizeof(T);
   constexpr int VN = Vec16<T>::N;
   const int d = a.head_dim;
@@ -242,7 +241,6 @@ attn_decode_kernel(AttnArgs a, int two_stage) {
 // grid (B * Hq), merges the splits of one (sequence, head) in a fixed order.
 template <typename T>
 __global__ void attn_combine_kernel(AttnArgs a) {
-  mll::pdl_begin();
   const int bh = blockIdx.x;
   const int d = a.head_dim, S = a.n_splits;
   const float* ml = a.part_ml + (size_t)bh * S * 2;
@@ -270,7 +268,6 @@ __global__ void attn_combine_kernel(AttnArgs a) {
 template <typename T, int DT>
 __global__ void __launch_bounds__(256)
 attn_prefill_kernel(AttnArgs a) {
-  mll::pdl_begin();
   constexpr int BM = 64, BN = MLL_PAGE;
   const int d = a.head_dim;
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;

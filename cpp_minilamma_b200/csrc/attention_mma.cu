@@ -27,7 +27,6 @@ struct DecodeMmaArgs {
   __nv_bfloat16* out;            // [B, Hq * d]
   int n_heads, n_kv_heads, max_blocks, n_splits, window;
   float scale;
-  Prefetch pf;
   int* counters;                 // optional [B, gridDim.y], zero between launches: the last split merges
   // fused variant: q, k and v of the step's token come straight from the projection's output;
   // the kernel rotates them and writes the new key and value row into the cache itself
@@ -85,8 +84,6 @@ struct DecodeMmaSmem {
 template <int D, int STAGES, bool FUSED>
 __global__ void __launch_bounds__(128)
 attn_decode_mma_kernel(DecodeMmaArgs a) {
-  mll::pdl_begin_long();
-  l2_prefetch_by_grid(a.pf);
   using L = DecodeMmaSmem<D, STAGES>;
   constexpr int KSTEPS = D / 16;       // k-steps of the score product
   constexpr int NT_OUT = D / 32;       // value n-tiles (8 columns) per warp
@@ -354,7 +351,6 @@ attn_decode_mma_kernel(DecodeMmaArgs a) {
     }
   }
   cp_async_wait<0>();
-  pdl_launch_dependents();
 
   // rows g and g + 8 of the tile are heads h0 + g and h0 + g + 8; this thread holds columns
   // warp * D/4 + n * 8 + 2 t + {0, 1}
@@ -495,7 +491,6 @@ struct PrefillMmaSmem {
 template <int D>
 __global__ void __launch_bounds__(128, 3)
 attn_prefill_mma_kernel(PrefillMmaArgs a) {
-  mll::pdl_begin();
   using L = PrefillMmaSmem<D>;
   constexpr int KSTEPS = D / 16;
   constexpr int NT_OUT = D / 8;
@@ -693,7 +688,7 @@ MLL_API int mll_attn_decode_mma_supported(int dtype, int head_dim) {
 MLL_API int mll_attn_decode_mma(const void* q, const void* k_cache, const void* v_cache, const int* seq_slot,
                                 const int* seq_ctx, const int* block_table, float* scratch, void* out, int n_seqs,
                                 int n_heads, int n_kv_heads, int head_dim, int max_blocks, int n_splits, int window,
-                                float scale, const void* prefetch_ptr, long long prefetch_bytes, int* counters,
+                                float scale, int* counters,
                                 cudaStream_t stream) {
   MLL_REQUIRE(mll_attn_decode_mma_supported(MLL_BF16, head_dim), "attention decode (mma): head_dim %d", head_dim);
   MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention decode (mma): bad head counts");
@@ -704,7 +699,7 @@ MLL_API int mll_attn_decode_mma(const void* q, const void* k_cache, const void* 
                        seq_slot, seq_ctx, block_table, scratch,
                        scratch ? scratch + (size_t)n_seqs * n_heads * n_splits * head_dim : nullptr,
                        (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, n_splits, window, scale,
-                       mll::Prefetch{prefetch_ptr, prefetch_ptr ? (unsigned long long)prefetch_bytes : 0ull}, counters,
+                       counters,
                        nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0};
   if (head_dim == 64) return mll::launch_decode_mma<64, 3, false>(a, n_seqs, stream);
   if (head_dim == 128) return mll::launch_decode_mma<128, 3, false>(a, n_seqs, stream);
@@ -733,7 +728,7 @@ MLL_API int mll_attn_decode_mma_fused(const void* qkv, int qkv_ld, const float* 
                        seq_slot, seq_ctx, block_table, scratch,
                        scratch ? scratch + (size_t)n_seqs * n_heads * n_splits * head_dim : nullptr,
                        (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, n_splits, window, scale,
-                       mll::Prefetch{nullptr, 0ull}, counters,
+                       counters,
                        (const __nv_bfloat16*)qkv, cos_table, sin_table,
                        write_kv ? (__nv_bfloat16*)k_cache : nullptr, write_kv ? (__nv_bfloat16*)v_cache : nullptr,
                        qkv_ld, interleaved};

@@ -190,7 +190,6 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
                         const __grid_constant__ CUtensorMap vmap, PrefillTc5Args a) {
   using L = PrefillTc5Smem<D>;
   constexpr int DB = D / 64;  // 64-column boxes per row of Q, K or V
-  mll::pdl_begin();
   // later tiles of a sequence see more keys: they go first, so that the short ones fill the tail
   const int tile = (gridDim.x - 1 - blockIdx.x) / a.n_heads;   // all heads of a tile are neighbours
   const int row0 = a.tile_row0[tile];

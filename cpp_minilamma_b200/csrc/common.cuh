@@ -29,10 +29,7 @@ void mll_set_error(const char* fmt, ...);
     }                                 \
   } while (0)
 
-// Launches `kernel` on `stream`; with programmatic dependent launch switched on
-// (mll_set_pdl) the launch may begin while the previous kernel of the stream is still
-// draining: every kernel of this library calls pdl_wait() before it touches anything that
-// an earlier kernel wrote or still reads.  The outcome is picked up by MLL_LAUNCH_CHECK.
+// Launches `kernel` on `stream`; the outcome is picked up by MLL_LAUNCH_CHECK.
 #define MLL_LAUNCH(kernel, grid, block, smem, stream, ...) \
   mll_launch_status = mll::launch_kernel(kernel, dim3(grid), dim3(block), (size_t)(smem), stream, ##__VA_ARGS__)
 
@@ -48,7 +45,6 @@ void mll_set_error(const char* fmt, ...);
   } while (0)
 
 extern thread_local cudaError_t mll_launch_status;
-extern int mll_pdl_enabled;
 
 namespace mll {
 
@@ -60,54 +56,7 @@ inline cudaError_t launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 
   config.blockDim = block;
   config.dynamicSmemBytes = smem;
   config.stream = stream;
-  cudaLaunchAttribute attr[1];
-  if (mll_pdl_enabled) {
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    config.attrs = attr;
-    config.numAttrs = 1;
-  }
   return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
-}
-
-// Programmatic dependent launch: let the next kernel of the stream start its prologue now,
-// and wait until everything earlier kernels wrote is complete and visible.  Both are
-// no-ops for a kernel that was launched without the attribute.
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-// Start of a short kernel: nothing to overlap, so it lets the next kernel launch right away
-// and waits for its own inputs.  Longer kernels call pdl_launch_dependents() after their main
-// loop instead, so that the next kernel's prologue overlaps their tail and not their body.
-__device__ __forceinline__ void pdl_begin() {
-  pdl_launch_dependents();
-  pdl_wait();
-}
-__device__ __forceinline__ void pdl_begin_long() { pdl_wait(); }
-
-// A range of global memory (weights that a later kernel of the step will stream) that the
-// blocks of a latency-bound kernel ask the L2 cache to fetch while they do their own work.
-// Decode steps alternate kernels that wait on latencies with kernels that wait on HBM; the
-// hints keep HBM busy during the former.  ptr is 16-byte aligned, bytes a multiple of 16.
-struct Prefetch {
-  const void* ptr;
-  unsigned long long bytes;
-};
-
-// Called by one thread per block: block `block` of `blocks` requests every blocks-th 16 KB chunk.
-__device__ __forceinline__ void l2_prefetch_chunks(const Prefetch& pf, unsigned block, unsigned blocks) {
-  constexpr unsigned long long kChunk = 16384;
-  const unsigned long long chunks = (pf.bytes + kChunk - 1) / kChunk;
-  for (unsigned long long c = block; c < chunks; c += blocks) {
-    const unsigned long long off = c * kChunk;
-    const unsigned size = (unsigned)(pf.bytes - off < kChunk ? pf.bytes - off : kChunk);
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"((const char*)pf.ptr + off), "r"(size) : "memory");
-  }
-}
-__device__ __forceinline__ void l2_prefetch_by_grid(const Prefetch& pf) {
-  if (pf.bytes == 0 || threadIdx.x != 0 || threadIdx.y != 0 || threadIdx.z != 0) return;
-  const unsigned blocks = gridDim.x * gridDim.y * gridDim.z;
-  const unsigned block = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-  l2_prefetch_chunks(pf, block, blocks);
 }
 
 __device__ __forceinline__ float to_float(float v) { return v; }

@@ -19,13 +19,9 @@ void mll_set_error(const char* fmt, ...) {
 MLL_API const char* mll_last_error() { return g_error; }
 
 thread_local cudaError_t mll_launch_status = cudaSuccess;
-int mll_pdl_enabled = 0;
-
-// Switches programmatic dependent launch on (1) or off (0) for every later launch of this library.
-MLL_API void mll_set_pdl(int enabled) { mll_pdl_enabled = enabled ? 1 : 0; }
 
 // Identifies the build; the Python side checks it after loading the library.
-MLL_API int mll_abi_version() { return 13; }
+MLL_API int mll_abi_version() { return 14; }
 
 namespace mll {
 
@@ -33,7 +29,6 @@ namespace mll {
 template <typename TableT>
 __global__ void embedding_kernel(const int* __restrict__ tokens, const TableT* __restrict__ table,
                                  float* __restrict__ x, int width) {
-  mll::pdl_begin();
   const int t = blockIdx.x;
   const TableT* row = table + (size_t)tokens[t] * width;
   float* out = x + (size_t)t * width;
@@ -42,7 +37,6 @@ __global__ void embedding_kernel(const int* __restrict__ tokens, const TableT* _
 
 template <typename In, typename Out>
 __global__ void cast_kernel(const In* __restrict__ in, Out* __restrict__ out, size_t n) {
-  mll::pdl_begin();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; i < n; i += stride) out[i] = from_float<Out>(to_float(in[i]));
@@ -54,7 +48,6 @@ __global__ void cast_kernel(const In* __restrict__ in, Out* __restrict__ out, si
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int tokens,
                               int inter, int block) {
-  mll::pdl_begin();
   const size_t total = (size_t)tokens * inter;
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -113,7 +106,6 @@ struct Pack8<float> {
 
 template <typename T>
 __global__ void swiglu_vec8_kernel(const T* __restrict__ gu, T* __restrict__ out, int tokens, int inter, int block) {
-  mll::pdl_begin();
   const int groups = inter >> 3;
   const size_t total = (size_t)tokens * groups;
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -135,29 +127,12 @@ __global__ void swiglu_vec8_kernel(const T* __restrict__ gu, T* __restrict__ out
 // x[t, i] += bias[i] (bias float32, sum in float32)
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ x, const float* __restrict__ bias, size_t total, int width) {
-  mll::pdl_begin();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; idx < total; idx += stride) x[idx] = from_float<T>(to_float(x[idx]) + bias[idx % width]);
 }
 
-// Only asks the L2 cache to fetch a range (see Prefetch in common.cuh).
-__global__ void l2_prefetch_kernel(Prefetch pf) {
-  mll::pdl_begin();
-  l2_prefetch_by_grid(pf);
-}
-
 }  // namespace mll
-
-// Asks the L2 cache to fetch `bytes` from `ptr` (16-byte aligned, multiple of 16) with `blocks` blocks.
-MLL_API int mll_l2_prefetch(const void* ptr, long long bytes, int blocks, cudaStream_t stream) {
-  MLL_REQUIRE(ptr != nullptr && bytes >= 0 && blocks > 0, "l2_prefetch: bad arguments");
-  MLL_REQUIRE(((uintptr_t)ptr % 16 == 0) && bytes % 16 == 0, "l2_prefetch: range must be 16-byte aligned");
-  if (bytes == 0) return 0;
-  MLL_LAUNCH((mll::l2_prefetch_kernel), blocks, 32, 0, stream, mll::Prefetch{ptr, (unsigned long long)bytes});
-  MLL_LAUNCH_CHECK();
-  return 0;
-}
 
 MLL_API int mll_add_bias(void* x, const float* bias, int dtype, int n_rows, int width, cudaStream_t stream) {
   MLL_REQUIRE(n_rows >= 0 && width > 0, "add_bias: bad sizes rows=%d width=%d", n_rows, width);

@@ -7,7 +7,6 @@ implementation behind them.  Argument faults raise `KernelError` before any laun
 from __future__ import annotations
 
 import ctypes
-import os
 from typing import Optional
 
 import torch
@@ -15,7 +14,7 @@ import torch
 from .build import KernelBuildError, load_library
 
 PAGE = 64  # cache positions per page; equals MLL_PAGE in common.cuh
-ABI_VERSION = 13
+ABI_VERSION = 14
 MAX_TOP_K = 1024
 
 
@@ -38,15 +37,7 @@ def lib() -> ctypes.CDLL:
                 f"kernel library reports ABI {handle.mll_abi_version()}, the package expects {ABI_VERSION}; "
                 "remove csrc/_build and rebuild")
         _lib = handle
-        # Programmatic dependent launch is off unless MLL_PDL=1: measured on the 8B decode graph it
-        # made a step slower (5.8 ms against 4.0 ms), so it stays an experiment.
-        handle.mll_set_pdl(1 if os.environ.get("MLL_PDL", "0") == "1" else 0)
     return _lib
-
-
-def set_pdl(enabled: bool) -> None:
-    """Programmatic dependent launch for every later launch of this library (default off)."""
-    lib().mll_set_pdl(1 if enabled else 0)
 
 
 launches = 0  # kernels of this library launched so far (counted per successful call)
@@ -77,25 +68,6 @@ def _need(t: torch.Tensor, name: str, dtype=None, ndim=None) -> None:
         raise KernelError(f"{name}: expected {dtype}, got {t.dtype}")
     if ndim is not None and t.dim() != ndim:
         raise KernelError(f"{name}: expected {ndim} dimensions, got shape {tuple(t.shape)}")
-
-
-def hint(tensor: Optional[torch.Tensor], start_mb: float = 0.0, size_mb: float = 32.0):
-    """A prefetch hint: `size_mb` MiB of `tensor` from `start_mb` on, as (pointer, bytes), or None.
-    Kernels that take a hint ask the L2 cache to fetch that range while they run."""
-    if tensor is None:
-        return None
-    total = tensor.numel() * tensor.element_size()
-    start = int(start_mb * (1 << 20)) & ~15
-    size = min(int(size_mb * (1 << 20)), total - start) & ~15
-    if size <= 0:
-        return None
-    return (tensor.data_ptr() + start, size)
-
-
-def _hint_args(prefetch):
-    if prefetch is None:
-        return ctypes.c_void_p(0), ctypes.c_longlong(0)
-    return ctypes.c_void_p(prefetch[0]), ctypes.c_longlong(prefetch[1])
 
 
 def dtype_code(dtype: torch.dtype) -> int:
@@ -144,7 +116,7 @@ def linear_small_supported(rows: int, out_features: int, in_features: int, epilo
 
 
 def linear_small(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-                 epilogue: int = EPI_BF16, ranks: int = 0, prefetch=None) -> None:
+                 epilogue: int = EPI_BF16, ranks: int = 0) -> None:
     """out = x . w^T for at most 64 rows of bfloat16 x [M, K] and bfloat16 w [N, K], read once.
 
     epilogue EPI_BF16 / EPI_F32: out [M, N] in that dtype (+ float32 bias [N]);
@@ -164,7 +136,7 @@ def linear_small(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
         if bias.shape[0] != n:
             raise KernelError("linear_small: bias length differs from the output width")
     _check(lib().mll_linear_small(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), ctypes.c_int(rows), ctypes.c_int(n),
-                                  ctypes.c_int(k), ctypes.c_int(epilogue), ctypes.c_int(ranks), *_hint_args(prefetch),
+                                  ctypes.c_int(k), ctypes.c_int(epilogue), ctypes.c_int(ranks),
                                   _stream()), "linear_small")
 
 
@@ -256,14 +228,14 @@ def small_linear_kind(rows: int, out_features: int, in_features: int, epilogue: 
     return ""
 
 
-def small_linear(x, w, bias, out, epilogue: int = EPI_BF16, prefetch=None) -> bool:
+def small_linear(x, w, bias, out, epilogue: int = EPI_BF16) -> bool:
     kind = small_linear_kind(x.shape[0], w.shape[0], w.shape[1], epilogue)
     if kind == "tc5":
         linear_tc5(x, w, bias, out, epilogue)
     elif kind == "tma":
         linear_tma(x, w, bias, out, epilogue, 1 if x.shape[0] > 8 else 0)
     elif kind == "direct":
-        linear_small(x, w, bias, out, epilogue, prefetch=prefetch)
+        linear_small(x, w, bias, out, epilogue)
     return bool(kind)
 
 
@@ -282,7 +254,7 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int) -> None:
 
 
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
-                eps: float, rows: Optional[torch.Tensor] = None, prefetch=None) -> None:
+                eps: float, rows: Optional[torch.Tensor] = None) -> None:
     """x += delta (float32 residual, in place); out = rmsnorm(x) * weight.
 
     With `rows` (int32 [n]) only those rows of x are normalised into out [n, D] and x is
@@ -306,12 +278,12 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
         raise KernelError(f"rmsnorm: out has {out.shape[0]} rows, expected {n_rows}")
     _check(lib().mll_add_rmsnorm(_ptr(x), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows),
                                  dtype_code(out.dtype), ctypes.c_int(n_rows), ctypes.c_int(width),
-                                 ctypes.c_float(eps), *_hint_args(prefetch), _stream()), "rmsnorm")
+                                 ctypes.c_float(eps), _stream()), "rmsnorm")
 
 
 def rope_cache_write(qkv, bias, cos, sin, tok_pos, tok_seq, seq_slot, block_table, q_out, k_cache, v_cache,
                      n_heads: int, n_kv_heads: int, head_dim: int, interleaved: bool,
-                     write_kv: bool = True, prefetch=None) -> None:
+                     write_kv: bool = True) -> None:
     """Rotate q and k of qkv [T, (Hq + 2 Hk) d], write q to q_out [T, Hq d] and k, v into the
     paged cache [n_pages, Hk, PAGE, d] at each token's slot and position."""
     _need(qkv, "rope qkv", None, 2)
@@ -344,7 +316,7 @@ def rope_cache_write(qkv, bias, cos, sin, tok_pos, tok_seq, seq_slot, block_tabl
                                 dtype_code(qkv.dtype), ctypes.c_int(n), ctypes.c_int(qkv.shape[1]),
                                 ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim),
                                 ctypes.c_int(block_table.shape[1]), ctypes.c_int(int(interleaved)),
-                                ctypes.c_int(int(write_kv)), *_hint_args(prefetch), _stream()), "rope_cache_write")
+                                ctypes.c_int(int(write_kv)), _stream()), "rope_cache_write")
 
 
 def _check_attention(q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim):
@@ -374,7 +346,7 @@ USE_TCGEN05_PREFILL = True      # off: the mma.sync kernel takes the tensor-core
 
 def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch, out, n_seqs: int,
                      n_heads: int, n_kv_heads: int, head_dim: int, n_splits: int, window: int,
-                     scale: float, prefetch=None, counters: Optional[torch.Tensor] = None) -> None:
+                     scale: float, counters: Optional[torch.Tensor] = None) -> None:
     """One query token per sequence (q row i belongs to sequence i) over the paged cache.
     bfloat16 with head_dim 64/128/256 runs on tensor cores, everything else on the general kernel."""
     _check_attention(q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim)
@@ -398,7 +370,7 @@ def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratc
                                          _ptr(block_table), _ptr(scratch), _ptr(out), ctypes.c_int(n_seqs),
                                          ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim),
                                          ctypes.c_int(block_table.shape[1]), ctypes.c_int(n_splits),
-                                         ctypes.c_int(window), ctypes.c_float(scale), *_hint_args(prefetch),
+                                         ctypes.c_int(window), ctypes.c_float(scale),
                                          _ptr(counters if n_splits > 1 else None), _stream()),
                "attention_decode (tensor cores)")
         if n_splits > 1 and counters is None:

@@ -28,7 +28,6 @@ struct LinearArgs {
   const float* bias;       // optional [N]
   void* out;               // [M, N] (EPI_SWIGLU: [M, N / 2])
   int M, N, K, epilogue, chunks_per_warp;
-  Prefetch pf;
 };
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
@@ -58,7 +57,6 @@ template <int NT, bool CLUSTER, int LS_UNROLL, int LS_WARPS>
 __global__ void __launch_bounds__(LS_WARPS * 32)
 linear_small_kernel(LinearArgs a) {
   __shared__ float red[LS_WARPS][16][8 * NT];
-  l2_prefetch_by_grid(a.pf);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   int rank = 0, ranks = 1;
@@ -91,7 +89,6 @@ linear_small_kernel(LinearArgs a) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
 
-  pdl_wait();
   int c = first;
   for (; c + LS_UNROLL <= last; c += LS_UNROLL) {
     uint4 fa[LS_UNROLL], fb[LS_UNROLL];
@@ -123,7 +120,6 @@ linear_small_kernel(LinearArgs a) {
     }
   }
 
-  pdl_launch_dependents();  // the stream of weights is over: the next kernel may set itself up
   // this warp's 16 x (8 NT) partial tile: rows g and g + 8, batch columns n * 8 + 2 t + {0, 1}
 #pragma unroll
   for (int n = 0; n < NT; ++n) {
@@ -194,11 +190,6 @@ int launch_linear_small(const LinearArgs& a, int tiles, int ranks, cudaStream_t 
   cudaError_t err;
   config.attrs = attr;
   config.numAttrs = 0;
-  if (mll_pdl_enabled) {
-    attr[config.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[config.numAttrs].val.programmaticStreamSerializationAllowed = 1;
-    ++config.numAttrs;
-  }
   if (ranks > 1) {
     attr[config.numAttrs].id = cudaLaunchAttributeClusterDimension;
     attr[config.numAttrs].val.clusterDim.x = ranks;
@@ -235,7 +226,7 @@ MLL_API int mll_linear_small_supported(int M, int N, int K, int epilogue) {
 // with gate and up rows of w interleaved in blocks of 8 (2).  ranks: cluster size along K
 // (1, 2, 4 or 8), 0 = choose.
 MLL_API int mll_linear_small(const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
-                             int epilogue, int ranks, const void* prefetch_ptr, long long prefetch_bytes,
+                             int epilogue, int ranks,
                              cudaStream_t stream) {
   MLL_REQUIRE(mll_linear_small_supported(M, N, K, epilogue), "linear_small: unsupported sizes M=%d N=%d K=%d", M, N, K);
   MLL_REQUIRE(epilogue >= 0 && epilogue <= 2, "linear_small: unknown epilogue %d", epilogue);
@@ -251,8 +242,7 @@ MLL_API int mll_linear_small(const void* x, const void* w, const float* bias, vo
     while (ranks < 8 && tiles * ranks * 2 <= resident && chunks / (warps * ranks * 2) >= 4) ranks *= 2;
   }
   MLL_REQUIRE(ranks == 1 || ranks == 2 || ranks == 4 || ranks == 8, "linear_small: cluster size %d", ranks);
-  mll::LinearArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, out, M, N, K, epilogue, 0,
-                    mll::Prefetch{prefetch_ptr, prefetch_ptr ? (unsigned long long)prefetch_bytes : 0ull}};
+  mll::LinearArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, out, M, N, K, epilogue, 0};
   const int splits = warps * ranks;
   a.chunks_per_warp = (chunks + splits - 1) / splits;
   if (M <= 8) {

@@ -161,16 +161,14 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
 
   if (warp == 4) {
     if (lane == 0) {
-      // weights first (they do not depend on earlier kernels), activations after the wait
-      const int primed = min(count, L::STAGES);
+      const int primed = min(count, L::STAGES);  // the ring's first round needs no free-stage wait
       for (int i = 0; i < primed; ++i) {
         const unsigned full = c_smem(bars + i);
+        const unsigned dst = c_smem(base + (size_t)i * L::STAGE);
         c_mbar_expect_tx(full, L::STAGE);
-        c_tma_load_2d(c_smem(base + (size_t)i * L::STAGE), &wmap, (first + i) * C_KB, n0, full);
+        c_tma_load_2d(dst, &wmap, (first + i) * C_KB, n0, full);
+        c_tma_load_2d(dst + L::W_BYTES, &xmap, (first + i) * C_KB, 0, full);
       }
-      pdl_wait();
-      for (int i = 0; i < primed; ++i)
-        c_tma_load_2d(c_smem(base + (size_t)i * L::STAGE) + L::W_BYTES, &xmap, (first + i) * C_KB, 0, c_smem(bars + i));
       for (int i = primed; i < count; ++i) {
         const int s = i % L::STAGES;
         if (!c_mbar_wait(c_smem(bars + L::STAGES + s), ((i / L::STAGES) & 1) ^ 1)) break;
@@ -199,7 +197,6 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
         umma_commit(c_smem(bars + L::STAGES + s));  // the stage is free once these MMAs have read it
       }
       umma_commit(done_bar);  // arrives when every MMA issued above is complete
-      pdl_launch_dependents();  // the stream of weights is over: the next kernel may set itself up
     }
   }
 
@@ -227,7 +224,6 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
     }
   }
   tc_fence_before();
-  pdl_wait();  // no global write before the earlier kernels are complete
   __syncthreads();
   if (warp == 5) {  // every read of the accumulator is done
     __syncwarp();
@@ -300,11 +296,6 @@ int launch_linear_tc5(const CUtensorMap& wmap, const CUtensorMap& xmap, const Tc
   cudaLaunchAttribute attr[2];
   config.attrs = attr;
   config.numAttrs = 0;
-  if (mll_pdl_enabled) {
-    attr[config.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[config.numAttrs].val.programmaticStreamSerializationAllowed = 1;
-    ++config.numAttrs;
-  }
   if (ranks > 1) {
     attr[config.numAttrs].id = cudaLaunchAttributeClusterDimension;
     attr[config.numAttrs].val.clusterDim.x = ranks;

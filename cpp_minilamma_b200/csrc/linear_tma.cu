@@ -143,18 +143,14 @@ linear_tma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
 
   if (warp == 4) {
     if (lane == 0) {
-      // The weights do not depend on earlier kernels: the ring is filled with weight boxes
-      // before waiting for them; the activation boxes follow after the wait.
-      const int primed = min(count, T_STAGES);
+      const int primed = min(count, T_STAGES);  // the ring's first round needs no free-stage wait
       for (int i = 0; i < primed; ++i) {
         const unsigned full = smem_u32(bars + i);
+        const unsigned dst = smem_u32(base + (size_t)i * L::STAGE);
         mbar_expect_tx(full, L::STAGE);
-        tma_load_2d(smem_u32(base + (size_t)i * L::STAGE), &wmap, (first + i) * T_KB, n0, full);
+        tma_load_2d(dst, &wmap, (first + i) * T_KB, n0, full);
+        tma_load_2d(dst + L::W_BYTES, &xmap, (first + i) * T_KB, 0, full);
       }
-      pdl_wait();
-      for (int i = 0; i < primed; ++i)
-        tma_load_2d(smem_u32(base + (size_t)i * L::STAGE) + L::W_BYTES, &xmap, (first + i) * T_KB, 0,
-                    smem_u32(bars + i));
       for (int i = primed; i < count; ++i) {
         const int s = i % T_STAGES;
         if (!mbar_wait(smem_u32(bars + T_STAGES + s), ((i / T_STAGES) & 1) ^ 1)) break;
@@ -194,7 +190,6 @@ linear_tma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(bars + T_STAGES + s));
     }
-    if (warp == 0 && lane == 0) pdl_launch_dependents();  // the stream of weights is over
     // this warp's 16 x (8 NT) partial tile
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll
@@ -207,7 +202,6 @@ linear_tma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
       r1[1] = acc[n][3];
     }
   }
-  pdl_wait();  // no global write before the earlier kernels are complete (the producer thread already waited)
   if (CLUSTER) {
     cg::cluster_group cluster = cg::this_cluster();
     cluster.sync();  // every block's partial tile is complete and visible
@@ -341,11 +335,6 @@ int launch_linear_tma(const CUtensorMap& wmap, const CUtensorMap& xmap, const Tm
   cudaLaunchAttribute attr[2];
   config.attrs = attr;
   config.numAttrs = 0;
-  if (mll_pdl_enabled) {
-    attr[config.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[config.numAttrs].val.programmaticStreamSerializationAllowed = 1;
-    ++config.numAttrs;
-  }
   if (ranks > 1) {
     attr[config.numAttrs].id = cudaLaunchAttributeClusterDimension;
     attr[config.numAttrs].val.clusterDim.x = ranks;

@@ -17,7 +17,6 @@ template <typename DeltaT, typename OutT>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const DeltaT* __restrict__ delta,
                                    const float* __restrict__ weight, OutT* __restrict__ out,
                                    const int* __restrict__ rows, int width, float eps) {
-  mll::pdl_begin();
   extern __shared__ float row_buf[];
   __shared__ float scratch[32];
   const int r = blockIdx.x;
@@ -70,12 +69,7 @@ template <typename DeltaT, typename OutT, int NV>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_vec_kernel(float* __restrict__ x, const DeltaT* __restrict__ delta,
                        const float* __restrict__ weight, OutT* __restrict__ out,
-                       const int* __restrict__ rows, int width, float eps, int n_rows, Prefetch pf) {
-  mll::pdl_begin();
-  if ((int)blockIdx.x >= n_rows) {  // blocks beyond the rows only pass the prefetch hint to the L2
-    if (threadIdx.x == 0) l2_prefetch_chunks(pf, blockIdx.x - n_rows, gridDim.x - n_rows);
-    return;
-  }
+                       const int* __restrict__ rows, int width, float eps) {
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
@@ -127,21 +121,20 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const DeltaT* __restrict__ delta,
 
 template <typename DeltaT, typename OutT>
 int launch_add_rmsnorm(float* x, const void* delta, const float* weight, void* out, const int* rows,
-                       int n_rows, int width, float eps, Prefetch pf, cudaStream_t stream) {
+                       int n_rows, int width, float eps, cudaStream_t stream) {
   const bool aligned = width % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)weight % 16 == 0) &&
                        ((uintptr_t)out % 8 == 0) && (!delta || (uintptr_t)delta % 8 == 0);
   if (aligned && width <= 4 * 256 * 8) {
     const int groups = width / 4;
-    const int extra = pf.bytes ? 64 : 0;  // prefetch-only blocks
     if (groups <= 256 * 2)
-      MLL_LAUNCH((add_rmsnorm_vec_kernel<DeltaT, OutT, 2>), n_rows + extra, 256, 0, stream, x, (const DeltaT*)delta, weight,
-                 (OutT*)out, rows, width, eps, n_rows, pf);
+      MLL_LAUNCH((add_rmsnorm_vec_kernel<DeltaT, OutT, 2>), n_rows, 256, 0, stream, x, (const DeltaT*)delta, weight,
+                 (OutT*)out, rows, width, eps);
     else if (groups <= 256 * 4)
-      MLL_LAUNCH((add_rmsnorm_vec_kernel<DeltaT, OutT, 4>), n_rows + extra, 256, 0, stream, x, (const DeltaT*)delta, weight,
-                 (OutT*)out, rows, width, eps, n_rows, pf);
+      MLL_LAUNCH((add_rmsnorm_vec_kernel<DeltaT, OutT, 4>), n_rows, 256, 0, stream, x, (const DeltaT*)delta, weight,
+                 (OutT*)out, rows, width, eps);
     else
-      MLL_LAUNCH((add_rmsnorm_vec_kernel<DeltaT, OutT, 8>), n_rows + extra, 256, 0, stream, x, (const DeltaT*)delta, weight,
-                 (OutT*)out, rows, width, eps, n_rows, pf);
+      MLL_LAUNCH((add_rmsnorm_vec_kernel<DeltaT, OutT, 8>), n_rows, 256, 0, stream, x, (const DeltaT*)delta, weight,
+                 (OutT*)out, rows, width, eps);
     MLL_LAUNCH_CHECK();
     return 0;
   }
@@ -167,17 +160,16 @@ int launch_add_rmsnorm(float* x, const void* delta, const float* weight, void* o
 // [n_rows] gather list.
 MLL_API int mll_add_rmsnorm(float* x, const void* delta, const float* weight, void* out,
                             const int* rows, int act_dtype, int n_rows, int width, float eps,
-                            const void* prefetch_ptr, long long prefetch_bytes, cudaStream_t stream) {
-  const mll::Prefetch pf{prefetch_ptr, prefetch_ptr ? (unsigned long long)prefetch_bytes : 0ull};
+                            cudaStream_t stream) {
   MLL_REQUIRE(n_rows >= 0 && width > 0, "rmsnorm: bad sizes rows=%d width=%d", n_rows, width);
   MLL_REQUIRE(width <= 50 * 1024, "rmsnorm: width %d exceeds the 51200 floats one block can hold", width);
   MLL_REQUIRE(eps >= 0.f, "rmsnorm: eps must be non-negative");
   if (n_rows == 0) return 0;
   if (act_dtype == MLL_F32)
-    return mll::launch_add_rmsnorm<float, float>(x, delta, weight, out, rows, n_rows, width, eps, pf, stream);
+    return mll::launch_add_rmsnorm<float, float>(x, delta, weight, out, rows, n_rows, width, eps, stream);
   if (act_dtype == MLL_BF16)
     return mll::launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(x, delta, weight, out, rows, n_rows,
-                                                                 width, eps, pf, stream);
+                                                                 width, eps, stream);
   MLL_REQUIRE(false, "rmsnorm: unknown dtype %d", act_dtype);
   return -1;
 }

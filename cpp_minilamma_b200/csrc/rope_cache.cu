@@ -25,15 +25,12 @@ struct RopeArgs {
   void* k_cache;            // [n_pages, Hk, PAGE, d] of this layer
   void* v_cache;
   int ld, n_heads, n_kv_heads, head_dim, max_blocks, interleaved, write_kv;
-  Prefetch pf;
 };
 
 // grid (tokens, Hq + 2 Hk): one block per head of one token, one thread per pair, so that
 // no thread waits for more than one round of loads.
 template <typename T>
 __global__ void rope_cache_kernel(RopeArgs a) {
-  mll::pdl_begin();
-  l2_prefetch_by_grid(a.pf);
   const int t = blockIdx.x;
   const int hb = blockIdx.y;  // q heads, then k heads, then v heads
   const int d = a.head_dim, half = d >> 1;
@@ -98,8 +95,6 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
 }
 
 __global__ void __launch_bounds__(256) rope_cache_vec_kernel(RopeArgs a, long long n_items) {
-  mll::pdl_begin();
-  l2_prefetch_by_grid(a.pf);
   const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (item >= n_items) return;
   const int d = a.head_dim, half = d >> 1;
@@ -177,15 +172,14 @@ MLL_API int mll_rope_cache(const void* qkv, const float* bias, const float* cos_
                            const int* seq_slot, const int* block_table, void* q_out, void* k_cache,
                            void* v_cache, int dtype, int n_tokens, int ld, int n_heads, int n_kv_heads,
                            int head_dim, int max_blocks, int interleaved, int write_kv,
-                           const void* prefetch_ptr, long long prefetch_bytes, cudaStream_t stream) {
+                           cudaStream_t stream) {
   MLL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads >= 0, "rope: bad sizes");
   MLL_REQUIRE(head_dim > 0 && head_dim % 2 == 0, "rope: head_dim %d must be even", head_dim);
   MLL_REQUIRE(ld >= (n_heads + (write_kv ? 2 * n_kv_heads : 0)) * head_dim,
               "rope: row stride %d shorter than the q/k/v columns", ld);
   if (n_tokens == 0) return 0;
   mll::RopeArgs a{qkv, bias, cos_table, sin_table, tok_pos, tok_seq, seq_slot, block_table, q_out,
-                  k_cache, v_cache, ld, n_heads, n_kv_heads, head_dim, max_blocks, interleaved, write_kv,
-                  mll::Prefetch{prefetch_ptr, prefetch_ptr ? (unsigned long long)prefetch_bytes : 0ull}};
+                  k_cache, v_cache, ld, n_heads, n_kv_heads, head_dim, max_blocks, interleaved, write_kv};
   const int half = head_dim / 2;
   const int threads = half >= 128 ? 128 : (half >= 64 ? 64 : 32);
   MLL_REQUIRE(n_heads + 2 * n_kv_heads <= 65535, "rope: too many heads for one launch");

@@ -83,7 +83,6 @@ __device__ __forceinline__ int block_min_int(int v, int* scratch) {
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ tokens, int* __restrict__ status) {
-  mll::pdl_begin();
   __shared__ Best warp_best[32];
   __shared__ int bad;
   const float* row = logits + (size_t)blockIdx.x * vocab;
@@ -123,7 +122,6 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_temperature_kernel(const float* __restrict__ logits, int vocab, float temperature,
                           unsigned long long seed, const int* __restrict__ request,
                           const int* __restrict__ step, int* __restrict__ tokens, int* __restrict__ status) {
-  mll::pdl_begin();
   __shared__ float fscratch[33];
   __shared__ int iscratch[32];
   __shared__ int bad;
@@ -181,7 +179,6 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_top_k_kernel(const float* __restrict__ logits, int vocab, int top_k, float temperature,
                     unsigned long long seed, const int* __restrict__ request, const int* __restrict__ step,
                     int* __restrict__ tokens, int* __restrict__ status) {
-  mll::pdl_begin();
   __shared__ unsigned long long cand[SAMPLE_THREADS];
   __shared__ int hist[256];
   __shared__ float fscratch[33];

@@ -44,8 +44,7 @@ class _Captured:
         self.state = StepState(
             ws=engine.ws, n_tokens=batch, n_seqs=batch, tokens=d[0], tok_pos=d[1], tok_seq=d[2], seq_slot=d[3],
             seq_ctx=d[4], seq_qstart=d[5], seq_qlen=d[6], tile_seq=d[5][:0], tile_row0=d[5][:0], n_tiles=0,
-            want_rows=d[7], all_decode=True, max_ctx=engine.model.max_positions, small_rows=engine.small_rows,
-            prefetch=engine.prefetch_hints and engine.act_dtype == torch.bfloat16)
+            want_rows=d[7], all_decode=True, max_ctx=engine.model.max_positions, small_rows=engine.small_rows)
         self.rng_request, self.rng_step = d[8], d[9]
 
 

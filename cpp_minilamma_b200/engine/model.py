@@ -120,10 +120,5 @@ class Model:
             pending = layer.block.forward(step, x, pending, layer, cache.view(i))
         if want_rows is None or want_rows.shape[0] == 0:
             return None
-        if step.prefetch:
-            from ..csrc.kernels import hint
-            h = self.final_norm.forward(step, x, pending, rows=want_rows, out_name="h_final",
-                                        prefetch=hint(self.lm_head.first_weight(), 0, 24))
-        else:
-            h = self.final_norm.forward(step, x, pending, rows=want_rows, out_name="h_final")
+        h = self.final_norm.forward(step, x, pending, rows=want_rows, out_name="h_final")
         return self.lm_head.forward(step, h)

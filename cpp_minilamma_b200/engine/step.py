@@ -16,7 +16,6 @@ layer and from step to step.
 """
 from __future__ import annotations
 
-import os
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
@@ -99,8 +98,6 @@ class StepState:
     max_ctx: int
     decode_splits: int = 0                      # fixed split count (graph replay), 0 = choose per step
     small_rows: int = 0                         # steps with at most this many rows use the weight-streaming product
-    prefetch: bool = False                      # decode step: kernels pass L2 prefetch hints for the next weights
-    next_weight: Optional[torch.Tensor] = None  # set by a block: what streams after the current mixer
     host: Dict[str, list] = field(default_factory=dict)  # host copies for parts written in Python
 
 
@@ -138,10 +135,6 @@ class Engine:
         self._meta_dev: Optional[torch.Tensor] = None
         self._meta_copied = None
         self.small_rows = 64  # rows up to which linears may use this package's weight-streaming kernels
-        # Decode steps can let latency-bound kernels prefetch the next weights into L2 (MLL_PREFETCH=1).
-        # Off by default: measured on the 8B shape it costs time (4.26 against 4.02 ms a step) - a
-        # 33 MB product takes 7 us even from L2, so its launch and reduction, not HBM, set its time.
-        self.prefetch_hints = os.environ.get("MLL_PREFETCH", "0") == "1"
         self.launch_count = 0  # kernels of this package launched (estimate kept by the parts' callers)
 
     # ---- helpers shared by everything that generates with this engine -------------------- #
@@ -317,7 +310,6 @@ class Engine:
                           seq_qlen=seq_qlen, tile_seq=tile_seq, tile_row0=tile_row0, n_tiles=n_tiles,
                           want_rows=want, all_decode=all_decode, max_ctx=max(ctx), decode_splits=decode_splits,
                           small_rows=self.small_rows,
-                          prefetch=self.prefetch_hints and all_decode and self.act_dtype == torch.bfloat16,
                           host={"slots": [s.slot for s in seqs], "lens": lens, "starts": [s.start for s in seqs]})
         return state, out_rows
 

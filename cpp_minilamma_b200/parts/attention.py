@@ -89,9 +89,6 @@ class Attention(Mixer):
     def parameter_bytes(self) -> int:
         return self.qkv.parameter_bytes() + self.o.parameter_bytes()
 
-    def first_weight(self):
-        return self.qkv.weight
-
     def cache_need(self) -> CacheNeed:
         return CacheNeed(kv=KVNeed(self.n_kv_heads, self.head_dim, self.window))
 
@@ -114,10 +111,7 @@ class Attention(Mixer):
         act = self.ctx.act_dtype
         if cache.k is None:
             raise RuntimeError("attention: the cache view has no key/value storage")
-        # decode steps: while the latency-bound kernels run, the L2 fetches what the next products stream
-        hints = step.prefetch
-        after = step.next_weight if hints else None
-        qkv = self.qkv.forward(step, h, "qkv", prefetch=K.hint(self.o.weight, 0, 40) if hints else None)
+        qkv = self.qkv.forward(step, h, "qkv")
         cos, sin = self.position.tables()
         out = step.ws.buffer("attn", (T, Hq * d), act)
         splits, scratch, counters = 1, None, None
@@ -128,7 +122,7 @@ class Attention(Mixer):
                     "attn.scratch", (K.attention_decode_scratch_floats(step.n_seqs, Hq, d, splits),), torch.float32)
                 # one arrival counter per (sequence, kv head, chunk of 16 heads): the last split merges
                 counters = step.ws.zeros("attn.counters", (step.n_seqs * Hk * (-(-(Hq // Hk) // 16)),), torch.int32)
-        if (step.all_decode and self.bias is None and not hints and qkv.dtype == torch.bfloat16
+        if (step.all_decode and self.bias is None and qkv.dtype == torch.bfloat16
                 and K.attention_decode_fused_supported(act, d)):
             # one launch: rotate q and k, write k and v into the cache, attend
             K.attention_decode_fused(qkv, cos, sin, self.position.interleaved, not self.reads_cache_only,
@@ -138,12 +132,10 @@ class Attention(Mixer):
             q = step.ws.buffer("q", (T, Hq * d), act)
             K.rope_cache_write(qkv, self.bias, cos, sin, step.tok_pos, step.tok_seq, step.seq_slot,
                                cache.block_table, q, cache.k, cache.v, Hq, Hk, d,
-                               self.position.interleaved, write_kv=not self.reads_cache_only,
-                               prefetch=K.hint(after, 0, 32))
+                               self.position.interleaved, write_kv=not self.reads_cache_only)
             if step.all_decode:
                 K.attention_decode(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, cache.block_table, scratch, out,
-                                   step.n_seqs, Hq, Hk, d, splits, self.window, self.scale,
-                                   prefetch=K.hint(after, 32, 32), counters=counters)
+                                   step.n_seqs, Hq, Hk, d, splits, self.window, self.scale, counters=counters)
             else:
                 K.attention_prefill(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
                                     step.tile_seq, step.tile_row0, cache.block_table, out, step.n_tiles,

@@ -162,11 +162,6 @@ class Part:
         """Bytes of weights a step reads from this part (for the roofline)."""
         return 0
 
-    def first_weight(self) -> Optional[torch.Tensor]:
-        """The first large tensor `forward` streams, if any: the kernel before it may be asked
-        to prefetch part of it into the L2 cache (decode steps only)."""
-        return None
-
 
 class PositionEncoding(Part):
     role = "position_encoding"
@@ -180,10 +175,9 @@ class Norm(Part):
     role = "norm"
 
     def forward(self, step, x: torch.Tensor, delta: Optional[torch.Tensor],
-                rows: Optional[torch.Tensor] = None, out_name: str = "h", prefetch=None) -> torch.Tensor:
+                rows: Optional[torch.Tensor] = None, out_name: str = "h") -> torch.Tensor:
         """x += delta (in place, float32), return norm(x) in the activation dtype; with
-        `rows` only those rows, x unchanged.  `prefetch` is an optional L2 hint
-        (csrc.kernels.hint) that an implementation may pass to its kernel or ignore."""
+        `rows` only those rows, x unchanged."""
         raise NotImplementedError
 
 

@@ -19,20 +19,9 @@ class PreNormBlock(Block):
         return ["input", "post_mixer"]
 
     def forward(self, step, x, pending, layer, cache):
-        if not step.prefetch:
-            h = layer.norms["input"].forward(step, x, pending)
-            mixed = layer.mixer.forward(step, h, cache)
-            h = layer.norms["post_mixer"].forward(step, x, mixed)
-            return layer.feed_forward.forward(step, h)
-        # decode: each norm asks the L2 for the head of the weights that follow it, and the mixer
-        # learns what comes after it, so that its latency-bound kernels can do the same
-        from ..csrc.kernels import hint
-        after_mixer = layer.feed_forward.first_weight()
-        h = layer.norms["input"].forward(step, x, pending, prefetch=hint(layer.mixer.first_weight(), 0, 24))
-        step.next_weight = after_mixer
+        h = layer.norms["input"].forward(step, x, pending)
         mixed = layer.mixer.forward(step, h, cache)
-        step.next_weight = None
-        h = layer.norms["post_mixer"].forward(step, x, mixed, prefetch=hint(after_mixer, 64, 24))
+        h = layer.norms["post_mixer"].forward(step, x, mixed)
         return layer.feed_forward.forward(step, h)
 
 

@@ -67,9 +67,6 @@ class LMHead(Part):
     def parameter_bytes(self) -> int:
         return self.linear.parameter_bytes()
 
-    def first_weight(self):
-        return self.linear.weight
-
     def forward(self, step, h: torch.Tensor, out_name: str = "logits") -> torch.Tensor:
         return self.linear.forward(step, h, out_name, out_dtype=torch.float32)
 

@@ -30,10 +30,8 @@ class Linear:
     def parameter_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
 
-    def forward(self, step, x: torch.Tensor, out_name: str, out_dtype: Optional[torch.dtype] = None,
-                prefetch=None) -> torch.Tensor:
-        """x [T, K] in the activation dtype -> [T, N] in `out_dtype` (default: x's dtype).
-        `prefetch`: optional L2 hint for the weights of the next product (decode steps)."""
+    def forward(self, step, x: torch.Tensor, out_name: str, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """x [T, K] in the activation dtype -> [T, N] in `out_dtype` (default: x's dtype)."""
         rows = x.shape[0]
         if x.shape[1] != self.in_features:
             raise ValueError(f"{self.name}: input width {x.shape[1]} != {self.in_features}")
@@ -62,8 +60,7 @@ class Linear:
                                "a float32 run widens its matrices when it loads them")
         out = ws.buffer(out_name, (rows, self.out_features), out_dtype)
         if rows <= step.small_rows and K.small_linear(x, w, None, out,
-                                                       K.EPI_F32 if out_dtype == torch.float32 else K.EPI_BF16,
-                                                       prefetch=prefetch):
+                                                       K.EPI_F32 if out_dtype == torch.float32 else K.EPI_BF16):
             return out
         if out_dtype == torch.bfloat16:
             torch.mm(x, w.t(), out=out)

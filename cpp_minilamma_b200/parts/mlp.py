@@ -60,9 +60,6 @@ class SwiGLUFeedForward(FeedForward):
     def parameter_bytes(self) -> int:
         return self.gate_up.parameter_bytes() + self.down.parameter_bytes()
 
-    def first_weight(self):
-        return self.gate_up.weight
-
     def forward(self, step, h: torch.Tensor) -> torch.Tensor:
         rows = h.shape[0]
         w = self.gate_up.weight

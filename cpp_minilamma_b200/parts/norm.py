@@ -35,10 +35,10 @@ class RMSNorm(Norm):
     def parameter_bytes(self) -> int:
         return self.width * 4
 
-    def forward(self, step, x, delta, rows=None, out_name: str = "h", prefetch=None):
+    def forward(self, step, x, delta, rows=None, out_name: str = "h"):
         n = x.shape[0] if rows is None else rows.shape[0]
         out = step.ws.buffer(out_name, (n, self.width), self.ctx.act_dtype)
-        K.add_rmsnorm(x, delta, self.weight, out, self.eps, rows, prefetch=prefetch)
+        K.add_rmsnorm(x, delta, self.weight, out, self.eps, rows)
         return out
 
 
