@@ -171,10 +171,15 @@ def time_decode(llm, batch, steps, warmup, seed, sampler=None):
             sampler.begin()
         launches_before = K.launches
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # as the generation loop runs it: step i + 1, fed on the device with the tokens of step i, is
+        # enqueued before the host collects step i
         begin.record()
+        ticket = backend.submit([StepEntry(s, [t], [0]) for s, t in zip(slots, tokens)], list(range(batch)),
+                                [warmup + 1] * batch)
         for i in range(steps):
-            tokens = backend.step_and_sample([StepEntry(s, [t], [0]) for s, t in zip(slots, tokens)],
-                                             list(range(batch)), [warmup + i + 1] * batch)
+            ahead = backend.submit_ahead(slots, list(range(batch)), [warmup + i + 2] * batch) if i + 1 < steps else None
+            tokens = backend.collect(ticket)
+            ticket = ahead
         end.record()
         torch.cuda.synchronize()
         if sampler:

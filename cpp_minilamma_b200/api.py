@@ -65,12 +65,28 @@ class EngineBackend(Backend):
         self.engine.release(slot)
 
     def step_and_sample(self, entries, requests, steps):
+        return self.collect(self.submit(entries, requests, steps))
+
+    def submit(self, entries, requests, steps):
+        """Enqueue a step and its sampling; `collect` brings the token ids to the host."""
         self.steps += 1
         if self.graphs is not None and all(len(e.tokens) == 1 for e in entries):
-            return self.graphs.step([e.slot for e in entries], [e.tokens[0] for e in entries], self.params,
-                                    requests, steps)
+            return self.graphs.submit([e.slot for e in entries], [e.tokens[0] for e in entries], self.params,
+                                      requests, steps)
         logits = self.engine.step_borrowed(entries)
-        return self.sampler.sample(logits, self.params, requests, steps)
+        return self.sampler.sample_ticket(logits, self.params, requests, steps)
+
+    def submit_ahead(self, slots, requests, steps):
+        """Enqueue one more token for `slots`, which must be the slots of the previous `submit` in
+        the same order: that step's sampled tokens are taken on the device, before the host has
+        collected them.  Returns None when this backend cannot run ahead (no captured decode)."""
+        if self.graphs is None:
+            return None
+        self.steps += 1
+        return self.graphs.submit(list(slots), None, self.params, requests, steps)
+
+    def collect(self, ticket):
+        return self.sampler.collect(ticket)
 
 
 class LLM:

@@ -76,6 +76,15 @@ struct DecodeMmaSmem {
   static constexpr size_t BYTES = (size_t)STAGES * 2 * TILE * 2 + 16 * P_STRIDE * 2 + 2 * 4 * 16 * sizeof(float);
 };
 
+// How many context splits a sequence with `pages` pages of keys uses out of the `offered` ones:
+// at least one page per split; at most 16 splits until a split has 16 pages (1,024 keys) of its
+// own, because the merge grows with the number of splits.  (The host uses the same rule to choose
+// how many to offer: parts/attention.py.)
+__host__ __device__ inline int decode_splits_for(int pages, int offered) {
+  const int by_length = min(pages, max(16, pages / 16));
+  return max(1, min(offered, by_length));
+}
+
 // grid (B, Hk * head_chunks, n_splits); 128 threads.  FUSED: the rotary encoding and the cache
 // write of the step's token happen here instead of in a kernel of their own (one launch less
 // per layer): every block rotates its query heads in registers; the block whose pages include
@@ -107,7 +116,12 @@ attn_decode_mma_kernel(DecodeMmaArgs a) {
   const int first_key = a.window > 0 ? max(0, ctx - a.window) : 0;
   const int pages_total = (ctx + MLL_PAGE - 1) / MLL_PAGE;
   const int first_page = first_key / MLL_PAGE;
-  const int per_split = (pages_total - first_page + a.n_splits - 1) / a.n_splits;
+  // The launch offers n_splits blocks per (sequence, kv head); a sequence uses as many of them as
+  // its own length pays for (the rest leave at once), so one captured launch serves short and
+  // long contexts alike.  Without arrival counters a separate kernel merges all n_splits.
+  const int n_eff = a.counters ? decode_splits_for(pages_total - first_page, a.n_splits) : a.n_splits;
+  if (split >= n_eff) return;
+  const int per_split = (pages_total - first_page + n_eff - 1) / n_eff;
   const int p_begin = first_page + split * per_split;
   const int p_end = min(pages_total, p_begin + per_split);
   const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_blocks;
@@ -359,7 +373,7 @@ attn_decode_mma_kernel(DecodeMmaArgs a) {
     const int row = g + 8 * r;
     if (row >= ng) continue;
     const size_t head = (size_t)b * a.n_heads + h0 + row;
-    if (a.n_splits == 1) {
+    if (n_eff == 1) {
       const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
 #pragma unroll
       for (int n = 0; n < NT_OUT; ++n) {
@@ -381,7 +395,7 @@ attn_decode_mma_kernel(DecodeMmaArgs a) {
       }
     }
   }
-  if (a.n_splits == 1 || a.counters == nullptr) return;
+  if (n_eff == 1 || a.counters == nullptr) return;
 
   // The block that finishes last for this (sequence, kv head, head chunk) merges all splits.
   __shared__ int is_last;
@@ -390,18 +404,18 @@ attn_decode_mma_kernel(DecodeMmaArgs a) {
   if (tid == 0) {
     int* counter = a.counters + (size_t)b * gridDim.y + blockIdx.y;
     const int arrived = atomicAdd(counter, 1);
-    is_last = arrived == a.n_splits - 1;
+    is_last = arrived == n_eff - 1;
     if (is_last) *counter = 0;  // ready for the next launch
   }
   __syncthreads();
   if (!is_last) return;
   __threadfence();
   // weights of the splits per head, once: w_s = exp(m_s - max m) (zero for an empty split)
-  const int S = a.n_splits;
+  const int S = n_eff, stride = a.n_splits;  // splits in use; slots per head in the partial buffers
   float* w_s = reinterpret_cast<float*>(smem_raw);  // [ng][S] and [ng] sums, over the (finished) page ring
   float* l_s = w_s + 16 * S;
   for (int row = warp; row < ng; row += 4) {
-    const float* ml = a.part_ml + ((size_t)b * a.n_heads + h0 + row) * S * 2;
+    const float* ml = a.part_ml + ((size_t)b * a.n_heads + h0 + row) * stride * 2;
     float m = -INFINITY;
     for (int sp = lane; sp < S; sp += 32) m = fmaxf(m, __ldcg(ml + 2 * sp));
     m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
@@ -424,7 +438,7 @@ attn_decode_mma_kernel(DecodeMmaArgs a) {
   for (int idx = tid; idx < ng * D; idx += 128) {
     const int row = idx / D, col = idx % D;
     const size_t head = (size_t)b * a.n_heads + h0 + row;
-    const float* po = a.part_o + head * S * D + col;
+    const float* po = a.part_o + head * stride * D + col;
     float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
     int sp = 0;
     for (; sp + 4 <= S; sp += 4) {  // four independent loads in flight

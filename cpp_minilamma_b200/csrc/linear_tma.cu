@@ -143,14 +143,17 @@ linear_tma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
 
   if (warp == 4) {
     if (lane == 0) {
-      const int primed = min(count, T_STAGES);  // the ring's first round needs no free-stage wait
+      // the ring's first round needs no free-stage wait; all its weight boxes go out before the
+      // (small, L2-resident) activation boxes, so that the HBM requests start as early as possible
+      const int primed = min(count, T_STAGES);
       for (int i = 0; i < primed; ++i) {
         const unsigned full = smem_u32(bars + i);
-        const unsigned dst = smem_u32(base + (size_t)i * L::STAGE);
         mbar_expect_tx(full, L::STAGE);
-        tma_load_2d(dst, &wmap, (first + i) * T_KB, n0, full);
-        tma_load_2d(dst + L::W_BYTES, &xmap, (first + i) * T_KB, 0, full);
+        tma_load_2d(smem_u32(base + (size_t)i * L::STAGE), &wmap, (first + i) * T_KB, n0, full);
       }
+      for (int i = 0; i < primed; ++i)
+        tma_load_2d(smem_u32(base + (size_t)i * L::STAGE) + L::W_BYTES, &xmap, (first + i) * T_KB, 0,
+                    smem_u32(bars + i));
       for (int i = primed; i < count; ++i) {
         const int s = i % T_STAGES;
         if (!mbar_wait(smem_u32(bars + T_STAGES + s), ((i / T_STAGES) & 1) ^ 1)) break;

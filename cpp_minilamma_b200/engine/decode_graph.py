@@ -14,7 +14,7 @@ several times per layer (src/forward.cc:337-383, src/cuda_attention.cu:21-24).
 """
 from __future__ import annotations
 
-from typing import Dict, List, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -68,13 +68,22 @@ class DecodeGraphs:
 
     def step(self, slots: Sequence[int], tokens: Sequence[int], params: SamplingParams,
              requests: Sequence[int], steps: Sequence[int]) -> List[int]:
-        """One token for each slot: reserve, refresh the index buffer, run (eagerly the
-        first time, then from the graph), sample, and bring the token ids to the host."""
+        """One token for each slot, brought to the host (waits for the step)."""
+        return self.sampler.collect(self.submit(slots, tokens, params, requests, steps))
+
+    def submit(self, slots: Sequence[int], tokens: Optional[Sequence[int]], params: SamplingParams,
+               requests: Sequence[int], steps: Sequence[int]):
+        """Enqueue one token for each slot: reserve, refresh the index buffer, run (eagerly the
+        first time, then from the graph), sample; returns the sampler's ticket for the token ids.
+
+        `tokens` None: the inputs are the tokens that the previous step sampled for the same
+        slots in the same order; they are taken on the device, so the host can enqueue this
+        step before it has seen them."""
         from ..csrc import kernels as K
         engine = self.engine
         batch = len(slots)
         vocab = engine.vocab_size
-        for t in tokens:
+        for t in tokens or ():
             if not 0 <= t < vocab:
                 raise ValueError(f"token {t} outside the vocabulary [0, {vocab})")
         starts = [engine.cache.seq_len[s] for s in slots]
@@ -92,11 +101,13 @@ class DecodeGraphs:
         else:
             cap.copied.synchronize()  # the previous replay's copy has read the pinned buffer
         f = cap.fields
-        f[0], f[1], f[3] = tokens, starts, slots
+        f[0], f[1], f[3] = (tokens if tokens is not None else 0), starts, slots
         f[4] = np.asarray(starts, dtype=np.int32) + 1
         f[8], f[9] = requests, steps
         cap.dev.copy_(cap.host, non_blocking=True)
         cap.copied.record()
+        if tokens is None:
+            cap.state.tokens.copy_(self.sampler.out[:batch])  # device to device, after the index buffer's copy
         if cap.graph is None and not fresh and cap.failures < 3:
             before = K.launches
             graph = torch.cuda.CUDAGraph()
@@ -112,7 +123,7 @@ class DecodeGraphs:
                 K.launches = before
                 torch.cuda.synchronize()
                 self._body(cap, params)
-                return self.sampler.fetch(batch)
+                return self.sampler.ticket(batch)
             cap.launches = K.launches - before
             K.launches = before
             if self._generation != engine.ws.generation:
@@ -120,7 +131,7 @@ class DecodeGraphs:
                 self._generation = engine.ws.generation
                 self._captured.pop(key, None)
                 self._body(cap, params)
-                return self.sampler.fetch(batch)
+                return self.sampler.ticket(batch)
             cap.graph = graph
         if cap.graph is not None:
             cap.graph.replay()
@@ -130,7 +141,7 @@ class DecodeGraphs:
             self._body(cap, params)
             if self._generation != engine.ws.generation:
                 self._generation = engine.ws.generation
-        return self.sampler.fetch(batch)
+        return self.sampler.ticket(batch)
 
     def _body(self, cap: _Captured, params: SamplingParams) -> None:
         logits = self.engine.model.forward(cap.state, self.engine.cache, cap.state.tokens, cap.state.want_rows)

@@ -127,38 +127,82 @@ def generate(backend: Backend, prompts: Sequence[Sequence[int]], max_new_tokens,
 
 
 def _run_batch(backend, requests, prompts, budgets, stops, results, stats=None) -> None:
+    """One batch from its prompts to its last token.
+
+    A backend that has `submit`, `submit_ahead` and `collect` is kept one step ahead: while
+    the host looks at the tokens of step t, step t + 1 (fed on the device with those same
+    tokens) is already running.  The step ahead is enqueued only when no sequence can end by
+    length at step t; if one ends by a stop token, the step ahead has computed a row for it
+    that is dropped, and the others' rows are used."""
     slots = backend.acquire(len(requests))
     live = dict(zip(requests, slots))  # request -> slot, in request order
+    submit = getattr(backend, "submit", None)
+    ahead = getattr(backend, "submit_ahead", None) if submit is not None else None
+    last = {}
+    timing = {"steps": 0}
+
+    def apply(order, sampled):
+        """Take one sampled token per request of `order`; returns the requests that go on."""
+        goes_on = []
+        for r, token in zip(order, sampled):
+            done = None
+            if token in stops:
+                done = "stop"
+            else:
+                results[r].tokens.append(int(token))
+                if len(results[r].tokens) >= budgets[r]:
+                    done = "length"
+            if done:
+                results[r].finish_reason = done
+                backend.release(live.pop(r))
+            else:
+                last[r] = int(token)
+                goes_on.append(r)
+        return goes_on
+
+    def count(kind, n_tokens):
+        if stats is not None:
+            stats[kind + "_steps"] = stats.get(kind + "_steps", 0) + 1
+            stats[kind + "_tokens"] = stats.get(kind + "_tokens", 0) + n_tokens
+
     try:
-        entries = [StepEntry(live[r], list(prompts[r]), [len(prompts[r]) - 1]) for r in requests]
-        produced = 0
-        while live:
-            order = list(live)
-            began = time.perf_counter()
-            sampled = backend.step_and_sample(entries, order, [produced] * len(order))
-            if stats is not None:
-                kind = "prefill" if produced == 0 else "decode"
-                if produced == 0:
-                    decode_began = time.perf_counter()
+        order = list(live)
+        entries = [StepEntry(live[r], list(prompts[r]), [len(prompts[r]) - 1]) for r in order]
+        began = time.perf_counter()
+        step = 0
+        count("prefill", sum(len(e.tokens) for e in entries))
+        ticket = submit(entries, order, [0] * len(order)) if submit else None
+        decode_began = None
+        while True:
+            spec = None
+            if ahead is not None and all(len(results[r].tokens) + 1 < budgets[r] for r in order):
+                spec = ahead([live[r] for r in order], order, [step + 1] * len(order))
+                if spec is not None:
+                    count("decode", len(order))
+            sampled = backend.collect(ticket) if submit else backend.step_and_sample(entries, order, [step] * len(order))
+            if decode_began is None:
+                decode_began = time.perf_counter()
+                if stats is not None:
                     stats["prefill_s"] = stats.get("prefill_s", 0.0) + decode_began - began
-                stats[kind + "_steps"] = stats.get(kind + "_steps", 0) + 1
-                stats[kind + "_tokens"] = stats.get(kind + "_tokens", 0) + sum(len(e.tokens) for e in entries)
-            produced += 1
-            entries = []
-            for r, token in zip(order, sampled):
-                done = None
-                if token in stops:
-                    done = "stop"
-                else:
-                    results[r].tokens.append(int(token))
-                    if len(results[r].tokens) >= budgets[r]:
-                        done = "length"
-                if done:
-                    results[r].finish_reason = done
-                    backend.release(live.pop(r))
-                else:
-                    entries.append(StepEntry(live[r], [int(token)], [0]))
-        if stats is not None and produced:
+            before = order
+            order = apply(order, sampled)
+            step += 1
+            if spec is not None:
+                if order == before:   # nobody ended: the step ahead is the next step
+                    ticket = spec
+                    continue
+                by_request = dict(zip(before, backend.collect(spec)))  # rows of ended sequences are dropped
+                if not order:
+                    break
+                order = apply(order, [by_request[r] for r in order])
+                step += 1
+            if not order:
+                break
+            entries = [StepEntry(live[r], [last[r]], [0]) for r in order]
+            count("decode", len(order))
+            if submit:
+                ticket = submit(entries, order, [step] * len(order))
+        if stats is not None and decode_began is not None:
             # everything after the prompt step: decode steps, sampling, host bookkeeping
             stats["decode_s"] = stats.get("decode_s", 0.0) + time.perf_counter() - decode_began
     finally:

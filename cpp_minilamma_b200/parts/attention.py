@@ -101,9 +101,12 @@ class Attention(Mixer):
         span = max_ctx if self.window <= 0 else min(max_ctx, self.window + K.PAGE)
         pages = max(1, -(-span // K.PAGE))
         # as many splits as keep every block resident at once (two per multiprocessor) - a second,
-        # nearly empty wave costs more than coarser splits - at least two pages per split, and at
-        # most 16: the merge of the splits grows with their number
-        return max(1, min(_TARGET_BLOCKS // blocks, pages // 2, 16))
+        # nearly empty wave costs more than coarser splits - at least one page per split, and at
+        # most 16 until a split has 16 pages of its own: the merge grows with the number of splits.
+        # The tensor-core kernel applies the same rule to each sequence's own length (a short
+        # sequence uses fewer of the offered splits), so a launch captured for the longest
+        # context serves the short ones at their own split count.
+        return max(1, min(_TARGET_BLOCKS // blocks, pages, max(16, pages // 16)))
 
     def forward(self, step, h: torch.Tensor, cache) -> torch.Tensor:
         T = h.shape[0]

@@ -51,7 +51,11 @@ class DeviceSampler:
         self.rows = rows
         self.out = torch.zeros(2 * rows, dtype=torch.int32, device=self.device)   # tokens | status
         self.counters = torch.zeros(2 * rows, dtype=torch.int32, device=self.device)  # request | step
-        self.host = torch.zeros(2 * rows, dtype=torch.int32, pin_memory=True)
+        # two pinned copies and their events: the tokens of one step can be on their way to the
+        # host while the next step, which overwrites `out`, is already enqueued
+        self.hosts = [torch.zeros(2 * rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.events = [torch.cuda.Event(), torch.cuda.Event()]
+        self._turn = 0
 
     def launch(self, logits: torch.Tensor, params: SamplingParams, request: torch.Tensor, step: torch.Tensor) -> None:
         """Enqueue the sampling kernel for logits float32 [n, vocab]; `request` and `step`
@@ -67,17 +71,36 @@ class DeviceSampler:
             K.sample(logits, params.temperature, min(params.top_k, logits.shape[1]), params.seed, request, step,
                      tokens, status)
 
-    def fetch(self, n: int) -> List[int]:
-        """Bring the n sampled token ids to the host (synchronises the stream)."""
-        self.host.copy_(self.out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        if int(self.host[self.rows:self.rows + n].max()) != 0:
+    def ticket(self, n: int):
+        """Enqueue the copy of the n token ids just sampled to the host; `collect` waits for it.
+        At most two tickets may be outstanding."""
+        turn = self._turn
+        self._turn ^= 1
+        self.hosts[turn].copy_(self.out, non_blocking=True)
+        self.events[turn].record()
+        return (turn, n, self.rows)
+
+    def collect(self, ticket) -> List[int]:
+        """The token ids of a ticket (waits for that step, not for later ones)."""
+        turn, n, rows = ticket
+        self.events[turn].synchronize()
+        host = self.hosts[turn]
+        if int(host[rows:rows + n].max()) != 0:
             raise FloatingPointError("logits are not finite")  # src/sampler.cc:10-19
-        return self.host[:n].tolist()
+        return host[:n].tolist()
+
+    def fetch(self, n: int) -> List[int]:
+        """Bring the n sampled token ids to the host (waits for the step)."""
+        return self.collect(self.ticket(n))
 
     def sample(self, logits: torch.Tensor, params: SamplingParams, requests: Sequence[int],
                steps: Sequence[int]) -> List[int]:
         """logits float32 [n, vocab] -> n token ids on the host (this call synchronises)."""
+        return self.collect(self.sample_ticket(logits, params, requests, steps))
+
+    def sample_ticket(self, logits: torch.Tensor, params: SamplingParams, requests: Sequence[int],
+                      steps: Sequence[int]):
+        """As `sample`, but returns a ticket for `collect` instead of waiting."""
         n = logits.shape[0]
         if n > self.rows:
             self._alloc(max(n, 2 * self.rows))
@@ -85,4 +108,4 @@ class DeviceSampler:
             self.counters[:n].copy_(torch.tensor(list(requests), dtype=torch.int32))
             self.counters[self.rows:self.rows + n].copy_(torch.tensor(list(steps), dtype=torch.int32))
         self.launch(logits, params, self.counters[:n], self.counters[self.rows:self.rows + n])
-        return self.fetch(n)
+        return self.ticket(n)

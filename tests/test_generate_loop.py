@@ -119,3 +119,71 @@ def test_slots_go_back_when_the_backend_fails():
     with pytest.raises(RuntimeError, match="boom"):
         generate(backend, [[1], [2]], 3)
     assert not backend.held
+
+
+class ScriptedAhead(Scripted):
+    """The same script behind `submit` / `submit_ahead` / `collect`: a step ahead takes its input
+    tokens from what the previous step sampled ("on the device"), so it can be enqueued before
+    the host has collected them.  Checks the contract of `submit_ahead`."""
+
+    def __init__(self, *args, **kw):
+        super().__init__(*args, **kw)
+        self.pending = []          # tickets not yet collected
+        self.last_step = None      # (slots, sampled tokens) of the latest submitted step
+        self.ahead_calls = 0
+
+    def submit(self, entries, requests, steps):
+        sampled = Scripted.step_and_sample(self, entries, requests, steps)
+        self.last_step = ([e.slot for e in entries], sampled)
+        self.pending.append(sampled)
+        assert len(self.pending) <= 2, "more than two steps in flight"
+        return len(self.log) - 1
+
+    def submit_ahead(self, slots, requests, steps):
+        from cpp_minilamma_b200 import StepEntry
+        assert self.last_step is not None and list(slots) == self.last_step[0], "not the previous step's slots, in order"
+        assert len(self.pending) == 1, "a step ahead goes out while exactly one step is uncollected"
+        self.ahead_calls += 1
+        return self.submit([StepEntry(s, [t], [0]) for s, t in zip(slots, self.last_step[1])], requests, steps)
+
+    def collect(self, ticket):
+        return self.pending.pop(0)
+
+    def step_and_sample(self, entries, requests, steps):
+        return self.collect(self.submit(entries, requests, steps))
+
+
+@pytest.mark.parametrize("case", [
+    dict(scripts={0: [10, 11, 12], 1: [20, 21, 22], 2: [30, 31, 32]}, prompts=[[1, 2, 3], [6] * 9, [7, 8]], budget=3, stops=()),
+    dict(scripts={0: [10, 99, 12, 13], 1: [20, 21, 22, 23], 2: [99, 0, 0, 0]}, prompts=[[1], [2, 3], [4]], budget=4, stops=(99,)),
+    dict(scripts={i: list(range(100 * i, 100 * i + 10)) for i in range(3)}, prompts=[[1], [2], [3]], budget=[1, 0, 4], stops=()),
+    dict(scripts={0: [5, 6, 7, 8, 9, 99, 1], 1: [5, 99, 7, 8, 9, 10, 11], 2: [1, 2, 3, 4, 5, 6, 99]}, prompts=[[1], [2], [3]],
+         budget=[7, 7, 6], stops=(99,)),
+    dict(scripts={i: [i + 1] * 12 for i in range(6)}, prompts=[[1]] * 6, budget=[12, 3, 5, 1, 12, 2], stops=()),
+])
+def test_running_one_step_ahead_changes_no_result(case):
+    plain, ahead = Scripted(case["scripts"]), ScriptedAhead(case["scripts"])
+    a = generate(plain, case["prompts"], case["budget"], stop_ids=set(case["stops"]))
+    b = generate(ahead, case["prompts"], case["budget"], stop_ids=set(case["stops"]))
+    assert [(c.tokens, c.finish_reason) for c in a] == [(c.tokens, c.finish_reason) for c in b]
+    assert not ahead.held and not ahead.pending
+    # every token that a sequence was fed is one it kept (no row of an ended sequence leaks into a live one)
+    kept = {r: list(case["prompts"][r]) + c.tokens for r, c in enumerate(b)}
+    for step in ahead.log:
+        for r, tokens, _, s in step:
+            if s > 0:
+                assert tokens == [case["scripts"][r][s - 1]]
+    # a step ahead is never sent when a sequence could end by length at the step before it
+    assert ahead.ahead_calls > 0 or all(n <= 2 for n in ([case["budget"]] * 3 if isinstance(case["budget"], int) else case["budget"]))
+
+
+def test_step_ahead_rows_of_a_stopped_sequence_are_dropped():
+    scripts = {0: [10, 99, 12, 13, 14], 1: [20, 21, 22, 23, 24]}
+    backend = ScriptedAhead(scripts)
+    out = generate(backend, [[1], [2]], 5, stop_ids={99})
+    assert [c.tokens for c in out] == [[10], [20, 21, 22, 23, 24]]
+    # request 0 stopped at its second token; the step that was already ahead fed it once more (dropped)
+    fed_to_0 = [tokens for step in backend.log for r, tokens, _, _ in step if r == 0]
+    assert fed_to_0 == [[1], [10], [99]]
+    fed_to_1 = [tokens for step in backend.log for r, tokens, _, _ in step if r == 1]
+    assert fed_to_1 == [[2], [20], [21], [22], [23]]

@@ -276,3 +276,36 @@ def test_long_context_chunked_prefill_then_decode(tmp_path, dtype):
     # the planted key does carry weight: without position 70 the last logits differ visibly
     cut = plain_logits(folder, tokens[:70] + tokens[71:], dtype)
     assert np.abs(cut[-1] - ref[-1]).max() > 0.02 * np.abs(ref[-1]).max()
+
+
+@pytest.mark.parametrize("name,dtype,sampling", [("A", "float32", {}), ("D", "bfloat16", {}),
+                                                   ("B", "bfloat16", dict(temperature=0.9, top_k=20, seed=5))])
+def test_generation_one_step_ahead_equals_step_by_step(model_folders, name, dtype, sampling):
+    """The generation loop keeps the device one step ahead of the host (the next step takes its input
+    tokens on the device).  The same requests through a backend without that ability give the same
+    tokens, with stop tokens that end sequences in the middle of a batch."""
+    from cpp_minilamma_b200 import EngineBackend, SamplingParams
+    from cpp_minilamma_b200.engine.generate import generate
+
+    class StepByStep:
+        """The engine backend without `submit`: the loop falls back to one synchronous call a step."""
+        def __init__(self, inner):
+            self.inner = inner
+            self.n_slots, self.n_pages, self.max_positions = inner.n_slots, inner.n_pages, inner.max_positions
+        def acquire(self, count): return self.inner.acquire(count)
+        def release(self, slot): self.inner.release(slot)
+        def step_and_sample(self, entries, requests, steps): return self.inner.step_and_sample(entries, requests, steps)
+
+    folder, llm = load(model_folders, name, dtype, max_seqs=4)
+    prompts = [tc.random_tokens(name, n, 800 + n) for n in (5, 9, 2, 17, 3, 30)]
+    params = SamplingParams(sampling.get("temperature", 0.0), sampling.get("top_k", 0), sampling.get("seed", 1))
+    free_run = generate(StepByStep(EngineBackend(llm.engine, params)), prompts, 24, set())
+    # stop tokens taken from the free run, so that sequences really end early at different steps
+    stops = {free_run[0].tokens[3], free_run[3].tokens[10]}
+    plain = generate(StepByStep(EngineBackend(llm.engine, params)), prompts, [24, 24, 1, 24, 2, 24], stops)
+    ahead_backend = EngineBackend(llm.engine, params)
+    ahead = generate(ahead_backend, prompts, [24, 24, 1, 24, 2, 24], stops)
+    assert [(c.tokens, c.finish_reason) for c in ahead] == [(c.tokens, c.finish_reason) for c in plain]
+    assert any(c.finish_reason == "stop" for c in ahead) and any(c.finish_reason == "length" for c in ahead)
+    assert llm.engine.cache.n_free_slots == llm.engine.cache.n_slots
+    llm.engine.cache.check()
