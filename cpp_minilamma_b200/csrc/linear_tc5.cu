@@ -2,14 +2,17 @@
 //
 // The fifth-generation tensor cores read both operands straight from shared memory and keep
 // the accumulator in tensor memory, so the block needs no fragment loads at all:
-//   * warp 4, one thread: TMA producer.  Per k-block of 64 it loads a [128 weight rows x 64]
-//     box and the [16..64 activation rows x 64] box (128-byte swizzle, K-major) into a ring
-//     of stages guarded by full/empty mbarriers;
-//   * warp 5, one thread: issues four tcgen05.mma (M = 128 weight rows, N = batch rows padded
-//     to 16/32/64, K = 16) per stage from shared-memory descriptors and releases the stage
-//     with tcgen05.commit; the same warp allocates and frees the block's TMEM columns;
-//   * warps 0-3: after the last commit they read the 128 x N float32 accumulator from TMEM
-//     (tcgen05.ld, one row per thread) into shared memory.
+//   * warps 4 and 6, one thread each: TMA producers for the even and the odd k-blocks.  Per
+//     k-block of 64 a producer loads a [128 weight rows x 64] box and the [16..64 activation
+//     rows x 64] box (128-byte swizzle, K-major) into a ring of stages guarded by full/empty
+//     mbarriers;
+//   * warps 5 and 7, one thread each: issue four tcgen05.mma (M = 128 weight rows, N = batch
+//     rows padded to 16/32/64, K = 16) per stage from shared-memory descriptors, each into an
+//     accumulator of its own, and release the stage with tcgen05.commit; warp 5 allocates and
+//     frees the block's TMEM columns.  (One thread issuing every box or every MMA of a block
+//     caps the block's stream; two of each measured 1 % of a decode step.);
+//   * warps 0-3: after the last commits they read the two 128 x N float32 accumulators from
+//     TMEM (tcgen05.ld, one row per thread) and add them into shared memory.
 // "Swap-AB": the weights are the M operand, the batch is N, so a decode step with 1..64
 // sequences fills the 128-row MMA.  K is split over the blocks of a cluster; partial tiles
 // are summed in rank order through distributed shared memory (reproducible); the epilogue
@@ -37,7 +40,7 @@ namespace mll {
 enum : int { CEPI_BF16 = 0, CEPI_F32 = 1, CEPI_SWIGLU = 2 };
 constexpr int C_ROWS = 128;     // weight rows per block (the MMA's M)
 constexpr int C_KB = 64;        // k elements per stage: one 128-byte swizzle span
-constexpr int C_THREADS = 192;  // 4 epilogue warps, 1 producer warp, 1 MMA warp
+constexpr int C_THREADS = 256;  // 4 epilogue warps, then producer A, MMA A, producer B, MMA B (even / odd k-blocks)
 constexpr unsigned C_SPIN_LIMIT = 4u << 20;
 
 struct Tc5Args {
@@ -111,7 +114,7 @@ struct Tc5Smem {
   static constexpr int STAGE = W_BYTES + X_BYTES;    // a multiple of 1024
   static constexpr int STAGES = NB <= 16 ? 6 : (NB <= 32 ? 5 : 4);  // about 100 KB of ring: two blocks per multiprocessor
   static constexpr int RED_FLOATS = C_ROWS * NB;
-  static constexpr int TMEM_COLS = NB < 32 ? 32 : NB;
+  static constexpr int TMEM_COLS = 2 * NB < 32 ? 32 : 2 * NB;  // one accumulator per MMA issuer
   // the float32 tile that the epilogue works on reuses the ring once the last MMA is done
   static constexpr int RING = STAGES * STAGE > RED_FLOATS * 4 ? STAGES * STAGE : RED_FLOATS * 4;
   static constexpr size_t BYTES = 1024 + (size_t)RING + 128;
@@ -146,10 +149,10 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
       c_mbar_init(c_smem(bars + s), 1);             // full: the producer's expect_tx arrival
       c_mbar_init(c_smem(bars + L::STAGES + s), 1);  // empty: one tcgen05.commit per use
     }
-    c_mbar_init(done_bar, 1);
+    c_mbar_init(done_bar, 2);  // both MMA issuers commit to it
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) {  // this warp owns the block's tensor memory
+  if (warp == 5) {  // this warp allocates and frees the block's tensor memory
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(c_smem(tmem_slot)),
                  "r"((unsigned)L::TMEM_COLS));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
@@ -159,17 +162,22 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
   tc_fence_after();
   const unsigned tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  // Two producers and two MMA issuers share the k-blocks (even / odd): one thread that issues every
+  // TMA box, or every MMA, of a block caps the block's stream well below what the ring allows.
+  if (warp == 4 || warp == 6) {
     if (lane == 0) {
-      const int primed = min(count, L::STAGES);  // the ring's first round needs no free-stage wait
-      for (int i = 0; i < primed; ++i) {
+      const int mine = warp == 4 ? 0 : 1;
+      // the ring's first round needs no free-stage wait; its weight boxes go out before the
+      // (small, L2-resident) activation boxes, so that the HBM requests start as early as possible
+      const int primed = min(count, L::STAGES);
+      for (int i = mine; i < primed; i += 2) {
         const unsigned full = c_smem(bars + i);
-        const unsigned dst = c_smem(base + (size_t)i * L::STAGE);
         c_mbar_expect_tx(full, L::STAGE);
-        c_tma_load_2d(dst, &wmap, (first + i) * C_KB, n0, full);
-        c_tma_load_2d(dst + L::W_BYTES, &xmap, (first + i) * C_KB, 0, full);
+        c_tma_load_2d(c_smem(base + (size_t)i * L::STAGE), &wmap, (first + i) * C_KB, n0, full);
       }
-      for (int i = primed; i < count; ++i) {
+      for (int i = mine; i < primed; i += 2)
+        c_tma_load_2d(c_smem(base + (size_t)i * L::STAGE) + L::W_BYTES, &xmap, (first + i) * C_KB, 0, c_smem(bars + i));
+      for (int i = primed + ((primed & 1) != mine ? 1 : 0); i < count; i += 2) {
         const int s = i % L::STAGES;
         if (!c_mbar_wait(c_smem(bars + L::STAGES + s), ((i / L::STAGES) & 1) ^ 1)) break;
         const unsigned full = c_smem(bars + s);
@@ -179,21 +187,20 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
         c_tma_load_2d(dst + L::W_BYTES, &xmap, (first + i) * C_KB, 0, full);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 5 || warp == 7) {
     if (lane == 0) {
+      const int mine = warp == 5 ? 0 : 1;
       constexpr unsigned idesc = umma_idesc_bf16(C_ROWS, NB);
-      bool ok = true;
-      for (int i = 0; i < count && ok; ++i) {
+      for (int i = mine; i < count; i += 2) {
         const int s = i % L::STAGES;
-        ok = c_mbar_wait(c_smem(bars + s), (i / L::STAGES) & 1);
-        if (!ok) break;
+        if (!c_mbar_wait(c_smem(bars + s), (i / L::STAGES) & 1)) break;
         tc_fence_after();
         const unsigned wt = c_smem(base + (size_t)s * L::STAGE);
         const unsigned xt = wt + L::W_BYTES;
 #pragma unroll
         for (int k = 0; k < C_KB / 16; ++k)
-          umma_bf16(tmem_base, umma_desc_sw128(wt + k * 32), umma_desc_sw128(xt + k * 32), idesc,
-                    (i > 0 || k > 0) ? 1u : 0u);
+          umma_bf16(tmem_base + mine * NB, umma_desc_sw128(wt + k * 32), umma_desc_sw128(xt + k * 32), idesc,
+                    (i > mine || k > 0) ? 1u : 0u);
         umma_commit(c_smem(bars + L::STAGES + s));  // the stage is free once these MMAs have read it
       }
       umma_commit(done_bar);  // arrives when every MMA issued above is complete
@@ -208,15 +215,20 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
     if (ok && count > 0) {
 #pragma unroll
       for (int c = 0; c < NB; c += 16) {
-        unsigned v[16];
+        unsigned v[16], w[16];
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
               "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
             : "r"(tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)c));
+        asm volatile(  // the odd k-blocks' accumulator (left unwritten when the block has a single k-block)
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+            : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]),
+              "=r"(w[8]), "=r"(w[9]), "=r"(w[10]), "=r"(w[11]), "=r"(w[12]), "=r"(w[13]), "=r"(w[14]), "=r"(w[15])
+            : "r"(tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)(NB + c)));
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int j = 0; j < 16; ++j) row[c + j] = __uint_as_float(v[j]);
+        for (int j = 0; j < 16; ++j) row[c + j] = __uint_as_float(v[j]) + (count > 1 ? __uint_as_float(w[j]) : 0.f);
       }
     } else {
 #pragma unroll
