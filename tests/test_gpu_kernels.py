@@ -615,9 +615,9 @@ def test_linear_tma_refuses():
                      torch.zeros((2, 16), dtype=torch.bfloat16, device=DEV))
 
 
-@pytest.mark.parametrize("rows", [1, 3, 8, 16, 17, 33, 64])
+@pytest.mark.parametrize("rows", [1, 3, 8, 13, 16])
 @pytest.mark.parametrize("n,k,ranks", [(16, 32, 1), (40, 64, 2), (4104, 4096, 0), (512, 14336, 8), (128, 4096, 4),
-                                        (100, 224, 1), (7, 8, 1), (257, 200, 2), (1000, 1096, 0)])
+                                        (100, 224, 1), (7, 8, 1), (257, 200, 2), (1000, 1096, 0), (6144, 4096, 0)])
 def test_linear_tc5(rows, n, k, ranks):
     # the tcgen05 / TMEM kernel: same contract as the TMA kernel
     x = rnd((rows, k), torch.bfloat16, 50)
@@ -639,7 +639,7 @@ def test_linear_tc5(rows, n, k, ranks):
     assert K.take_device_error() == 0
 
 
-@pytest.mark.parametrize("rows", [1, 8, 13, 64])
+@pytest.mark.parametrize("rows", [1, 8, 13, 16])
 @pytest.mark.parametrize("inter,k,ranks", [(176, 64, 1), (1000, 4096, 0), (64, 14336, 8), (40, 72, 1)])
 def test_linear_tc5_swiglu(rows, inter, k, ranks):
     gate = rnd((inter, k), torch.bfloat16, 53, 0.05)
