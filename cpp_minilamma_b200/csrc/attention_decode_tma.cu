@@ -1,0 +1,497 @@
+// Decode attention (one query token per sequence) over the paged cache, bfloat16, head_dim 64 or
+// 128: pages arrive by TMA, and the four compute warps of a block never meet inside the page loop.
+//
+// One block per (sequence, kv head [, chunk of 16 query heads], split of the context):
+//   * warp 4, one thread: producer.  Per page it loads the keys and the values of the block's kv
+//     head ([64 positions x 64 dims] boxes, 128-byte swizzle) into a ring of three stages guarded
+//     by full/empty mbarriers; page numbers are looked up one page ahead.
+//   * warps 0-3: warp w owns keys 16 w .. 16 w + 15 of EVERY page.  It scores the (up to 16)
+//     query heads against its 16 keys (mma.sync m16n8k16, fragments by ldmatrix from the swizzled
+//     tile), keeps a running maximum and sum of its own (online softmax, float32), uses the
+//     probabilities straight from the accumulator registers as the A operand, and accumulates
+//     its own [16 heads x head_dim] output over its 16 value rows.  Nothing is exchanged between
+//     warps per page: no block-wide barrier, no probabilities through shared memory; each warp
+//     reads only its quarter of a page.
+//   * after the last page the four partial results (maximum, sum, output) are merged through
+//     shared memory, once; with context splits the block then writes its partial result and the
+//     block that arrives last merges the splits (attention_decode.cuh).
+// The fused variant also rotates q in registers and the step's new key, and writes the new key
+// and value row into the cache and into the block's copy of the last page, as the mma.sync
+// kernel's fused variant does (attention_mma.cu).  Rows of the last page beyond the context are
+// masked (keys) and zeroed in shared memory (values): the cache may hold anything there.
+//
+// Every mbarrier wait is bounded; a wait that runs out raises an error flag (read through
+// mll_take_device_error) and makes the block's later waits return at once; the block then
+// stores nothing.  No load uses cluster multicast.
+//
+// Arithmetic: that of the general kernel in attention.cu (the reference's src/forward.cc:265-298);
+// only the order of the sums differs.
+#include <cuda.h>
+
+#include "attention_decode.cuh"
+#include "tensor_map.h"
+
+__device__ int mll_attn_decode_tma_error_flag = 0;
+
+namespace mll {
+
+constexpr int DT_STAGES = 3;
+constexpr int DT_THREADS = 160;  // four compute warps and the producer warp
+constexpr unsigned DT_SPIN_LIMIT = 4u << 20;
+
+template <int D>
+struct DecodeTmaSmem {
+  static constexpr int BOXES = D / 64;
+  static constexpr int BOX_BYTES = MLL_PAGE * 128;      // [64 rows x 128 bytes]
+  static constexpr int HALF = BOXES * BOX_BYTES;        // one page's keys (or values)
+  static constexpr int STAGE = 2 * HALF;
+  static constexpr int RING = DT_STAGES * STAGE;        // 96 KB for head_dim 128: two blocks per multiprocessor
+  static constexpr int MERGE_FLOATS = 4 * (16 * D + 32);  // the warps' partial results, over the ring once it is drained
+  static_assert(MERGE_FLOATS * 4 + (16 * D + 32) * 4 <= RING, "the merge buffers must fit into the ring");
+  static constexpr int BAR_OFF = RING;                  // full[S], empty[S]
+  static constexpr size_t BYTES = (size_t)RING + 64;
+};
+
+__device__ __forceinline__ unsigned dt_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool dt_mbar_test(unsigned bar, unsigned parity) {
+  unsigned done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done != 0;
+}
+__device__ __forceinline__ void dt_mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag) {
+  if (*abort_flag) return;
+  for (unsigned spin = 0; spin < DT_SPIN_LIMIT; ++spin) {
+    if (dt_mbar_test(bar, parity)) return;
+    if (spin > 64) {
+      __nanosleep(32);
+      if ((spin & 255) == 0 && *abort_flag) return;
+    }
+  }
+  *abort_flag = 1;
+  atomicExch(&mll_attn_decode_tma_error_flag, 1);
+}
+__device__ __forceinline__ void dt_tma_load_2d(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+// Byte offset of 16-byte chunk `chunk` (8 bfloat16) of row `row` in a K or V half: the half is
+// D / 64 boxes of [64 rows x 128 bytes], and the 128-byte swizzle xors the chunk index within
+// the box with the row's low three bits.
+__device__ __forceinline__ unsigned dt_chunk_offset(int row, int chunk) {
+  return (unsigned)((chunk >> 3) * (MLL_PAGE * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
+__device__ __forceinline__ void dt_ldmatrix_x4(unsigned (&r)[4], unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void dt_ldmatrix_x4_trans(unsigned (&r)[4], unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+// grid (B, Hk * head_chunks, n_splits); 160 threads.
+template <int D, bool FUSED>
+__global__ void __launch_bounds__(DT_THREADS, 2)
+attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                       DecodeMmaArgs a) {
+  using L = DecodeTmaSmem<D>;
+  constexpr int KSTEPS = D / 16;  // k-steps of the score product
+  constexpr int NT = D / 8;       // output n-tiles (8 columns) per warp: every warp holds all columns
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + L::BAR_OFF);
+  // no static shared memory in this kernel: it would sit before the ring and could move it off its boundary
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * DT_STAGES);
+  const unsigned ring = dt_smem(smem_raw);
+  const unsigned full = dt_smem(bars), empty = dt_smem(bars + DT_STAGES);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int group = a.n_heads / a.n_kv_heads;
+  const int chunks = (group + 15) / 16;
+  const int b = blockIdx.x;
+  const int kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks;
+  const int split = blockIdx.z;
+  const int ng = min(16, group - chunk * 16);
+  const int h0 = kvh * group + chunk * 16;
+
+  const int ctx = a.seq_ctx[b];
+  const int first_key = a.window > 0 ? max(0, ctx - a.window) : 0;
+  const int pages_total = (ctx + MLL_PAGE - 1) / MLL_PAGE;
+  const int first_page = first_key / MLL_PAGE;
+  // a sequence uses as many of the offered splits as its own length pays for (attention_decode.cuh)
+  const int n_eff = decode_splits_for(pages_total - first_page, a.n_splits);
+  if (split >= n_eff) return;
+  if (ring & 1023u) {  // cannot hold swizzled tiles: report and leave (uniform for the block)
+    if (tid == 0) atomicExch(&mll_attn_decode_tma_error_flag, 2);
+    return;
+  }
+  const int per_split = (pages_total - first_page + n_eff - 1) / n_eff;
+  const int p_begin = first_page + split * per_split;
+  const int p_end = min(pages_total, p_begin + per_split);
+  const int n_pages = max(0, p_end - p_begin);
+  const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_blocks;
+
+  if (tid == 0) {
+    for (int s = 0; s < DT_STAGES; ++s) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full + 8 * s), "r"(1u));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty + 8 * s), "r"(4u));  // one arrival per compute warp
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  float o[NT][4];
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // rows g and g + 8, this warp's keys only
+
+  if (warp == 4) {
+    // ---- producer ---------------------------------------------------------------------------- //
+    if (lane == 0 && n_pages > 0) {
+      int page = table[p_begin];
+      for (int it = 0; it < n_pages; ++it) {
+        const int st = it % DT_STAGES;
+        dt_mbar_wait(empty + 8 * st, ((it / DT_STAGES) & 1) ^ 1, abort_flag);  // the stage's previous use (none in the first round)
+        if (*abort_flag) break;
+        const int row = (page * a.n_kv_heads + kvh) * MLL_PAGE;
+        if (it + 1 < n_pages) page = table[p_begin + it + 1];  // looked up while this page's loads fly
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full + 8 * st), "r"((unsigned)L::STAGE)
+                     : "memory");
+        const unsigned dst = ring + st * L::STAGE;
+#pragma unroll
+        for (int bx = 0; bx < L::BOXES; ++bx) {
+          dt_tma_load_2d(dst + bx * L::BOX_BYTES, &kmap, bx * 64, row, full + 8 * st);
+          dt_tma_load_2d(dst + L::HALF + bx * L::BOX_BYTES, &vmap, bx * 64, row, full + 8 * st);
+        }
+      }
+    }
+  } else {
+    // ---- compute warps ----------------------------------------------------------------------- //
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
+
+    // FUSED: the block whose pages include the sequence's last one fetches the new key pair and
+    // value pair of its kv head now (one pair per thread), long before the page comes up
+    const bool owns_new_row = FUSED && a.k_write != nullptr && ctx > 0 && p_begin <= pages_total - 1 &&
+                              pages_total - 1 < p_end;
+    __nv_bfloat16 new_k0 = __float2bfloat16_rn(0.f), new_k1 = new_k0;
+    unsigned new_v = 0;
+    if (owns_new_row && tid < D / 2) {
+      const __nv_bfloat16* k_in = a.qkv + (size_t)b * a.qkv_ld + (size_t)(a.n_heads + kvh) * D;
+      const __nv_bfloat16* v_in = k_in + (size_t)a.n_kv_heads * D;
+      const int e0 = a.interleaved ? 2 * tid : tid, e1 = a.interleaved ? 2 * tid + 1 : tid + D / 2;
+      const float x0 = __bfloat162float(k_in[e0]), x1 = __bfloat162float(k_in[e1]);
+      new_v = *reinterpret_cast<const unsigned*>(v_in + 2 * tid);
+      float y0 = x0, y1 = x1;
+      if (a.cos_table != nullptr) {
+        const float c = a.cos_table[(size_t)(ctx - 1) * (D / 2) + tid], sv = a.sin_table[(size_t)(ctx - 1) * (D / 2) + tid];
+        y0 = x0 * c - x1 * sv;
+        y1 = x0 * sv + x1 * c;
+      }
+      new_k0 = __float2bfloat16_rn(y0);
+      new_k1 = __float2bfloat16_rn(y1);
+    }
+
+    // query fragments (A operand), rows = heads of this chunk, zero beyond ng
+    unsigned qf[KSTEPS][4];
+    {
+      const __nv_bfloat16* q0 = FUSED ? a.qkv + (size_t)b * a.qkv_ld + (size_t)h0 * D
+                                      : a.q + ((size_t)b * a.n_heads + h0) * D;
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        const int col = ks * 16 + 2 * t;
+        qf[ks][0] = g < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + col) : 0u;
+        qf[ks][1] = g + 8 < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + col) : 0u;
+        qf[ks][2] = g < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + col + 8) : 0u;
+        qf[ks][3] = g + 8 < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + col + 8) : 0u;
+      }
+      if (FUSED && a.cos_table != nullptr && ctx > 0) {
+        // the token's position is ctx - 1 for every head; registers [2j] and [2j + 1] hold rows g and
+        // g + 8 at columns col + 8 j, col + 8 j + 1
+        const float* cs = a.cos_table + (size_t)(ctx - 1) * (D / 2);
+        const float* sn = a.sin_table + (size_t)(ctx - 1) * (D / 2);
+        if (a.interleaved) {  // pairs (2i, 2i + 1): both halves of a pair sit in one register
+#pragma unroll
+          for (int ks = 0; ks < KSTEPS; ++ks)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const int pair = ks * 8 + t + 4 * j;
+              const float c = cs[pair], sv = sn[pair];
+#pragma unroll
+              for (int r = 0; r < 2; ++r) {
+                const float2 x = unpack_bf162(qf[ks][2 * j + r]);
+                qf[ks][2 * j + r] = pack_bf162(x.x * c - x.y * sv, x.x * sv + x.y * c);
+              }
+            }
+        } else {  // pairs (i, i + d/2): the partner sits in the same place of k-step ks + KSTEPS / 2
+#pragma unroll
+          for (int ks = 0; ks < KSTEPS / 2; ++ks)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const int i0 = ks * 16 + 2 * t + 8 * j;
+              const float c0 = cs[i0], s0 = sn[i0], c1 = cs[i0 + 1], s1 = sn[i0 + 1];
+#pragma unroll
+              for (int r = 0; r < 2; ++r) {
+                const float2 lo = unpack_bf162(qf[ks][2 * j + r]), hi = unpack_bf162(qf[ks + KSTEPS / 2][2 * j + r]);
+                qf[ks][2 * j + r] = pack_bf162(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);
+                qf[ks + KSTEPS / 2][2 * j + r] = pack_bf162(lo.x * s0 + hi.x * c0, lo.y * s1 + hi.y * c1);
+              }
+            }
+        }
+      }
+    }
+
+    for (int it = 0; it < n_pages; ++it) {
+      const int p = p_begin + it;
+      const int st = it % DT_STAGES;
+      dt_mbar_wait(full + 8 * st, (it / DT_STAGES) & 1, abort_flag);
+      const unsigned kt = ring + st * L::STAGE, vt = kt + L::HALF;
+      if (p == pages_total - 1) {
+        if (FUSED && owns_new_row) {
+          // the step's token lies in this page: its key (rotated) and value replace whatever the cache held
+          const int row = (ctx - 1) % MLL_PAGE;
+          if (tid < D / 2) {
+            const size_t cache_row = (((size_t)table[p] * a.n_kv_heads + kvh) * MLL_PAGE + row) * D;
+            const int e0 = a.interleaved ? 2 * tid : tid, e1 = a.interleaved ? 2 * tid + 1 : tid + D / 2;
+            unsigned char* k_half = smem_raw + st * L::STAGE;
+            unsigned char* v_half = k_half + L::HALF;
+            *reinterpret_cast<__nv_bfloat16*>(k_half + dt_chunk_offset(row, e0 >> 3) + (e0 & 7) * 2) = new_k0;
+            *reinterpret_cast<__nv_bfloat16*>(k_half + dt_chunk_offset(row, e1 >> 3) + (e1 & 7) * 2) = new_k1;
+            a.k_write[cache_row + e0] = new_k0;
+            a.k_write[cache_row + e1] = new_k1;
+            *reinterpret_cast<unsigned*>(v_half + dt_chunk_offset(row, (2 * tid) >> 3) + ((2 * tid) & 7) * 2) = new_v;
+            *reinterpret_cast<unsigned*>(a.v_write + cache_row + 2 * tid) = new_v;
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");  // the compute warps only; once per block
+        }
+        const int valid = ctx - p * MLL_PAGE;  // positions of this page that the sequence has
+        if (valid < MLL_PAGE) {                // the rest of the page may hold anything: zero this warp's value rows
+          unsigned char* v_half = smem_raw + st * L::STAGE + L::HALF;
+          for (int idx = lane; idx < 16 * (D / 8); idx += 32) {
+            const int row = warp * 16 + idx / (D / 8), ch = idx % (D / 8);
+            if (row >= valid) *reinterpret_cast<uint4*>(v_half + dt_chunk_offset(row, ch)) = make_uint4(0, 0, 0, 0);
+          }
+          __syncwarp();
+        }
+      }
+
+      // scores of the 16 heads against this warp's 16 keys: two n-tiles of 8 keys
+      float s_acc[2][4];
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s_acc[n][i] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        // matrices: (keys 0-7, dims 0-7), (keys 0-7, dims 8-15), (keys 8-15, dims 0-7), (keys 8-15, dims 8-15)
+        unsigned kb[4];
+        const int key = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
+        const int ch = ks * 2 + ((lane >> 3) & 1);
+        dt_ldmatrix_x4(kb, kt + dt_chunk_offset(key, ch));
+        mma_16816(s_acc[0], qf[ks], kb[0], kb[1]);
+        mma_16816(s_acc[1], qf[ks], kb[2], kb[3]);
+      }
+      // scale, mask, the warp's row maxima
+      float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int kpos = p * MLL_PAGE + warp * 16 + n * 8 + 2 * t + (i & 1);
+          const bool ok = kpos < ctx && kpos >= first_key;
+          const float v = ok ? s_acc[n][i] * a.scale : -INFINITY;
+          s_acc[n][i] = v;
+          tile_max[i >> 1] = fmaxf(tile_max[i >> 1], v);
+        }
+      float alpha[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+        const float m_new = fmaxf(m_run[r], tile_max[r]);
+        alpha[r] = m_new > -INFINITY ? __expf(m_run[r] - m_new) : 1.f;
+        float sum = 0.f;
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const float pv = m_new > -INFINITY ? __expf(s_acc[n][2 * r + i] - m_new) : 0.f;
+            s_acc[n][2 * r + i] = pv;
+            sum += pv;
+          }
+        l_run[r] = l_run[r] * alpha[r] + sum;  // this thread's share of the row; the quad is summed after the loop
+        m_run[r] = m_new;
+      }
+      // the probabilities as the A fragment of a 16-key step: (row g, keys 2t..), (row g + 8, keys 2t..),
+      // (row g, keys 8 + 2t..), (row g + 8, keys 8 + 2t..)
+      unsigned pa[4];
+      pa[0] = pack_bf162(s_acc[0][0], s_acc[0][1]);
+      pa[1] = pack_bf162(s_acc[0][2], s_acc[0][3]);
+      pa[2] = pack_bf162(s_acc[1][0], s_acc[1][1]);
+      pa[3] = pack_bf162(s_acc[1][2], s_acc[1][3]);
+      // out = alpha * out + P[16 x 16] . V[this warp's 16 keys x head_dim]
+#pragma unroll
+      for (int n = 0; n < NT; n += 2) {
+        // transposed 8x8 tiles of V: (keys 0-7, cols n), (keys 8-15, cols n), (keys 0-7, cols n+1), (keys 8-15, cols n+1)
+        unsigned vb[4];
+        const int key = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+        dt_ldmatrix_x4_trans(vb, vt + dt_chunk_offset(key, n + (lane >> 4)));
+        o[n][0] *= alpha[0];
+        o[n][1] *= alpha[0];
+        o[n][2] *= alpha[1];
+        o[n][3] *= alpha[1];
+        o[n + 1][0] *= alpha[0];
+        o[n + 1][1] *= alpha[0];
+        o[n + 1][2] *= alpha[1];
+        o[n + 1][3] *= alpha[1];
+        mma_16816(o[n], pa, vb[0], vb[1]);
+        mma_16816(o[n + 1], pa, vb[2], vb[3]);
+      }
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty + 8 * st) : "memory");
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+  }
+
+  // ---- the four warps' partial results, merged through the drained ring --------------------- //
+  __syncthreads();  // every page has been consumed: the ring is free
+  float* part = reinterpret_cast<float*>(smem_raw);       // [4 warps][16 rows][D], then [4][16] maxima, [4][16] sums
+  float* part_m = part + 4 * 16 * D;
+  float* part_l = part_m + 4 * 16;
+  float* merged = part_l + 4 * 16;                        // [16][D], then [16] maxima, [16] sums
+  float* merged_m = merged + 16 * D;
+  float* merged_l = merged_m + 16;
+  if (warp < 4) {
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      const int col = n * 8 + 2 * t;
+      *reinterpret_cast<float2*>(part + ((size_t)warp * 16 + g) * D + col) = make_float2(o[n][0], o[n][1]);
+      *reinterpret_cast<float2*>(part + ((size_t)warp * 16 + g + 8) * D + col) = make_float2(o[n][2], o[n][3]);
+    }
+    if (t == 0) {
+      part_m[warp * 16 + g] = m_run[0];
+      part_m[warp * 16 + g + 8] = m_run[1];
+      part_l[warp * 16 + g] = l_run[0];
+      part_l[warp * 16 + g + 8] = l_run[1];
+    }
+  }
+  __syncthreads();
+  const bool failed = *abort_flag != 0;
+  for (int idx = tid; idx < ng * D; idx += DT_THREADS) {
+    const int row = idx / D, col = idx % D;
+    const float m0 = part_m[row], m1 = part_m[16 + row], m2 = part_m[32 + row], m3 = part_m[48 + row];
+    const float m = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+    const float w0 = m0 > -INFINITY ? __expf(m0 - m) : 0.f, w1 = m1 > -INFINITY ? __expf(m1 - m) : 0.f;
+    const float w2 = m2 > -INFINITY ? __expf(m2 - m) : 0.f, w3 = m3 > -INFINITY ? __expf(m3 - m) : 0.f;
+    const float l = (part_l[row] * w0 + part_l[16 + row] * w1) + (part_l[32 + row] * w2 + part_l[48 + row] * w3);
+    const float v = (part[(size_t)row * D + col] * w0 + part[((size_t)16 + row) * D + col] * w1) +
+                    (part[((size_t)32 + row) * D + col] * w2 + part[((size_t)48 + row) * D + col] * w3);
+    merged[(size_t)row * D + col] = v;
+    if (col == 0) {
+      merged_m[row] = m;
+      merged_l[row] = l;
+    }
+  }
+  __syncthreads();
+  if (failed) return;
+  for (int idx = tid; idx < ng * D; idx += DT_THREADS) {
+    const int row = idx / D, col = idx % D;
+    const size_t head = (size_t)b * a.n_heads + h0 + row;
+    if (n_eff == 1) {
+      const float l = merged_l[row];
+      a.out[head * D + col] = __float2bfloat16_rn(l > 0.f ? merged[(size_t)row * D + col] / l : 0.f);
+    } else {
+      a.part_o[(head * a.n_splits + split) * D + col] = merged[(size_t)row * D + col];
+      if (col == 0) {
+        float* ml = a.part_ml + (head * a.n_splits + split) * 2;
+        ml[0] = merged_m[row];
+        ml[1] = merged_l[row];
+      }
+    }
+  }
+  if (n_eff == 1) return;
+  merge_decode_splits<D, DT_THREADS>(a, b, h0, ng, n_eff, merged_l + 16);
+}
+
+template <int D, bool FUSED>
+int launch_decode_tma(const CUtensorMap& kmap, const CUtensorMap& vmap, const DecodeMmaArgs& a, int n_seqs,
+                      cudaStream_t stream) {
+  const size_t smem = DecodeTmaSmem<D>::BYTES;
+  auto kernel = attn_decode_tma_kernel<D, FUSED>;
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (err != cudaSuccess) {
+    mll_set_error("attention decode (tma): cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
+    return (int)err;
+  }
+  const int group = a.n_heads / a.n_kv_heads;
+  dim3 grid(n_seqs, a.n_kv_heads * ((group + 15) / 16), a.n_splits);
+  MLL_LAUNCH((kernel), grid, DT_THREADS, smem, stream, kmap, vmap, a);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace mll
+
+// Used by mll_take_device_error(): this file's flag, read and cleared.
+extern "C" int mll_attn_decode_tma_take_error() {
+  int flag = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&flag, mll_attn_decode_tma_error_flag, sizeof(int)) != cudaSuccess) return -1;
+  if (flag) cudaMemcpyToSymbol(mll_attn_decode_tma_error_flag, &zero, sizeof(int));
+  return flag;
+}
+
+MLL_API int mll_attn_decode_tma_supported(int dtype, int head_dim) {
+  return dtype == MLL_BF16 && (head_dim == 64 || head_dim == 128);
+}
+
+// One query token per sequence over the paged cache (bfloat16, head_dim 64 or 128).  Either q [B, Hq d]
+// (already rotated) or, for the fused variant, qkv [B, qkv_ld] with the rotary tables as in
+// mll_attn_decode_mma_fused (then q is ignored).  n_pages: pages of k_cache and v_cache.  With
+// n_splits > 1, scratch and counters (int32, one per (sequence, kv head x head chunk), zero
+// before the first launch; left zero) are required: the last block of a group merges the splits.
+MLL_API int mll_attn_decode_tma(const void* q, const void* qkv, int qkv_ld, const float* cos_table,
+                                const float* sin_table, int interleaved, int write_kv, void* k_cache, void* v_cache,
+                                long long n_pages, const int* seq_slot, const int* seq_ctx, const int* block_table,
+                                float* scratch, void* out, int n_seqs, int n_heads, int n_kv_heads, int head_dim,
+                                int max_blocks, int n_splits, int window, float scale, int* counters,
+                                cudaStream_t stream) {
+  MLL_REQUIRE(mll_attn_decode_tma_supported(MLL_BF16, head_dim), "attention decode (tma): head_dim %d", head_dim);
+  MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention decode (tma): bad head counts");
+  MLL_REQUIRE(n_seqs >= 0 && n_splits >= 1 && n_splits <= 65535, "attention decode (tma): bad batch or split count");
+  MLL_REQUIRE(n_splits == 1 || (scratch != nullptr && counters != nullptr),
+              "attention decode (tma): %d splits need scratch memory and arrival counters", n_splits);
+  MLL_REQUIRE(q != nullptr || qkv != nullptr, "attention decode (tma): neither q nor qkv");
+  MLL_REQUIRE(qkv == nullptr || (qkv_ld >= (n_heads + (write_kv ? 2 * n_kv_heads : 0)) * head_dim && qkv_ld % 2 == 0),
+              "attention decode (tma): row stride %d shorter than the q/k/v columns", qkv_ld);
+  MLL_REQUIRE((cos_table == nullptr) == (sin_table == nullptr), "attention decode (tma): one rotary table is missing");
+  MLL_REQUIRE(n_pages > 0 && n_pages * n_kv_heads * MLL_PAGE < (1ll << 31),
+              "attention decode (tma): %lld pages are more than the row coordinate holds", n_pages);
+  MLL_REQUIRE(((uintptr_t)k_cache | (uintptr_t)v_cache) % 16 == 0, "attention decode (tma): caches must be 16-byte aligned");
+  if (n_seqs == 0) return 0;
+  CUtensorMap kmap, vmap;
+  if (mll::tensor_map_bf16(k_cache, n_pages * n_kv_heads * MLL_PAGE, head_dim, MLL_PAGE, &kmap) != 0) return -1;
+  if (mll::tensor_map_bf16(v_cache, n_pages * n_kv_heads * MLL_PAGE, head_dim, MLL_PAGE, &vmap) != 0) return -1;
+  const bool fused = qkv != nullptr;
+  mll::DecodeMmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
+                       seq_slot, seq_ctx, block_table, scratch,
+                       scratch ? scratch + (size_t)n_seqs * n_heads * n_splits * head_dim : nullptr,
+                       (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, n_splits, window, scale, counters,
+                       (const __nv_bfloat16*)qkv, fused ? cos_table : nullptr, fused ? sin_table : nullptr,
+                       fused && write_kv ? (__nv_bfloat16*)k_cache : nullptr,
+                       fused && write_kv ? (__nv_bfloat16*)v_cache : nullptr, qkv_ld, interleaved};
+  if (head_dim == 64)
+    return fused ? mll::launch_decode_tma<64, true>(kmap, vmap, a, n_seqs, stream)
+                 : mll::launch_decode_tma<64, false>(kmap, vmap, a, n_seqs, stream);
+  return fused ? mll::launch_decode_tma<128, true>(kmap, vmap, a, n_seqs, stream)
+               : mll::launch_decode_tma<128, false>(kmap, vmap, a, n_seqs, stream);
+}

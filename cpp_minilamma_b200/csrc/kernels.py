@@ -14,7 +14,7 @@ import torch
 from .build import KernelBuildError, load_library
 
 PAGE = 64  # cache positions per page; equals MLL_PAGE in common.cuh
-ABI_VERSION = 14
+ABI_VERSION = 15
 MAX_TOP_K = 1024
 
 
@@ -196,7 +196,8 @@ def linear_tc5(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], o
 
 def take_device_error() -> int:
     """Non-zero when a kernel's bounded wait ran out since the last call (then cleared): bit 0 the TMA
-    linear kernel, bit 1 the tcgen05 linear kernel, bit 2 the tcgen05 attention kernel; synchronises."""
+    linear kernel, bit 1 the tcgen05 linear kernel, bit 2 the tcgen05 prefill attention kernel, bit 3 the TMA decode
+    attention kernel; synchronises."""
     return int(lib().mll_take_device_error())
 
 
@@ -365,6 +366,10 @@ def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratc
         group = n_heads // n_kv_heads
         if counters.shape[0] < n_seqs * n_kv_heads * ((group + 15) // 16):
             raise KernelError("attention decode: counters shorter than sequences x kv heads x head chunks")
+    if q.dtype == torch.bfloat16 and _tma_decode(q, None, None, None, False, False, k_cache, v_cache, seq_slot, seq_ctx,
+                                                block_table, scratch, out, n_seqs, n_heads, n_kv_heads, head_dim,
+                                                n_splits, window, scale, counters):
+        return
     if USE_TENSOR_CORE_DECODE and lib().mll_attn_decode_mma_supported(code, head_dim):
         _check(lib().mll_attn_decode_mma(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx),
                                          _ptr(block_table), _ptr(scratch), _ptr(out), ctypes.c_int(n_seqs),
@@ -387,6 +392,26 @@ def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratc
 
 
 USE_FUSED_DECODE = True  # off: rotary encoding and cache write stay a kernel of their own in decode steps
+USE_TMA_DECODE = True    # off: the cp.async / mma.sync decode kernel also takes head sizes 64 and 128
+
+
+def _tma_decode(q, qkv, cos, sin, interleaved, write_kv, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch, out,
+                n_seqs, n_heads, n_kv_heads, head_dim, n_splits, window, scale, counters) -> bool:
+    """Runs the TMA-fed decode kernel when it takes the problem (bfloat16, head_dim 64/128, arrival
+    counters whenever the context is split); returns whether it did."""
+    if not (USE_TMA_DECODE and USE_TENSOR_CORE_DECODE and lib().mll_attn_decode_tma_supported(dtype_code(out.dtype), head_dim)):
+        return False
+    if n_splits > 1 and counters is None:
+        return False
+    _check(lib().mll_attn_decode_tma(_ptr(q), _ptr(qkv), ctypes.c_int(qkv.shape[1] if qkv is not None else 0),
+                                     _ptr(cos), _ptr(sin), ctypes.c_int(int(interleaved)), ctypes.c_int(int(write_kv)),
+                                     _ptr(k_cache), _ptr(v_cache), ctypes.c_longlong(k_cache.shape[0]), _ptr(seq_slot),
+                                     _ptr(seq_ctx), _ptr(block_table), _ptr(scratch), _ptr(out), ctypes.c_int(n_seqs),
+                                     ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim),
+                                     ctypes.c_int(block_table.shape[1]), ctypes.c_int(n_splits), ctypes.c_int(window),
+                                     ctypes.c_float(scale), _ptr(counters if n_splits > 1 else None), _stream()),
+           "attention_decode (TMA)")
+    return True
 
 
 def attention_decode_fused_supported(dtype: torch.dtype, head_dim: int) -> bool:
@@ -428,6 +453,9 @@ def attention_decode_fused(qkv, cos, sin, interleaved: bool, write_kv: bool, k_c
         _need(counters, "attention counters", torch.int32, 1)
         if counters.shape[0] < n_seqs * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16):
             raise KernelError("attention decode: counters shorter than sequences x kv heads x head chunks")
+    if _tma_decode(None, qkv, cos, sin, interleaved, write_kv, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch,
+                   out, n_seqs, n_heads, n_kv_heads, head_dim, n_splits, window, scale, counters):
+        return
     _check(lib().mll_attn_decode_mma_fused(_ptr(qkv), ctypes.c_int(qkv.shape[1]), _ptr(cos), _ptr(sin),
                                            ctypes.c_int(int(interleaved)), ctypes.c_int(int(write_kv)), _ptr(k_cache),
                                            _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx), _ptr(block_table),

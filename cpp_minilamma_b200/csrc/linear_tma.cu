@@ -361,6 +361,7 @@ int launch_linear_tma(const CUtensorMap& wmap, const CUtensorMap& xmap, const Tm
 // (synchronises with the device).
 extern "C" int mll_tc5_take_error();
 extern "C" int mll_attn_tc5_take_error();
+extern "C" int mll_attn_decode_tma_take_error();
 
 MLL_API int mll_take_device_error() {
   int flag = 0, zero = 0;
@@ -368,8 +369,9 @@ MLL_API int mll_take_device_error() {
   if (flag) cudaMemcpyToSymbol(mll_device_error_flag, &zero, sizeof(int));
   const int other = mll_tc5_take_error();
   const int attention = mll_attn_tc5_take_error();
-  if (other < 0 || attention < 0) return -1;
-  return flag | (other ? 2 : 0) | (attention ? 4 : 0);
+  const int decode = mll_attn_decode_tma_take_error();
+  if (other < 0 || attention < 0 || decode < 0) return -1;
+  return flag | (other ? 2 : 0) | (attention ? 4 : 0) | (decode ? 8 : 0);
 }
 
 MLL_API int mll_linear_tma_supported(int M, int N, int K, int epilogue) {

@@ -161,13 +161,16 @@ class PagedCase:
                 torch.tensor(self.ctx_lens, dtype=torch.int32, device=DEV), self.table.to(DEV))
 
 
-@pytest.fixture(params=["tensor_core", "general"])
+@pytest.fixture(params=["tma", "tensor_core", "general"])
 def decode_impl(request):
-    """bfloat16 decode attention has a tensor-core kernel for head sizes 64/128/256; the
+    """bfloat16 decode attention has two tensor-core kernels: the TMA-fed one (head sizes 64/128,
+    needs arrival counters when the context is split) and the cp.async one (64/128/256); the
     general kernel must stay right at those sizes too."""
-    K.USE_TENSOR_CORE_DECODE = request.param == "tensor_core"
-    yield request.param
+    K.USE_TENSOR_CORE_DECODE = request.param != "general"
+    K.USE_TMA_DECODE = request.param == "tma"
+    yield "general" if request.param == "general" else "tensor_core"
     K.USE_TENSOR_CORE_DECODE = True
+    K.USE_TMA_DECODE = True
 
 
 DECODE_SHAPES = [  # heads, kv heads, head_dim
@@ -198,9 +201,18 @@ def test_attention_decode(dtype, hq, hk, d, splits, decode_impl):
         merged = torch.full_like(out, float("nan"))
         K.attention_decode(q.reshape(len(ctx), hq * d).to(DEV), kc, vc, slots, ctx_t, table, scratch, merged,
                            len(ctx), hq, hk, d, splits, 0, 1.0 / math.sqrt(d), counters=counters)
-        np.testing.assert_allclose(as64(merged), as64(out), rtol=1e-2 if dtype == torch.bfloat16 else 1e-5,
-                                   atol=1e-3 if dtype == torch.bfloat16 else 1e-6)
+        if K.USE_TMA_DECODE and dtype == torch.bfloat16 and d in (64, 128):
+            # with counters the TMA-fed kernel ran, without them the cp.async kernel: two kernels with
+            # their own order of sums, each held to the plain reference
+            for b, c in enumerate(ctx):
+                ref = pl.causal_attention(as64(q[b:b + 1]), as64(case.k[b]), as64(case.v[b]), q_positions=[c - 1])
+                np.testing.assert_allclose(as64(merged[b]).reshape(hq, d), ref[0],
+                                           **attention_tol(dtype, decode_impl, as64(case.v[b])), err_msg=f"seq {b} ctx {c}")
+        else:  # the same kernel, merged by its last block instead of the combine kernel
+            np.testing.assert_allclose(as64(merged), as64(out), rtol=1e-2 if dtype == torch.bfloat16 else 1e-5,
+                                       atol=1e-3 if dtype == torch.bfloat16 else 1e-6)
         assert int(counters.abs().sum()) == 0
+        assert K.take_device_error() == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -221,8 +233,9 @@ def test_attention_decode_far_key_stands_out(dtype, far, decode_impl):
     for splits in (1, 5):
         out = torch.empty((2, hq * d), dtype=dtype, device=DEV)
         scratch = torch.empty(K.attention_decode_scratch_floats(2, hq, d, splits), dtype=torch.float32, device=DEV)
+        counters = torch.zeros(2 * hk, dtype=torch.int32, device=DEV)  # the tensor-core kernels merge their splits themselves
         K.attention_decode(q.reshape(2, hq * d).to(DEV), kc, vc, slots, ctx_t, table, scratch, out,
-                           2, hq, hk, d, splits, 0, 1.0 / math.sqrt(d))
+                           2, hq, hk, d, splits, 0, 1.0 / math.sqrt(d), counters=counters)
         got = as64(out[0]).reshape(hq, d)
         for h in range(hq):
             np.testing.assert_allclose(got[h], 3.0 + h // (hq // hk), rtol=1e-2, atol=1e-2)
@@ -250,8 +263,9 @@ def test_attention_decode_window_edge(dtype, window, decode_impl):
     for splits in (1, 4):
         out = torch.empty((3, hq * d), dtype=dtype, device=DEV)
         scratch = torch.empty(K.attention_decode_scratch_floats(3, hq, d, splits), dtype=torch.float32, device=DEV)
+        counters = torch.zeros(3 * hk, dtype=torch.int32, device=DEV)
         K.attention_decode(q.reshape(3, hq * d).to(DEV), kc, vc, slots, ctx_t, table, scratch, out,
-                           3, hq, hk, d, splits, window, 1.0 / math.sqrt(d))
+                           3, hq, hk, d, splits, window, 1.0 / math.sqrt(d), counters=counters)
         for b, c in enumerate(ctx):
             ref = pl.causal_attention(as64(q[b:b + 1]), as64(case.k[b]), as64(case.v[b]), window=window,
                                       q_positions=[c - 1])
@@ -264,9 +278,11 @@ def test_attention_decode_window_edge(dtype, window, decode_impl):
 @pytest.mark.parametrize("interleaved", [True, False])
 @pytest.mark.parametrize("splits,window", [(1, 0), (3, 0), (2, 70)])
 @pytest.mark.parametrize("encoded", [True, False])
-def test_attention_decode_fused_with_rope_and_cache_write(hq, hk, d, interleaved, splits, window, encoded):
+@pytest.mark.parametrize("tma", [True, False])
+def test_attention_decode_fused_with_rope_and_cache_write(hq, hk, d, interleaved, splits, window, encoded, tma, monkeypatch):
     """One launch (rotate q and k, write k and v, attend) against the separate kernels and the plain
     reference.  The slot of the new token holds NaN before the call, here and in the separate path."""
+    monkeypatch.setattr(K, "USE_TMA_DECODE", tma)   # the TMA-fed kernel (head sizes 64/128) or the cp.async one
     dtype = torch.bfloat16
     ctx = [1, 63, 64, 65, 300, 129]
     B = len(ctx)
@@ -307,6 +323,7 @@ def test_attention_decode_fused_with_rope_and_cache_write(hq, hk, d, interleaved
                        1.0 / math.sqrt(d), counters=counters)
     same = lambda a, b: torch.equal(a.view(torch.int16), b.view(torch.int16))
     assert same(kc, kc2) and same(vc, vc2)          # the cache, bit for bit (NaN places included)
+    assert K.take_device_error() == 0
     for b, c in enumerate(ctx):
         k_all = np.concatenate([as64(case.k[b])[:c - 1], k_new[b:b + 1]])
         v_all = np.concatenate([as64(case.v[b])[:c - 1], v_new[b:b + 1]])
