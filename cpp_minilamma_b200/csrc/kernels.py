@@ -201,7 +201,8 @@ def take_device_error() -> int:
     return int(lib().mll_take_device_error())
 
 
-TC5_MAX_ROWS = 16     # rows up to which tall matrices go to the tcgen05 kernel (above: 4.4 against the library's 5.6 TB/s)
+TMA_MAX_ROWS = 8      # rows up to which tall matrices go to the TMA + mma.sync kernel (its batch tile is 8 rows)
+TC5_MAX_ROWS = 16     # rows up to which tall matrices go to the tcgen05 kernel (its batch tile is 16 rows)
 DIRECT_MAX_ROWS = 8   # rows up to which the other matrices go to the direct kernel
 TALL = 16384          # output features from which a matrix counts as tall
 
@@ -209,23 +210,26 @@ TALL = 16384          # output features from which a matrix counts as tall
 def small_linear_kind(rows: int, out_features: int, in_features: int, epilogue: int = EPI_BF16) -> str:
     """Which of this library's weight-streaming kernels takes the problem: "tc5", "tma", "direct" or "".
 
-    Measured on the 8B shapes (CUDA-graph timing, B200): the TMA-fed kernels (tcgen05 or
-    mma.sync consumers) win on tall matrices (gate/up, lm_head), where a deep queue of loads
-    counts; the direct kernel wins on the 4096-row projections, where a launch is short and
-    its finer split over the machine counts; beyond that the library GEMM is used."""
+    Measured on the 8B shapes (CUDA-graph timing, B200).  Tall matrices (gate/up, lm_head), where a
+    deep queue of TMA loads counts: up to 8 rows the kernel with mma.sync consumers (gate/up + SwiGLU
+    40.6 us, tcgen05 43.3), from 9 to 16 rows the tcgen05 kernel (43.6 us, the other 53.5 with its
+    second batch tile).  The 4096/6144-row projections, where a launch is short and a finer split
+    over the machine counts: the direct kernel up to 8 rows.  Beyond that the library GEMM."""
     if SMALL_LINEAR == "none":
         return ""
     if SMALL_LINEAR != "auto":  # a forced kind (tests, experiments)
         supported = {"tc5": linear_tc5_supported, "tma": linear_tma_supported, "direct": linear_small_supported}
         return SMALL_LINEAR if rows <= 64 and supported[SMALL_LINEAR](rows, out_features, in_features, epilogue) else ""
-    if out_features >= TALL and rows <= TC5_MAX_ROWS and linear_tc5_supported(rows, out_features, in_features,
-                                                                               epilogue):
-        return "tc5"
+    if out_features >= TALL:
+        if rows <= TMA_MAX_ROWS and linear_tma_supported(rows, out_features, in_features, epilogue):
+            return "tma"
+        if rows <= TC5_MAX_ROWS and linear_tc5_supported(rows, out_features, in_features, epilogue):
+            return "tc5"
     if rows <= DIRECT_MAX_ROWS:
         if linear_small_supported(rows, out_features, in_features, epilogue):
             return "direct"
-        if linear_tc5_supported(rows, out_features, in_features, epilogue):
-            return "tc5"
+        if linear_tma_supported(rows, out_features, in_features, epilogue):
+            return "tma"
     return ""
 
 
