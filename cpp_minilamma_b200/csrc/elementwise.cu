@@ -104,6 +104,16 @@ struct Pack8<float> {
   }
 };
 
+// silu(g) * u.  The float32 path keeps the accurate exponential and division; a bfloat16 result
+// is rounded to 8 bits anyway, so it takes the fast ones (a prefill step spends a tenth of its
+// non-GEMM time here, and the accurate forms make the kernel compute-bound).
+template <typename T>
+__device__ __forceinline__ float silu_mul(float g, float u);
+template <>
+__device__ __forceinline__ float silu_mul<float>(float g, float u) { return g / (1.f + expf(-g)) * u; }
+template <>
+__device__ __forceinline__ float silu_mul<__nv_bfloat16>(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
+
 template <typename T>
 __global__ void swiglu_vec8_kernel(const T* __restrict__ gu, T* __restrict__ out, int tokens, int inter, int block) {
   const int groups = inter >> 3;
@@ -119,7 +129,7 @@ __global__ void swiglu_vec8_kernel(const T* __restrict__ gu, T* __restrict__ out
     Pack8<T>::load(gp, g);
     Pack8<T>::load(up, u);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) r[i] = g[i] / (1.f + expf(-g[i])) * u[i];
+    for (int i = 0; i < 8; ++i) r[i] = silu_mul<T>(g[i], u[i]);
     Pack8<T>::store(out + (size_t)t * inter + (size_t)b * 8, r);
   }
 }
