@@ -139,7 +139,6 @@ def _run_batch(backend, requests, prompts, budgets, stops, results, stats=None) 
     submit = getattr(backend, "submit", None)
     ahead = getattr(backend, "submit_ahead", None) if submit is not None else None
     last = {}
-    timing = {"steps": 0}
 
     def apply(order, sampled):
         """Take one sampled token per request of `order`; returns the requests that go on."""
