@@ -234,13 +234,14 @@ MLL_API int mll_linear_small(const void* x, const void* w, const float* bias, vo
   MLL_REQUIRE(epilogue != mll::EPI_SWIGLU || bias == nullptr, "linear_small: the SwiGLU epilogue takes no bias");
   const int tiles = (N + 15) / 16;
   const int chunks = K / 32;
-  const int warps = mll_linear_small_warps == 8 && M <= 8 ? 8 : 4;
-  // Up to 8 rows, when two k-ranks of every tile fit on the machine at the 8-fold unrolled
-  // kernel's occupancy (128 registers: 4 blocks per multiprocessor): twice the loads in flight
-  // per warp and half the trips (o 8.7 against 9.2 us, down 23.0 against 24.4 on the 8B shape;
-  // q/k/v has too many tiles for one wave and stays with the 4-fold kernel).
-  const bool deep = M <= 8 && warps == 4 && mll_linear_small_unroll == 4 && ranks <= 0 && tiles * 2 <= 148 * 4 &&
-                    chunks / (warps * 2) >= 8;
+  // With the knobs at their defaults the variant is chosen here (8B shape, 8 rows, CUDA-graph timing):
+  //   * two k-ranks of every tile fit on the machine at the 8-fold unrolled kernel's occupancy (128
+  //     registers: 4 blocks per multiprocessor): that kernel, twice the loads in flight per warp and
+  //     half the trips (o 8.7 against 9.2 us, down 22.0 against 24.4);
+  //   * more tiles than that (q/k/v): 8 warps per block and no k-ranks (12.1 against 12.6 us).
+  const bool defaults = mll_linear_small_warps == 4 && mll_linear_small_unroll == 4 && ranks <= 0 && M <= 8;
+  const bool deep = defaults && tiles * 2 <= 148 * 4 && chunks / (4 * 2) >= 8;
+  const int warps = (mll_linear_small_warps == 8 && M <= 8) || (defaults && !deep && chunks >= 64) ? 8 : 4;
   if (deep) ranks = 2;
   if (ranks <= 0) {
     // split K while every block still fits on the machine at once and a warp keeps at least 4 chunks
