@@ -238,7 +238,7 @@ MLL_API int mll_linear_small(const void* x, const void* w, const float* bias, vo
   //   * two k-ranks of every tile fit on the machine at the 8-fold unrolled kernel's occupancy (128
   //     registers: 4 blocks per multiprocessor): that kernel, twice the loads in flight per warp and
   //     half the trips (o 8.7 against 9.2 us, down 22.0 against 24.4);
-  //   * more tiles than that (q/k/v): 8 warps per block and no k-ranks (12.1 against 12.6 us).
+  //   * more tiles than that (q/k/v): 8 warps per block, 8-fold unrolled, no k-ranks (11.0 against 12.6 us).
   const bool defaults = mll_linear_small_warps == 4 && mll_linear_small_unroll == 4 && ranks <= 0 && M <= 8;
   const bool deep = defaults && tiles * 2 <= 148 * 4 && chunks / (4 * 2) >= 8;
   const int warps = (mll_linear_small_warps == 8 && M <= 8) || (defaults && !deep && chunks >= 64) ? 8 : 4;
@@ -254,6 +254,7 @@ MLL_API int mll_linear_small(const void* x, const void* w, const float* bias, vo
   const int splits = warps * ranks;
   a.chunks_per_warp = (chunks + splits - 1) / splits;
   if (M <= 8) {
+    if (warps == 8 && (mll_linear_small_unroll == 8 || defaults)) return mll::launch_linear_small<1, 8, 8>(a, tiles, ranks, stream);
     if (warps == 8) return mll::launch_linear_small<1, 4, 8>(a, tiles, ranks, stream);
     if (mll_linear_small_unroll == 2) return mll::launch_linear_small<1, 2, 4>(a, tiles, ranks, stream);
     if (mll_linear_small_unroll == 8 || deep) return mll::launch_linear_small<1, 8, 4>(a, tiles, ranks, stream);
