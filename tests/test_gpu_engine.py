@@ -309,3 +309,35 @@ def test_generation_one_step_ahead_equals_step_by_step(model_folders, name, dtyp
     assert any(c.finish_reason == "stop" for c in ahead) and any(c.finish_reason == "length" for c in ahead)
     assert llm.engine.cache.n_free_slots == llm.engine.cache.n_slots
     llm.engine.cache.check()
+
+
+@pytest.mark.parametrize("name,dtype", [("D", "bfloat16"), ("C", "float32")])
+def test_long_generation_crosses_pages_under_graphs_and_run_ahead(model_folders, name, dtype):
+    """80 new tokens from prompts of 60 and 3 tokens: the sequences cross page boundaries (64, 128)
+    while decode steps replay a captured graph one step ahead of the host.  Same tokens as the
+    step-by-step loop, and each token is the plain implementation's argmax (ties aside)."""
+    from cpp_minilamma_b200 import EngineBackend, SamplingParams
+    from cpp_minilamma_b200.engine.generate import generate
+
+    class StepByStep:
+        def __init__(self, inner):
+            self.inner = inner
+            self.n_slots, self.n_pages, self.max_positions = inner.n_slots, inner.n_pages, inner.max_positions
+        def acquire(self, count): return self.inner.acquire(count)
+        def release(self, slot): self.inner.release(slot)
+        def step_and_sample(self, entries, requests, steps): return self.inner.step_and_sample(entries, requests, steps)
+
+    folder, llm = load(model_folders, name, dtype, max_seqs=2)
+    prompts = [tc.random_tokens(name, 60, 901), tc.random_tokens(name, 3, 902)]
+    ahead = generate(EngineBackend(llm.engine, SamplingParams()), prompts, 80, set())
+    plain = generate(StepByStep(EngineBackend(llm.engine, SamplingParams(), use_graphs=False)), prompts, 80, set())
+    assert [c.tokens for c in ahead] == [c.tokens for c in plain]
+    for prompt, completion in zip(prompts, ahead):
+        ref = plain_logits(folder, list(prompt) + completion.tokens, dtype)
+        for i, token in enumerate(completion.tokens):
+            row = ref[len(prompt) - 1 + i]
+            best = int(np.argmax(row))
+            if token != best:
+                assert row[best] - row[token] <= (2e-4 if dtype == "float32" else 0.04 * np.abs(row).max()), \
+                    f"{name} {dtype}: token {i} is {token}, plain argmax {best}"
+    llm.engine.cache.check()
