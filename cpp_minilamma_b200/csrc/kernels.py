@@ -203,7 +203,7 @@ def take_device_error() -> int:
 
 TMA_MAX_ROWS = 8      # rows up to which tall matrices go to the TMA + mma.sync kernel (its batch tile is 8 rows)
 TC5_MAX_ROWS = 16     # rows up to which tall matrices go to the tcgen05 kernel (its batch tile is 16 rows)
-DIRECT_MAX_ROWS = 8   # rows up to which the other matrices go to the direct kernel
+DIRECT_MAX_ROWS = 16  # rows up to which the other matrices go to the direct kernel
 TALL = 16384          # output features from which a matrix counts as tall
 
 
@@ -214,7 +214,8 @@ def small_linear_kind(rows: int, out_features: int, in_features: int, epilogue: 
     deep queue of TMA loads counts: up to 8 rows the kernel with mma.sync consumers (gate/up + SwiGLU
     40.6 us, tcgen05 43.3), from 9 to 16 rows the tcgen05 kernel (43.6 us, the other 53.5 with its
     second batch tile).  The 4096/6144-row projections, where a launch is short and a finer split
-    over the machine counts: the direct kernel up to 8 rows.  Beyond that the library GEMM."""
+    over the machine counts: the direct kernel up to 16 rows (it chooses its variant by rows and tiles).
+    Beyond that the library GEMM."""
     if SMALL_LINEAR == "none":
         return ""
     if SMALL_LINEAR != "auto":  # a forced kind (tests, experiments)

@@ -209,9 +209,9 @@ int launch_linear_small(const LinearArgs& a, int tiles, int ranks, cudaStream_t 
 
 }  // namespace mll
 
-// tuning knob for experiments: chunks in flight per warp for M <= 8 (2, 4 or 8)
+// tuning knob for experiments: chunks in flight per warp for M <= 16 (2 only up to 8 rows, 4 or 8)
 extern "C" __attribute__((visibility("default"))) int mll_linear_small_unroll = 4;
-// tuning knob for experiments: warps per block for M <= 8 (4 or 8)
+// tuning knob for experiments: warps per block for M <= 16 (4 or 8)
 extern "C" __attribute__((visibility("default"))) int mll_linear_small_warps = 4;
 
 // Whether mll_linear_small takes this problem (the caller uses the library GEMM otherwise).
@@ -239,10 +239,16 @@ MLL_API int mll_linear_small(const void* x, const void* w, const float* bias, vo
   //     registers: 4 blocks per multiprocessor): that kernel, twice the loads in flight per warp and
   //     half the trips (o 8.7 against 9.2 us, down 22.0 against 24.4);
   //   * more tiles than that (q/k/v): 8 warps per block, 8-fold unrolled, no k-ranks (11.0 against 12.6 us).
-  const bool defaults = mll_linear_small_warps == 4 && mll_linear_small_unroll == 4 && ranks <= 0 && M <= 8;
+  const bool knobs_default = mll_linear_small_warps == 4 && mll_linear_small_unroll == 4 && ranks <= 0;
+  const bool defaults = knobs_default && M <= 8;
   const bool deep = defaults && tiles * 2 <= 148 * 4 && chunks / (4 * 2) >= 8;
-  const int warps = (mll_linear_small_warps == 8 && M <= 8) || (defaults && !deep && chunks >= 64) ? 8 : 4;
+  //   * 9 to 16 rows (two batch tiles): 8 warps per block, no k-ranks, 8-fold unrolled when one wave of
+  //     that kernel takes all tiles (o 8.7, down 23.3, q/k/v 11.8 us at 16 rows; library 9.8 / 23.5 / 12.5).
+  const bool two_tiles = knobs_default && M > 8 && M <= 16 && chunks >= 64;
+  const int warps = (mll_linear_small_warps == 8 && M <= 16) || (defaults && !deep && chunks >= 64) || two_tiles ? 8 : 4;
+  const bool wide_unroll = mll_linear_small_unroll == 8 || (two_tiles && tiles <= 148 * 2);
   if (deep) ranks = 2;
+  if (two_tiles) ranks = 1;
   if (ranks <= 0) {
     // split K while every block still fits on the machine at once and a warp keeps at least 4 chunks
     const int resident = 148 * (warps == 8 ? 5 : 10);
@@ -260,7 +266,12 @@ MLL_API int mll_linear_small(const void* x, const void* w, const float* bias, vo
     if (mll_linear_small_unroll == 8 || deep) return mll::launch_linear_small<1, 8, 4>(a, tiles, ranks, stream);
     return mll::launch_linear_small<1, 4, 4>(a, tiles, ranks, stream);
   }
-  if (M <= 16) return mll::launch_linear_small<2, 4, 4>(a, tiles, ranks, stream);
+  if (M <= 16) {
+    if (warps == 8 && wide_unroll) return mll::launch_linear_small<2, 8, 8>(a, tiles, ranks, stream);
+    if (warps == 8) return mll::launch_linear_small<2, 4, 8>(a, tiles, ranks, stream);
+    if (mll_linear_small_unroll == 8) return mll::launch_linear_small<2, 8, 4>(a, tiles, ranks, stream);
+    return mll::launch_linear_small<2, 4, 4>(a, tiles, ranks, stream);
+  }
   if (M <= 32) return mll::launch_linear_small<4, 2, 4>(a, tiles, ranks, stream);
   return mll::launch_linear_small<8, 2, 4>(a, tiles, ranks, stream);
 }
