@@ -120,4 +120,32 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
 }
 
+// Rows whose RMS norm is still to be applied.  The kernel that added to the residual stream wrote, for
+// every row m, `partials` sums of squares over column tiles at sumsq[m * stride + p] and the row itself
+// multiplied by the norm's weight; a product over such rows multiplies its result by
+// 1 / sqrt(sum_p sumsq[m][p] / width + eps), which is what the norm would have put into the row.
+struct RowNormIn {
+  const float* sumsq;  // null: the rows are taken as they are
+  int partials, stride;
+  float eps;
+};
+
+// That factor for one row, computed by LANES consecutive lanes of a warp (LANES 16 or 32; `sub` is the
+// lane's index among them, `mask` names them) in a fixed order; every one of them gets the result.
+template <int LANES>
+__device__ __forceinline__ float row_norm_factor(const float* row_partials, int partials, int width, float eps,
+                                                 int sub, unsigned mask) {
+  float s = 0.f;
+  for (int p0 = sub; p0 < partials; p0 += 8 * LANES) {
+    float v[8];  // eight loads in flight: the sum below must not wait for one load after the other
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = p0 + i * LANES < partials ? row_partials[p0 + i * LANES] : 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += v[i];
+  }
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) s += __shfl_xor_sync(mask, s, o);
+  return 1.f / sqrtf(s / (float)width + eps);
+}
+
 }  // namespace mll

@@ -7,14 +7,14 @@ implementation behind them.  Argument faults raise `KernelError` before any laun
 from __future__ import annotations
 
 import ctypes
-from typing import Optional
+from typing import NamedTuple, Optional
 
 import torch
 
 from .build import KernelBuildError, load_library
 
 PAGE = 64  # cache positions per page; equals MLL_PAGE in common.cuh
-ABI_VERSION = 15
+ABI_VERSION = 16
 MAX_TOP_K = 1024
 
 
@@ -108,7 +108,34 @@ def add_bias(x: torch.Tensor, bias: torch.Tensor) -> None:
                               ctypes.c_int(x.shape[1]), _stream()), "add_bias")
 
 
-EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
+EPI_BF16, EPI_F32, EPI_SWIGLU, EPI_RESID = 0, 1, 2, 3
+NORM_TILE = 16  # columns per partial sum of squares that the residual epilogue writes
+
+
+class RowNorm(NamedTuple):
+    """Rows that still lack their RMS norm's factor: `sumsq` float32 [rows, stride] holds `partials`
+    partial sums of squares per row; the factor is 1 / sqrt(sum / width + eps)."""
+    sumsq: torch.Tensor
+    partials: int
+    eps: float
+
+
+class ResidualOut(NamedTuple):
+    """Where the residual epilogue writes: `resid` float32 [rows, N] (+= result), `next_weight` float32 [N]
+    (out = resid * next_weight in bfloat16), `sumsq` float32 [rows, stride >= ceil(N / NORM_TILE)]."""
+    resid: torch.Tensor
+    next_weight: torch.Tensor
+    sumsq: torch.Tensor
+
+
+def _row_norm_args(row_norm: Optional["RowNorm"], rows: int, what: str):
+    if row_norm is None:
+        return ctypes.c_void_p(None), ctypes.c_int(0), ctypes.c_int(0), ctypes.c_float(0.0)
+    _need(row_norm.sumsq, what + " partial sums", torch.float32, 2)
+    if row_norm.sumsq.shape[0] < rows or row_norm.sumsq.shape[1] < row_norm.partials:
+        raise KernelError(f"{what}: partial sums {tuple(row_norm.sumsq.shape)} for {rows} rows of {row_norm.partials}")
+    return (_ptr(row_norm.sumsq), ctypes.c_int(row_norm.partials), ctypes.c_int(row_norm.sumsq.shape[1]),
+            ctypes.c_float(row_norm.eps))
 
 
 def linear_small_supported(rows: int, out_features: int, in_features: int, epilogue: int = EPI_BF16) -> bool:
@@ -116,11 +143,15 @@ def linear_small_supported(rows: int, out_features: int, in_features: int, epilo
 
 
 def linear_small(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-                 epilogue: int = EPI_BF16, ranks: int = 0) -> None:
+                 epilogue: int = EPI_BF16, ranks: int = 0, row_norm: Optional[RowNorm] = None,
+                 residual: Optional[ResidualOut] = None) -> None:
     """out = x . w^T for at most 64 rows of bfloat16 x [M, K] and bfloat16 w [N, K], read once.
 
     epilogue EPI_BF16 / EPI_F32: out [M, N] in that dtype (+ float32 bias [N]);
-    EPI_SWIGLU: w holds gate and up rows interleaved in blocks of 8, out [M, N / 2] = silu(gate) * up."""
+    EPI_SWIGLU: w holds gate and up rows interleaved in blocks of 8, out [M, N / 2] = silu(gate) * up;
+    EPI_RESID (at most 16 rows, with `residual`): the result is added to the residual stream, out [M, N]
+    is the new stream times the next norm's weight (not yet its factor), with partial sums of squares.
+    `row_norm`: x is such an output; the result is multiplied by the rows' factors."""
     _need(x, "linear_small x", torch.bfloat16, 2)
     _need(w, "linear_small w", torch.bfloat16, 2)
     rows, k = x.shape
@@ -135,9 +166,23 @@ def linear_small(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
         _need(bias, "linear_small bias", torch.float32, 1)
         if bias.shape[0] != n:
             raise KernelError("linear_small: bias length differs from the output width")
-    _check(lib().mll_linear_small(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), ctypes.c_int(rows), ctypes.c_int(n),
-                                  ctypes.c_int(k), ctypes.c_int(epilogue), ctypes.c_int(ranks),
-                                  _stream()), "linear_small")
+    if (epilogue == EPI_RESID) != (residual is not None):
+        raise KernelError("linear_small: the residual epilogue and its outputs go together")
+    resid = next_w = out_sumsq = None
+    out_stride = 0
+    if residual is not None:
+        resid, next_w, out_sumsq = residual
+        _need(resid, "linear_small resid", torch.float32, 2)
+        _need(next_w, "linear_small next weight", torch.float32, 1)
+        _need(out_sumsq, "linear_small sums of squares", torch.float32, 2)
+        if tuple(resid.shape) != (rows, n) or next_w.shape[0] != n or out_sumsq.shape[0] < rows:
+            raise KernelError(f"linear_small: resid {tuple(resid.shape)}, next weight {tuple(next_w.shape)}, sums "
+                              f"{tuple(out_sumsq.shape)} do not fit out {(rows, n)}")
+        out_stride = out_sumsq.shape[1]
+    _check(lib().mll_linear_small_fused(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), ctypes.c_int(rows), ctypes.c_int(n),
+                                        ctypes.c_int(k), ctypes.c_int(epilogue), ctypes.c_int(ranks),
+                                        *_row_norm_args(row_norm, rows, "linear_small"), _ptr(resid), _ptr(next_w),
+                                        _ptr(out_sumsq), ctypes.c_int(out_stride), _stream()), "linear_small")
 
 
 def linear_tma_supported(rows: int, out_features: int, in_features: int, epilogue: int = EPI_BF16) -> bool:
@@ -145,7 +190,7 @@ def linear_tma_supported(rows: int, out_features: int, in_features: int, epilogu
 
 
 def linear_tma(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-               epilogue: int = EPI_BF16, ranks: int = 0) -> None:
+               epilogue: int = EPI_BF16, ranks: int = 0, row_norm: Optional[RowNorm] = None) -> None:
     """As `linear_small`, with the weights streamed through a TMA + mbarrier pipeline.  Takes
     any N, any K that is a multiple of 8, at most 64 rows."""
     _need(x, "linear_tma x", torch.bfloat16, 2)
@@ -162,9 +207,9 @@ def linear_tma(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], o
         _need(bias, "linear_tma bias", torch.float32, 1)
         if bias.shape[0] != n:
             raise KernelError("linear_tma: bias length differs from the output width")
-    _check(lib().mll_linear_tma(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), ctypes.c_int(rows), ctypes.c_int(n),
-                                ctypes.c_int(k), ctypes.c_int(epilogue), ctypes.c_int(ranks), _stream()),
-           "linear_tma")
+    _check(lib().mll_linear_tma_fused(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), ctypes.c_int(rows), ctypes.c_int(n),
+                                      ctypes.c_int(k), ctypes.c_int(epilogue), ctypes.c_int(ranks),
+                                      *_row_norm_args(row_norm, rows, "linear_tma"), _stream()), "linear_tma")
 
 
 def linear_tc5_supported(rows: int, out_features: int, in_features: int, epilogue: int = EPI_BF16) -> bool:
@@ -172,7 +217,7 @@ def linear_tc5_supported(rows: int, out_features: int, in_features: int, epilogu
 
 
 def linear_tc5(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-               epilogue: int = EPI_BF16, ranks: int = 0) -> None:
+               epilogue: int = EPI_BF16, ranks: int = 0, row_norm: Optional[RowNorm] = None) -> None:
     """As `linear_tma`, with the product on the fifth-generation tensor cores: tcgen05.mma reads
     the TMA-filled stages from shared memory and accumulates in tensor memory."""
     _need(x, "linear_tc5 x", torch.bfloat16, 2)
@@ -189,9 +234,9 @@ def linear_tc5(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], o
         _need(bias, "linear_tc5 bias", torch.float32, 1)
         if bias.shape[0] != n:
             raise KernelError("linear_tc5: bias length differs from the output width")
-    _check(lib().mll_linear_tc5(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), ctypes.c_int(rows), ctypes.c_int(n),
-                                ctypes.c_int(k), ctypes.c_int(epilogue), ctypes.c_int(ranks), _stream()),
-           "linear_tc5")
+    _check(lib().mll_linear_tc5_fused(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), ctypes.c_int(rows), ctypes.c_int(n),
+                                      ctypes.c_int(k), ctypes.c_int(epilogue), ctypes.c_int(ranks),
+                                      *_row_norm_args(row_norm, rows, "linear_tc5"), _stream()), "linear_tc5")
 
 
 def take_device_error() -> int:
@@ -234,15 +279,29 @@ def small_linear_kind(rows: int, out_features: int, in_features: int, epilogue: 
     return ""
 
 
-def small_linear(x, w, bias, out, epilogue: int = EPI_BF16) -> bool:
-    kind = small_linear_kind(x.shape[0], w.shape[0], w.shape[1], epilogue)
+def small_linear(x, w, bias, out, epilogue: int = EPI_BF16, row_norm: Optional[RowNorm] = None,
+                 residual: Optional[ResidualOut] = None) -> bool:
+    """Run the product on the kernel that `small_linear_kind` names; False when there is none (then
+    nothing ran).  The residual epilogue exists in the direct kernel only."""
+    kind = small_linear_kind(x.shape[0], w.shape[0], w.shape[1], EPI_BF16 if epilogue == EPI_RESID else epilogue)
+    if epilogue == EPI_RESID and kind != "direct":
+        return False
     if kind == "tc5":
-        linear_tc5(x, w, bias, out, epilogue)
+        linear_tc5(x, w, bias, out, epilogue, 0, row_norm)
     elif kind == "tma":
-        linear_tma(x, w, bias, out, epilogue, 1 if x.shape[0] > 8 else 0)
+        linear_tma(x, w, bias, out, epilogue, 1 if x.shape[0] > 8 else 0, row_norm)
     elif kind == "direct":
-        linear_small(x, w, bias, out, epilogue)
+        linear_small(x, w, bias, out, epilogue, 0, row_norm, residual)
     return bool(kind)
+
+
+def fused_norm_rows(rows: int) -> bool:
+    """Whether products over `rows` rows may fold the norms around them in (the residual epilogue
+    exists in the direct kernel, which takes few rows)."""
+    return FUSE_NORM and 1 <= rows <= DIRECT_MAX_ROWS
+
+
+FUSE_NORM = True  # off: every norm is a kernel of its own
 
 
 SMALL_LINEAR = "auto"  # "auto", a forced kind ("tc5", "tma", "direct"), or "none" (library GEMM only)
@@ -285,6 +344,19 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
     _check(lib().mll_add_rmsnorm(_ptr(x), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows),
                                  dtype_code(out.dtype), ctypes.c_int(n_rows), ctypes.c_int(width),
                                  ctypes.c_float(eps), _stream()), "rmsnorm")
+
+
+def apply_row_norm(values: torch.Tensor, row_norm: RowNorm, out: torch.Tensor) -> None:
+    """out = values * the rows' norm factors (bfloat16 [T, D]): finishes a norm that the product behind it
+    cannot finish itself."""
+    _need(values, "apply_row_norm values", torch.bfloat16, 2)
+    _need(out, "apply_row_norm out", torch.bfloat16, 2)
+    if out.shape != values.shape:
+        raise KernelError(f"apply_row_norm: out {tuple(out.shape)} differs from values {tuple(values.shape)}")
+    sumsq, partials, stride, eps = _row_norm_args(row_norm, values.shape[0], "apply_row_norm")
+    _check(lib().mll_apply_row_norm(_ptr(values), sumsq, partials, stride, eps, _ptr(out),
+                                    ctypes.c_int(values.shape[0]), ctypes.c_int(values.shape[1]), _stream()),
+           "apply_row_norm")
 
 
 def rope_cache_write(qkv, bias, cos, sin, tok_pos, tok_seq, seq_slot, block_table, q_out, k_cache, v_cache,

@@ -11,6 +11,12 @@
 // the result is reproducible, and the epilogue (bias, SwiGLU, bfloat16 or float32 output)
 // runs once on the full sum.
 //
+// Two optional fusions with the RMS norm around the product (the reference keeps them apart:
+// src/forward.cc:385-414 adds, normalises and multiplies in separate calls):
+//   * the rows may arrive not yet normalised (RowNormIn): the result is multiplied by the row's factor;
+//   * epilogue EPI_RESID adds the result to the float32 residual stream, and writes the new row times the
+//     next norm's weight, in bfloat16, with the tile's share of the row's sum of squares.
+//
 // The reference calls cublasSgemm with rows = 1 for every linear (src/cuda_matmul.cc:181-186).
 #include <cooperative_groups.h>
 
@@ -20,7 +26,7 @@ namespace cg = cooperative_groups;
 
 namespace mll {
 
-enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
+enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_RESID = 3 };
 
 struct LinearArgs {
   const __nv_bfloat16* x;  // [M, K]
@@ -28,6 +34,11 @@ struct LinearArgs {
   const float* bias;       // optional [N]
   void* out;               // [M, N] (EPI_SWIGLU: [M, N / 2])
   int M, N, K, epilogue, chunks_per_warp;
+  RowNormIn in;            // x still lacks its norm's factor
+  float* resid;            // EPI_RESID: float32 residual [M, N], updated in place
+  const float* next_w;     // EPI_RESID: weight [N] of the norm that follows
+  float* out_sumsq;        // EPI_RESID: [M, out_stride], entry [m][tile] = sum over the tile's columns of resid^2
+  int out_stride;
 };
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
@@ -51,12 +62,17 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
 }
 
 
-// grid: (row tiles * cluster size); block: 128 threads.  NT: n-tiles of 8 batch rows.
-// LS_UNROLL: 32-element chunks in flight per warp; LS_WARPS: warps per block (K is split over them)
-template <int NT, bool CLUSTER, int LS_UNROLL, int LS_WARPS>
-__global__ void __launch_bounds__(LS_WARPS * 32)
+// grid: (row tiles * cluster size); block: LS_WARPS warps.  NT: n-tiles of 8 batch rows.
+// LS_UNROLL: 32-element chunks in flight per warp; LS_WARPS: warps per block (K is split over them);
+// OCC: resident warps per multiprocessor that the register allocation aims at (0: the compiler's choice).
+// Without it the compiler's own occupancy guess decides how many of the loads stay in flight, and an
+// unrelated edit of the epilogue moved that guess (o of the 8B shape: 8.7 -> 11.9 us); 16 gives the
+// loop 128 registers, 24 gives it 80.
+template <int NT, bool CLUSTER, int LS_UNROLL, int LS_WARPS, int OCC>
+__global__ void __launch_bounds__(LS_WARPS * 32, OCC / LS_WARPS)
 linear_small_kernel(LinearArgs a) {
   __shared__ float red[LS_WARPS][16][8 * NT];
+  __shared__ float row_factor[8 * NT];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   int rank = 0, ranks = 1;
@@ -151,6 +167,16 @@ linear_small_kernel(LinearArgs a) {
     cluster.sync();  // rank 0 has read its peers' shared memory; they may leave
     if (rank != 0) return;
   }
+  if (a.in.sumsq) {
+    // the rows' norm factors, from partial sums that lie in the L2 cache: plain loads here, at the end, cost
+    // 0.6 us (q/k/v of the 8B shape); fetching them into shared memory during the main loop cost 1.5 us,
+    // through the share of the L1 cache that the buffer takes from the activations
+    for (int m = warp; m < a.M; m += LS_WARPS) {
+      const float f = row_norm_factor<32>(a.in.sumsq + (size_t)m * a.in.stride, a.in.partials, a.K, a.in.eps, lane,
+                                          0xffffffffu);
+      if (lane == 0) row_factor[m] = f;
+    }
+  }
   __syncthreads();
 
   // epilogue on the full sums: element (row, m) of the tile is y[m][n0 + row]
@@ -160,15 +186,37 @@ linear_small_kernel(LinearArgs a) {
     for (int i = threadIdx.x; i < 8 * 8 * NT; i += LS_WARPS * 32) {
       const int m = i >> 3, r = i & 7;
       if (m < a.M && n0 + r + 8 < a.N) {
-        const float gate = red[0][r][m], up = red[0][r + 8][m];
+        const float f = a.in.sumsq ? row_factor[m] : 1.f;
+        const float gate = red[0][r][m] * f, up = red[0][r + 8][m] * f;
         out[(size_t)m * half + (n0 >> 1) + r] = __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
       }
+    }
+  } else if (a.epilogue == EPI_RESID) {
+    // whole warps run the loop (its bound is a multiple of 32): 16 consecutive lanes hold one row's tile
+    __nv_bfloat16* out = (__nv_bfloat16*)a.out;
+    for (int i = threadIdx.x; i < 16 * 8 * NT; i += LS_WARPS * 32) {
+      const int m = i >> 4, r = i & 15;
+      float now = 0.f;
+      if (m < a.M && n0 + r < a.N) {
+        float v = red[0][r][m];
+        if (a.in.sumsq) v *= row_factor[m];
+        if (a.bias) v += a.bias[n0 + r];
+        const size_t at = (size_t)m * a.N + n0 + r;
+        now = a.resid[at] + v;
+        a.resid[at] = now;
+        out[at] = __float2bfloat16_rn(now * a.next_w[n0 + r]);
+      }
+      float sq = now * now;
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      if (r == 0 && m < a.M) a.out_sumsq[(size_t)m * a.out_stride + tile] = sq;
     }
   } else {
     for (int i = threadIdx.x; i < 16 * 8 * NT; i += LS_WARPS * 32) {
       const int m = i >> 4, r = i & 15;
       if (m < a.M && n0 + r < a.N) {
         float v = red[0][r][m];
+        if (a.in.sumsq) v *= row_factor[m];
         if (a.bias) v += a.bias[n0 + r];
         if (a.epilogue == EPI_F32)
           ((float*)a.out)[(size_t)m * a.N + n0 + r] = v;
@@ -179,7 +227,7 @@ linear_small_kernel(LinearArgs a) {
   }
 }
 
-template <int NT, int U, int LS_WARPS>
+template <int NT, int U, int LS_WARPS, int OCC>
 int launch_linear_small(const LinearArgs& a, int tiles, int ranks, cudaStream_t stream) {
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(tiles * ranks);
@@ -196,9 +244,9 @@ int launch_linear_small(const LinearArgs& a, int tiles, int ranks, cudaStream_t 
     attr[config.numAttrs].val.clusterDim.y = 1;
     attr[config.numAttrs].val.clusterDim.z = 1;
     ++config.numAttrs;
-    err = cudaLaunchKernelEx(&config, linear_small_kernel<NT, true, U, LS_WARPS>, a);
+    err = cudaLaunchKernelEx(&config, linear_small_kernel<NT, true, U, LS_WARPS, OCC>, a);
   } else {
-    err = cudaLaunchKernelEx(&config, linear_small_kernel<NT, false, U, LS_WARPS>, a);
+    err = cudaLaunchKernelEx(&config, linear_small_kernel<NT, false, U, LS_WARPS, OCC>, a);
   }
   if (err != cudaSuccess) {
     mll_set_error("linear_small: launch failed: %s", cudaGetErrorString(err));
@@ -208,11 +256,6 @@ int launch_linear_small(const LinearArgs& a, int tiles, int ranks, cudaStream_t 
 }
 
 }  // namespace mll
-
-// tuning knob for experiments: chunks in flight per warp for M <= 16 (2 only up to 8 rows, 4 or 8)
-extern "C" __attribute__((visibility("default"))) int mll_linear_small_unroll = 4;
-// tuning knob for experiments: warps per block for M <= 16 (4 or 8)
-extern "C" __attribute__((visibility("default"))) int mll_linear_small_warps = 4;
 
 // Whether mll_linear_small takes this problem (the caller uses the library GEMM otherwise).
 MLL_API int mll_linear_small_supported(int M, int N, int K, int epilogue) {
@@ -225,53 +268,69 @@ MLL_API int mll_linear_small_supported(int M, int N, int K, int epilogue) {
 // out: bfloat16 [M, N] (epilogue 0), float32 [M, N] (1), or bfloat16 [M, N / 2] = silu(gate) * up
 // with gate and up rows of w interleaved in blocks of 8 (2).  ranks: cluster size along K
 // (1, 2, 4 or 8), 0 = choose.
-MLL_API int mll_linear_small(const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
-                             int epilogue, int ranks,
-                             cudaStream_t stream) {
-  MLL_REQUIRE(mll_linear_small_supported(M, N, K, epilogue), "linear_small: unsupported sizes M=%d N=%d K=%d", M, N, K);
-  MLL_REQUIRE(epilogue >= 0 && epilogue <= 2, "linear_small: unknown epilogue %d", epilogue);
+// in_sumsq (optional, float32 [M, in_stride], in_partials of each row used): x lacks its RMS norm's
+// factor 1 / sqrt(sum / K + in_eps), which the result is multiplied by.
+// Epilogue 3 (at most 16 rows): resid (float32 [M, N]) += result; out (bfloat16 [M, N]) = resid * next_w;
+// out_sumsq (float32 [M, out_stride], out_stride >= ceil(N / 16)): entry [m][j] = sum of resid[m]^2 over
+// columns 16 j .. 16 j + 15.
+MLL_API int mll_linear_small_fused(const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
+                                   int epilogue, int ranks, const float* in_sumsq, int in_partials, int in_stride,
+                                   float in_eps, float* resid, const float* next_w, float* out_sumsq, int out_stride,
+                                   cudaStream_t stream) {
+  MLL_REQUIRE(epilogue >= 0 && epilogue <= 3, "linear_small: unknown epilogue %d", epilogue);
+  MLL_REQUIRE(mll_linear_small_supported(M, N, K, epilogue == mll::EPI_RESID ? 0 : epilogue),
+              "linear_small: unsupported sizes M=%d N=%d K=%d", M, N, K);
   MLL_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "linear_small: operands must be 16-byte aligned");
   MLL_REQUIRE(epilogue != mll::EPI_SWIGLU || bias == nullptr, "linear_small: the SwiGLU epilogue takes no bias");
+  if (in_sumsq) {
+    MLL_REQUIRE(in_partials >= 1 && in_stride >= in_partials, "linear_small: partial sums: %d of stride %d",
+                in_partials, in_stride);
+    MLL_REQUIRE(in_eps >= 0.f, "linear_small: eps must be non-negative");
+  }
+  if (epilogue == mll::EPI_RESID) {
+    MLL_REQUIRE(M <= 16, "linear_small: the residual epilogue takes at most 16 rows, got %d", M);
+    MLL_REQUIRE(resid && next_w && out_sumsq && out_stride >= (N + 15) / 16,
+                "linear_small: the residual epilogue needs resid, next_w and out_sumsq with stride >= %d", (N + 15) / 16);
+  }
   const int tiles = (N + 15) / 16;
   const int chunks = K / 32;
-  // With the knobs at their defaults the variant is chosen here (8B shape, 8 rows, CUDA-graph timing):
-  //   * two k-ranks of every tile fit on the machine at the 8-fold unrolled kernel's occupancy (128
-  //     registers: 4 blocks per multiprocessor): that kernel, twice the loads in flight per warp and
-  //     half the trips (o 8.7 against 9.2 us, down 22.0 against 24.4);
-  //   * more tiles than that (q/k/v): 8 warps per block, 8-fold unrolled, no k-ranks (11.0 against 12.6 us).
-  const bool knobs_default = mll_linear_small_warps == 4 && mll_linear_small_unroll == 4 && ranks <= 0;
-  const bool defaults = knobs_default && M <= 8;
-  const bool deep = defaults && tiles * 2 <= 148 * 4 && chunks / (4 * 2) >= 8;
-  //   * 9 to 16 rows (two batch tiles): 8 warps per block, no k-ranks, 8-fold unrolled when one wave of
-  //     that kernel takes all tiles (o 8.7, down 23.3, q/k/v 11.8 us at 16 rows; library 9.8 / 23.5 / 12.5).
-  const bool two_tiles = knobs_default && M > 8 && M <= 16 && chunks >= 64;
-  const int warps = (mll_linear_small_warps == 8 && M <= 16) || (defaults && !deep && chunks >= 64) || two_tiles ? 8 : 4;
-  const bool wide_unroll = mll_linear_small_unroll == 8 || (two_tiles && tiles <= 148 * 2);
-  if (deep) ranks = 2;
-  if (two_tiles) ranks = 1;
+  // The variant (8B shapes, CUDA-graph timings at 8 / 16 rows, us; ideal = bytes / 6.65 TB/s):
+  //   * K of 2048 or more, at most 16 rows: 8 warps per block.  All tiles in one wave of the 128-register
+  //     kernel (2 blocks per multiprocessor): that one, 8 chunks in flight per warp (o 7.8 / 8.5, ideal 5.0;
+  //     down 21.6 / 24.1, ideal 17.7); more tiles: the 80-register kernel with 4 chunks in flight, 3 blocks per
+  //     multiprocessor (q/k/v 10.0-10.6 / 11.6-12.4, ideal 7.6).  Both without k-ranks at these sizes.
+  //   * otherwise 4 warps and the compiler's register choice.
+  const bool wide = chunks >= 64 && M <= 16;
+  const bool one_wave = tiles <= 148 * 2;
+  const int warps = wide ? 8 : 4;
   if (ranks <= 0) {
     // split K while every block still fits on the machine at once and a warp keeps at least 4 chunks
-    const int resident = 148 * (warps == 8 ? 5 : 10);
+    const int resident = 148 * (wide ? (one_wave ? 2 : 3) : 10);
     ranks = 1;
     while (ranks < 8 && tiles * ranks * 2 <= resident && chunks / (warps * ranks * 2) >= 4) ranks *= 2;
   }
   MLL_REQUIRE(ranks == 1 || ranks == 2 || ranks == 4 || ranks == 8, "linear_small: cluster size %d", ranks);
-  mll::LinearArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, out, M, N, K, epilogue, 0};
+  mll::LinearArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, bias, out, M, N, K, epilogue, 0,
+                    mll::RowNormIn{in_sumsq, in_partials, in_stride, in_eps}, resid, next_w, out_sumsq, out_stride};
   const int splits = warps * ranks;
   a.chunks_per_warp = (chunks + splits - 1) / splits;
   if (M <= 8) {
-    if (warps == 8 && (mll_linear_small_unroll == 8 || defaults)) return mll::launch_linear_small<1, 8, 8>(a, tiles, ranks, stream);
-    if (warps == 8) return mll::launch_linear_small<1, 4, 8>(a, tiles, ranks, stream);
-    if (mll_linear_small_unroll == 2) return mll::launch_linear_small<1, 2, 4>(a, tiles, ranks, stream);
-    if (mll_linear_small_unroll == 8 || deep) return mll::launch_linear_small<1, 8, 4>(a, tiles, ranks, stream);
-    return mll::launch_linear_small<1, 4, 4>(a, tiles, ranks, stream);
+    if (wide && one_wave) return mll::launch_linear_small<1, 8, 8, 16>(a, tiles, ranks, stream);
+    if (wide) return mll::launch_linear_small<1, 4, 8, 24>(a, tiles, ranks, stream);
+    return mll::launch_linear_small<1, 4, 4, 0>(a, tiles, ranks, stream);
   }
   if (M <= 16) {
-    if (warps == 8 && wide_unroll) return mll::launch_linear_small<2, 8, 8>(a, tiles, ranks, stream);
-    if (warps == 8) return mll::launch_linear_small<2, 4, 8>(a, tiles, ranks, stream);
-    if (mll_linear_small_unroll == 8) return mll::launch_linear_small<2, 8, 4>(a, tiles, ranks, stream);
-    return mll::launch_linear_small<2, 4, 4>(a, tiles, ranks, stream);
+    if (wide && one_wave) return mll::launch_linear_small<2, 8, 8, 16>(a, tiles, ranks, stream);
+    if (wide) return mll::launch_linear_small<2, 4, 8, 24>(a, tiles, ranks, stream);
+    return mll::launch_linear_small<2, 4, 4, 0>(a, tiles, ranks, stream);
   }
-  if (M <= 32) return mll::launch_linear_small<4, 2, 4>(a, tiles, ranks, stream);
-  return mll::launch_linear_small<8, 2, 4>(a, tiles, ranks, stream);
+  if (M <= 32) return mll::launch_linear_small<4, 2, 4, 0>(a, tiles, ranks, stream);
+  return mll::launch_linear_small<8, 2, 4, 0>(a, tiles, ranks, stream);
+}
+
+MLL_API int mll_linear_small(const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
+                             int epilogue, int ranks, cudaStream_t stream) {
+  MLL_REQUIRE(epilogue != mll::EPI_RESID, "linear_small: the residual epilogue needs mll_linear_small_fused");
+  return mll_linear_small_fused(x, w, bias, out, M, N, K, epilogue, ranks, nullptr, 0, 0, 0.f, nullptr, nullptr,
+                                nullptr, 0, stream);
 }

@@ -47,6 +47,7 @@ struct Tc5Args {
   const float* bias;
   void* out;
   int M, N, K, epilogue, blocks_per_rank;
+  RowNormIn in;  // x still lacks its norm's factor (sumsq null: it does not)
 };
 
 __device__ __forceinline__ unsigned c_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -117,7 +118,7 @@ struct Tc5Smem {
   static constexpr int TMEM_COLS = 2 * NB < 32 ? 32 : 2 * NB;  // one accumulator per MMA issuer
   // the float32 tile that the epilogue works on reuses the ring once the last MMA is done
   static constexpr int RING = STAGES * STAGE > RED_FLOATS * 4 ? STAGES * STAGE : RED_FLOATS * 4;
-  static constexpr size_t BYTES = 1024 + (size_t)RING + 128;
+  static constexpr size_t BYTES = 1024 + (size_t)RING + 128 + NB * 4;  // ring, barriers and tensor-memory slot, row factors
 };
 
 template <int NB, bool CLUSTER>
@@ -129,6 +130,7 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
   float* red = reinterpret_cast<float*>(base);  // [128][NB], over the ring: written only after the last MMA
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(base + L::RING);  // full[S], empty[S], done
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * L::STAGES + 1);
+  float* row_factor = reinterpret_cast<float*>(base + L::RING + 128);  // [NB]
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int rank = 0, ranks = 1;
@@ -209,6 +211,13 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
 
   // epilogue warps: accumulator row (weight row) = TMEM lane, one row per thread
   if (warp < 4) {
+    if (a.in.sumsq && rank == 0) {  // while the products run: the rows' norm factors, for the epilogue
+      for (int m = warp; m < a.M; m += 4) {
+        const float f = row_norm_factor<32>(a.in.sumsq + (size_t)m * a.in.stride, a.in.partials, a.K, a.in.eps, lane,
+                                            0xffffffffu);
+        if (lane == 0) row_factor[m] = f;
+      }
+    }
     const bool ok = c_mbar_wait(done_bar, 0);
     tc_fence_after();
     float* row = red + (warp * 32 + lane) * NB;
@@ -265,7 +274,8 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
       const int m = i / (C_ROWS / 2), j = i % (C_ROWS / 2);
       const int row = (j >> 3) * 16 + (j & 7);  // gate row; its up row is 8 further
       if (m < a.M && n0 + row + 8 < a.N) {
-        const float gate = red[row * NB + m], up = red[(row + 8) * NB + m];
+        const float f = a.in.sumsq ? row_factor[m] : 1.f;
+        const float gate = red[row * NB + m] * f, up = red[(row + 8) * NB + m] * f;
         out[(size_t)m * half + (n0 >> 1) + j] = __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
       }
     }
@@ -274,6 +284,7 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
       const int m = i / C_ROWS, row = i % C_ROWS;
       if (m < a.M && n0 + row < a.N) {
         float v = red[row * NB + m];
+        if (a.in.sumsq) v *= row_factor[m];
         if (a.bias) v += a.bias[n0 + row];
         if (a.epilogue == CEPI_F32)
           ((float*)a.out)[(size_t)m * a.N + n0 + row] = v;
@@ -346,9 +357,12 @@ MLL_API int mll_linear_tc5_supported(int M, int N, int K, int epilogue) {
   return 1;
 }
 
-// Same contract as mll_linear_tma.  ranks: cluster size along K (1, 2, 4 or 8), 0 = choose.
-MLL_API int mll_linear_tc5(const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
-                           int epilogue, int ranks, cudaStream_t stream) {
+// Same contract as mll_linear_tma_fused.  ranks: cluster size along K (1, 2, 4 or 8), 0 = choose.
+MLL_API int mll_linear_tc5_fused(const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
+                                 int epilogue, int ranks, const float* in_sumsq, int in_partials, int in_stride,
+                                 float in_eps, cudaStream_t stream) {
+  MLL_REQUIRE(!in_sumsq || (in_partials >= 1 && in_stride >= in_partials && in_eps >= 0.f),
+              "linear_tc5: partial sums: %d of stride %d", in_partials, in_stride);
   MLL_REQUIRE(mll_linear_tc5_supported(M, N, K, epilogue), "linear_tc5: unsupported sizes M=%d N=%d K=%d", M, N, K);
   MLL_REQUIRE(epilogue >= 0 && epilogue <= 2, "linear_tc5: unknown epilogue %d", epilogue);
   MLL_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "linear_tc5: operands must be 16-byte aligned");
@@ -367,6 +381,12 @@ MLL_API int mll_linear_tc5(const void* x, const void* w, const float* bias, void
   CUtensorMap wmap, xmap;
   if (mll::tensor_map_bf16(w, N, K, mll::C_ROWS, &wmap) != 0) return -1;
   if (mll::tensor_map_bf16(x, M, K, nb, &xmap) != 0) return -1;
-  mll::Tc5Args a{bias, out, M, N, K, epilogue, (k_blocks + ranks - 1) / ranks};
+  mll::Tc5Args a{bias, out, M, N, K, epilogue, (k_blocks + ranks - 1) / ranks,
+                 mll::RowNormIn{in_sumsq, in_partials, in_stride, in_eps}};
   return mll::launch_linear_tc5<16>(wmap, xmap, a, tiles, ranks, stream);
+}
+
+MLL_API int mll_linear_tc5(const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
+                           int epilogue, int ranks, cudaStream_t stream) {
+  return mll_linear_tc5_fused(x, w, bias, out, M, N, K, epilogue, ranks, nullptr, 0, 0, 0.f, stream);
 }

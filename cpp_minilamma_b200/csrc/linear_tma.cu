@@ -46,6 +46,7 @@ struct TmaLinearArgs {
   const float* bias;  // optional [N]
   void* out;          // [M, N] (SwiGLU: [M, N / 2])
   int M, N, K, epilogue, blocks_per_rank;
+  RowNormIn in;       // x still lacks its norm's factor (sumsq null: it does not)
 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -99,7 +100,7 @@ struct TmaSmem {
   static constexpr int X_BYTES = 8 * NT * T_KB * 2;       // 1024 per n-tile
   static constexpr int STAGE = W_BYTES + X_BYTES;         // a multiple of 1024
   static constexpr int RED_FLOATS = T_ROWS * 8 * NT;
-  static constexpr size_t BYTES = 1024 /* alignment slack */ + (size_t)T_STAGES * STAGE + RED_FLOATS * 4 + 64;
+  static constexpr size_t BYTES = 1024 /* alignment slack */ + (size_t)T_STAGES * STAGE + RED_FLOATS * 4 + 64 + 8 * NT * 4;
 };
 
 // grid: row tiles * cluster size; block: 160 threads.
@@ -112,6 +113,7 @@ linear_tma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   float* red = reinterpret_cast<float*>(base + (size_t)T_STAGES * L::STAGE);          // [64][8 NT]
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(red + L::RED_FLOATS);  // full[S], empty[S]
+  float* row_factor = reinterpret_cast<float*>(bars + 8);                                 // [8 NT]
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int rank = 0, ranks = 1;
@@ -171,6 +173,14 @@ linear_tma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
     const unsigned a_xor = row & 7;
     const unsigned a_hi = lane >> 4;  // second 16-byte chunk of the k-step
     const unsigned x_chunk = lane >> 3;  // B: chunks 2 ks + {0, 1} and 2 (ks + 1) + {0, 1}
+    if (a.in.sumsq && rank == 0) {
+      // the first stage is a memory latency away: time for the rows' norm factors, which the epilogue needs
+      for (int m = warp; m < a.M; m += 4) {
+        const float f = row_norm_factor<32>(a.in.sumsq + (size_t)m * a.in.stride, a.in.partials, a.K, a.in.eps, lane,
+                                            0xffffffffu);
+        if (lane == 0) row_factor[m] = f;
+      }
+    }
     for (int i = 0; i < count; ++i) {
       const int s = i % T_STAGES;
       if (!mbar_wait(smem_u32(bars + s), (i / T_STAGES) & 1)) break;
@@ -229,7 +239,8 @@ linear_tma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
       const int m = i / (T_ROWS / 2), j = i % (T_ROWS / 2);  // j: output column within the tile's 32
       const int row = (j >> 3) * 16 + (j & 7);               // gate row; its up row is 8 further
       if (m < a.M && n0 + row + 8 < a.N) {
-        const float gate = red[row * COLS + m], up = red[(row + 8) * COLS + m];
+        const float f = a.in.sumsq ? row_factor[m] : 1.f;
+        const float gate = red[row * COLS + m] * f, up = red[(row + 8) * COLS + m] * f;
         out[(size_t)m * half + (n0 >> 1) + j] = __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
       }
     }
@@ -238,6 +249,7 @@ linear_tma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
       const int m = i / T_ROWS, row = i % T_ROWS;
       if (m < a.M && n0 + row < a.N) {
         float v = red[row * COLS + m];
+        if (a.in.sumsq) v *= row_factor[m];
         if (a.bias) v += a.bias[n0 + row];
         if (a.epilogue == TEPI_F32)
           ((float*)a.out)[(size_t)m * a.N + n0 + row] = v;
@@ -381,9 +393,13 @@ MLL_API int mll_linear_tma_supported(int M, int N, int K, int epilogue) {
 }
 
 // x: bfloat16 [M, K]; w: bfloat16 [N, K]; bias: optional float32 [N]; out and epilogue as in
-// mll_linear_small.  ranks: cluster size along K (1, 2, 4 or 8), 0 = choose.
-MLL_API int mll_linear_tma(const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
-                           int epilogue, int ranks, cudaStream_t stream) {
+// mll_linear_small.  ranks: cluster size along K (1, 2, 4 or 8), 0 = choose.  in_sumsq, in_partials,
+// in_stride, in_eps: as in mll_linear_small_fused (x lacks its RMS norm's factor), or null.
+MLL_API int mll_linear_tma_fused(const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
+                                 int epilogue, int ranks, const float* in_sumsq, int in_partials, int in_stride,
+                                 float in_eps, cudaStream_t stream) {
+  MLL_REQUIRE(!in_sumsq || (in_partials >= 1 && in_stride >= in_partials && in_eps >= 0.f),
+              "linear_tma: partial sums: %d of stride %d", in_partials, in_stride);
   MLL_REQUIRE(mll_linear_tma_supported(M, N, K, epilogue), "linear_tma: unsupported sizes M=%d N=%d K=%d", M, N, K);
   MLL_REQUIRE(epilogue >= 0 && epilogue <= 2, "linear_tma: unknown epilogue %d", epilogue);
   MLL_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "linear_tma: operands must be 16-byte aligned");
@@ -400,9 +416,15 @@ MLL_API int mll_linear_tma(const void* x, const void* w, const float* bias, void
   CUtensorMap wmap, xmap;
   if (mll::tensor_map_bf16(w, N, K, mll::T_ROWS, &wmap) != 0) return -1;
   if (mll::tensor_map_bf16(x, M, K, 8 * nt, &xmap) != 0) return -1;
-  mll::TmaLinearArgs a{bias, out, M, N, K, epilogue, (k_blocks + ranks - 1) / ranks};
+  mll::TmaLinearArgs a{bias, out, M, N, K, epilogue, (k_blocks + ranks - 1) / ranks,
+                       mll::RowNormIn{in_sumsq, in_partials, in_stride, in_eps}};
   if (nt == 1) return mll::launch_linear_tma<1>(wmap, xmap, a, tiles, ranks, stream);
   if (nt == 2) return mll::launch_linear_tma<2>(wmap, xmap, a, tiles, ranks, stream);
   if (nt == 4) return mll::launch_linear_tma<4>(wmap, xmap, a, tiles, ranks, stream);
   return mll::launch_linear_tma<8>(wmap, xmap, a, tiles, ranks, stream);
+}
+
+MLL_API int mll_linear_tma(const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
+                           int epilogue, int ranks, cudaStream_t stream) {
+  return mll_linear_tma_fused(x, w, bias, out, M, N, K, epilogue, ranks, nullptr, 0, 0, 0.f, stream);
 }

@@ -153,7 +153,37 @@ int launch_add_rmsnorm(float* x, const void* delta, const float* weight, void* o
   return 0;
 }
 
+// Finishes a norm whose rows were left without their factor (RowNormIn), for a product that cannot do
+// it itself: out[m, i] = values[m, i] * factor(m).  One block per row.
+__global__ void apply_row_norm_kernel(const __nv_bfloat16* __restrict__ values, RowNormIn in,
+                                      __nv_bfloat16* __restrict__ out, int width) {
+  __shared__ float factor;
+  const int m = blockIdx.x;
+  if (threadIdx.x < 32) {
+    const float f = row_norm_factor<32>(in.sumsq + (size_t)m * in.stride, in.partials, width, in.eps, threadIdx.x,
+                                        0xffffffffu);
+    if (threadIdx.x == 0) factor = f;
+  }
+  __syncthreads();
+  const float f = factor;
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    out[(size_t)m * width + i] = __float2bfloat16_rn(__bfloat162float(values[(size_t)m * width + i]) * f);
+}
+
 }  // namespace mll
+
+// values, out: bfloat16 [n_rows, width]; sumsq: float32 [n_rows, stride] with `partials` sums of squares
+// per row; out = values / sqrt(sum / width + eps).
+MLL_API int mll_apply_row_norm(const void* values, const float* sumsq, int partials, int stride, float eps, void* out,
+                               int n_rows, int width, cudaStream_t stream) {
+  MLL_REQUIRE(n_rows >= 0 && width > 0 && partials >= 1 && stride >= partials && eps >= 0.f,
+              "apply_row_norm: bad sizes rows=%d width=%d partials=%d stride=%d", n_rows, width, partials, stride);
+  if (n_rows == 0) return 0;
+  MLL_LAUNCH((mll::apply_row_norm_kernel), n_rows, 256, 0, stream, (const __nv_bfloat16*)values,
+             mll::RowNormIn{sumsq, partials, stride, eps}, (__nv_bfloat16*)out, width);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
 
 // x: float32 [*, width] residual stream; delta: optional [*, width] of `act_dtype`;
 // weight: float32 [width]; out: [n_rows, width] of `act_dtype`; rows: optional int32

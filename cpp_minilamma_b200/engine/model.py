@@ -115,9 +115,16 @@ class Model:
             raise RuntimeError("the model has no weights bound")
         x = self.embedding.forward(step, tokens)
         pending = None
-        for i, entry in enumerate(self.spec.schedule):
+        schedule = self.spec.schedule
+        for i, entry in enumerate(schedule):
             layer = self.layers[entry.layer]
-            pending = layer.block.forward(step, x, pending, layer, cache.view(i))
+            if layer.block.first_reader(layer) is None:
+                pending = layer.block.forward(step, x, pending, layer, cache.view(i))
+                continue
+            # this arrangement can fold a norm into the products around it: tell it who reads the stream next
+            follower = self.layers[schedule[i + 1].layer] if i + 1 < len(schedule) else None
+            reader = follower.block.first_reader(follower) if follower else None
+            pending = layer.block.forward(step, x, pending, layer, cache.view(i), next_reader=reader)
         if want_rows is None or want_rows.shape[0] == 0:
             return None
         h = self.final_norm.forward(step, x, pending, rows=want_rows, out_name="h_final")

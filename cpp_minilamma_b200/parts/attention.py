@@ -15,7 +15,7 @@ from typing import List, Optional
 import torch
 
 from ..csrc import kernels as K
-from .base import (BuildContext, CacheNeed, KVNeed, Mixer, PartSpec, WeightSpec, register_part)
+from .base import (BuildContext, CacheNeed, KVNeed, Mixer, PartSpec, PreNormed, WeightSpec, register_part)
 from .linear import Linear
 from .rope import shared_position_encoding
 
@@ -108,8 +108,11 @@ class Attention(Mixer):
         # context serves the short ones at their own split count.
         return max(1, min(_TARGET_BLOCKS // blocks, pages, max(16, pages // 16)))
 
-    def forward(self, step, h: torch.Tensor, cache) -> torch.Tensor:
-        T = h.shape[0]
+    takes_prenormed = True  # the q/k/v product may read rows whose norm it finishes itself
+    adds_residual = True    # the output product may add to the residual stream and prepare the next norm
+
+    def forward(self, step, h, cache, into=None):
+        T = (h.values if isinstance(h, PreNormed) else h).shape[0]
         d, Hq, Hk = self.head_dim, self.n_heads, self.n_kv_heads
         act = self.ctx.act_dtype
         if cache.k is None:
@@ -143,9 +146,10 @@ class Attention(Mixer):
                 K.attention_prefill(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
                                     step.tile_seq, step.tile_row0, cache.block_table, out, step.n_tiles,
                                     Hq, Hk, d, self.window, self.scale)
+        if self.o_bias_t is None:
+            return self.o.forward(step, out, "o", into=into)
         o = self.o.forward(step, out, "o")
-        if self.o_bias_t is not None:
-            K.add_bias(o, self.o_bias_t)
+        K.add_bias(o, self.o_bias_t)
         return o
 
 

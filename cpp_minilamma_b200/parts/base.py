@@ -13,6 +13,9 @@ Roles and their interfaces
   mixer              `Mixer.cache_need()`, `Mixer.forward(step, h, cache)` -> [T, D]
   feed-forward       `FeedForward.forward(step, h)` -> [T, D]
   block              `Block.forward(step, x, pending, layer, cache)` -> pending delta
+A part may offer more than its role asks (see `PreNormed`): the flags `takes_prenormed` and
+`adds_residual` of a mixer or feed-forward, `Norm.prenorm_weight`, `Block.first_reader`.  They are off by
+default, and a part that leaves them off never meets the objects they bring.
 Every part also lists the tensors it loads (`weight_specs`) and receives them by name
 (`bind`).  The reference has one hard-wired graph (src/forward.cc:385-414); these seams
 are this library's own.
@@ -109,6 +112,34 @@ class CacheNeed:
 
 
 # --------------------------------------------------------------------------- #
+# a norm folded into the products around it                                    #
+# --------------------------------------------------------------------------- #
+@dataclass
+class PreNormed:
+    """Rows of the residual stream on their way through a norm y = x * w / rms(x): `values` [T, D]
+    holds x * w, `sumsq` float32 [T, stride] holds `partials` partial sums of x^2 per row.  The product
+    that reads them multiplies its result by 1 / sqrt(sum / D + eps), so that no kernel runs for the norm.
+    The part that ended the previous sub-layer writes it (it has already added its output to the residual
+    stream), `norm` is the norm it was written for, and only a part with `takes_prenormed` is given one."""
+
+    values: torch.Tensor
+    sumsq: torch.Tensor
+    partials: int
+    eps: float
+    norm: "Norm"
+
+
+@dataclass
+class ResidualTarget:
+    """Offered to a part with `adds_residual`: it may add its output to the float32 residual stream `x`
+    itself and return a `PreNormed` for `norm`, the norm that reads the stream next, instead of returning
+    the output.  It may also ignore the offer."""
+
+    x: torch.Tensor
+    norm: "Norm"
+
+
+# --------------------------------------------------------------------------- #
 # build context and part bases                                                 #
 # --------------------------------------------------------------------------- #
 @dataclass
@@ -177,12 +208,19 @@ class Norm(Part):
     def forward(self, step, x: torch.Tensor, delta: Optional[torch.Tensor],
                 rows: Optional[torch.Tensor] = None, out_name: str = "h") -> torch.Tensor:
         """x += delta (in place, float32), return norm(x) in the activation dtype; with
-        `rows` only those rows, x unchanged."""
+        `rows` only those rows, x unchanged.  A `PreNormed` made for this norm is handed on as it is."""
         raise NotImplementedError
+
+    def prenorm_weight(self):
+        """(weight float32 [D], eps) if the norm is x * weight / sqrt(mean(x^2) + eps) and may be folded
+        into the products around it (`PreNormed`), else None."""
+        return None
 
 
 class Mixer(Part):
     role = "mixer"
+    takes_prenormed = False  # True: `h` may be a PreNormed
+    adds_residual = False    # True: forward has a keyword `into` (a ResidualTarget or None) and may return a PreNormed
 
     def cache_need(self) -> CacheNeed:
         return CacheNeed()
@@ -193,6 +231,8 @@ class Mixer(Part):
 
 class FeedForward(Part):
     role = "feed_forward"
+    takes_prenormed = False  # as for a mixer
+    adds_residual = False
 
     def forward(self, step, h: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
@@ -208,8 +248,15 @@ class Block(Part):
 
     def forward(self, step, x: torch.Tensor, pending: Optional[torch.Tensor], layer, cache):
         """Run one layer on residual x [T, D] (float32).  `pending` is a delta still to be
-        added to x (so that the next norm kernel can fuse the add); returns the new pending."""
+        added to x (so that the next norm kernel can fuse the add); returns the new pending.
+        A block whose `first_reader` is not None also takes the keyword `next_reader` (the first reader
+        of the layer that runs next, or None) and may then return, and be given, a `PreNormed`."""
         raise NotImplementedError
+
+    def first_reader(self, layer):
+        """(norm, part): the norm that reads the residual stream first in this arrangement and the part that
+        takes its output - if the layer before may fold that norm away (`PreNormed`), else None."""
+        return None
 
 
 # --------------------------------------------------------------------------- #

@@ -6,7 +6,9 @@ W is row-major [out, in] as in the reference (src/cuda_matmul.cc:181-186, one
   * float32 weight: a true float32 product (TF32 must be off; it is refused otherwise);
     bfloat16 activations are widened first and the result narrowed afterwards.
 Large products go to the library GEMM (as the reference's do); small batches of rows go
-to this package's own weight-streaming kernel when it is available for the shape.
+to this package's own weight-streaming kernel when it is available for the shape.  That kernel can
+also finish the norm in front of the product (input `PreNormed`) and start the one behind it
+(`into`, a `ResidualTarget`), so that neither norm is a kernel of its own.
 """
 from __future__ import annotations
 
@@ -15,6 +17,7 @@ from typing import Optional
 import torch
 
 from ..csrc import kernels as K
+from .base import PreNormed, ResidualTarget
 
 
 class Linear:
@@ -30,8 +33,17 @@ class Linear:
     def parameter_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
 
-    def forward(self, step, x: torch.Tensor, out_name: str, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        """x [T, K] in the activation dtype -> [T, N] in `out_dtype` (default: x's dtype)."""
+    def forward(self, step, x, out_name: str, out_dtype: Optional[torch.dtype] = None,
+                into: Optional[ResidualTarget] = None):
+        """x [T, K] in the activation dtype -> [T, N] in `out_dtype` (default: x's dtype).
+
+        x may be a `PreNormed` (bfloat16 only: nothing else makes one).  With `into`, the product may add
+        its result to the residual stream and return a `PreNormed` for the norm named there; it does so for
+        the few rows of a decode step, and returns the plain result otherwise."""
+        row_norm = None
+        if isinstance(x, PreNormed):
+            row_norm = K.RowNorm(x.sumsq, x.partials, x.eps)
+            x = x.values
         rows = x.shape[0]
         if x.shape[1] != self.in_features:
             raise ValueError(f"{self.name}: input width {x.shape[1]} != {self.in_features}")
@@ -39,6 +51,8 @@ class Linear:
         w = self.weight
         ws = step.ws
         if w.dtype == torch.float32:
+            if row_norm is not None:
+                raise RuntimeError(f"{self.name}: rows without their norm's factor reached a float32 product")
             if torch.backends.cuda.matmul.allow_tf32:
                 raise RuntimeError(f"{self.name}: TF32 is enabled; the float32 path needs true 32-bit products")
             if x.dtype != torch.float32:
@@ -58,15 +72,38 @@ class Linear:
         if x.dtype != torch.bfloat16:
             raise RuntimeError(f"{self.name}: bfloat16 weight with {x.dtype} activations; "
                                "a float32 run widens its matrices when it loads them")
+        if into is not None and rows <= step.small_rows and out_dtype == torch.bfloat16:
+            made = self._into_residual(ws, x, row_norm, out_name, into)
+            if made is not None:
+                return made
         out = ws.buffer(out_name, (rows, self.out_features), out_dtype)
         if rows <= step.small_rows and K.small_linear(x, w, None, out,
-                                                       K.EPI_F32 if out_dtype == torch.float32 else K.EPI_BF16):
+                                                       K.EPI_F32 if out_dtype == torch.float32 else K.EPI_BF16,
+                                                       row_norm):
             return out
+        if row_norm is not None:  # no kernel of this package takes the shape: finish the norm first
+            normed = ws.buffer(out_name + ".x", (rows, self.in_features), torch.bfloat16)
+            K.apply_row_norm(x, row_norm, normed)
+            x = normed
         if out_dtype == torch.bfloat16:
             torch.mm(x, w.t(), out=out)
         else:  # bfloat16 operands, float32 result (the logits)
             _mm_bf16_to_f32(x, w, out)
         return out
+
+
+    def _into_residual(self, ws, x, row_norm, out_name: str, into: ResidualTarget) -> Optional[PreNormed]:
+        prenorm = into.norm.prenorm_weight()
+        rows, width = x.shape[0], self.out_features
+        if prenorm is None or into.x.shape != (rows, width) or not K.fused_norm_rows(rows):
+            return None
+        weight, eps = prenorm
+        partials = -(-width // K.NORM_TILE)
+        values = ws.buffer(out_name + ".pre", (rows, width), torch.bfloat16)
+        sumsq = ws.buffer(out_name + ".sumsq", (rows, partials), torch.float32)
+        if not K.small_linear(x, self.weight, None, values, K.EPI_RESID, row_norm, K.ResidualOut(into.x, weight, sumsq)):
+            return None
+        return PreNormed(values, sumsq, partials, eps, into.norm)
 
 
 _MM_OUT_DTYPE_WITH_OUT = None

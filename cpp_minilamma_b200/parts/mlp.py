@@ -14,7 +14,7 @@ from typing import List, Optional
 import torch
 
 from ..csrc import kernels as K
-from .base import BuildContext, FeedForward, WeightSpec, register_part
+from .base import BuildContext, FeedForward, PreNormed, WeightSpec, register_part
 from .linear import Linear
 
 INTERLEAVE = 8
@@ -36,6 +36,8 @@ class SwiGLUFeedForward(FeedForward):
     """params: intermediate, names {"gate","up","down"} (tensor name stems)."""
 
     capturable = True
+    takes_prenormed = True  # the gate/up product may read rows whose norm it finishes itself
+    adds_residual = True    # the down product may add to the residual stream and prepare the next norm
 
     def __init__(self, params, ctx: BuildContext):
         super().__init__(params, ctx)
@@ -60,21 +62,22 @@ class SwiGLUFeedForward(FeedForward):
     def parameter_bytes(self) -> int:
         return self.gate_up.parameter_bytes() + self.down.parameter_bytes()
 
-    def forward(self, step, h: torch.Tensor) -> torch.Tensor:
-        rows = h.shape[0]
+    def forward(self, step, h, into=None):
+        values, row_norm = (h.values, K.RowNorm(h.sumsq, h.partials, h.eps)) if isinstance(h, PreNormed) else (h, None)
+        rows = values.shape[0]
         w = self.gate_up.weight
         fused = (rows <= step.small_rows and self.block == INTERLEAVE and w.dtype == torch.bfloat16
-                 and h.dtype == torch.bfloat16
+                 and values.dtype == torch.bfloat16
                  and bool(K.small_linear_kind(rows, 2 * self.inter, w.shape[1], K.EPI_SWIGLU)))
         if fused:
             # few rows: one weight-streaming kernel whose epilogue applies the activation
             act = step.ws.buffer("act", (rows, self.inter), torch.bfloat16)
-            K.small_linear(h, w, None, act, K.EPI_SWIGLU)
+            K.small_linear(values, w, None, act, K.EPI_SWIGLU, row_norm)
         else:
             gu = self.gate_up.forward(step, h, "gu")
             act = step.ws.buffer("act", (rows, self.inter), gu.dtype)
             K.swiglu(gu, act, self.block)
-        return self.down.forward(step, act, "down")
+        return self.down.forward(step, act, "down", into=into)
 
 
 register_part("feed_forward", "swiglu", SwiGLUFeedForward)

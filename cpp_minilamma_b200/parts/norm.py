@@ -11,7 +11,7 @@ from typing import List, Optional
 import torch
 
 from ..csrc import kernels as K
-from .base import BuildContext, Norm, WeightSpec, register_part
+from .base import BuildContext, Norm, PreNormed, WeightSpec, register_part
 
 
 class RMSNorm(Norm):
@@ -35,7 +35,14 @@ class RMSNorm(Norm):
     def parameter_bytes(self) -> int:
         return self.width * 4
 
+    def prenorm_weight(self):
+        return self.weight, self.eps
+
     def forward(self, step, x, delta, rows=None, out_name: str = "h"):
+        if isinstance(delta, PreNormed):
+            if delta.norm is not self or rows is not None:
+                raise RuntimeError(f"{self.name}: given rows that were prepared for another norm")
+            return delta  # x is up to date; the product that reads the rows applies the factor
         n = x.shape[0] if rows is None else rows.shape[0]
         out = step.ws.buffer(out_name, (n, self.width), self.ctx.act_dtype)
         K.add_rmsnorm(x, delta, self.weight, out, self.eps, rows)

@@ -341,3 +341,37 @@ def test_long_generation_crosses_pages_under_graphs_and_run_ahead(model_folders,
                 assert row[best] - row[token] <= (2e-4 if dtype == "float32" else 0.04 * np.abs(row).max()), \
                     f"{name} {dtype}: token {i} is {token}, plain argmax {best}"
     llm.engine.cache.check()
+
+
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_decode_with_norms_folded_into_products_and_apart(model_folders, name, monkeypatch):
+    # decode steps of few rows fold every norm but the first and the last into the products around it;
+    # with that switched off each norm is a kernel of its own.  Both against the plain implementation.
+    from cpp_minilamma_b200.csrc import kernels as K
+    folder, llm = load(model_folders, name, "bfloat16")
+    layers = tc.TINY[name]["num_hidden_layers"]
+    lengths = [40, 70, 9]
+    requests = [tc.random_tokens(name, n, 900 + i) for i, n in enumerate(lengths)]
+    refs = [plain_logits(folder, tokens, "bfloat16") for tokens in requests]
+    norm_calls = []
+    real = K.add_rmsnorm
+    monkeypatch.setattr(K, "add_rmsnorm", lambda *a, **kw: (norm_calls.append(1), real(*a, **kw))[1])
+    for folded in (True, False):
+        monkeypatch.setattr(K, "FUSE_NORM", folded)
+        slots = llm.engine.acquire(len(requests))
+        heads = [n - 8 for n in lengths]
+        llm.engine.step([StepEntry(s, t[:h], []) for s, t, h in zip(slots, requests, heads)])
+        rows = [[] for _ in requests]
+        for k in range(8):
+            del norm_calls[:]
+            got = llm.engine.step([StepEntry(s, [t[h + k]], [0]) for s, t, h in zip(slots, requests, heads)]).cpu().numpy()
+            # B: every width is a multiple of 32; D: the direct kernel does not take the down product (K = 328),
+            # so that each layer's input norm stays a kernel
+            expected = {"B": 2, "D": 2 + layers - 1}[name] if folded else 2 * layers + 1
+            assert len(norm_calls) == expected, (folded, len(norm_calls))
+            for i in range(len(requests)):
+                rows[i].append(got[i])
+        for s in slots:
+            llm.engine.release(s)
+        for i, (n, h) in enumerate(zip(lengths, heads)):
+            assert_close(np.stack(rows[i]), refs[i][h:], "bfloat16", f"{name} folded={folded} request {i}")

@@ -668,3 +668,114 @@ def test_linear_tc5_swiglu(rows, inter, k, ranks):
     want = pl.swiglu(as64(x) @ as64(gate).T, as64(x) @ as64(up).T)
     np.testing.assert_allclose(as64(out), want, rtol=8e-3, atol=8e-3 * np.abs(want).max())
     assert K.take_device_error() == 0
+
+
+# ---- a norm folded into the products around it ---------------------------------------- #
+def _prenormed(rows, k, seed, eps):
+    """A residual stream, the norm's weight, and what the residual epilogue leaves of them: the rows
+    times the weight in bfloat16 and partial sums of squares per 16 columns."""
+    stream = rnd((rows, k), torch.float32, seed, 3.0)
+    weight = 1.0 + rnd((k,), torch.float32, seed + 1, 0.2)
+    values = (stream * weight).to(torch.bfloat16)
+    partials = -(-k // K.NORM_TILE)
+    stride = partials + 3  # the stride may exceed the count; what lies beyond is not read
+    sumsq = torch.full((rows, stride), float("nan"), dtype=torch.float32)
+    padded = torch.zeros((rows, partials * K.NORM_TILE), dtype=torch.float64)
+    padded[:, :k] = stream.double() ** 2
+    sumsq[:, :partials] = padded.view(rows, partials, K.NORM_TILE).sum(-1).float()
+    factor = 1.0 / np.sqrt((as64(stream) ** 2).mean(-1, keepdims=True) + eps)
+    return stream, weight, values, K.RowNorm(sumsq.to(DEV), partials, eps), factor
+
+
+@pytest.mark.parametrize("rows", [1, 3, 8, 13, 16])
+@pytest.mark.parametrize("n,k", [(48, 64), (4104, 4096), (100, 224), (6144, 4096), (512, 8192)])
+@pytest.mark.parametrize("kind", ["direct", "tma", "tc5"])
+def test_linear_finishes_the_norm_before_it(rows, n, k, kind):
+    # the product of rows that lack their norm's factor, times the factor, against norm then product
+    eps = 1e-5
+    stream, weight, values, row_norm, factor = _prenormed(rows, k, 60, eps)
+    w = rnd((n, k), torch.bfloat16, 62, 0.05)
+    bias = rnd((n,), torch.float32, 63)
+    run = {"direct": K.linear_small, "tma": K.linear_tma, "tc5": K.linear_tc5}[kind]
+    want = (as64(values) * factor) @ as64(w).T
+    against_norm = pl.rms_norm(as64(stream), as64(weight), eps) @ as64(w).T
+    np.testing.assert_allclose(want, against_norm, rtol=0, atol=8e-3 * np.abs(against_norm).max())
+    out = torch.full((rows, n), float("nan"), dtype=torch.float32, device=DEV)
+    run(values.to(DEV), w.to(DEV), bias.to(DEV), out, K.EPI_F32, 0, row_norm)
+    np.testing.assert_allclose(as64(out), want + as64(bias), rtol=2e-5, atol=2e-5 * np.abs(want).max())
+    out = torch.full((rows, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    run(values.to(DEV), w.to(DEV), None, out, K.EPI_BF16, 2 if k >= 4096 else 1, row_norm)
+    np.testing.assert_allclose(as64(out), want, rtol=8e-3, atol=8e-3 * np.abs(want).max())
+    assert K.take_device_error() == 0
+
+
+@pytest.mark.parametrize("rows", [2, 8, 11])
+@pytest.mark.parametrize("kind", ["direct", "tma", "tc5"])
+def test_linear_swiglu_finishes_the_norm_before_it(rows, kind):
+    inter, k, eps = 176, 320, 1e-6
+    stream, weight, values, row_norm, factor = _prenormed(rows, k, 64, eps)
+    gate = rnd((inter, k), torch.bfloat16, 66, 0.05)
+    up = rnd((inter, k), torch.bfloat16, 67, 0.05)
+    fused = torch.stack([gate.view(inter // 8, 8, k), up.view(inter // 8, 8, k)], dim=1).reshape(2 * inter, k)
+    run = {"direct": K.linear_small, "tma": K.linear_tma, "tc5": K.linear_tc5}[kind]
+    out = torch.full((rows, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    run(values.to(DEV), fused.contiguous().to(DEV), None, out, K.EPI_SWIGLU, 0, row_norm)
+    h = as64(values) * factor
+    want = pl.swiglu(h @ as64(gate).T, h @ as64(up).T)
+    np.testing.assert_allclose(as64(out), want, rtol=8e-3, atol=8e-3 * np.abs(want).max())
+    assert K.take_device_error() == 0
+
+
+@pytest.mark.parametrize("rows", [1, 3, 8, 13, 16])
+@pytest.mark.parametrize("n,k,ranks", [(48, 64, 1), (4096, 4096, 0), (100, 224, 1), (4096, 14336, 0), (520, 4096, 4)])
+@pytest.mark.parametrize("normed_input", [False, True])
+def test_linear_small_adds_to_the_residual_and_starts_the_next_norm(rows, n, k, ranks, normed_input):
+    eps = 1e-5
+    if normed_input:
+        _, _, x, row_norm, factor = _prenormed(rows, k, 70, eps)
+    else:
+        x, row_norm, factor = rnd((rows, k), torch.bfloat16, 70), None, 1.0
+    w = rnd((n, k), torch.bfloat16, 72, 0.05)
+    resid = rnd((rows, n), torch.float32, 73, 2.0)
+    next_w = 1.0 + rnd((n,), torch.float32, 74, 0.2)
+    tiles = -(-n // K.NORM_TILE)
+    stride = tiles + 5
+    resid_dev = resid.to(DEV)
+    values = torch.full((rows, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    sumsq = torch.full((rows, stride), float("nan"), dtype=torch.float32, device=DEV)
+    K.linear_small(x.to(DEV), w.to(DEV), None, values, K.EPI_RESID, ranks, row_norm,
+                   K.ResidualOut(resid_dev, next_w.to(DEV), sumsq))
+    want = as64(resid) + (as64(x) * factor) @ as64(w).T
+    np.testing.assert_allclose(as64(resid_dev), want, rtol=2e-5, atol=2e-5 * np.abs(want).max())
+    np.testing.assert_allclose(as64(values), want * as64(next_w), rtol=8e-3, atol=1e-3)
+    # the partial sums are those of the stream as the kernel wrote it, and only the first `tiles` are written
+    got = as64(resid_dev)
+    padded = np.zeros((rows, tiles * K.NORM_TILE))
+    padded[:, :n] = got ** 2
+    np.testing.assert_allclose(as64(sumsq)[:, :tiles], padded.reshape(rows, tiles, K.NORM_TILE).sum(-1), rtol=1e-5)
+    assert torch.isnan(sumsq[:, tiles:]).all()
+    # the pair is a norm: values * factor from the sums is rms_norm(new stream) * next_w
+    factor_out = 1.0 / np.sqrt(as64(sumsq)[:, :tiles].sum(-1, keepdims=True) / n + eps)
+    normed = pl.rms_norm(got, as64(next_w), eps)
+    np.testing.assert_allclose(as64(values) * factor_out, normed, rtol=8e-3, atol=1e-3)
+
+
+def test_apply_row_norm():
+    rows, k, eps = 5, 200, 1e-5
+    _, _, values, row_norm, factor = _prenormed(rows, k, 80, eps)
+    out = torch.full((rows, k), float("nan"), dtype=torch.bfloat16, device=DEV)
+    K.apply_row_norm(values.to(DEV), row_norm, out)
+    np.testing.assert_allclose(as64(out), as64(values) * factor, rtol=4e-3, atol=1e-6)
+
+
+def test_linear_small_residual_refuses():
+    x = torch.zeros((17, 64), dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros((32, 64), dtype=torch.bfloat16, device=DEV)
+    target = K.ResidualOut(torch.zeros((17, 32), device=DEV), torch.ones((32,), device=DEV), torch.zeros((17, 4), device=DEV))
+    with pytest.raises(K.KernelError, match="at most 16 rows"):
+        K.linear_small(x, w, None, torch.zeros((17, 32), dtype=torch.bfloat16, device=DEV), K.EPI_RESID, 0, None, target)
+    with pytest.raises(K.KernelError, match="go together"):
+        K.linear_small(x[:4], w, None, torch.zeros((4, 32), dtype=torch.bfloat16, device=DEV), K.EPI_RESID)
+    short = K.ResidualOut(torch.zeros((4, 32), device=DEV), torch.ones((32,), device=DEV), torch.zeros((4, 1), device=DEV))
+    with pytest.raises(K.KernelError, match="stride"):
+        K.linear_small(x[:4], w, None, torch.zeros((4, 32), dtype=torch.bfloat16, device=DEV), K.EPI_RESID, 0, None, short)
