@@ -26,10 +26,13 @@
 //
 // Arithmetic: that of the general kernel in attention.cu (the reference's src/forward.cc:265-298);
 // only the order of the sums differs.
+#include <cooperative_groups.h>
 #include <cuda.h>
 
 #include "attention_decode.cuh"
 #include "tensor_map.h"
+
+namespace cg = cooperative_groups;
 
 __device__ int mll_attn_decode_tma_error_flag = 0;
 
@@ -95,7 +98,7 @@ __device__ __forceinline__ void dt_ldmatrix_x4_trans(unsigned (&r)[4], unsigned 
 }
 
 // grid (B, Hk * head_chunks, n_splits); 160 threads.
-template <int D, bool FUSED>
+template <int D, bool FUSED, bool CLUSTER>
 __global__ void __launch_bounds__(DT_THREADS, 2)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                        DecodeMmaArgs a) {
@@ -125,284 +128,313 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
   const int first_page = first_key / MLL_PAGE;
   // a sequence uses as many of the offered splits as its own length pays for (attention_decode.cuh)
   const int n_eff = decode_splits_for(pages_total - first_page, a.n_splits);
-  if (split >= n_eff) return;
-  if (ring & 1023u) {  // cannot hold swizzled tiles: report and leave (uniform for the block)
-    if (tid == 0) atomicExch(&mll_attn_decode_tma_error_flag, 2);
-    return;
-  }
-  const int per_split = (pages_total - first_page + n_eff - 1) / n_eff;
-  const int p_begin = first_page + split * per_split;
-  const int p_end = min(pages_total, p_begin + per_split);
-  const int n_pages = max(0, p_end - p_begin);
-  const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_blocks;
-
-  if (tid == 0) {
-    for (int s = 0; s < DT_STAGES; ++s) {
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full + 8 * s), "r"(1u));
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty + 8 * s), "r"(4u));  // one arrival per compute warp
-    }
-    *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  __syncthreads();
-
-  float o[NT][4];
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // rows g and g + 8, this warp's keys only
-
-  if (warp == 4) {
-    // ---- producer ---------------------------------------------------------------------------- //
-    if (lane == 0 && n_pages > 0) {
-      int page = table[p_begin];
-      for (int it = 0; it < n_pages; ++it) {
-        const int st = it % DT_STAGES;
-        dt_mbar_wait(empty + 8 * st, ((it / DT_STAGES) & 1) ^ 1, abort_flag);  // the stage's previous use (none in the first round)
-        if (*abort_flag) break;
-        const int row = (page * a.n_kv_heads + kvh) * MLL_PAGE;
-        if (it + 1 < n_pages) page = table[p_begin + it + 1];  // looked up while this page's loads fly
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full + 8 * st), "r"((unsigned)L::STAGE)
-                     : "memory");
-        const unsigned dst = ring + st * L::STAGE;
-#pragma unroll
-        for (int bx = 0; bx < L::BOXES; ++bx) {
-          dt_tma_load_2d(dst + bx * L::BOX_BYTES, &kmap, bx * 64, row, full + 8 * st);
-          dt_tma_load_2d(dst + L::HALF + bx * L::BOX_BYTES, &vmap, bx * 64, row, full + 8 * st);
-        }
-      }
-    }
-  } else {
-    // ---- compute warps ----------------------------------------------------------------------- //
-#pragma unroll
-    for (int n = 0; n < NT; ++n)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
-
-    // FUSED: the block whose pages include the sequence's last one fetches the new key pair and
-    // value pair of its kv head now (one pair per thread), long before the page comes up
-    const bool owns_new_row = FUSED && a.k_write != nullptr && ctx > 0 && p_begin <= pages_total - 1 &&
-                              pages_total - 1 < p_end;
-    __nv_bfloat16 new_k0 = __float2bfloat16_rn(0.f), new_k1 = new_k0;
-    unsigned new_v = 0;
-    if (owns_new_row && tid < D / 2) {
-      const __nv_bfloat16* k_in = a.qkv + (size_t)b * a.qkv_ld + (size_t)(a.n_heads + kvh) * D;
-      const __nv_bfloat16* v_in = k_in + (size_t)a.n_kv_heads * D;
-      const int e0 = a.interleaved ? 2 * tid : tid, e1 = a.interleaved ? 2 * tid + 1 : tid + D / 2;
-      const float x0 = __bfloat162float(k_in[e0]), x1 = __bfloat162float(k_in[e1]);
-      new_v = *reinterpret_cast<const unsigned*>(v_in + 2 * tid);
-      float y0 = x0, y1 = x1;
-      if (a.cos_table != nullptr) {
-        const float c = a.cos_table[(size_t)(ctx - 1) * (D / 2) + tid], sv = a.sin_table[(size_t)(ctx - 1) * (D / 2) + tid];
-        y0 = x0 * c - x1 * sv;
-        y1 = x0 * sv + x1 * c;
-      }
-      new_k0 = __float2bfloat16_rn(y0);
-      new_k1 = __float2bfloat16_rn(y1);
-    }
-
-    // query fragments (A operand), rows = heads of this chunk, zero beyond ng
-    unsigned qf[KSTEPS][4];
-    {
-      const __nv_bfloat16* q0 = FUSED ? a.qkv + (size_t)b * a.qkv_ld + (size_t)h0 * D
-                                      : a.q + ((size_t)b * a.n_heads + h0) * D;
-#pragma unroll
-      for (int ks = 0; ks < KSTEPS; ++ks) {
-        const int col = ks * 16 + 2 * t;
-        qf[ks][0] = g < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + col) : 0u;
-        qf[ks][1] = g + 8 < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + col) : 0u;
-        qf[ks][2] = g < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + col + 8) : 0u;
-        qf[ks][3] = g + 8 < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + col + 8) : 0u;
-      }
-      if (FUSED && a.cos_table != nullptr && ctx > 0) {
-        // the token's position is ctx - 1 for every head; registers [2j] and [2j + 1] hold rows g and
-        // g + 8 at columns col + 8 j, col + 8 j + 1
-        const float* cs = a.cos_table + (size_t)(ctx - 1) * (D / 2);
-        const float* sn = a.sin_table + (size_t)(ctx - 1) * (D / 2);
-        if (a.interleaved) {  // pairs (2i, 2i + 1): both halves of a pair sit in one register
-#pragma unroll
-          for (int ks = 0; ks < KSTEPS; ++ks)
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-              const int pair = ks * 8 + t + 4 * j;
-              const float c = cs[pair], sv = sn[pair];
-#pragma unroll
-              for (int r = 0; r < 2; ++r) {
-                const float2 x = unpack_bf162(qf[ks][2 * j + r]);
-                qf[ks][2 * j + r] = pack_bf162(x.x * c - x.y * sv, x.x * sv + x.y * c);
-              }
-            }
-        } else {  // pairs (i, i + d/2): the partner sits in the same place of k-step ks + KSTEPS / 2
-#pragma unroll
-          for (int ks = 0; ks < KSTEPS / 2; ++ks)
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-              const int i0 = ks * 16 + 2 * t + 8 * j;
-              const float c0 = cs[i0], s0 = sn[i0], c1 = cs[i0 + 1], s1 = sn[i0 + 1];
-#pragma unroll
-              for (int r = 0; r < 2; ++r) {
-                const float2 lo = unpack_bf162(qf[ks][2 * j + r]), hi = unpack_bf162(qf[ks + KSTEPS / 2][2 * j + r]);
-                qf[ks][2 * j + r] = pack_bf162(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);
-                qf[ks + KSTEPS / 2][2 * j + r] = pack_bf162(lo.x * s0 + hi.x * c0, lo.y * s1 + hi.y * c1);
-              }
-            }
-        }
-      }
-    }
-
-    for (int it = 0; it < n_pages; ++it) {
-      const int p = p_begin + it;
-      const int st = it % DT_STAGES;
-      dt_mbar_wait(full + 8 * st, (it / DT_STAGES) & 1, abort_flag);
-      const unsigned kt = ring + st * L::STAGE, vt = kt + L::HALF;
-      if (p == pages_total - 1) {
-        if (FUSED && owns_new_row) {
-          // the step's token lies in this page: its key (rotated) and value replace whatever the cache held
-          const int row = (ctx - 1) % MLL_PAGE;
-          if (tid < D / 2) {
-            const size_t cache_row = (((size_t)table[p] * a.n_kv_heads + kvh) * MLL_PAGE + row) * D;
-            const int e0 = a.interleaved ? 2 * tid : tid, e1 = a.interleaved ? 2 * tid + 1 : tid + D / 2;
-            unsigned char* k_half = smem_raw + st * L::STAGE;
-            unsigned char* v_half = k_half + L::HALF;
-            *reinterpret_cast<__nv_bfloat16*>(k_half + dt_chunk_offset(row, e0 >> 3) + (e0 & 7) * 2) = new_k0;
-            *reinterpret_cast<__nv_bfloat16*>(k_half + dt_chunk_offset(row, e1 >> 3) + (e1 & 7) * 2) = new_k1;
-            a.k_write[cache_row + e0] = new_k0;
-            a.k_write[cache_row + e1] = new_k1;
-            *reinterpret_cast<unsigned*>(v_half + dt_chunk_offset(row, (2 * tid) >> 3) + ((2 * tid) & 7) * 2) = new_v;
-            *reinterpret_cast<unsigned*>(a.v_write + cache_row + 2 * tid) = new_v;
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");  // the compute warps only; once per block
-        }
-        const int valid = ctx - p * MLL_PAGE;  // positions of this page that the sequence has
-        if (valid < MLL_PAGE) {                // the rest of the page may hold anything: zero this warp's value rows
-          unsigned char* v_half = smem_raw + st * L::STAGE + L::HALF;
-          for (int idx = lane; idx < 16 * (D / 8); idx += 32) {
-            const int row = warp * 16 + idx / (D / 8), ch = idx % (D / 8);
-            if (row >= valid) *reinterpret_cast<uint4*>(v_half + dt_chunk_offset(row, ch)) = make_uint4(0, 0, 0, 0);
-          }
-          __syncwarp();
-        }
-      }
-
-      // scores of the 16 heads against this warp's 16 keys: two n-tiles of 8 keys
-      float s_acc[2][4];
-#pragma unroll
-      for (int n = 0; n < 2; ++n)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) s_acc[n][i] = 0.f;
-#pragma unroll
-      for (int ks = 0; ks < KSTEPS; ++ks) {
-        // matrices: (keys 0-7, dims 0-7), (keys 0-7, dims 8-15), (keys 8-15, dims 0-7), (keys 8-15, dims 8-15)
-        unsigned kb[4];
-        const int key = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
-        const int ch = ks * 2 + ((lane >> 3) & 1);
-        dt_ldmatrix_x4(kb, kt + dt_chunk_offset(key, ch));
-        mma_16816(s_acc[0], qf[ks], kb[0], kb[1]);
-        mma_16816(s_acc[1], qf[ks], kb[2], kb[3]);
-      }
-      // scale, mask, the warp's row maxima
-      float tile_max[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-      for (int n = 0; n < 2; ++n)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int kpos = p * MLL_PAGE + warp * 16 + n * 8 + 2 * t + (i & 1);
-          const bool ok = kpos < ctx && kpos >= first_key;
-          const float v = ok ? s_acc[n][i] * a.scale : -INFINITY;
-          s_acc[n][i] = v;
-          tile_max[i >> 1] = fmaxf(tile_max[i >> 1], v);
-        }
-      float alpha[2];
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
-        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
-        const float m_new = fmaxf(m_run[r], tile_max[r]);
-        alpha[r] = m_new > -INFINITY ? __expf(m_run[r] - m_new) : 1.f;
-        float sum = 0.f;
-#pragma unroll
-        for (int n = 0; n < 2; ++n)
-#pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            const float pv = m_new > -INFINITY ? __expf(s_acc[n][2 * r + i] - m_new) : 0.f;
-            s_acc[n][2 * r + i] = pv;
-            sum += pv;
-          }
-        l_run[r] = l_run[r] * alpha[r] + sum;  // this thread's share of the row; the quad is summed after the loop
-        m_run[r] = m_new;
-      }
-      // the probabilities as the A fragment of a 16-key step: (row g, keys 2t..), (row g + 8, keys 2t..),
-      // (row g, keys 8 + 2t..), (row g + 8, keys 8 + 2t..)
-      unsigned pa[4];
-      pa[0] = pack_bf162(s_acc[0][0], s_acc[0][1]);
-      pa[1] = pack_bf162(s_acc[0][2], s_acc[0][3]);
-      pa[2] = pack_bf162(s_acc[1][0], s_acc[1][1]);
-      pa[3] = pack_bf162(s_acc[1][2], s_acc[1][3]);
-      // out = alpha * out + P[16 x 16] . V[this warp's 16 keys x head_dim]
-#pragma unroll
-      for (int n = 0; n < NT; n += 2) {
-        // transposed 8x8 tiles of V: (keys 0-7, cols n), (keys 8-15, cols n), (keys 0-7, cols n+1), (keys 8-15, cols n+1)
-        unsigned vb[4];
-        const int key = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
-        dt_ldmatrix_x4_trans(vb, vt + dt_chunk_offset(key, n + (lane >> 4)));
-        o[n][0] *= alpha[0];
-        o[n][1] *= alpha[0];
-        o[n][2] *= alpha[1];
-        o[n][3] *= alpha[1];
-        o[n + 1][0] *= alpha[0];
-        o[n + 1][1] *= alpha[0];
-        o[n + 1][2] *= alpha[1];
-        o[n + 1][3] *= alpha[1];
-        mma_16816(o[n], pa, vb[0], vb[1]);
-        mma_16816(o[n + 1], pa, vb[2], vb[3]);
-      }
-      __syncwarp();
-      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty + 8 * st) : "memory");
-    }
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
-      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
-    }
-  }
-
-  // ---- the four warps' partial results, merged through the drained ring --------------------- //
-  __syncthreads();  // every page has been consumed: the ring is free
+  const bool misplaced = (ring & 1023u) != 0;  // cannot hold swizzled tiles: report, and do no work (uniform for the block)
+  if (misplaced && tid == 0) atomicExch(&mll_attn_decode_tma_error_flag, 2);
+  // splits beyond the sequence's own count have no work; in a cluster they still meet the others at its barriers
+  const bool active = split < n_eff && !misplaced;
+  if (!CLUSTER && !active) return;
+  // where the block's result lies once its four warps are merged (over the drained ring)
   float* part = reinterpret_cast<float*>(smem_raw);       // [4 warps][16 rows][D], then [4][16] maxima, [4][16] sums
   float* part_m = part + 4 * 16 * D;
   float* part_l = part_m + 4 * 16;
   float* merged = part_l + 4 * 16;                        // [16][D], then [16] maxima, [16] sums
   float* merged_m = merged + 16 * D;
   float* merged_l = merged_m + 16;
-  if (warp < 4) {
+  bool failed = true;
+  if (active) {
+    const int per_split = (pages_total - first_page + n_eff - 1) / n_eff;
+    const int p_begin = first_page + split * per_split;
+    const int p_end = min(pages_total, p_begin + per_split);
+    const int n_pages = max(0, p_end - p_begin);
+    const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_blocks;
+
+    if (tid == 0) {
+      for (int s = 0; s < DT_STAGES; ++s) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full + 8 * s), "r"(1u));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty + 8 * s), "r"(4u));  // one arrival per compute warp
+      }
+      *abort_flag = 0;
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    float o[NT][4];
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // rows g and g + 8, this warp's keys only
+
+    if (warp == 4) {
+      // ---- producer ---------------------------------------------------------------------------- //
+      if (lane == 0 && n_pages > 0) {
+        int page = table[p_begin];
+        for (int it = 0; it < n_pages; ++it) {
+          const int st = it % DT_STAGES;
+          dt_mbar_wait(empty + 8 * st, ((it / DT_STAGES) & 1) ^ 1, abort_flag);  // the stage's previous use (none in the first round)
+          if (*abort_flag) break;
+          const int row = (page * a.n_kv_heads + kvh) * MLL_PAGE;
+          if (it + 1 < n_pages) page = table[p_begin + it + 1];  // looked up while this page's loads fly
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full + 8 * st), "r"((unsigned)L::STAGE)
+                       : "memory");
+          const unsigned dst = ring + st * L::STAGE;
 #pragma unroll
-    for (int n = 0; n < NT; ++n) {
-      const int col = n * 8 + 2 * t;
-      *reinterpret_cast<float2*>(part + ((size_t)warp * 16 + g) * D + col) = make_float2(o[n][0], o[n][1]);
-      *reinterpret_cast<float2*>(part + ((size_t)warp * 16 + g + 8) * D + col) = make_float2(o[n][2], o[n][3]);
+          for (int bx = 0; bx < L::BOXES; ++bx) {
+            dt_tma_load_2d(dst + bx * L::BOX_BYTES, &kmap, bx * 64, row, full + 8 * st);
+            dt_tma_load_2d(dst + L::HALF + bx * L::BOX_BYTES, &vmap, bx * 64, row, full + 8 * st);
+          }
+        }
+      }
+    } else {
+      // ---- compute warps ----------------------------------------------------------------------- //
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
+
+      // FUSED: the block whose pages include the sequence's last one fetches the new key pair and
+      // value pair of its kv head now (one pair per thread), long before the page comes up
+      const bool owns_new_row = FUSED && a.k_write != nullptr && ctx > 0 && p_begin <= pages_total - 1 &&
+                                pages_total - 1 < p_end;
+      __nv_bfloat16 new_k0 = __float2bfloat16_rn(0.f), new_k1 = new_k0;
+      unsigned new_v = 0;
+      if (owns_new_row && tid < D / 2) {
+        const __nv_bfloat16* k_in = a.qkv + (size_t)b * a.qkv_ld + (size_t)(a.n_heads + kvh) * D;
+        const __nv_bfloat16* v_in = k_in + (size_t)a.n_kv_heads * D;
+        const int e0 = a.interleaved ? 2 * tid : tid, e1 = a.interleaved ? 2 * tid + 1 : tid + D / 2;
+        const float x0 = __bfloat162float(k_in[e0]), x1 = __bfloat162float(k_in[e1]);
+        new_v = *reinterpret_cast<const unsigned*>(v_in + 2 * tid);
+        float y0 = x0, y1 = x1;
+        if (a.cos_table != nullptr) {
+          const float c = a.cos_table[(size_t)(ctx - 1) * (D / 2) + tid], sv = a.sin_table[(size_t)(ctx - 1) * (D / 2) + tid];
+          y0 = x0 * c - x1 * sv;
+          y1 = x0 * sv + x1 * c;
+        }
+        new_k0 = __float2bfloat16_rn(y0);
+        new_k1 = __float2bfloat16_rn(y1);
+      }
+
+      // query fragments (A operand), rows = heads of this chunk, zero beyond ng
+      unsigned qf[KSTEPS][4];
+      {
+        const __nv_bfloat16* q0 = FUSED ? a.qkv + (size_t)b * a.qkv_ld + (size_t)h0 * D
+                                        : a.q + ((size_t)b * a.n_heads + h0) * D;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+          const int col = ks * 16 + 2 * t;
+          qf[ks][0] = g < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + col) : 0u;
+          qf[ks][1] = g + 8 < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + col) : 0u;
+          qf[ks][2] = g < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + col + 8) : 0u;
+          qf[ks][3] = g + 8 < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + col + 8) : 0u;
+        }
+        if (FUSED && a.cos_table != nullptr && ctx > 0) {
+          // the token's position is ctx - 1 for every head; registers [2j] and [2j + 1] hold rows g and
+          // g + 8 at columns col + 8 j, col + 8 j + 1
+          const float* cs = a.cos_table + (size_t)(ctx - 1) * (D / 2);
+          const float* sn = a.sin_table + (size_t)(ctx - 1) * (D / 2);
+          if (a.interleaved) {  // pairs (2i, 2i + 1): both halves of a pair sit in one register
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks)
+#pragma unroll
+              for (int j = 0; j < 2; ++j) {
+                const int pair = ks * 8 + t + 4 * j;
+                const float c = cs[pair], sv = sn[pair];
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                  const float2 x = unpack_bf162(qf[ks][2 * j + r]);
+                  qf[ks][2 * j + r] = pack_bf162(x.x * c - x.y * sv, x.x * sv + x.y * c);
+                }
+              }
+          } else {  // pairs (i, i + d/2): the partner sits in the same place of k-step ks + KSTEPS / 2
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS / 2; ++ks)
+#pragma unroll
+              for (int j = 0; j < 2; ++j) {
+                const int i0 = ks * 16 + 2 * t + 8 * j;
+                const float c0 = cs[i0], s0 = sn[i0], c1 = cs[i0 + 1], s1 = sn[i0 + 1];
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                  const float2 lo = unpack_bf162(qf[ks][2 * j + r]), hi = unpack_bf162(qf[ks + KSTEPS / 2][2 * j + r]);
+                  qf[ks][2 * j + r] = pack_bf162(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);
+                  qf[ks + KSTEPS / 2][2 * j + r] = pack_bf162(lo.x * s0 + hi.x * c0, lo.y * s1 + hi.y * c1);
+                }
+              }
+          }
+        }
+      }
+
+      for (int it = 0; it < n_pages; ++it) {
+        const int p = p_begin + it;
+        const int st = it % DT_STAGES;
+        dt_mbar_wait(full + 8 * st, (it / DT_STAGES) & 1, abort_flag);
+        const unsigned kt = ring + st * L::STAGE, vt = kt + L::HALF;
+        if (p == pages_total - 1) {
+          if (FUSED && owns_new_row) {
+            // the step's token lies in this page: its key (rotated) and value replace whatever the cache held
+            const int row = (ctx - 1) % MLL_PAGE;
+            if (tid < D / 2) {
+              const size_t cache_row = (((size_t)table[p] * a.n_kv_heads + kvh) * MLL_PAGE + row) * D;
+              const int e0 = a.interleaved ? 2 * tid : tid, e1 = a.interleaved ? 2 * tid + 1 : tid + D / 2;
+              unsigned char* k_half = smem_raw + st * L::STAGE;
+              unsigned char* v_half = k_half + L::HALF;
+              *reinterpret_cast<__nv_bfloat16*>(k_half + dt_chunk_offset(row, e0 >> 3) + (e0 & 7) * 2) = new_k0;
+              *reinterpret_cast<__nv_bfloat16*>(k_half + dt_chunk_offset(row, e1 >> 3) + (e1 & 7) * 2) = new_k1;
+              a.k_write[cache_row + e0] = new_k0;
+              a.k_write[cache_row + e1] = new_k1;
+              *reinterpret_cast<unsigned*>(v_half + dt_chunk_offset(row, (2 * tid) >> 3) + ((2 * tid) & 7) * 2) = new_v;
+              *reinterpret_cast<unsigned*>(a.v_write + cache_row + 2 * tid) = new_v;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");  // the compute warps only; once per block
+          }
+          const int valid = ctx - p * MLL_PAGE;  // positions of this page that the sequence has
+          if (valid < MLL_PAGE) {                // the rest of the page may hold anything: zero this warp's value rows
+            unsigned char* v_half = smem_raw + st * L::STAGE + L::HALF;
+            for (int idx = lane; idx < 16 * (D / 8); idx += 32) {
+              const int row = warp * 16 + idx / (D / 8), ch = idx % (D / 8);
+              if (row >= valid) *reinterpret_cast<uint4*>(v_half + dt_chunk_offset(row, ch)) = make_uint4(0, 0, 0, 0);
+            }
+            __syncwarp();
+          }
+        }
+
+        // scores of the 16 heads against this warp's 16 keys: two n-tiles of 8 keys
+        float s_acc[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) s_acc[n][i] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+          // matrices: (keys 0-7, dims 0-7), (keys 0-7, dims 8-15), (keys 8-15, dims 0-7), (keys 8-15, dims 8-15)
+          unsigned kb[4];
+          const int key = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
+          const int ch = ks * 2 + ((lane >> 3) & 1);
+          dt_ldmatrix_x4(kb, kt + dt_chunk_offset(key, ch));
+          mma_16816(s_acc[0], qf[ks], kb[0], kb[1]);
+          mma_16816(s_acc[1], qf[ks], kb[2], kb[3]);
+        }
+        // scale, mask, the warp's row maxima
+        float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int kpos = p * MLL_PAGE + warp * 16 + n * 8 + 2 * t + (i & 1);
+            const bool ok = kpos < ctx && kpos >= first_key;
+            const float v = ok ? s_acc[n][i] * a.scale : -INFINITY;
+            s_acc[n][i] = v;
+            tile_max[i >> 1] = fmaxf(tile_max[i >> 1], v);
+          }
+        float alpha[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+          tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+          const float m_new = fmaxf(m_run[r], tile_max[r]);
+          alpha[r] = m_new > -INFINITY ? __expf(m_run[r] - m_new) : 1.f;
+          float sum = 0.f;
+#pragma unroll
+          for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              const float pv = m_new > -INFINITY ? __expf(s_acc[n][2 * r + i] - m_new) : 0.f;
+              s_acc[n][2 * r + i] = pv;
+              sum += pv;
+            }
+          l_run[r] = l_run[r] * alpha[r] + sum;  // this thread's share of the row; the quad is summed after the loop
+          m_run[r] = m_new;
+        }
+        // the probabilities as the A fragment of a 16-key step: (row g, keys 2t..), (row g + 8, keys 2t..),
+        // (row g, keys 8 + 2t..), (row g + 8, keys 8 + 2t..)
+        unsigned pa[4];
+        pa[0] = pack_bf162(s_acc[0][0], s_acc[0][1]);
+        pa[1] = pack_bf162(s_acc[0][2], s_acc[0][3]);
+        pa[2] = pack_bf162(s_acc[1][0], s_acc[1][1]);
+        pa[3] = pack_bf162(s_acc[1][2], s_acc[1][3]);
+        // out = alpha * out + P[16 x 16] . V[this warp's 16 keys x head_dim]
+#pragma unroll
+        for (int n = 0; n < NT; n += 2) {
+          // transposed 8x8 tiles of V: (keys 0-7, cols n), (keys 8-15, cols n), (keys 0-7, cols n+1), (keys 8-15, cols n+1)
+          unsigned vb[4];
+          const int key = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+          dt_ldmatrix_x4_trans(vb, vt + dt_chunk_offset(key, n + (lane >> 4)));
+          o[n][0] *= alpha[0];
+          o[n][1] *= alpha[0];
+          o[n][2] *= alpha[1];
+          o[n][3] *= alpha[1];
+          o[n + 1][0] *= alpha[0];
+          o[n + 1][1] *= alpha[0];
+          o[n + 1][2] *= alpha[1];
+          o[n + 1][3] *= alpha[1];
+          mma_16816(o[n], pa, vb[0], vb[1]);
+          mma_16816(o[n + 1], pa, vb[2], vb[3]);
+        }
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty + 8 * st) : "memory");
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+      }
     }
-    if (t == 0) {
-      part_m[warp * 16 + g] = m_run[0];
-      part_m[warp * 16 + g + 8] = m_run[1];
-      part_l[warp * 16 + g] = l_run[0];
-      part_l[warp * 16 + g + 8] = l_run[1];
+
+    // ---- the four warps' partial results, merged through the drained ring --------------------- //
+    __syncthreads();  // every page has been consumed: the ring is free
+    if (warp < 4) {
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        const int col = n * 8 + 2 * t;
+        *reinterpret_cast<float2*>(part + ((size_t)warp * 16 + g) * D + col) = make_float2(o[n][0], o[n][1]);
+        *reinterpret_cast<float2*>(part + ((size_t)warp * 16 + g + 8) * D + col) = make_float2(o[n][2], o[n][3]);
+      }
+      if (t == 0) {
+        part_m[warp * 16 + g] = m_run[0];
+        part_m[warp * 16 + g + 8] = m_run[1];
+        part_l[warp * 16 + g] = l_run[0];
+        part_l[warp * 16 + g + 8] = l_run[1];
+      }
     }
+    __syncthreads();
+    failed = *abort_flag != 0;
+    for (int idx = tid; idx < ng * D; idx += DT_THREADS) {
+      const int row = idx / D, col = idx % D;
+      const float m0 = part_m[row], m1 = part_m[16 + row], m2 = part_m[32 + row], m3 = part_m[48 + row];
+      const float m = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      const float w0 = m0 > -INFINITY ? __expf(m0 - m) : 0.f, w1 = m1 > -INFINITY ? __expf(m1 - m) : 0.f;
+      const float w2 = m2 > -INFINITY ? __expf(m2 - m) : 0.f, w3 = m3 > -INFINITY ? __expf(m3 - m) : 0.f;
+      const float l = (part_l[row] * w0 + part_l[16 + row] * w1) + (part_l[32 + row] * w2 + part_l[48 + row] * w3);
+      const float v = (part[(size_t)row * D + col] * w0 + part[((size_t)16 + row) * D + col] * w1) +
+                      (part[((size_t)32 + row) * D + col] * w2 + part[((size_t)48 + row) * D + col] * w3);
+      merged[(size_t)row * D + col] = v;
+      if (col == 0) {
+        merged_m[row] = m;
+        merged_l[row] = l;
+      }
+    }
+    __syncthreads();
   }
-  __syncthreads();
-  const bool failed = *abort_flag != 0;
-  for (int idx = tid; idx < ng * D; idx += DT_THREADS) {
-    const int row = idx / D, col = idx % D;
-    const float m0 = part_m[row], m1 = part_m[16 + row], m2 = part_m[32 + row], m3 = part_m[48 + row];
-    const float m = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-    const float w0 = m0 > -INFINITY ? __expf(m0 - m) : 0.f, w1 = m1 > -INFINITY ? __expf(m1 - m) : 0.f;
-    const float w2 = m2 > -INFINITY ? __expf(m2 - m) : 0.f, w3 = m3 > -INFINITY ? __expf(m3 - m) : 0.f;
-    const float l = (part_l[row] * w0 + part_l[16 + row] * w1) + (part_l[32 + row] * w2 + part_l[48 + row] * w3);
-    const float v = (part[(size_t)row * D + col] * w0 + part[((size_t)16 + row) * D + col] * w1) +
-                    (part[((size_t)32 + row) * D + col] * w2 + part[((size_t)48 + row) * D + col] * w3);
-    merged[(size_t)row * D + col] = v;
-    if (col == 0) {
-      merged_m[row] = m;
-      merged_l[row] = l;
+  if (CLUSTER) {
+    // The splits of one (sequence, kv head, head chunk) are the blocks of one cluster: their results meet in
+    // distributed shared memory instead of global memory, an arrival counter and a second pass by the last
+    // block (about 3 us less on a 10-16 us launch).  Every block of the cluster comes here, with or without work.
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();  // every block's merged result is in its shared memory
+    if (active && !failed) {
+      const int share = (ng * D + n_eff - 1) / n_eff;  // split number `split` writes outputs [split * share, + share)
+      for (int idx = split * share + tid; idx < min(ng * D, (split + 1) * share); idx += DT_THREADS) {
+        const int row = idx / D, col = idx % D;
+        float m = -INFINITY;
+        for (int sp = 0; sp < n_eff; ++sp) m = fmaxf(m, *cluster.map_shared_rank(merged_m + row, sp));
+        float l = 0.f, v = 0.f;
+        for (int sp = 0; sp < n_eff; ++sp) {  // in split order: the same sum on every run
+          const float ms = *cluster.map_shared_rank(merged_m + row, sp);
+          const float w = ms > -INFINITY ? __expf(ms - m) : 0.f;
+          l = fmaf(*cluster.map_shared_rank(merged_l + row, sp), w, l);
+          v = fmaf(*cluster.map_shared_rank(merged + (size_t)row * D + col, sp), w, v);
+        }
+        a.out[((size_t)b * a.n_heads + h0 + row) * D + col] = __float2bfloat16_rn(l > 0.f ? v / l : 0.f);
+      }
     }
+    cluster.sync();  // nobody leaves while another block may still read its shared memory
+    return;
   }
-  __syncthreads();
   if (failed) return;
   for (int idx = tid; idx < ng * D; idx += DT_THREADS) {
     const int row = idx / D, col = idx % D;
@@ -423,21 +455,81 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
   merge_decode_splits<D, DT_THREADS>(a, b, h0, ng, n_eff, merged_l + 16);
 }
 
-template <int D, bool FUSED>
-int launch_decode_tma(const CUtensorMap& kmap, const CUtensorMap& vmap, const DecodeMmaArgs& a, int n_seqs,
-                      cudaStream_t stream) {
+// cluster: the splits of a group are the blocks of one thread-block cluster and merge through distributed
+// shared memory (n_splits 2 .. 16); otherwise through global memory and arrival counters.
+template <int D, bool FUSED, bool CLUSTER>
+int launch_decode_tma_as(const CUtensorMap& kmap, const CUtensorMap& vmap, const DecodeMmaArgs& a, int n_seqs,
+                         cudaStream_t stream) {
   const size_t smem = DecodeTmaSmem<D>::BYTES;
-  auto kernel = attn_decode_tma_kernel<D, FUSED>;
+  auto kernel = attn_decode_tma_kernel<D, FUSED, CLUSTER>;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (err == cudaSuccess && CLUSTER && a.n_splits > 8)
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
   if (err != cudaSuccess) {
     mll_set_error("attention decode (tma): cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
     return (int)err;
   }
   const int group = a.n_heads / a.n_kv_heads;
-  dim3 grid(n_seqs, a.n_kv_heads * ((group + 15) / 16), a.n_splits);
-  MLL_LAUNCH((kernel), grid, DT_THREADS, smem, stream, kmap, vmap, a);
-  MLL_LAUNCH_CHECK();
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(n_seqs, a.n_kv_heads * ((group + 15) / 16), a.n_splits);
+  config.blockDim = dim3(DT_THREADS);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (CLUSTER) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = a.n_splits;
+    config.attrs = attr;
+    config.numAttrs = 1;
+  }
+  err = cudaLaunchKernelEx(&config, kernel, kmap, vmap, a);
+  if (err != cudaSuccess) {
+    mll_set_error("attention decode (tma): launch failed: %s", cudaGetErrorString(err));
+    return (int)err;
+  }
   return 0;
+}
+
+// Whether a cluster of `n_splits` of these blocks can be resident (asked once per kernel and size).
+template <int D, bool FUSED>
+bool decode_cluster_fits(int n_splits) {
+  static int known[17] = {0};  // 0 unknown, 1 fits, 2 does not
+  if (n_splits < 2 || n_splits > 16) return false;
+  if (known[n_splits] == 0) {
+    auto kernel = attn_decode_tma_kernel<D, FUSED, true>;
+    const size_t smem = DecodeTmaSmem<D>::BYTES;
+    int clusters = 0;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err == cudaSuccess && n_splits > 8)
+      err = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (err == cudaSuccess) {
+      cudaLaunchConfig_t config = {};
+      config.gridDim = dim3(1, 1, n_splits);
+      config.blockDim = dim3(DT_THREADS);
+      config.dynamicSmemBytes = smem;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 1;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = n_splits;
+      config.attrs = attr;
+      config.numAttrs = 1;
+      err = cudaOccupancyMaxActiveClusters(&clusters, kernel, &config);
+    }
+    if (err != cudaSuccess) cudaGetLastError();  // not an error of the caller's: the other merge is used
+    known[n_splits] = (err == cudaSuccess && clusters >= 1) ? 1 : 2;
+  }
+  return known[n_splits] == 1;
+}
+
+template <int D, bool FUSED>
+int launch_decode_tma(const CUtensorMap& kmap, const CUtensorMap& vmap, const DecodeMmaArgs& a, int n_seqs,
+                      int cluster_merge, cudaStream_t stream) {
+  if (cluster_merge && decode_cluster_fits<D, FUSED>(a.n_splits))
+    return launch_decode_tma_as<D, FUSED, true>(kmap, vmap, a, n_seqs, stream);
+  return launch_decode_tma_as<D, FUSED, false>(kmap, vmap, a, n_seqs, stream);
 }
 
 }  // namespace mll
@@ -459,12 +551,14 @@ MLL_API int mll_attn_decode_tma_supported(int dtype, int head_dim) {
 // mll_attn_decode_mma_fused (then q is ignored).  n_pages: pages of k_cache and v_cache.  With
 // n_splits > 1, scratch and counters (int32, one per (sequence, kv head x head chunk), zero
 // before the first launch; left zero) are required: the last block of a group merges the splits.
+// cluster_merge != 0: with 2 to 16 splits the blocks of a group form a thread-block cluster and merge
+// through distributed shared memory instead (scratch and counters stay untouched).
 MLL_API int mll_attn_decode_tma(const void* q, const void* qkv, int qkv_ld, const float* cos_table,
                                 const float* sin_table, int interleaved, int write_kv, void* k_cache, void* v_cache,
                                 long long n_pages, const int* seq_slot, const int* seq_ctx, const int* block_table,
                                 float* scratch, void* out, int n_seqs, int n_heads, int n_kv_heads, int head_dim,
                                 int max_blocks, int n_splits, int window, float scale, int* counters,
-                                cudaStream_t stream) {
+                                int cluster_merge, cudaStream_t stream) {
   MLL_REQUIRE(mll_attn_decode_tma_supported(MLL_BF16, head_dim), "attention decode (tma): head_dim %d", head_dim);
   MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention decode (tma): bad head counts");
   MLL_REQUIRE(n_seqs >= 0 && n_splits >= 1 && n_splits <= 65535, "attention decode (tma): bad batch or split count");
@@ -490,8 +584,8 @@ MLL_API int mll_attn_decode_tma(const void* q, const void* qkv, int qkv_ld, cons
                        fused && write_kv ? (__nv_bfloat16*)k_cache : nullptr,
                        fused && write_kv ? (__nv_bfloat16*)v_cache : nullptr, qkv_ld, interleaved};
   if (head_dim == 64)
-    return fused ? mll::launch_decode_tma<64, true>(kmap, vmap, a, n_seqs, stream)
-                 : mll::launch_decode_tma<64, false>(kmap, vmap, a, n_seqs, stream);
-  return fused ? mll::launch_decode_tma<128, true>(kmap, vmap, a, n_seqs, stream)
-               : mll::launch_decode_tma<128, false>(kmap, vmap, a, n_seqs, stream);
+    return fused ? mll::launch_decode_tma<64, true>(kmap, vmap, a, n_seqs, cluster_merge, stream)
+                 : mll::launch_decode_tma<64, false>(kmap, vmap, a, n_seqs, cluster_merge, stream);
+  return fused ? mll::launch_decode_tma<128, true>(kmap, vmap, a, n_seqs, cluster_merge, stream)
+               : mll::launch_decode_tma<128, false>(kmap, vmap, a, n_seqs, cluster_merge, stream);
 }

@@ -14,7 +14,7 @@ import torch
 from .build import KernelBuildError, load_library
 
 PAGE = 64  # cache positions per page; equals MLL_PAGE in common.cuh
-ABI_VERSION = 16
+ABI_VERSION = 17
 MAX_TOP_K = 1024
 
 
@@ -470,6 +470,7 @@ def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratc
 
 USE_FUSED_DECODE = True  # off: rotary encoding and cache write stay a kernel of their own in decode steps
 USE_TMA_DECODE = True    # off: the cp.async / mma.sync decode kernel also takes head sizes 64 and 128
+USE_CLUSTER_MERGE = True  # off: the TMA decode kernel merges its context splits through global memory and counters
 
 
 def _tma_decode(q, qkv, cos, sin, interleaved, write_kv, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch, out,
@@ -486,7 +487,8 @@ def _tma_decode(q, qkv, cos, sin, interleaved, write_kv, k_cache, v_cache, seq_s
                                      _ptr(seq_ctx), _ptr(block_table), _ptr(scratch), _ptr(out), ctypes.c_int(n_seqs),
                                      ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim),
                                      ctypes.c_int(block_table.shape[1]), ctypes.c_int(n_splits), ctypes.c_int(window),
-                                     ctypes.c_float(scale), _ptr(counters if n_splits > 1 else None), _stream()),
+                                     ctypes.c_float(scale), _ptr(counters if n_splits > 1 else None),
+                                     ctypes.c_int(int(USE_CLUSTER_MERGE)), _stream()),
            "attention_decode (TMA)")
     return True
 

@@ -161,16 +161,19 @@ class PagedCase:
                 torch.tensor(self.ctx_lens, dtype=torch.int32, device=DEV), self.table.to(DEV))
 
 
-@pytest.fixture(params=["tma", "tensor_core", "general"])
+@pytest.fixture(params=["tma", "tma_global_merge", "tensor_core", "general"])
 def decode_impl(request):
     """bfloat16 decode attention has two tensor-core kernels: the TMA-fed one (head sizes 64/128,
-    needs arrival counters when the context is split) and the cp.async one (64/128/256); the
+    needs arrival counters when the context is split; it merges the splits inside a thread-block
+    cluster, or - second variant - through global memory) and the cp.async one (64/128/256); the
     general kernel must stay right at those sizes too."""
     K.USE_TENSOR_CORE_DECODE = request.param != "general"
-    K.USE_TMA_DECODE = request.param == "tma"
+    K.USE_TMA_DECODE = request.param.startswith("tma")
+    K.USE_CLUSTER_MERGE = request.param == "tma"
     yield "general" if request.param == "general" else "tensor_core"
     K.USE_TENSOR_CORE_DECODE = True
     K.USE_TMA_DECODE = True
+    K.USE_CLUSTER_MERGE = True
 
 
 DECODE_SHAPES = [  # heads, kv heads, head_dim
@@ -180,7 +183,7 @@ DECODE_SHAPES = [  # heads, kv heads, head_dim
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("hq,hk,d", DECODE_SHAPES)
-@pytest.mark.parametrize("splits", [1, 3, 8])
+@pytest.mark.parametrize("splits", [1, 3, 8, 16])
 def test_attention_decode(dtype, hq, hk, d, splits, decode_impl):
     ctx = [1, 63, 64, 65, 300, 129]
     case = PagedCase(ctx, hk, d, dtype, seed=hq * 7 + d)
@@ -278,11 +281,12 @@ def test_attention_decode_window_edge(dtype, window, decode_impl):
 @pytest.mark.parametrize("interleaved", [True, False])
 @pytest.mark.parametrize("splits,window", [(1, 0), (3, 0), (2, 70)])
 @pytest.mark.parametrize("encoded", [True, False])
-@pytest.mark.parametrize("tma", [True, False])
+@pytest.mark.parametrize("tma", ["cluster", "global", False])
 def test_attention_decode_fused_with_rope_and_cache_write(hq, hk, d, interleaved, splits, window, encoded, tma, monkeypatch):
     """One launch (rotate q and k, write k and v, attend) against the separate kernels and the plain
     reference.  The slot of the new token holds NaN before the call, here and in the separate path."""
-    monkeypatch.setattr(K, "USE_TMA_DECODE", tma)   # the TMA-fed kernel (head sizes 64/128) or the cp.async one
+    monkeypatch.setattr(K, "USE_TMA_DECODE", bool(tma))   # the TMA-fed kernel (head sizes 64/128) or the cp.async one
+    monkeypatch.setattr(K, "USE_CLUSTER_MERGE", tma == "cluster")  # its splits merged in a cluster or through global memory
     dtype = torch.bfloat16
     ctx = [1, 63, 64, 65, 300, 129]
     B = len(ctx)
