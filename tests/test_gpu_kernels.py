@@ -183,7 +183,7 @@ DECODE_SHAPES = [  # heads, kv heads, head_dim
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("hq,hk,d", DECODE_SHAPES)
-@pytest.mark.parametrize("splits", [1, 3, 8, 16])
+@pytest.mark.parametrize("splits", [1, 3, 8, 16, 20])  # 20: more than a cluster holds, merged through global memory
 def test_attention_decode(dtype, hq, hk, d, splits, decode_impl):
     ctx = [1, 63, 64, 65, 300, 129]
     case = PagedCase(ctx, hk, d, dtype, seed=hq * 7 + d)
