@@ -148,4 +148,32 @@ __device__ __forceinline__ float row_norm_factor(const float* row_partials, int 
   return 1.f / sqrtf(s / (float)width + eps);
 }
 
+// The same for two rows at once (the second only if `second`): their loads are in flight together, so that
+// a warp with two rows to do pays one memory latency, and each sum is formed as above.
+__device__ __forceinline__ void row_norm_factors2(const float* row_a, const float* row_b, bool second, int partials,
+                                                  int width, float eps, int lane, float& fa, float& fb) {
+  float sa = 0.f, sb = 0.f;
+  for (int p0 = lane; p0 < partials; p0 += 8 * 32) {
+    float va[8], vb[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const bool in = p0 + i * 32 < partials;
+      va[i] = in ? row_a[p0 + i * 32] : 0.f;
+      vb[i] = in && second ? row_b[p0 + i * 32] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      sa += va[i];
+      sb += vb[i];
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    sa += __shfl_xor_sync(0xffffffffu, sa, o);
+    sb += __shfl_xor_sync(0xffffffffu, sb, o);
+  }
+  fa = 1.f / sqrtf(sa / (float)width + eps);
+  fb = 1.f / sqrtf(sb / (float)width + eps);
+}
+
 }  // namespace mll

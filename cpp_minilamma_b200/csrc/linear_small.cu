@@ -171,10 +171,23 @@ linear_small_kernel(LinearArgs a) {
     // the rows' norm factors, from partial sums that lie in the L2 cache: plain loads here, at the end, cost
     // 0.6 us (q/k/v of the 8B shape); fetching them into shared memory during the main loop cost 1.5 us,
     // through the share of the L1 cache that the buffer takes from the activations
-    for (int m = warp; m < a.M; m += LS_WARPS) {
-      const float f = row_norm_factor<32>(a.in.sumsq + (size_t)m * a.in.stride, a.in.partials, a.K, a.in.eps, lane,
-                                          0xffffffffu);
-      if (lane == 0) row_factor[m] = f;
+    if (NT == 1) {  // at most 8 rows: one per warp of the 8-warp variants (the two-row form cost them 0.4 us)
+      for (int m = warp; m < a.M; m += LS_WARPS) {
+        const float f = row_norm_factor<32>(a.in.sumsq + (size_t)m * a.in.stride, a.in.partials, a.K, a.in.eps, lane,
+                                            0xffffffffu);
+        if (lane == 0) row_factor[m] = f;
+      }
+    } else {
+      for (int m = warp; m < a.M; m += 2 * LS_WARPS) {  // rows m and m + LS_WARPS, their loads in flight together
+        const bool second = m + LS_WARPS < a.M;
+        float f0, f1;
+        row_norm_factors2(a.in.sumsq + (size_t)m * a.in.stride, a.in.sumsq + (size_t)(m + LS_WARPS) * a.in.stride,
+                          second, a.in.partials, a.K, a.in.eps, lane, f0, f1);
+        if (lane == 0) {
+          row_factor[m] = f0;
+          if (second) row_factor[m + LS_WARPS] = f1;
+        }
+      }
     }
   }
   __syncthreads();

@@ -175,10 +175,15 @@ linear_tma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
     const unsigned x_chunk = lane >> 3;  // B: chunks 2 ks + {0, 1} and 2 (ks + 1) + {0, 1}
     if (a.in.sumsq && rank == 0) {
       // the first stage is a memory latency away: time for the rows' norm factors, which the epilogue needs
-      for (int m = warp; m < a.M; m += 4) {
-        const float f = row_norm_factor<32>(a.in.sumsq + (size_t)m * a.in.stride, a.in.partials, a.K, a.in.eps, lane,
-                                            0xffffffffu);
-        if (lane == 0) row_factor[m] = f;
+      for (int m = warp; m < a.M; m += 8) {  // rows m and m + 4, their loads in flight together
+        const bool second = m + 4 < a.M;
+        float f0, f1;
+        row_norm_factors2(a.in.sumsq + (size_t)m * a.in.stride, a.in.sumsq + (size_t)(m + 4) * a.in.stride, second,
+                          a.in.partials, a.K, a.in.eps, lane, f0, f1);
+        if (lane == 0) {
+          row_factor[m] = f0;
+          if (second) row_factor[m + 4] = f1;
+        }
       }
     }
     for (int i = 0; i < count; ++i) {
