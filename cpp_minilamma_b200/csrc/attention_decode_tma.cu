@@ -13,8 +13,11 @@
 //     warps per page: no block-wide barrier, no probabilities through shared memory; each warp
 //     reads only its quarter of a page.
 //   * after the last page the four partial results (maximum, sum, output) are merged through
-//     shared memory, once; with context splits the block then writes its partial result and the
-//     block that arrives last merges the splits (attention_decode.cuh).
+//     shared memory, once.  With 2 to 16 context splits the blocks of a (sequence, kv head, chunk) form a
+//     thread-block cluster: after a cluster barrier every split reads its share of all splits' results
+//     through distributed shared memory and writes that share of the output.  With more splits (or
+//     cluster_merge off) the block writes its partial result to global memory and the block that arrives
+//     last merges the splits (attention_decode.cuh).
 // The fused variant also rotates q in registers and the step's new key, and writes the new key
 // and value row into the cache and into the block's copy of the last page, as the mma.sync
 // kernel's fused variant does (attention_mma.cu).  Rows of the last page beyond the context are
@@ -22,7 +25,8 @@
 //
 // Every mbarrier wait is bounded; a wait that runs out raises an error flag (read through
 // mll_take_device_error) and makes the block's later waits return at once; the block then
-// stores nothing.  No load uses cluster multicast.
+// stores nothing.  The cluster barriers are reached by every block of a cluster on every path (blocks
+// without work and blocks that gave up included).  No load uses cluster multicast.
 //
 // Arithmetic: that of the general kernel in attention.cu (the reference's src/forward.cc:265-298);
 // only the order of the sums differs.
