@@ -538,12 +538,15 @@ int launch_decode_tma(const CUtensorMap& kmap, const CUtensorMap& vmap, const De
 
 }  // namespace mll
 
-// Used by mll_take_device_error(): this file's flag, read and cleared.
-extern "C" int mll_attn_decode_tma_take_error() {
-  int flag = 0, zero = 0;
-  if (cudaMemcpyFromSymbol(&flag, mll_attn_decode_tma_error_flag, sizeof(int)) != cudaSuccess) return -1;
-  if (flag) cudaMemcpyToSymbol(mll_attn_decode_tma_error_flag, &zero, sizeof(int));
-  return flag;
+// The device address of this file's error flag (nullptr if it cannot be had); device_error.cu reads,
+// clears and hands it to the sampling kernels.
+extern "C" int* mll_attn_decode_tma_error_address() {
+  int* address = nullptr;
+  if (cudaGetSymbolAddress((void**)&address, mll_attn_decode_tma_error_flag) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return address;
 }
 
 MLL_API int mll_attn_decode_tma_supported(int dtype, int head_dim) {

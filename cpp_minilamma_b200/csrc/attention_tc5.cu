@@ -438,12 +438,15 @@ int launch_prefill_tc5(const CUtensorMap& qmap, const CUtensorMap& kmap, const C
 
 }  // namespace mll
 
-// Used by mll_take_device_error(): this file's flag, read and cleared.
-extern "C" int mll_attn_tc5_take_error() {
-  int flag = 0, zero = 0;
-  if (cudaMemcpyFromSymbol(&flag, mll_attn_tc5_error_flag, sizeof(int)) != cudaSuccess) return -1;
-  if (flag) cudaMemcpyToSymbol(mll_attn_tc5_error_flag, &zero, sizeof(int));
-  return flag;
+// The device address of this file's error flag (nullptr if it cannot be had); device_error.cu reads,
+// clears and hands it to the sampling kernels.
+extern "C" int* mll_attn_tc5_error_address() {
+  int* address = nullptr;
+  if (cudaGetSymbolAddress((void**)&address, mll_attn_tc5_error_flag) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return address;
 }
 
 MLL_API int mll_attn_prefill_tc5_supported(int dtype, int head_dim) {

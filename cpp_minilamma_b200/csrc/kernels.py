@@ -7,7 +7,7 @@ implementation behind them.  Argument faults raise `KernelError` before any laun
 from __future__ import annotations
 
 import ctypes
-from typing import NamedTuple, Optional
+from typing import Dict, NamedTuple, Optional
 
 import torch
 
@@ -41,11 +41,13 @@ def lib() -> ctypes.CDLL:
 
 
 launches = 0  # kernels of this library launched so far (counted per successful call)
+calls: Dict[str, int] = {}  # the same, per kind of launch (the name each wrapper gives its kernel)
 
 
 def _check(code: int, what: str, kernels: int = 1) -> None:
     global launches
     launches += kernels
+    calls[what] = calls.get(what, 0) + 1
     if code != 0:
         message = lib().mll_last_error().decode("utf-8", "replace")
         raise KernelError(f"{what}: {message} (code {code})")
@@ -489,7 +491,8 @@ def _tma_decode(q, qkv, cos, sin, interleaved, write_kv, k_cache, v_cache, seq_s
                                      ctypes.c_int(block_table.shape[1]), ctypes.c_int(n_splits), ctypes.c_int(window),
                                      ctypes.c_float(scale), _ptr(counters if n_splits > 1 else None),
                                      ctypes.c_int(int(USE_CLUSTER_MERGE)), _stream()),
-           "attention_decode (TMA)")
+           "attention_decode (TMA, cluster merge)" if USE_CLUSTER_MERGE and 2 <= n_splits <= 16
+           else "attention_decode (TMA)")
     return True
 
 

@@ -343,12 +343,15 @@ int launch_linear_tc5(const CUtensorMap& wmap, const CUtensorMap& xmap, const Tc
 
 }  // namespace mll
 
-// Used by mll_take_device_error(): this file's flag, read and cleared.
-extern "C" int mll_tc5_take_error() {
-  int flag = 0, zero = 0;
-  if (cudaMemcpyFromSymbol(&flag, mll_tc5_error_flag, sizeof(int)) != cudaSuccess) return -1;
-  if (flag) cudaMemcpyToSymbol(mll_tc5_error_flag, &zero, sizeof(int));
-  return flag;
+// The device address of this file's error flag (nullptr if it cannot be had); device_error.cu reads,
+// clears and hands it to the sampling kernels.
+extern "C" int* mll_linear_tc5_error_address() {
+  int* address = nullptr;
+  if (cudaGetSymbolAddress((void**)&address, mll_tc5_error_flag) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return address;
 }
 
 // At most 16 rows.  The kernel is written for 16, 32 or 64 batch columns, but one shape with 32

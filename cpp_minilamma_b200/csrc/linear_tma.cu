@@ -374,21 +374,15 @@ int launch_linear_tma(const CUtensorMap& wmap, const CUtensorMap& xmap, const Tm
 
 }  // namespace mll
 
-// Reads and clears the flag that device code raises when a bounded wait runs out
-// (synchronises with the device).
-extern "C" int mll_tc5_take_error();
-extern "C" int mll_attn_tc5_take_error();
-extern "C" int mll_attn_decode_tma_take_error();
-
-MLL_API int mll_take_device_error() {
-  int flag = 0, zero = 0;
-  if (cudaMemcpyFromSymbol(&flag, mll_device_error_flag, sizeof(int)) != cudaSuccess) return -1;
-  if (flag) cudaMemcpyToSymbol(mll_device_error_flag, &zero, sizeof(int));
-  const int other = mll_tc5_take_error();
-  const int attention = mll_attn_tc5_take_error();
-  const int decode = mll_attn_decode_tma_take_error();
-  if (other < 0 || attention < 0 || decode < 0) return -1;
-  return flag | (other ? 2 : 0) | (attention ? 4 : 0) | (decode ? 8 : 0);
+// The device address of this file's error flag (nullptr if it cannot be had); device_error.cu reads,
+// clears and hands it to the sampling kernels.
+extern "C" int* mll_linear_tma_error_address() {
+  int* address = nullptr;
+  if (cudaGetSymbolAddress((void**)&address, mll_device_error_flag) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return address;
 }
 
 MLL_API int mll_linear_tma_supported(int M, int N, int K, int epilogue) {

@@ -51,10 +51,14 @@ class Linear:
         w = self.weight
         ws = step.ws
         if w.dtype == torch.float32:
-            if row_norm is not None:
-                raise RuntimeError(f"{self.name}: rows without their norm's factor reached a float32 product")
             if torch.backends.cuda.matmul.allow_tf32:
                 raise RuntimeError(f"{self.name}: TF32 is enabled; the float32 path needs true 32-bit products")
+            if row_norm is not None:
+                # a matrix stored in 32-bit inside a bfloat16 run, behind a product that folded the norm away:
+                # finish the norm here, then widen like any other bfloat16 input
+                normed = ws.buffer(out_name + ".x", (rows, self.in_features), torch.bfloat16)
+                K.apply_row_norm(x, row_norm, normed)
+                x = normed
             if x.dtype != torch.float32:
                 wide = ws.buffer(out_name + ".x32", (rows, self.in_features), torch.float32)
                 K.cast(x, wide)

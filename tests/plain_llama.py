@@ -101,7 +101,7 @@ def linear(x, weight, bias=None):
     """y[o] = sum_k W[o, k] x[k], W row-major [out, in]
     (matumal/matuml_ops.cc:155-161); the bias is added only where the tensor
     exists (src/forward.cc:159-161, 328-335)."""
-    y = x.astype(np.float64) @ weight.astype(np.float64).T
+    y = np.asarray(x, dtype=np.float64) @ np.asarray(weight, dtype=np.float64).T
     if bias is not None:
         y = y + bias.astype(np.float64)
     return y

@@ -185,6 +185,42 @@ def test_run_dtype_differs_from_storage(model_folders, dtype, storage):
     assert_close(np.concatenate(got), plain_logits(folder, tokens, dtype), dtype, f"run {dtype} on {storage}")
 
 
+def test_bfloat16_run_with_some_matrices_stored_in_32_bit(model_folders, tmp_path):
+    # a matrix stored in 32-bit stays 32-bit in a bfloat16 run.  When only some are (here layer 1's q_proj and
+    # gate_proj), a decode step's bfloat16 o/down product folds the following norm away and the float32
+    # product behind it has to finish that norm itself
+    import shutil
+    import plain_llama as pl
+    from cpp_minilamma_b200.weights.safetensors_io import write_safetensors
+    name = "B"
+    folder = str(tmp_path / "mixed")
+    shutil.copytree(model_folders(name, "bfloat16"), folder)
+    _, weights = pl.read_model_folder(folder)
+    wide = {"model.layers.1.self_attn.q_proj.weight", "model.layers.1.mlp.gate_proj.weight"}
+    write_safetensors(os.path.join(folder, "model.safetensors"),
+                      {n: torch.tensor(w).to(torch.float32 if n in wide else torch.bfloat16) for n, w in weights.items()},
+                      {"format": "pt"})
+    llm = ml.load(folder, dtype="bfloat16", max_tokens=4096)
+    assert llm.model.layers[1].mixer.qkv.weight.dtype == torch.float32
+    assert llm.model.layers[1].feed_forward.gate_up.weight.dtype == torch.float32
+    assert llm.model.layers[0].mixer.qkv.weight.dtype == torch.bfloat16
+    lengths = [40, 70, 9]
+    requests = [tc.random_tokens(name, n, 850 + i) for i, n in enumerate(lengths)]
+    slots = llm.engine.acquire(len(requests))
+    heads = [n - 8 for n in lengths]
+    first = llm.engine.step([StepEntry(s, t[:h], list(range(h))) for s, t, h in zip(slots, requests, heads)]).cpu().numpy()
+    rows = [[] for _ in requests]
+    for k in range(8):
+        got = llm.engine.step([StepEntry(s, [t[h + k]], [0]) for s, t, h in zip(slots, requests, heads)]).cpu().numpy()
+        for i in range(len(requests)):
+            rows[i].append(got[i])
+    at = 0
+    for i, (tokens, h) in enumerate(zip(requests, heads)):
+        ref = plain_logits(folder, tokens, "bfloat16")
+        assert_close(np.concatenate([first[at:at + h], np.stack(rows[i])]), ref, "bfloat16", f"mixed storage request {i}")
+        at += h
+
+
 def test_cli_generate_matches_the_api(model_folders, capsys):
     from cpp_minilamma_b200.cli import main
     folder, llm = load(model_folders, "B", "float32")
