@@ -73,8 +73,12 @@ class EngineBackend(Backend):
         if self.graphs is not None and all(len(e.tokens) == 1 for e in entries):
             return self.graphs.submit([e.slot for e in entries], [e.tokens[0] for e in entries], self.params,
                                       requests, steps)
-        logits = self.engine.step_borrowed(entries)
-        return self.sampler.sample_ticket(logits, self.params, requests, steps)
+        if self.params.is_greedy:
+            return self.sampler.sample_ticket(self.engine.step_borrowed(entries), self.params, requests, steps)
+        # the sampler's random-number counters cross to the device with the step's index arrays
+        logits = self.engine.step_borrowed(entries, extras={"rng_request": requests, "rng_step": steps})
+        return self.sampler.sample_ticket(logits, self.params, requests, steps,
+                                          on_device=(self.engine.extras["rng_request"], self.engine.extras["rng_step"]))
 
     def submit_ahead(self, slots, requests, steps):
         """Enqueue one more token for `slots`, which must be the slots of the previous `submit` in
@@ -86,7 +90,12 @@ class EngineBackend(Backend):
         return self.graphs.submit(list(slots), None, self.params, requests, steps)
 
     def collect(self, ticket):
-        return self.sampler.collect(ticket)
+        from .csrc.kernels import DeviceKernelError
+        try:
+            return self.sampler.collect(ticket)
+        except DeviceKernelError:
+            self.engine.after_device_error()
+            raise
 
 
 class LLM:

@@ -150,10 +150,25 @@ class CacheGroup:
         n = len(self.pages[slot])
         self.pages[slot] = []
         if n:
+            # nobody reads the row of a slot that is not live, so the device's copy may stay as it is
+            # until the slot is handed out again and grows
             self.table_host[slot, :n] = -1
-            self._dirty.add(slot)
+            self._dirty.discard(slot)
+
+    def take_updates(self) -> Optional[np.ndarray]:
+        """The rows that changed since the last call as int32 [n, 1 + max_blocks] (column 0: the slot), or
+        None.  The caller brings them to the device (`scatter_rows` into `table_dev`)."""
+        if not self._dirty:
+            return None
+        slots = sorted(self._dirty)
+        self._dirty.clear()
+        rows = np.empty((len(slots), 1 + self.max_blocks), dtype=np.int32)
+        rows[:, 0] = slots
+        rows[:, 1:] = self.table_host[slots]
+        return rows
 
     def flush(self) -> None:
+        """Upload the changed rows now, one blocking copy each (for callers outside an engine's step)."""
         for slot in sorted(self._dirty):
             self.table_dev[slot].copy_(torch.from_numpy(self.table_host[slot]), non_blocking=False)
         self._dirty.clear()
@@ -272,9 +287,24 @@ class SequenceCache:
             self.seq_len[slot] = old + extra
 
     def flush(self) -> None:
-        """Upload the block-table rows that changed since the last call."""
+        """Upload the block-table rows that changed since the last call (blocking copies; the engine's
+        steps use `take_table_updates` instead and send the rows along with their index arrays)."""
         for g in self.groups:
             g.flush()
+
+    def take_table_updates(self) -> List[Tuple[CacheGroup, np.ndarray]]:
+        """(group, int32 [n, 1 + max_blocks]) for every group whose block table changed since the last
+        call; the caller owns bringing them to the device before the next kernel reads the tables."""
+        out = []
+        for g in self.groups:
+            rows = g.take_updates()
+            if rows is not None:
+                out.append((g, rows))
+        return out
+
+    def table_update_capacity(self, n_seqs: int) -> int:
+        """Integers that the updates of a step with `n_seqs` sequences can take at most."""
+        return len(self.groups) * n_seqs * (1 + self.max_blocks)
 
     # ---- views ---------------------------------------------------------------- #
     def view(self, entry: int) -> CacheView:

@@ -46,6 +46,9 @@ void mll_set_error(const char* fmt, ...);
 
 extern thread_local cudaError_t mll_launch_status;
 
+// Multiprocessors of the current device (asked once per device; the kernels size their grids by it).
+int mll_sm_count();
+
 namespace mll {
 
 template <typename... KernelArgs, typename... Args>

@@ -21,7 +21,30 @@ MLL_API const char* mll_last_error() { return g_error; }
 thread_local cudaError_t mll_launch_status = cudaSuccess;
 
 // Identifies the build; the Python side checks it after loading the library.
-MLL_API int mll_abi_version() { return 17; }
+MLL_API int mll_abi_version() { return 18; }
+
+// Cache positions per page, for the Python side to check against its own constant.
+MLL_API int mll_page() { return MLL_PAGE; }
+
+int mll_sm_count() {
+  constexpr int kMaxDevices = 64;
+  static int known[kMaxDevices] = {0};
+  int device = 0, count = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) {
+    cudaGetLastError();
+    device = 0;
+  }
+  if (known[device] == 0) {
+    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count < 1) {
+      cudaGetLastError();
+      count = 148;  // a B200, the device this library is written for
+    }
+    known[device] = count;
+  }
+  return known[device];
+}
+
+MLL_API int mll_multiprocessor_count() { return mll_sm_count(); }
 
 namespace mll {
 
@@ -142,14 +165,32 @@ __global__ void add_bias_kernel(T* __restrict__ x, const float* __restrict__ bia
   for (; idx < total; idx += stride) x[idx] = from_float<T>(to_float(x[idx]) + bias[idx % width]);
 }
 
+// table[staged[r][0]][:] = staged[r][1 : 1 + width] for r < n_rows: rows of a block table that changed on
+// the host, brought over inside the step's index buffer.
+__global__ void scatter_rows_kernel(int* __restrict__ table, const int* __restrict__ staged, int width, int table_rows) {
+  const int* row = staged + (size_t)blockIdx.x * (width + 1);
+  const int target = row[0];
+  if (target < 0 || target >= table_rows) return;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) table[(size_t)target * width + i] = row[1 + i];
+}
+
 }  // namespace mll
+
+// table: int32 [table_rows, width]; staged: int32 [n_rows, 1 + width], column 0 the row of `table` to replace.
+MLL_API int mll_scatter_rows(int* table, const int* staged, int n_rows, int width, int table_rows, cudaStream_t stream) {
+  MLL_REQUIRE(n_rows >= 0 && width > 0 && table_rows > 0, "scatter_rows: bad sizes rows=%d width=%d", n_rows, width);
+  if (n_rows == 0) return 0;
+  MLL_LAUNCH((mll::scatter_rows_kernel), n_rows, width >= 128 ? 128 : 32, 0, stream, table, staged, width, table_rows);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
 
 MLL_API int mll_add_bias(void* x, const float* bias, int dtype, int n_rows, int width, cudaStream_t stream) {
   MLL_REQUIRE(n_rows >= 0 && width > 0, "add_bias: bad sizes rows=%d width=%d", n_rows, width);
   if (n_rows == 0) return 0;
   const size_t total = (size_t)n_rows * width;
   long long blocks = (long long)((total + 255) / 256);
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > mll_sm_count() * 16) blocks = mll_sm_count() * 16;
   if (dtype == MLL_F32)
     MLL_LAUNCH((mll::add_bias_kernel<float>), (int)blocks, 256, 0, stream, (float*)x, bias, total, width);
   else if (dtype == MLL_BF16)
@@ -181,7 +222,7 @@ MLL_API int mll_cast(const void* in, int in_dtype, void* out, int out_dtype, lon
   if (n == 0) return 0;
   const int threads = 256;
   long long blocks = (n + threads - 1) / threads;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > mll_sm_count() * 16) blocks = mll_sm_count() * 16;
   if (in_dtype == MLL_F32 && out_dtype == MLL_BF16)
     MLL_LAUNCH((mll::cast_kernel<float, __nv_bfloat16>), (int)blocks, threads, 0, stream, (const float*)in, (__nv_bfloat16*)out, (size_t)n);
   else if (in_dtype == MLL_BF16 && out_dtype == MLL_F32)
@@ -203,7 +244,7 @@ MLL_API int mll_swiglu(const void* gu, void* out, int dtype, int n_tokens, int i
                    ((uintptr_t)out % 16 == 0);
   if (vec) {
     long long groups = ((long long)n_tokens * (inter / 8) + threads - 1) / threads;
-    if (groups > 148 * 32) groups = 148 * 32;
+    if (groups > mll_sm_count() * 32) groups = mll_sm_count() * 32;
     if (dtype == MLL_F32)
       MLL_LAUNCH((mll::swiglu_vec8_kernel<float>), (int)groups, threads, 0, stream, (const float*)gu, (float*)out, n_tokens,
                                                                        inter, block);
@@ -215,7 +256,7 @@ MLL_API int mll_swiglu(const void* gu, void* out, int dtype, int n_tokens, int i
     return 0;
   }
   long long blocks = ((long long)n_tokens * inter + threads - 1) / threads;
-  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (blocks > mll_sm_count() * 32) blocks = mll_sm_count() * 32;
   if (dtype == MLL_F32)
     MLL_LAUNCH((mll::swiglu_kernel<float>), (int)blocks, threads, 0, stream, (const float*)gu, (float*)out, n_tokens, inter, block);
   else if (dtype == MLL_BF16)

@@ -11,15 +11,20 @@ from typing import Dict, NamedTuple, Optional
 
 import torch
 
+from ..cache.paged import PAGE  # cache positions per page; the library's MLL_PAGE is checked against it on load
 from .build import KernelBuildError, load_library
 
-PAGE = 64  # cache positions per page; equals MLL_PAGE in common.cuh
-ABI_VERSION = 17
+ABI_VERSION = 18
 MAX_TOP_K = 1024
 
 
 class KernelError(RuntimeError):
     pass
+
+
+class DeviceKernelError(KernelError):
+    """A kernel gave up on the device (a bounded wait ran out, or its shared memory was misplaced): what the
+    step computed is not to be used."""
 
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
@@ -36,8 +41,15 @@ def lib() -> ctypes.CDLL:
             raise KernelBuildError(
                 f"kernel library reports ABI {handle.mll_abi_version()}, the package expects {ABI_VERSION}; "
                 "remove csrc/_build and rebuild")
+        if handle.mll_page() != PAGE:
+            raise KernelBuildError(f"kernel library built for pages of {handle.mll_page()} positions, the cache uses {PAGE}")
         _lib = handle
     return _lib
+
+
+def multiprocessor_count() -> int:
+    """Multiprocessors of the current CUDA device (the library asks the driver once per device)."""
+    return int(lib().mll_multiprocessor_count())
 
 
 launches = 0  # kernels of this library launched so far (counted per successful call)
@@ -108,6 +120,17 @@ def add_bias(x: torch.Tensor, bias: torch.Tensor) -> None:
         raise KernelError("add_bias: bias length differs from the row width")
     _check(lib().mll_add_bias(_ptr(x), _ptr(bias), dtype_code(x.dtype), ctypes.c_int(x.shape[0]),
                               ctypes.c_int(x.shape[1]), _stream()), "add_bias")
+
+
+def scatter_rows(table: torch.Tensor, staged: torch.Tensor, n_rows: int) -> None:
+    """table[staged[r, 0], :] = staged[r, 1:] for r < n_rows: block-table rows that changed on the host.
+    table int32 [rows, width]; staged int32, n_rows * (1 + width) values."""
+    _need(table, "scatter_rows table", torch.int32, 2)
+    _need(staged, "scatter_rows staged", torch.int32)
+    if staged.numel() < n_rows * (1 + table.shape[1]):
+        raise KernelError("scatter_rows: staged rows shorter than the count says")
+    _check(lib().mll_scatter_rows(_ptr(table), _ptr(staged), ctypes.c_int(n_rows), ctypes.c_int(table.shape[1]),
+                                  ctypes.c_int(table.shape[0]), _stream()), "scatter_rows")
 
 
 EPI_BF16, EPI_F32, EPI_SWIGLU, EPI_RESID = 0, 1, 2, 3
@@ -241,11 +264,26 @@ def linear_tc5(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], o
                                       *_row_norm_args(row_norm, rows, "linear_tc5"), _stream()), "linear_tc5")
 
 
+DEVICE_ERROR_BITS = ("the TMA linear kernel", "the tcgen05 linear kernel", "the tcgen05 prefill attention kernel",
+                     "the TMA decode attention kernel")
+
+
 def take_device_error() -> int:
-    """Non-zero when a kernel's bounded wait ran out since the last call (then cleared): bit 0 the TMA
-    linear kernel, bit 1 the tcgen05 linear kernel, bit 2 the tcgen05 prefill attention kernel, bit 3 the TMA decode
-    attention kernel; synchronises."""
+    """Non-zero when a kernel gave up since the flags were last read (then cleared): bit i stands for
+    DEVICE_ERROR_BITS[i]; synchronises.  The sampling kernels read and clear the same flags on the
+    device and hand them to `DeviceSampler.collect` in their status word."""
     return int(lib().mll_take_device_error())
+
+
+def raise_device_error(mask: int) -> None:
+    """Set the flags of `mask` from the host, as a kernel that gave up would (for tests of the host side)."""
+    _check(lib().mll_raise_device_error(ctypes.c_int(mask)), "raise_device_error", kernels=0)
+
+
+def device_error_message(mask: int) -> str:
+    names = [name for i, name in enumerate(DEVICE_ERROR_BITS) if mask & (1 << i)] or [f"mask {mask}"]
+    return ("a bounded wait ran out (or a block's shared memory was misplaced) in " + ", ".join(names)
+            + "; the step's results are not valid")
 
 
 TMA_MAX_ROWS = 8      # rows up to which tall matrices go to the TMA + mma.sync kernel (its batch tile is 8 rows)
@@ -547,6 +585,9 @@ def attention_decode_fused(qkv, cos, sin, interleaved: bool, write_kv: bool, k_c
                                            ctypes.c_int(window), ctypes.c_float(scale),
                                            _ptr(counters if n_splits > 1 else None), _stream()),
            "attention_decode (fused)")
+
+
+PREFILL_TILE = 64  # query rows per entry of the work list that `attention_prefill` takes
 
 
 def attention_prefill(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0,

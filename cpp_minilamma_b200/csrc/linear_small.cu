@@ -314,11 +314,11 @@ MLL_API int mll_linear_small_fused(const void* x, const void* w, const float* bi
   //     multiprocessor (q/k/v 10.0-10.6 / 11.6-12.4, ideal 7.6).  Both without k-ranks at these sizes.
   //   * otherwise 4 warps and the compiler's register choice.
   const bool wide = chunks >= 64 && M <= 16;
-  const bool one_wave = tiles <= 148 * 2;
+  const bool one_wave = tiles <= mll_sm_count() * 2;
   const int warps = wide ? 8 : 4;
   if (ranks <= 0) {
     // split K while every block still fits on the machine at once and a warp keeps at least 4 chunks
-    const int resident = 148 * (wide ? (one_wave ? 2 : 3) : 10);
+    const int resident = mll_sm_count() * (wide ? (one_wave ? 2 : 3) : 10);
     ranks = 1;
     while (ranks < 8 && tiles * ranks * 2 <= resident && chunks / (warps * ranks * 2) >= 4) ranks *= 2;
   }

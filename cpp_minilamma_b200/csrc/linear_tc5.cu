@@ -380,7 +380,7 @@ MLL_API int mll_linear_tc5_fused(const void* x, const void* w, const float* bias
   if (ranks <= 0) {
     // split K while all blocks can be resident together (2 per multiprocessor)
     // and each keeps >= 8 k-blocks
-    const int resident = 148 * 2;
+    const int resident = mll_sm_count() * 2;
     ranks = 1;
     while (ranks < 8 && tiles * ranks * 2 <= resident && k_blocks / (ranks * 2) >= 8) ranks *= 2;
   }

@@ -408,7 +408,7 @@ MLL_API int mll_linear_tma_fused(const void* x, const void* w, const float* bias
   if (ranks <= 0) {
     // as many blocks as can be resident together (7 per multiprocessor), each with >= 8 k-blocks
     ranks = 1;
-    while (ranks < 8 && tiles * ranks * 2 <= 148 * 7 && k_blocks / (ranks * 2) >= 8) ranks *= 2;
+    while (ranks < 8 && tiles * ranks * 2 <= mll_sm_count() * 7 && k_blocks / (ranks * 2) >= 8) ranks *= 2;
   }
   MLL_REQUIRE(ranks == 1 || ranks == 2 || ranks == 4 || ranks == 8, "linear_tma: cluster size %d", ranks);
   const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));

@@ -8,10 +8,25 @@
 //     equal logits are ordered by lower id here (the reference leaves that open).
 // The reference draws u from std::mt19937; here u is a pure function of
 // (seed, request, step) - three chained splitmix64 rounds - so that a request's tokens do
-// not depend on its place in a batch.  Non-finite logits (:10-19) set status[row] = 1.
+// not depend on its place in a batch.  Non-finite logits (:10-19) set bit 0 of status[row].
+// The sampling kernel is the last kernel of a step, and its status words are what the host reads with
+// the tokens: the block of row 0 therefore also reads and clears the error flags of the kernels that
+// can give up (device_error.h) and passes them on in bits 8-11 of status[0].
 #include "common.cuh"
+#include "device_error.h"
 
 namespace mll {
+
+__device__ __forceinline__ int take_error_bits(const MllDeviceErrorWords& errors) {
+  int bits = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    if (errors.word[i] != nullptr && *(volatile int*)errors.word[i] != 0) {
+      atomicExch(errors.word[i], 0);
+      bits |= 0x100 << i;
+    }
+  return bits;
+}
 
 __device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
   z += 0x9E3779B97F4A7C15ull;
@@ -82,7 +97,8 @@ __device__ __forceinline__ int block_min_int(int v, int* scratch) {
 }
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
-argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ tokens, int* __restrict__ status) {
+argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ tokens, int* __restrict__ status,
+              MllDeviceErrorWords errors) {
   __shared__ Best warp_best[32];
   __shared__ int bad;
   const float* row = logits + (size_t)blockIdx.x * vocab;
@@ -112,7 +128,7 @@ argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ tok
     }
     if (threadIdx.x == 0) {
       tokens[blockIdx.x] = best.i == 0x7fffffff ? 0 : best.i;
-      status[blockIdx.x] = bad;
+      status[blockIdx.x] = bad | (blockIdx.x == 0 ? take_error_bits(errors) : 0);
     }
   }
 }
@@ -121,7 +137,8 @@ argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ tok
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_temperature_kernel(const float* __restrict__ logits, int vocab, float temperature,
                           unsigned long long seed, const int* __restrict__ request,
-                          const int* __restrict__ step, int* __restrict__ tokens, int* __restrict__ status) {
+                          const int* __restrict__ step, int* __restrict__ tokens, int* __restrict__ status,
+                          MllDeviceErrorWords errors) {
   __shared__ float fscratch[33];
   __shared__ int iscratch[32];
   __shared__ int bad;
@@ -163,7 +180,7 @@ sample_temperature_kernel(const float* __restrict__ logits, int vocab, float tem
     tokens[blockIdx.x] = pick;
   }
   __syncthreads();
-  if (tid == 0) status[blockIdx.x] = bad;
+  if (tid == 0) status[blockIdx.x] = bad | (blockIdx.x == 0 ? take_error_bits(errors) : 0);
 }
 
 __device__ __forceinline__ unsigned order_key(float v) {
@@ -178,7 +195,7 @@ __device__ __forceinline__ float key_value(unsigned k) {
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_top_k_kernel(const float* __restrict__ logits, int vocab, int top_k, float temperature,
                     unsigned long long seed, const int* __restrict__ request, const int* __restrict__ step,
-                    int* __restrict__ tokens, int* __restrict__ status) {
+                    int* __restrict__ tokens, int* __restrict__ status, MllDeviceErrorWords errors) {
   __shared__ unsigned long long cand[SAMPLE_THREADS];
   __shared__ int hist[256];
   __shared__ float fscratch[33];
@@ -297,7 +314,7 @@ sample_top_k_kernel(const float* __restrict__ logits, int vocab, int top_k, floa
   if (tid == 0) {
     const int at = pick == 0x7fffffff ? kept - 1 : pick;
     tokens[blockIdx.x] = (int)(0xffffffffu - (unsigned)(cand[at] & 0xffffffffull));
-    status[blockIdx.x] = bad;
+    status[blockIdx.x] = bad | (blockIdx.x == 0 ? take_error_bits(errors) : 0);
   }
 }
 
@@ -308,7 +325,9 @@ MLL_API int mll_argmax(const float* logits, int n_rows, int vocab, int* tokens, 
                        cudaStream_t stream) {
   MLL_REQUIRE(n_rows >= 0 && vocab > 0, "argmax: bad sizes rows=%d vocab=%d", n_rows, vocab);
   if (n_rows == 0) return 0;
-  MLL_LAUNCH((mll::argmax_kernel), n_rows, mll::SAMPLE_THREADS, 0, stream, logits, vocab, tokens, status);
+  MllDeviceErrorWords errors;
+  mll_device_error_words(&errors);  // all null if they cannot be had: the kernel then passes nothing on
+  MLL_LAUNCH((mll::argmax_kernel), n_rows, mll::SAMPLE_THREADS, 0, stream, logits, vocab, tokens, status, errors);
   MLL_LAUNCH_CHECK();
   return 0;
 }
@@ -325,10 +344,12 @@ MLL_API int mll_sample(const float* logits, int n_rows, int vocab, float tempera
   MLL_REQUIRE(top_k <= mll::SAMPLE_THREADS,
               "sample: top_k %d above the supported maximum of %d", top_k, mll::SAMPLE_THREADS);
   if (n_rows == 0) return 0;
+  MllDeviceErrorWords errors;
+  mll_device_error_words(&errors);
   if (top_k == 0)
-    MLL_LAUNCH((mll::sample_temperature_kernel), n_rows, mll::SAMPLE_THREADS, 0, stream, logits, vocab, temperature, seed, request, step, tokens, status);
+    MLL_LAUNCH((mll::sample_temperature_kernel), n_rows, mll::SAMPLE_THREADS, 0, stream, logits, vocab, temperature, seed, request, step, tokens, status, errors);
   else
-    MLL_LAUNCH((mll::sample_top_k_kernel), n_rows, mll::SAMPLE_THREADS, 0, stream, logits, vocab, top_k, temperature, seed, request, step, tokens, status);
+    MLL_LAUNCH((mll::sample_top_k_kernel), n_rows, mll::SAMPLE_THREADS, 0, stream, logits, vocab, top_k, temperature, seed, request, step, tokens, status, errors);
   MLL_LAUNCH_CHECK();
   return 0;
 }

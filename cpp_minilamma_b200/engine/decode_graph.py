@@ -19,6 +19,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
+from ..parts.base import StepShape
 from ..sampling.sampler import DeviceSampler, SamplingParams
 from .step import Engine, StepState
 
@@ -26,26 +27,60 @@ _FIELDS = 10  # tokens, tok_pos, tok_seq, seq_slot, seq_ctx, seq_qstart, seq_qle
 
 
 class _Captured:
-    def __init__(self, engine: Engine, batch: int):
+    """The fixed-address buffers of one captured step: the ten index arrays of `batch` integers each, then
+    the index arrays that parts prepare for decode steps (sizes fixed by the batch size), then room for the
+    block-table rows that changed.  One copy from pinned memory refreshes the part that is in use."""
+
+    def __init__(self, engine: Engine, batch: int, shape: StepShape):
         self.batch = batch
-        self.host = torch.zeros(_FIELDS * batch, dtype=torch.int32, pin_memory=True)
-        self.dev = torch.zeros(_FIELDS * batch, dtype=torch.int32, device=engine.device)
+        # parts' own index arrays: laid out once from what they prepare for this first step
+        self.meta_layout = []  # (key, part, name, offset, count)
+        at = _FIELDS * batch
+        for key, part in engine.providers.items():
+            for name, values in part.prepare_step(shape).items():
+                count = len(values)
+                self.meta_layout.append((key, part, name, at, count))
+                at += count
+        self.updates_at = at
+        size = at + engine.cache.table_update_capacity(batch)
+        self.host = torch.zeros(size, dtype=torch.int32, pin_memory=True)
+        self.dev = torch.zeros(size, dtype=torch.int32, device=engine.device)
         self.copied = torch.cuda.Event()
         self.graph = None
         self.failures = 0  # captures that did not go through (the step then ran eagerly)
         self.launches = 0
-        h = self.host.numpy().reshape(_FIELDS, batch)
+        h = self.host.numpy()[:_FIELDS * batch].reshape(_FIELDS, batch)
         h[2] = np.arange(batch)   # sequence of each token
         h[5] = np.arange(batch)   # first query row of each sequence
         h[6] = 1                  # one query token per sequence
         h[7] = np.arange(batch)   # the logits of every row are wanted
         self.fields = h
-        d = self.dev.view(_FIELDS, batch)
+        d = self.dev[:_FIELDS * batch].view(_FIELDS, batch)
         self.state = StepState(
             ws=engine.ws, n_tokens=batch, n_seqs=batch, tokens=d[0], tok_pos=d[1], tok_seq=d[2], seq_slot=d[3],
-            seq_ctx=d[4], seq_qstart=d[5], seq_qlen=d[6], tile_seq=d[5][:0], tile_row0=d[5][:0], n_tiles=0,
-            want_rows=d[7], all_decode=True, max_ctx=engine.model.max_positions, small_rows=engine.small_rows)
+            seq_ctx=d[4], seq_qstart=d[5], seq_qlen=d[6], want_rows=d[7], all_decode=True,
+            max_ctx=engine.model.max_positions, small_rows=engine.small_rows, shape=shape)
+        for key, _, name, offset, count in self.meta_layout:
+            self.state.meta.setdefault(key, {})[name] = self.dev[offset:offset + count]
+        for part in engine.model.all_parts():
+            fixed = part.capture_parameters(batch, engine.model.max_positions)
+            if fixed:
+                self.state.fixed[part] = fixed
         self.rng_request, self.rng_step = d[8], d[9]
+
+    def refresh_meta(self, shape: StepShape) -> None:
+        """The parts' index arrays for this step, into their fixed places."""
+        h = self.host.numpy()
+        prepared = {}
+        for key, part, name, offset, count in self.meta_layout:
+            if key not in prepared:
+                prepared[key] = part.prepare_step(shape)
+            values = prepared[key].get(name, ())
+            if len(values) != count:
+                raise RuntimeError(f"{type(part).__name__}: index array {name!r} has {len(values)} entries in this "
+                                   f"decode step and had {count} in the first one; decode steps are replayed from a "
+                                   "graph and need index arrays whose sizes follow from the batch size alone")
+            h[offset:offset + count] = values
 
 
 class DecodeGraphs:
@@ -56,15 +91,9 @@ class DecodeGraphs:
         self._generation = engine.ws.generation
         self.replays = 0
 
-    def _splits(self, batch: int) -> int:
-        """One split count for all attention layers of a captured step: chosen from the batch
-        size alone, since the graph must serve every context length."""
-        best = 1
-        for layer in self.engine.model.layers:
-            chooser = getattr(layer.mixer, "decode_splits", None)
-            if chooser is not None:
-                best = max(best, chooser(batch, self.engine.model.max_positions))
-        return best
+    def drop(self) -> None:
+        """Forget every captured graph (they are captured again on later steps)."""
+        self._captured.clear()
 
     def step(self, slots: Sequence[int], tokens: Sequence[int], params: SamplingParams,
              requests: Sequence[int], steps: Sequence[int]) -> List[int]:
@@ -88,24 +117,42 @@ class DecodeGraphs:
                 raise ValueError(f"token {t} outside the vocabulary [0, {vocab})")
         starts = [engine.cache.seq_len[s] for s in slots]
         engine.cache.reserve([(s, 1) for s in slots])
-        engine.cache.flush()
+        updates = engine.cache.take_table_updates()
         if self._generation != engine.ws.generation:  # a workspace buffer moved: old graphs point at freed memory
             self._captured.clear()
             self._generation = engine.ws.generation
         key = (batch, params.is_greedy, params.temperature, params.top_k, params.seed)
         cap = self._captured.get(key)
         fresh = cap is None
+        shape = StepShape(list(slots), starts, [1] * batch)
         if fresh:
-            cap = self._captured[key] = _Captured(engine, batch)
-            cap.state.decode_splits = self._splits(batch)
+            cap = self._captured[key] = _Captured(engine, batch, shape)
         else:
             cap.copied.synchronize()  # the previous replay's copy has read the pinned buffer
+        cap.state.shape = shape
         f = cap.fields
         f[0], f[1], f[3] = (tokens if tokens is not None else 0), starts, slots
         f[4] = np.asarray(starts, dtype=np.int32) + 1
         f[8], f[9] = requests, steps
-        cap.dev.copy_(cap.host, non_blocking=True)
+        if cap.meta_layout:
+            cap.refresh_meta(shape)
+        used = cap.updates_at
+        staged = []
+        h = cap.host.numpy()
+        for group, rows in updates:  # block-table rows that changed: behind the index arrays, in the same copy
+            if used + rows.size > h.shape[0]:
+                # more rows than this batch can have changed itself (left over from a step that never ran):
+                # bring them over one by one
+                for row in rows:
+                    group.table_dev[int(row[0])].copy_(torch.from_numpy(row[1:].copy()))
+                continue
+            h[used:used + rows.size] = rows.reshape(-1)
+            staged.append((group, cap.dev[used:used + rows.size], rows.shape[0]))
+            used += rows.size
+        cap.dev[:used].copy_(cap.host[:used], non_blocking=True)
         cap.copied.record()
+        for group, region, n_rows in staged:
+            K.scatter_rows(group.table_dev, region, n_rows)
         if tokens is None:
             cap.state.tokens.copy_(self.sampler.out[:batch])  # device to device, after the index buffer's copy
         if cap.graph is None and not fresh and cap.failures < 3:

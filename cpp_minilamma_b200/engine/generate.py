@@ -18,9 +18,8 @@ import time
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence, Set
 
+from ..cache.paged import PAGE
 from .step import StepEntry
-
-PAGE = 64
 
 
 class GenerationError(ValueError):

@@ -32,7 +32,9 @@ class Model:
         self.act_dtype = act_dtype
         self.device = torch.device(device)
         positions = spec.max_positions if max_positions is None else min(spec.max_positions, max_positions)
-        self.ctx = BuildContext(spec.hidden_size, act_dtype, self.device, positions)
+        multiprocessors = (torch.cuda.get_device_properties(self.device).multi_processor_count
+                           if self.device.type == "cuda" else 0)
+        self.ctx = BuildContext(spec.hidden_size, act_dtype, self.device, positions, multiprocessors=multiprocessors)
         self.max_positions = positions
         self.embedding = build_part("embedding", spec.embedding, self.ctx)
         self.layers: List[Layer] = []

@@ -10,22 +10,26 @@ work (token range, position range: :434-450) are made here on the host for the w
 batch, so that no kernel is launched on a bad argument.
 
 All per-step index arrays (token ids, positions, sequence of each token, slots, context
-lengths, attention tiles, wanted rows) are packed into one int32 buffer that crosses to
-the device in one copy.  Activations live in a workspace that is reused from layer to
-layer and from step to step.
+lengths, wanted rows, the index arrays that parts prepare for their own kernels, and the
+block-table rows that changed) are packed into one int32 buffer that crosses to the device
+in one copy from pinned memory.  Activations live in a workspace that is reused from layer
+to layer and from step to step.  A step therefore allocates nothing, copies one buffer to
+the device and none back (the reference counts the same in test/forward_test.cc:412-420);
+the exceptions are a step cut into several chunks and wanted rows that are not in order,
+which assemble their logits in a tensor of their own.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Callable, Dict, List, Optional, Sequence, Tuple
+from typing import Any, Dict, Hashable, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
 
 from ..cache.paged import PAGE, CacheError, SequenceCache
+from ..parts.base import StepShape
 from .model import Model
 
-ATTN_TILE = 64  # query rows per prefill attention tile
 
 
 class StepError(ValueError):
@@ -47,6 +51,7 @@ class Workspace:
     def __init__(self, device):
         self.device = device
         self._flat: Dict[str, torch.Tensor] = {}
+        self._zeroed: set = set()
         self.generation = 0
 
     def buffer(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
@@ -69,8 +74,14 @@ class Workspace:
         flat = self._flat.get(name)
         if flat is None or flat.dtype != dtype or flat.numel() < count:
             self._flat[name] = torch.zeros(max(count, 64), dtype=dtype, device=self.device)
+            self._zeroed.add(name)
             self.generation += 1
         return self._flat[name][:count].view(shape)
+
+    def rezero(self) -> None:
+        """Zero every buffer handed out by `zeros` again (after a kernel that may have left its counters dirty)."""
+        for name in self._zeroed:
+            self._flat[name].zero_()
 
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self._flat.values())
@@ -78,7 +89,12 @@ class Workspace:
 
 @dataclass
 class StepState:
-    """Everything the parts see of a step (device tensors are int32 views of one buffer)."""
+    """Everything the parts see of a step (device tensors are int32 views of one buffer).
+
+    The fields up to `max_ctx` are the engine's own and the same for every model.  `meta` holds the
+    index arrays that parts prepared for this step (`Part.prepare_step`, by the part's
+    `step_metadata_key()` and the array's name), `fixed` the launch parameters of a captured step
+    (`Part.capture_parameters`, by part), `extras` arrays that the caller of the step sent along."""
 
     ws: Workspace
     n_tokens: int
@@ -90,15 +106,77 @@ class StepState:
     seq_ctx: torch.Tensor
     seq_qstart: torch.Tensor
     seq_qlen: torch.Tensor
-    tile_seq: torch.Tensor
-    tile_row0: torch.Tensor
-    n_tiles: int
     want_rows: Optional[torch.Tensor]
     all_decode: bool
     max_ctx: int
-    decode_splits: int = 0                      # fixed split count (graph replay), 0 = choose per step
     small_rows: int = 0                         # steps with at most this many rows use the weight-streaming product
-    host: Dict[str, list] = field(default_factory=dict)  # host copies for parts written in Python
+    shape: Optional[StepShape] = None           # the same step as host lists, for parts written in Python
+    meta: Dict[Hashable, Dict[str, torch.Tensor]] = field(default_factory=dict)
+    fixed: Dict[Any, Dict[str, int]] = field(default_factory=dict)
+    extras: Dict[str, torch.Tensor] = field(default_factory=dict)
+
+
+def metadata_providers(parts) -> Dict[Hashable, Any]:
+    """key -> the first of `parts` with that `step_metadata_key()`: who prepares each kind of index array."""
+    providers: Dict[Hashable, Any] = {}
+    for part in parts:
+        key = part.step_metadata_key()
+        if key is not None and key not in providers:
+            providers[key] = part
+    return providers
+
+
+def step_arrays(shape: StepShape, tokens, want_rows: Sequence[int], providers: Dict[Hashable, Any],
+                extras: Optional[Dict[str, Sequence[int]]] = None) -> List[Tuple[Any, np.ndarray]]:
+    """(name, int32 array) for everything the step's kernels index by, in packing order."""
+    lens = shape.lens
+    n_seqs = shape.n_seqs
+    arrays: List[Tuple[Any, np.ndarray]] = [
+        ("tokens", np.asarray(tokens, dtype=np.int32)),
+        ("tok_pos", np.concatenate([np.arange(s, s + n, dtype=np.int32) for s, n in zip(shape.starts, lens)])),
+        ("tok_seq", np.repeat(np.arange(n_seqs, dtype=np.int32), lens)),
+        ("seq_slot", np.asarray(shape.slots, dtype=np.int32)),
+        ("seq_ctx", np.asarray([s + n for s, n in zip(shape.starts, lens)], dtype=np.int32)),
+        ("seq_qstart", np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.int32)),
+        ("seq_qlen", np.asarray(lens, dtype=np.int32)),
+        ("want_rows", np.asarray(want_rows, dtype=np.int32)),
+    ]
+    for key, part in providers.items():
+        for name, values in part.prepare_step(shape).items():
+            arrays.append((("meta", key, name), np.asarray(values, dtype=np.int32).reshape(-1)))
+    for name, values in (extras or {}).items():
+        arrays.append((("extra", name), np.asarray(values, dtype=np.int32).reshape(-1)))
+    return arrays
+
+
+def state_from_views(ws: Workspace, shape: StepShape, views: Dict[Any, torch.Tensor], small_rows: int) -> StepState:
+    state = StepState(ws=ws, n_tokens=shape.n_tokens, n_seqs=shape.n_seqs, tokens=views["tokens"],
+                      tok_pos=views["tok_pos"], tok_seq=views["tok_seq"], seq_slot=views["seq_slot"],
+                      seq_ctx=views["seq_ctx"], seq_qstart=views["seq_qstart"], seq_qlen=views["seq_qlen"],
+                      want_rows=views["want_rows"] if views["want_rows"].shape[0] else None,
+                      all_decode=shape.all_decode, max_ctx=shape.max_ctx, small_rows=small_rows, shape=shape)
+    for name, view in views.items():
+        if isinstance(name, tuple) and name[0] == "meta":
+            state.meta.setdefault(name[1], {})[name[2]] = view
+        elif isinstance(name, tuple) and name[0] == "extra":
+            state.extras[name[1]] = view
+    return state
+
+
+def make_step_state(device, slots: Sequence[int], starts: Sequence[int], lens: Sequence[int], tokens=None,
+                    want_rows: Sequence[int] = (), parts=(), ws: Optional[Workspace] = None,
+                    small_rows: int = 0) -> StepState:
+    """A `StepState` outside an engine, for running a part alone (tests, experiments): the same arrays, packed
+    and copied once.  `parts`: the parts that will see the state; their index arrays are prepared."""
+    shape = StepShape(list(slots), list(starts), list(lens))
+    arrays = step_arrays(shape, tokens if tokens is not None else [0] * shape.n_tokens, want_rows,
+                         metadata_providers(parts))
+    flat = torch.from_numpy(np.concatenate([a for _, a in arrays])).to(device)
+    views, at = {}, 0
+    for name, a in arrays:
+        views[name] = flat[at:at + a.shape[0]]
+        at += a.shape[0]
+    return state_from_views(ws or Workspace(device), shape, views, small_rows)
 
 
 @dataclass
@@ -129,11 +207,13 @@ class Engine:
                                    max_seqs if max_seqs is not None else min(n_pages, 4096),
                                    model.max_positions, model.act_dtype, self.device)
         self.ws = Workspace(self.device)
-        self.max_step_tokens = max(int(max_step_tokens), ATTN_TILE)
+        self.max_step_tokens = max(int(max_step_tokens), PAGE)
         self.vocab_size = model.spec.vocab_size
+        self.providers = metadata_providers(model.all_parts())
         self._meta_host: Optional[torch.Tensor] = None
         self._meta_dev: Optional[torch.Tensor] = None
         self._meta_copied = None
+        self.extras: Dict[str, torch.Tensor] = {}  # device views of the extras that the last step was given
         self.small_rows = 64  # rows up to which linears may use this package's weight-streaming kernels
         self.launch_count = 0  # kernels of this package launched (estimate kept by the parts' callers)
 
@@ -163,17 +243,40 @@ class Engine:
         the entries and of each entry's `want`, or None when nothing is wanted.  The
         result is the caller's own tensor."""
         borrowed = self.step_borrowed(entries)
+        self.check_device_error()
         return None if borrowed is None else borrowed.clone()
 
-    def step_borrowed(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
-        """As `step`, but the result may alias workspace memory that the next step overwrites."""
+    def check_device_error(self) -> None:
+        """Waits for the device and raises `DeviceKernelError` if a kernel gave up since the flags were
+        last read (a bounded wait that ran out).  `step` calls it: its callers read the logits next, so
+        the wait costs them nothing they would not pay anyway.  The generation loop does not come here; it
+        gets the same flags with the sampled tokens (`DeviceSampler.collect`)."""
+        from ..csrc import kernels as K
+        mask = K.take_device_error()
+        if mask:
+            self.after_device_error()
+            raise K.DeviceKernelError(K.device_error_message(mask))
+
+    def after_device_error(self) -> None:
+        """A kernel that gave up may have left arrival counters non-zero and the workspace half written:
+        zero the counters and drop the captured decode graphs, so that later steps start clean."""
+        self.ws.rezero()
+        if getattr(self, "_graphs", None) is not None:
+            self._graphs.drop()
+
+    def step_borrowed(self, entries: Sequence[StepEntry],
+                      extras: Optional[Dict[str, Sequence[int]]] = None) -> Optional[torch.Tensor]:
+        """As `step`, but the result may alias workspace memory that the next step overwrites, and the
+        device's error flags are not looked at.  `extras`: further integer arrays that cross to the device
+        with the step's index arrays (the sampler's counters, say); their device views are in
+        `self.extras` afterwards."""
         chunks, n_want = self._plan(entries)
         out: Optional[torch.Tensor] = None
         if n_want and len(chunks) > 1:
             out = torch.empty((n_want, self.vocab_size), dtype=torch.float32, device=self.device)
         result = None
-        for chunk in chunks:
-            logits, out_rows = self._run_chunk(chunk)
+        for i, chunk in enumerate(chunks):
+            logits, out_rows = self._run_chunk(chunk, extras if i == len(chunks) - 1 else None)
             if logits is None:
                 continue
             if len(chunks) == 1 and out_rows == list(range(n_want)):
@@ -212,7 +315,7 @@ class Engine:
             self.cache.reserve(growth)  # all or nothing; raises CacheFull / CacheError
         except CacheError:
             raise
-        self.cache.flush()
+        # the block-table rows that changed travel with the first chunk's index arrays (build_state)
 
         chunks: List[List[_ChunkSeq]] = [[]]
         room = self.max_step_tokens
@@ -239,7 +342,9 @@ class Engine:
     # ---- one chunk ------------------------------------------------------------------- #
     def _meta(self, n_ints: int):
         if self._meta_host is None or self._meta_host.numel() < n_ints:
-            size = max(n_ints, 4096)
+            if self._meta_copied is not None:
+                self._meta_copied.synchronize()
+            size = max(2 * n_ints, 4096)
             pin = self.device.type == "cuda"
             self._meta_host = torch.empty(size, dtype=torch.int32, pin_memory=pin)
             self._meta_dev = torch.empty(size, dtype=torch.int32, device=self.device)
@@ -249,71 +354,48 @@ class Engine:
             self._meta_copied.synchronize()
         return self._meta_host, self._meta_dev
 
-    def build_state(self, seqs: Sequence[_ChunkSeq], decode_splits: int = 0) -> Tuple[StepState, List[int]]:
-        """Pack the chunk's index arrays, copy them to the device, return the step state and
-        the output rows of the wanted logits (in the order they will be produced)."""
-        n_seqs = len(seqs)
-        lens = [len(s.tokens) for s in seqs]
-        n_tokens = sum(lens)
-        all_decode = all(n == 1 for n in lens)
-        tiles_seq: List[int] = []
-        tiles_row: List[int] = []
-        if not all_decode:
-            order = sorted(range(n_seqs), key=lambda i: -(seqs[i].start + lens[i]))  # long contexts first
-            for i in order:
-                for row0 in range(0, lens[i], ATTN_TILE):
-                    tiles_seq.append(i)
-                    tiles_row.append(row0)
-        n_tiles = len(tiles_seq)
+    def build_state(self, seqs: Sequence[_ChunkSeq],
+                    extras: Optional[Dict[str, Sequence[int]]] = None) -> Tuple[StepState, List[int]]:
+        """Pack the chunk's index arrays and the cache's changed block-table rows, copy them to the
+        device (one copy), apply the rows, and return the step state and the output rows of the wanted
+        logits (in the order they will be produced)."""
+        from ..csrc import kernels as K
+        shape = StepShape([s.slot for s in seqs], [s.start for s in seqs], [len(s.tokens) for s in seqs])
         want_rows: List[int] = []
         out_rows: List[int] = []
-        qstart = []
         offset = 0
-        for s, n in zip(seqs, lens):
-            qstart.append(offset)
+        for s, n in zip(seqs, shape.lens):
             for row, out_row in s.want:
                 want_rows.append(offset + row)
                 out_rows.append(out_row)
             offset += n
-        n_want = len(want_rows)
-
-        total = 3 * n_tokens + 4 * n_seqs + 2 * n_tiles + n_want
+        arrays = step_arrays(shape, np.concatenate([np.asarray(s.tokens, dtype=np.int32) for s in seqs]),
+                             want_rows, self.providers, extras)
+        updates = self.cache.take_table_updates()  # (group, int32 [n, 1 + max_blocks]) per group with changes
+        total = sum(a.shape[0] for _, a in arrays) + sum(rows.size for _, rows in updates)
         host, dev = self._meta(total)
         h = host.numpy()
-        o = 0
-
-        def put(values, count):
-            nonlocal o
-            h[o:o + count] = values
-            view = dev[o:o + count]
-            o += count
-            return view
-
-        tokens = put(np.concatenate([np.asarray(s.tokens, dtype=np.int32) for s in seqs]), n_tokens)
-        tok_pos = put(np.concatenate([np.arange(s.start, s.start + n, dtype=np.int32)
-                                      for s, n in zip(seqs, lens)]), n_tokens)
-        tok_seq = put(np.repeat(np.arange(n_seqs, dtype=np.int32), lens), n_tokens)
-        seq_slot = put([s.slot for s in seqs], n_seqs)
-        ctx = [s.start + n for s, n in zip(seqs, lens)]
-        seq_ctx = put(ctx, n_seqs)
-        seq_qstart = put(qstart, n_seqs)
-        seq_qlen = put(lens, n_seqs)
-        tile_seq = put(tiles_seq, n_tiles)
-        tile_row0 = put(tiles_row, n_tiles)
-        want = put(want_rows, n_want) if n_want else None
+        views: Dict[Any, torch.Tensor] = {}
+        at = 0
+        for name, a in arrays:
+            h[at:at + a.shape[0]] = a
+            views[name] = dev[at:at + a.shape[0]]
+            at += a.shape[0]
+        staged = []
+        for group, rows in updates:
+            h[at:at + rows.size] = rows.reshape(-1)
+            staged.append((group, dev[at:at + rows.size], rows.shape[0]))
+            at += rows.size
         dev[:total].copy_(host[:total], non_blocking=True)
         if self._meta_copied is not None:
             self._meta_copied.record()
-
-        state = StepState(ws=self.ws, n_tokens=n_tokens, n_seqs=n_seqs, tokens=tokens, tok_pos=tok_pos,
-                          tok_seq=tok_seq, seq_slot=seq_slot, seq_ctx=seq_ctx, seq_qstart=seq_qstart,
-                          seq_qlen=seq_qlen, tile_seq=tile_seq, tile_row0=tile_row0, n_tiles=n_tiles,
-                          want_rows=want, all_decode=all_decode, max_ctx=max(ctx), decode_splits=decode_splits,
-                          small_rows=self.small_rows,
-                          host={"slots": [s.slot for s in seqs], "lens": lens, "starts": [s.start for s in seqs]})
+        for group, region, n_rows in staged:
+            K.scatter_rows(group.table_dev, region, n_rows)
+        state = state_from_views(self.ws, shape, views, self.small_rows)
         return state, out_rows
 
-    def _run_chunk(self, seqs: Sequence[_ChunkSeq]):
-        state, out_rows = self.build_state(seqs)
+    def _run_chunk(self, seqs: Sequence[_ChunkSeq], extras=None):
+        state, out_rows = self.build_state(seqs, extras)
+        self.extras = state.extras
         logits = self.model.forward(state, self.cache, state.tokens, state.want_rows)
         return logits, out_rows

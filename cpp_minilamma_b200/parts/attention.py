@@ -19,7 +19,7 @@ from .base import (BuildContext, CacheNeed, KVNeed, Mixer, PartSpec, PreNormed, 
 from .linear import Linear
 from .rope import shared_position_encoding
 
-_TARGET_BLOCKS = 2 * 148  # decode attention aims at two blocks per SM
+PREFILL_TILE = K.PREFILL_TILE  # query rows per tile of the prefill attention kernels' work list
 
 
 class Attention(Mixer):
@@ -52,6 +52,7 @@ class Attention(Mixer):
         if self.n_heads % self.n_kv_heads:
             raise ValueError(f"attention: {self.n_heads} heads are not a multiple of {self.n_kv_heads} kv heads")
         self.position = shared_position_encoding(params.get("position") or PartSpec("none"), ctx)
+        self.target_blocks = 2 * max(ctx.multiprocessors, 1)  # decode attention aims at two blocks per multiprocessor
         self.qkv: Optional[Linear] = None
         self.o: Optional[Linear] = None
         self.bias: Optional[torch.Tensor] = None
@@ -93,6 +94,27 @@ class Attention(Mixer):
         return CacheNeed(kv=KVNeed(self.n_kv_heads, self.head_dim, self.window))
 
     # ---- step ------------------------------------------------------------- #
+    def step_metadata_key(self):
+        return ("attention.prefill_tiles", PREFILL_TILE)  # every attention layer reads the same tile list
+
+    def prepare_step(self, shape):
+        """The prefill kernels' work list: one tile of up to PREFILL_TILE query rows per entry, as
+        (sequence, first row within the sequence's new tokens), long contexts first so that the longest
+        tiles start first.  Steps of single tokens need none."""
+        if shape.all_decode:
+            return {}
+        order = sorted(range(shape.n_seqs), key=lambda i: -(shape.starts[i] + shape.lens[i]))
+        tile_seq, tile_row0 = [], []
+        for i in order:
+            for row0 in range(0, shape.lens[i], PREFILL_TILE):
+                tile_seq.append(i)
+                tile_row0.append(row0)
+        return {"tile_seq": tile_seq, "tile_row0": tile_row0}
+
+    def capture_parameters(self, batch: int, max_positions: int):
+        # a captured step serves every context length: the split count follows from the batch size alone
+        return {"splits": self.decode_splits(batch, max_positions)}
+
     def decode_splits(self, n_seqs: int, max_ctx: int) -> int:
         group = self.n_heads // self.n_kv_heads
         heads_per_block = max(1, min(group, 2048 // self.head_dim))
@@ -106,7 +128,7 @@ class Attention(Mixer):
         # The tensor-core kernel applies the same rule to each sequence's own length (a short
         # sequence uses fewer of the offered splits), so a launch captured for the longest
         # context serves the short ones at their own split count.
-        return max(1, min(_TARGET_BLOCKS // blocks, pages, max(16, pages // 16)))
+        return max(1, min(self.target_blocks // blocks, pages, max(16, pages // 16)))
 
     takes_prenormed = True  # the q/k/v product may read rows whose norm it finishes itself
     adds_residual = True    # the output product may add to the residual stream and prepare the next norm
@@ -122,7 +144,8 @@ class Attention(Mixer):
         out = step.ws.buffer("attn", (T, Hq * d), act)
         splits, scratch, counters = 1, None, None
         if step.all_decode:
-            splits = step.decode_splits if step.decode_splits else self.decode_splits(step.n_seqs, step.max_ctx)
+            fixed = step.fixed.get(self)
+            splits = fixed["splits"] if fixed else self.decode_splits(step.n_seqs, step.max_ctx)
             if splits > 1:
                 scratch = step.ws.buffer(
                     "attn.scratch", (K.attention_decode_scratch_floats(step.n_seqs, Hq, d, splits),), torch.float32)
@@ -143,9 +166,10 @@ class Attention(Mixer):
                 K.attention_decode(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, cache.block_table, scratch, out,
                                    step.n_seqs, Hq, Hk, d, splits, self.window, self.scale, counters=counters)
             else:
+                tiles = step.meta[self.step_metadata_key()]
                 K.attention_prefill(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
-                                    step.tile_seq, step.tile_row0, cache.block_table, out, step.n_tiles,
-                                    Hq, Hk, d, self.window, self.scale)
+                                    tiles["tile_seq"], tiles["tile_row0"], cache.block_table, out,
+                                    tiles["tile_seq"].shape[0], Hq, Hk, d, self.window, self.scale)
         if self.o_bias_t is None:
             return self.o.forward(step, out, "o", into=into)
         o = self.o.forward(step, out, "o")

@@ -149,6 +149,34 @@ class BuildContext:
     device: torch.device
     max_positions: int
     shared: Dict[Any, Any] = field(default_factory=dict)  # tables shared between layers
+    multiprocessors: int = 0  # of the device, asked once when the model is built (0: not a CUDA device)
+
+
+@dataclass
+class StepShape:
+    """What a step looks like from the host: for each sequence of the batch its slot, the position of its
+    first new token and the number of tokens it brings.  Parts read it when they prepare index arrays of
+    their own for the step (`Part.prepare_step`); a part written in Python may also walk it in `forward`."""
+
+    slots: List[int]
+    starts: List[int]
+    lens: List[int]
+
+    @property
+    def n_seqs(self) -> int:
+        return len(self.slots)
+
+    @property
+    def n_tokens(self) -> int:
+        return sum(self.lens)
+
+    @property
+    def all_decode(self) -> bool:
+        return all(n == 1 for n in self.lens)
+
+    @property
+    def max_ctx(self) -> int:
+        return max(s + n for s, n in zip(self.starts, self.lens))
 
 
 class WeightStore:
@@ -176,7 +204,7 @@ class Part:
     role = "part"
     # True when `forward` only enqueues work whose arguments live in device memory at fixed
     # addresses, so that a decode step can be captured in a CUDA graph and replayed.  A part
-    # that reads host-side step information (step.host) or allocates must leave it False.
+    # that reads host-side step information (step.shape) or allocates must leave it False.
     capturable = False
 
     def __init__(self, params: Dict[str, Any], ctx: BuildContext):
@@ -192,6 +220,25 @@ class Part:
     def parameter_bytes(self) -> int:
         """Bytes of weights a step reads from this part (for the roofline)."""
         return 0
+
+    # ---- index arrays and launch parameters of the part's own ------------------------------------- #
+    def step_metadata_key(self):
+        """None, or a hashable key: the part's kernels want index arrays of their own on the device for
+        every step (tile lists, work queues ...).  Parts with equal keys share one preparation per step."""
+        return None
+
+    def prepare_step(self, shape: "StepShape") -> Dict[str, Any]:
+        """name -> sequence of integers for this step.  The engine packs them into the one int32 buffer
+        that crosses to the device per step and hands them back as device views in
+        `step.meta[key][name]`.  In a step where every sequence brings one token the sizes must depend on
+        the number of sequences alone (such steps are replayed from a captured graph)."""
+        return {}
+
+    def capture_parameters(self, batch: int, max_positions: int) -> Dict[str, int]:
+        """Launch parameters that must not change between replays of a captured decode step of `batch`
+        sequences (a captured graph serves every context length).  The part finds them in
+        `step.fixed[self]` during such steps and chooses freely otherwise."""
+        return {}
 
 
 class PositionEncoding(Part):

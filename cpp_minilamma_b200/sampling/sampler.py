@@ -85,7 +85,13 @@ class DeviceSampler:
         turn, n, rows = ticket
         self.events[turn].synchronize()
         host = self.hosts[turn]
-        if int(host[rows:rows + n].max()) != 0:
+        status = host[rows:rows + n]
+        # row 0's word also carries, in bits 8 and up, the error flags of kernels that gave up during the step
+        gave_up = int(status[0]) >> 8
+        if gave_up:
+            from ..csrc.kernels import DeviceKernelError, device_error_message
+            raise DeviceKernelError(device_error_message(gave_up))
+        if int((status & 0xFF).max()) != 0:
             raise FloatingPointError("logits are not finite")  # src/sampler.cc:10-19
         return host[:n].tolist()
 
@@ -99,11 +105,15 @@ class DeviceSampler:
         return self.collect(self.sample_ticket(logits, params, requests, steps))
 
     def sample_ticket(self, logits: torch.Tensor, params: SamplingParams, requests: Sequence[int],
-                      steps: Sequence[int]):
-        """As `sample`, but returns a ticket for `collect` instead of waiting."""
+                      steps: Sequence[int], on_device=None):
+        """As `sample`, but returns a ticket for `collect` instead of waiting.  `on_device`: the same
+        counters as int32 device tensors (request, step), when the caller has brought them over already."""
         n = logits.shape[0]
         if n > self.rows:
             self._alloc(max(n, 2 * self.rows))
+        if on_device is not None and not params.is_greedy:
+            self.launch(logits, params, on_device[0], on_device[1])
+            return self.ticket(n)
         if not params.is_greedy:
             self.counters[:n].copy_(torch.tensor(list(requests), dtype=torch.int32))
             self.counters[self.rows:self.rows + n].copy_(torch.tensor(list(steps), dtype=torch.int32))

@@ -14,7 +14,7 @@ import plain_llama as pl
 from cpp_minilamma_b200 import StepEntry
 from cpp_minilamma_b200.cache import SequenceCache
 from cpp_minilamma_b200.config.base import ModelConfig, take_int
-from cpp_minilamma_b200.engine.step import StepState, Workspace
+from cpp_minilamma_b200.engine.step import make_step_state
 from cpp_minilamma_b200.parts import (BuildContext, CacheNeed, LayerSpec, Mixer, ModelSpec, PartSpec, ScheduleEntry,
                                       StateNeed, WeightSpec, WeightStore, build_part, register_part)
 from cpp_minilamma_b200.parts.rope import inverse_frequencies
@@ -42,25 +42,10 @@ def rnd(shape, seed, scale=1.0):
     return torch.randn(shape, generator=torch.Generator().manual_seed(seed)) * scale
 
 
-def make_state(slots, starts, lens, tokens=None):
-    """A StepState for sequences in `slots` that bring `lens` tokens from positions `starts`."""
-    i32 = lambda a: torch.tensor(np.asarray(a, dtype=np.int32), device=DEV)
-    n_tokens = sum(lens)
-    tile_seq, tile_row0 = [], []
-    for i, n in enumerate(lens):
-        for r in range(0, n, 64):
-            tile_seq.append(i)
-            tile_row0.append(r)
-    ctx = [s + n for s, n in zip(starts, lens)]
-    return StepState(
-        ws=Workspace(DEV), n_tokens=n_tokens, n_seqs=len(slots),
-        tokens=i32(tokens if tokens is not None else [0] * n_tokens),
-        tok_pos=i32(np.concatenate([np.arange(s, s + n) for s, n in zip(starts, lens)])),
-        tok_seq=i32(np.repeat(np.arange(len(lens)), lens)), seq_slot=i32(slots), seq_ctx=i32(ctx),
-        seq_qstart=i32(np.concatenate([[0], np.cumsum(lens)[:-1]])), seq_qlen=i32(lens),
-        tile_seq=i32(tile_seq), tile_row0=i32(tile_row0), n_tiles=len(tile_seq), want_rows=None,
-        all_decode=all(n == 1 for n in lens), max_ctx=max(ctx),
-        host={"slots": list(slots), "lens": list(lens), "starts": list(starts)})
+def make_state(slots, starts, lens, tokens=None, parts=()):
+    """A StepState for sequences in `slots` that bring `lens` tokens from positions `starts`, with the index
+    arrays that `parts` prepare for themselves."""
+    return make_step_state(DEV, slots, starts, lens, tokens=tokens, parts=parts)
 
 
 def ctx_for(dtype, hidden, max_positions=512):
@@ -164,10 +149,10 @@ def test_attention_part_prefill_then_decode(dtype, window):
     # prompts of 70 and 5 tokens in one step, then one token each
     cache.reserve(list(zip(slots, lens)))
     cache.flush()
-    out1 = part.forward(make_state(slots, [0, 0], lens), h[:75].to(DEV), cache.view(0)).clone()
+    out1 = part.forward(make_state(slots, [0, 0], lens, parts=[part]), h[:75].to(DEV), cache.view(0)).clone()
     cache.reserve([(s, 1) for s in slots])
     cache.flush()
-    out2 = part.forward(make_state(slots, lens, [1, 1]), h[75:].to(DEV), cache.view(0)).clone()
+    out2 = part.forward(make_state(slots, lens, [1, 1], parts=[part]), h[75:].to(DEV), cache.view(0)).clone()
     cfg = {"num_attention_heads": hq, "num_key_value_heads": hk, "head_dim": d, "hidden_size": hidden,
            "rope_interleaved": True, "sliding_window": window or None}
     weights = {f"self_attn.{p}_proj.{kind}": host[f"a.{p}_proj.{kind}"] for p in "qkvo" for kind in ("weight", "bias")}
@@ -213,7 +198,7 @@ class RunningMeanMixer(Mixer):
     def forward(self, step, h, cache):
         out = step.ws.buffer("toy.out", tuple(h.shape), h.dtype)
         at = 0
-        for slot, n in zip(step.host["slots"], step.host["lens"]):  # tokens of a sequence in order
+        for slot, n in zip(step.shape.slots, step.shape.lens):  # tokens of a sequence in order
             rows = h[at:at + n].float()
             sums = cache.state["sum"][slot] + torch.cumsum(rows, dim=0)
             counts = cache.state["count"][slot] + torch.arange(1, n + 1, device=h.device, dtype=torch.float32)[:, None]
@@ -497,3 +482,142 @@ def test_toy_architecture_with_window_group_routing_and_other_encoding(tmp_path)
     out = llm.engine.step([StepEntry(a, tokens, list(range(300))), StepEntry(b, tokens[:7], [6])]).cpu().numpy()
     assert_close(out[:300], ref, "float32", "toy mix: whole")
     assert_close(out[300], mix_plain(weights, tokens[:7])[6], "float32", "toy mix: short neighbour")
+
+
+# ------------------------------------------------------------------------------------ #
+# a third toy architecture: a mixer whose kernels want an index array of their own      #
+# ------------------------------------------------------------------------------------ #
+class BucketGainMixer(Mixer):
+    """out_t = gain[min(pos_t // 16, 3)] * (W . h_t): the bucket of every token is an index array that the part
+    prepares on the host for each step and finds on the device in `step.meta`.  `forward` enqueues device work
+    at fixed addresses only, so decode steps are captured and replayed, and the array is refreshed inside the
+    captured step's buffer.  It also asks for a launch parameter that is fixed at capture."""
+
+    capturable = True
+    KEY = ("toy.bucket", 16)
+    prepared = 0
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.name = params["name"]
+        self.weight = self.gain = None
+
+    def weight_specs(self):
+        D = self.ctx.hidden_size
+        return [WeightSpec(self.name + ".w", (D, D)), WeightSpec(self.name + ".gain", (4,), kind="vector", init="norm")]
+
+    def bind(self, store):
+        self.weight = store.take(self.name + ".w")
+        self.gain = store.take(self.name + ".gain")
+
+    def step_metadata_key(self):
+        return self.KEY
+
+    def prepare_step(self, shape):
+        BucketGainMixer.prepared += 1
+        return {"bucket": [min(pos // 16, 3) for start, n in zip(shape.starts, shape.lens) for pos in range(start, start + n)]}
+
+    def capture_parameters(self, batch, max_positions):
+        return {"batch_at_capture": batch}
+
+    def forward(self, step, h, cache):
+        fixed = step.fixed.get(self)
+        assert fixed is None or fixed["batch_at_capture"] == step.n_seqs
+        bucket = step.meta[self.KEY]["bucket"]
+        assert bucket.shape[0] == h.shape[0] and bucket.dtype == torch.int32
+        gain = torch.index_select(self.gain, 0, bucket.long())[:, None]
+        return ((h.float() @ self.weight.float().t()) * gain).to(h.dtype)
+
+
+@dataclass
+class BucketConfig(ToyConfig):
+    def to_dict(self):
+        return {**super().to_dict(), "architectures": ["ToyBucketLM"]}
+
+
+def bucket_builder(cfg):
+    D = cfg.hidden_size
+
+    def norm(name):
+        return PartSpec("rms_norm", {"width": D, "eps": 1e-5, "name": name})
+
+    def ffn(i):
+        return PartSpec("swiglu", {"intermediate": INTER, "names": {p: f"l{i}.{p}" for p in ("gate", "up", "down")}})
+
+    attention = PartSpec("attention", {
+        "n_heads": HQ, "n_kv_heads": HK, "head_dim": HD, "window": 0,
+        "position": PartSpec("rotary", {"head_dim": HD, "theta": 100.0, "scaling": None, "interleaved": False}),
+        "names": {p: f"l0.{p}" for p in "qkvo"}})
+    layers = [LayerSpec(PartSpec("pre_norm"), attention, ffn(0), {"input": norm("l0.n1"), "post_mixer": norm("l0.n2")}),
+              LayerSpec(PartSpec("pre_norm"), PartSpec("bucket_gain", {"name": "l1.mix"}), ffn(1),
+                        {"input": norm("l1.n1"), "post_mixer": norm("l1.n2")})]
+    return ModelSpec(hidden_size=D, vocab_size=cfg.vocab_size, max_positions=256,
+                     embedding=PartSpec("token_embedding", {"vocab": cfg.vocab_size, "name": "emb"}),
+                     layers=layers, schedule=[ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(1)], final_norm=norm("final"),
+                     lm_head=PartSpec("linear_head", {"vocab": cfg.vocab_size, "name": "head", "tied_to": None}))
+
+
+def bucket_plain(weights, tokens):
+    T = len(tokens)
+    pos = np.arange(T)
+    inv = pl.rope_inverse_frequencies(HD, 100.0)
+    x = pl.embedding(weights["emb"], tokens)
+    for i in (0, 1, 1):
+        h = pl.rms_norm(x, weights[f"l{i}.n1"], 1e-5)
+        if i == 0:
+            q = pl.apply_rope(pl.linear(h, weights["l0.q.weight"]).reshape(T, HQ, HD), pos, inv, False)
+            k = pl.apply_rope(pl.linear(h, weights["l0.k.weight"]).reshape(T, HK, HD), pos, inv, False)
+            v = pl.linear(h, weights["l0.v.weight"]).reshape(T, HK, HD)
+            x = x + pl.linear(pl.causal_attention(q, k, v).reshape(T, HQ * HD), weights["l0.o.weight"])
+        else:
+            gain = weights["l1.mix.gain"].astype(np.float64)[np.minimum(pos // 16, 3)][:, None]
+            x = x + pl.linear(h, weights["l1.mix.w"]) * gain
+        h = pl.rms_norm(x, weights[f"l{i}.n2"], 1e-5)
+        x = x + pl.feed_forward(h, weights[f"l{i}.gate.weight"], weights[f"l{i}.up.weight"], weights[f"l{i}.down.weight"])
+    return pl.linear(pl.rms_norm(x, weights["final"], 1e-5), weights["head"])
+
+
+def test_toy_mixer_with_index_arrays_of_its_own_under_graph_replay(tmp_path):
+    from cpp_minilamma_b200 import EngineBackend, SamplingParams
+    from cpp_minilamma_b200.engine.generate import generate
+    register_part("mixer", "bucket_gain", BucketGainMixer)
+    ml.register_architecture("ToyBucketLM", BucketConfig, bucket_builder)
+    cfg = ml.config_from_dict({"architectures": ["ToyBucketLM"], "vocab_size": 89, "hidden_size": 40})
+    folder = ml.write_random_model(cfg, tmp_path, seed=9)
+    _, weights = pl.read_model_folder(folder)
+    llm = ml.load(folder, dtype="float32", max_tokens=64 * 12, max_seqs=3)
+    assert llm.model.capturable()
+    assert set(llm.engine.providers) == {BucketGainMixer.KEY, llm.model.layers[0].mixer.step_metadata_key()}
+    rng = np.random.RandomState(3)
+    requests = [[int(t) for t in rng.randint(0, 89, size=n)] for n in (70, 5, 20)]
+    # whole requests, and a batch of prompts followed by single tokens, against the plain implementation
+    for r in requests:
+        slot, = llm.engine.acquire(1)
+        BucketGainMixer.prepared = 0
+        got = llm.engine.step([StepEntry(slot, r, list(range(len(r))))])
+        assert BucketGainMixer.prepared == 1   # two schedule entries, one preparation
+        llm.engine.release(slot)
+        assert_close(got.cpu().numpy(), bucket_plain(weights, r), "float32", "bucket whole")
+    slots = llm.engine.acquire(3)
+    heads = [len(r) - 4 for r in requests]
+    llm.engine.step([StepEntry(s, r[:h], []) for s, r, h in zip(slots, requests, heads)])
+    for k in range(4):
+        out = llm.engine.step([StepEntry(s, [r[h + k]], [0]) for s, r, h in zip(slots, requests, heads)]).cpu().numpy()
+        for i, r in enumerate(requests):
+            assert_close(out[i], bucket_plain(weights, r)[heads[i] + k], "float32", f"bucket decode {i}")
+    for s in slots:
+        llm.engine.release(s)
+    # generation: 40 new tokens from prompts of 5 and 20 tokens, so that positions pass through every bucket while the
+    # decode steps replay a captured graph one step ahead of the host; same tokens as eager step-by-step launches
+    prompts = [requests[1], requests[2]]
+    eager = generate(EngineBackend(llm.engine, SamplingParams(), use_graphs=False), prompts, 40)
+    backend = EngineBackend(llm.engine, SamplingParams())
+    replayed = generate(backend, prompts, 40)
+    assert backend.graphs.replays > 30
+    assert [c.tokens for c in replayed] == [c.tokens for c in eager]
+    for prompt, completion in zip(prompts, replayed):
+        ref = bucket_plain(weights, list(prompt) + completion.tokens)
+        for i, token in enumerate(completion.tokens):
+            row = ref[len(prompt) - 1 + i]
+            assert token == int(np.argmax(row)) or row.max() - row[token] <= 2e-4
+    llm.engine.cache.check()
