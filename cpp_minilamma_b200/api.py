@@ -147,15 +147,18 @@ def load(folder, dtype="bfloat16", device="cuda:0", max_tokens: int = 16384, max
 
 def random_model(config: ModelConfig, seed: int = 0, dtype="bfloat16", device="cuda:0", max_tokens: int = 16384,
                  max_seqs: Optional[int] = None, max_positions: Optional[int] = None, matrix_std: float = 0.02,
-                 norm_std: float = 0.0, max_step_tokens: int = 8192) -> LLM:
-    """A model with seeded random weights drawn on the device (no files)."""
+                 norm_std: float = 0.0, max_step_tokens: int = 8192, stored_as=None) -> LLM:
+    """A model with seeded random weights drawn on the device (no files).  `stored_as`: the dtype a folder
+    would store the matrices in; they are rounded to it before they take the run's dtype, so that a
+    float32 run with stored_as="bfloat16" holds the very values of a bfloat16 run of the same seed."""
     device = require_cuda(device)
     run_dtype = parse_dtype(dtype)
+    stored = parse_dtype(stored_as) if stored_as is not None else run_dtype
     model = build_model(config, run_dtype, device, max_positions)
     tensors = {}
     specs = model.weight_specs()
     for index, spec in enumerate(specs):  # one at a time: the float32 draft of a tensor is freed before the next
         drawn = random_tensors([spec], seed * 4099 + index, torch.float32, device, matrix_std, norm_std)[spec.name]
-        tensors[spec.name] = drawn.to(torch.float32 if spec.kind == "vector" else run_dtype)
+        tensors[spec.name] = drawn.to(torch.float32) if spec.kind == "vector" else drawn.to(stored).to(run_dtype)
     model.bind(tensors)
     return LLM(config, model, max_tokens, max_seqs, max_step_tokens)

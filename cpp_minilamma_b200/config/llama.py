@@ -110,8 +110,10 @@ class LlamaConfig(ModelConfig):
         if take_bool(raw, "mlp_bias", False):
             raise ConfigError("config.json: mlp_bias=true is not supported (the feed-forward has no bias)")
         dtype = raw.get("torch_dtype", raw.get("dtype", "bfloat16"))
-        if dtype not in ("bfloat16", "float32"):
-            raise ConfigError(f"config.json: torch_dtype {dtype!r} not supported (bfloat16 or float32)")
+        if dtype not in ("bfloat16", "float32", "float16"):
+            # the dtype the folder's tensors are stored in (the reference reads F32 and F16 tensors,
+            # include/quantized_tensor.h:37-81); a run converts them to its own dtype when it loads them
+            raise ConfigError(f"config.json: torch_dtype {dtype!r} not supported (bfloat16, float16 or float32)")
         act = raw.get("hidden_act", "silu")
         return cls(
             vocab_size=take_int(raw, "vocab_size", minimum=1),

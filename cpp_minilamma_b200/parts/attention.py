@@ -147,8 +147,11 @@ class Attention(Mixer):
             fixed = step.fixed.get(self)
             splits = fixed["splits"] if fixed else self.decode_splits(step.n_seqs, step.max_ctx)
             if splits > 1:
+                # room for the most splits that this batch size can ever be given, so that the buffer does not
+                # grow (an allocation in the middle of a generation) when the contexts do
+                most = max(splits, self.decode_splits(step.n_seqs, self.ctx.max_positions))
                 scratch = step.ws.buffer(
-                    "attn.scratch", (K.attention_decode_scratch_floats(step.n_seqs, Hq, d, splits),), torch.float32)
+                    "attn.scratch", (K.attention_decode_scratch_floats(step.n_seqs, Hq, d, most),), torch.float32)
                 # one arrival counter per (sequence, kv head, chunk of 16 heads): the last split merges
                 counters = step.ws.zeros("attn.counters", (step.n_seqs * Hk * (-(-(Hq // Hk) // 16)),), torch.int32)
         if (step.all_decode and self.bias is None and qkv.dtype == torch.bfloat16

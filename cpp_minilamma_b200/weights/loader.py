@@ -8,6 +8,8 @@ error.)
 
 Where each tensor ends up:
   * matrix, stored BF16:  bfloat16 in a bfloat16 run, widened to float32 in a float32 run;
+  * matrix, stored F16:   rounded to bfloat16 in a bfloat16 run (the kernels have no float16 instance),
+                          widened exactly in a float32 run;
   * matrix, stored F32:   stays float32 in either run (its product then runs in float32);
   * vector (norm weights, biases): float32 always - every stored value is kept exactly;
   * int_table: int32.

@@ -57,7 +57,8 @@ def write_random_model(config: ModelConfig, folder, seed: int, matrix_std: float
     folder.mkdir(parents=True, exist_ok=True)
     _, builder = lookup_architecture(config.architecture)
     model = Model(builder(config), torch.float32, "cpu", max_positions=1)
-    storage = {"bfloat16": torch.bfloat16, "float32": torch.float32}[getattr(config, "torch_dtype", "bfloat16")]
+    storage = {"bfloat16": torch.bfloat16, "float32": torch.float32,
+               "float16": torch.float16}[getattr(config, "torch_dtype", "bfloat16")]
     tensors = random_tensors(model.weight_specs(), seed, storage, "cpu", matrix_std, norm_std)
     save_config(config, folder)
     write_safetensors(folder / "model.safetensors", tensors, {"format": "pt", "seed": str(seed)})

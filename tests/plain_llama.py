@@ -60,6 +60,8 @@ def read_model_folder(path):
             arr = np.frombuffer(raw, dtype="<f4").reshape(shape).copy()
         elif info["dtype"] == "BF16":
             arr = _bf16_bits_to_f32(np.frombuffer(raw, dtype="<u2")).reshape(shape).copy()
+        elif info["dtype"] == "F16":
+            arr = np.frombuffer(raw, dtype="<f2").astype(np.float32).reshape(shape)
         else:
             raise ValueError(f"plain reader: dtype {info['dtype']} of {name} not handled")
         tensors[name] = arr

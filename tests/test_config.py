@@ -56,7 +56,7 @@ def test_defaults():
     (dict(rope_scaling={"rope_type": "yarn", "factor": 2.0}), "rope_scaling type"),
     (dict(rope_scaling={"rope_type": "llama3", "factor": 8.0}), "low_freq_factor"),
     (dict(eos_token_id=5000), "outside the vocabulary"),
-    (dict(torch_dtype="float16"), "torch_dtype"),
+    (dict(torch_dtype="float8"), "torch_dtype"),
     (dict(tie_word_embeddings="yes"), "true or false"),
 ])
 def test_rejects(change, match):
@@ -96,3 +96,9 @@ def test_no_size_in_code():
     assert shapes["model.layers.0.mlp.down_proj.weight"] == (48, 40)
     assert shapes["lm_head.weight"] == (77, 48)
     assert model.parameter_count() == sum(__import__("math").prod(s) for s in shapes.values())
+
+
+def test_float16_storage_is_a_known_dtype():
+    # the dtype a folder is stored in; a run converts to its own (float32 or bfloat16) when it loads
+    cfg = ml.config_from_dict(raw("A", torch_dtype="float16"))
+    assert cfg.torch_dtype == "float16" and cfg.to_dict()["torch_dtype"] == "float16"

@@ -221,6 +221,28 @@ def test_bfloat16_run_with_some_matrices_stored_in_32_bit(model_folders, tmp_pat
         at += h
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_folder_stored_in_float16(model_folders, dtype):
+    # a float16 folder (Llama-2's storage) loads in either run: widened exactly for float32, rounded once to
+    # bfloat16 for bfloat16.  The plain implementation gets the same weights, rounded the same way.
+    import plain_llama as pl
+    name = "B"
+    folder = model_folders(name, "float16")
+    cfg, weights = pl.read_model_folder(folder)
+    assert cfg["torch_dtype"] == "float16"
+    llm = ml.load(folder, dtype=dtype, max_tokens=2048)
+    assert llm.model.layers[0].mixer.qkv.weight.dtype == (torch.float32 if dtype == "float32" else torch.bfloat16)
+    if dtype == "bfloat16":  # matrices are rounded; vectors (norm weights) are kept as float32
+        weights = {n: (pl.round_bf16(w).astype(np.float32) if w.ndim == 2 else w) for n, w in weights.items()}
+    tokens = tc.random_tokens(name, 50, 860)
+    slot, = llm.engine.acquire(1)
+    got = [llm.engine.step([StepEntry(slot, tokens[:40], list(range(40)))]).cpu().numpy()]
+    for t in range(40, 50):
+        got.append(llm.engine.step([StepEntry(slot, [tokens[t]], [0])]).cpu().numpy())
+    act_round = pl.round_bf16 if dtype == "bfloat16" else (lambda x: x)
+    assert_close(np.concatenate(got), pl.forward_sequence(cfg, weights, tokens, act_round=act_round), dtype, f"float16 folder, {dtype} run")
+
+
 def test_cli_generate_matches_the_api(model_folders, capsys):
     from cpp_minilamma_b200.cli import main
     folder, llm = load(model_folders, "B", "float32")
