@@ -146,10 +146,10 @@ class Attention(Mixer):
         if step.all_decode:
             fixed = step.fixed.get(self)
             splits = fixed["splits"] if fixed else self.decode_splits(step.n_seqs, step.max_ctx)
-            if splits > 1:
-                # room for the most splits that this batch size can ever be given, so that the buffer does not
-                # grow (an allocation in the middle of a generation) when the contexts do
-                most = max(splits, self.decode_splits(step.n_seqs, self.ctx.max_positions))
+            # room for the most splits that this batch size can ever be given, from its first decode step on, so
+            # that no buffer appears or grows (an allocation in the middle of a generation) when the contexts do
+            most = max(splits, self.decode_splits(step.n_seqs, self.ctx.max_positions))
+            if most > 1:
                 scratch = step.ws.buffer(
                     "attn.scratch", (K.attention_decode_scratch_floats(step.n_seqs, Hq, d, most),), torch.float32)
                 # one arrival counter per (sequence, kv head, chunk of 16 heads): the last split merges
