@@ -406,6 +406,7 @@ def main():
     args = parser.parse_args()
 
     if args.impl == "reference":
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
         import reference_arm
         return reference_arm.main(args)
     if args.gpus != 1:

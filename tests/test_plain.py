@@ -52,6 +52,27 @@ def test_matches_the_references_cpp_engine(tiny_a):
         assert pl.greedy(ours[len(prompt) - 1 + i]) == token
 
 
+def test_tiny_b_without_rope_scaling_matches_the_references_cpp_engine(tmp_path):
+    # what the reference can run of tiny B: multi-query attention (6 heads on 1), half-split rotary pairs, eps
+    # 1e-6, theta 500000, a tied head, three layers - everything but the llama3 rope scaling, which it does
+    # not have.  Its C++ forward ran these four sequences one token per forward (tests/golden/reference_driver.cc).
+    folder = tc.write_folder("B", "float32", tmp_path)
+    meta = json.loads((GOLDEN / "tinyB_noscale_reference.json").read_text())
+    digest = hashlib.sha256((Path(folder) / "model.safetensors").read_bytes()).hexdigest()
+    assert digest == meta["model_sha256"], "the seeded tiny-B weights changed: rerun tests/golden/make_golden.py"
+    cfg, weights = pl.read_model_folder(folder)
+    assert cfg["rope_scaling"] is not None and cfg["tie_word_embeddings"] and cfg["num_key_value_heads"] == 1
+    cfg = dict(cfg, rope_scaling=None)
+    golden = np.load(GOLDEN / "tinyB_noscale_reference_cpp_logits.npy")
+    assert [len(s) for s in meta["sequences"]] == [29, 13, 52, 18] and golden.shape == (112, 257)
+    ours = np.concatenate([pl.forward_sequence(cfg, weights, tokens) for tokens in meta["sequences"]])
+    np.testing.assert_allclose(ours, golden, atol=1e-4, rtol=0)
+    assert (ours.argmax(axis=1) == golden.argmax(axis=1)).all()
+    # the scaling does matter for these sequences: with it the logits move by far more than the tolerance
+    scaled = pl.forward_sequence(dict(cfg, rope_scaling=tc.TINY["B"]["rope_scaling"]), weights, meta["sequences"][2])
+    assert np.abs(scaled - golden[42:94]).max() > 1e-3
+
+
 def test_rms_norm_and_swiglu_values():
     x = np.array([[3.0, -4.0]])
     np.testing.assert_allclose(pl.rms_norm(x, np.array([1.0, 2.0]), 0.0), [[3 / np.sqrt(12.5), -8 / np.sqrt(12.5)]])
