@@ -1,29 +1,36 @@
 // Causal attention of many query tokens over the paged cache on the fifth-generation tensor
 // cores: TMA -> shared memory -> tcgen05.mma -> tensor memory (bfloat16, head_dim 64 or 128).
 //
-// One block of four warps owns 128 query rows of one head; thread i owns row i, which is
-// lane i of tensor memory, so the softmax needs no exchange between threads:
-//   * thread 0 loads the query tile once and the key and value pages (64 positions each)
-//     through a two-stage ring of TMA boxes with the 128-byte swizzle, and issues the MMAs;
-//   * S = Q K^T: M = 128 rows, N = 64 keys, both operands K-major, accumulator in one of two
-//     64-column buffers of tensor memory, so that the product of the next page runs while
-//     the threads work on this one;
-//   * each thread reads its row of S (tcgen05.ld), masks it where the page meets the
-//     diagonal, the window's edge or the end of the tile, keeps the running maximum and sum
-//     in float32 (base 2) and writes P as bfloat16 into a K-major swizzled tile;
-//   * O_page = P V: A = P from shared memory, B = the value page as it lies in the cache
-//     ([position][dim], that is MN-major), accumulator in 64 or 128 further columns; each
-//     thread folds it into its float32 output row: o = o * alpha + O_page.
-// Two blocks fit a multiprocessor (112 KB of shared memory, 256 columns of tensor memory
-// each): one block's MMAs run under the other's softmax.  Rows of the last page beyond the
-// context are zeroed in shared memory (P is zero there, but the cache may hold anything).
+// One block owns 128 query rows of one head.  Its six warps:
+//   * warps 0-3, the softmax: thread i owns query row i, which is lane i of tensor memory, so the
+//     softmax needs no exchange between threads.  Per page of 64 keys a thread reads its row of S
+//     (tcgen05.ld), masks it where the page meets the diagonal, the window's edge or the end of the
+//     tile, keeps the running maximum and sum in float32 (base 2), and writes P back over the first
+//     half of the S columns as packed bfloat16 (tcgen05.st);
+//   * warp 4, one thread: TMA loads with the 128-byte swizzle - the query tile once, then the key and
+//     the value pages (64 positions each) into a two-stage ring guarded by full / empty mbarriers;
+//   * warp 5, one thread: the MMAs.  S = Q K^T (M = 128 rows, N = 64 keys, both operands K-major) goes
+//     into one of two 64-column buffers of tensor memory, and the product of page i + 1 is issued
+//     before O += P_i V_i, so that it runs under the softmax of page i.  P V takes P as the
+//     tensor-memory A operand and the value page as it lies in the cache ([position][dim], MN-major)
+//     as B; O stays in tensor memory (64 or 128 further columns).  The warp also allocates and frees
+//     the block's 256 columns.
+// O and P are scaled by a maximum that follows the row's true maximum only in steps of 2^8: O in
+// tensor memory is rescaled when a row's maximum has grown by more than that, which is rare, and
+// O / l does not depend on the scale, so the result is exact all the same.  Two blocks fit a
+// multiprocessor (80 KB of shared memory, 256 columns of tensor memory each): one block's MMAs run
+// under the other's softmax.  Rows of the last page beyond the context are zeroed in shared memory
+// (P is zero there, but the cache may hold anything).  Tiles come as a list of 64-row entries; the
+// block of an entry that starts the second half of a 128-row tile returns at once.
 //
 // Every mbarrier wait is bounded; a wait that runs out raises an error flag (read through
-// mll_take_device_error), the block agrees on it at its next barrier, stores nothing, frees its
-// tensor memory and exits.  No load uses cluster multicast.
+// mll_take_device_error), makes the block's later waits return at once, the block stores nothing,
+// frees its tensor memory and exits.  Every warp-wide tensor-memory instruction sits in warp-uniform
+// control flow.  No load uses cluster multicast.
 //
-// The reference computes attention with one thread block per head and one pass per token
-// (src/cuda_attention.cu:19-120); formulas as in src/ops.cc:223-290.
+// The reference computes attention for one query token per call with two kernels, scores into a
+// buffer and then softmax and values in a second pass (src/cuda_attention.cu:77-163); the formulas
+// are those of its CPU path (src/forward.cc:265-298).
 #include <cuda.h>
 
 #include "common.cuh"
