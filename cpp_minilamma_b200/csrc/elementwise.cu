@@ -21,7 +21,7 @@ MLL_API const char* mll_last_error() { return g_error; }
 thread_local cudaError_t mll_launch_status = cudaSuccess;
 
 // Identifies the build; the Python side checks it after loading the library.
-MLL_API int mll_abi_version() { return 18; }
+MLL_API int mll_abi_version() { return 19; }
 
 // Cache positions per page, for the Python side to check against its own constant.
 MLL_API int mll_page() { return MLL_PAGE; }
@@ -165,6 +165,34 @@ __global__ void add_bias_kernel(T* __restrict__ x, const float* __restrict__ bia
   for (; idx < total; idx += stride) x[idx] = from_float<T>(to_float(x[idx]) + bias[idx % width]);
 }
 
+// As swiglu_vec8_kernel (bfloat16, gate and up interleaved in blocks of 8), for rows of gate/up that still lack their
+// RMS norm's factor (the product ran on x * w_norm): both are multiplied by the row's factor first.  One row per
+// blockIdx.y; warp 0 computes the factor from the row's partial sums of squares.
+__global__ void swiglu_rows_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int inter,
+                                   int block, RowNormIn in, int width) {
+  __shared__ float factor;
+  const int m = blockIdx.y;
+  if (threadIdx.x < 32) {
+    const float f = row_norm_factor<32>(in.sumsq + (size_t)m * in.stride, in.partials, width, in.eps, threadIdx.x,
+                                        0xffffffffu);
+    if (threadIdx.x == 0) factor = f;
+  }
+  __syncthreads();
+  const float f = factor;
+  const int groups = inter >> 3;
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= groups) return;
+  const __nv_bfloat16* row = gu + (size_t)m * 2 * inter;
+  const __nv_bfloat16* gp = block ? row + (size_t)b * 16 : row + (size_t)b * 8;
+  const __nv_bfloat16* up = block ? gp + 8 : row + inter + (size_t)b * 8;
+  float g[8], u[8], r[8];
+  Pack8<__nv_bfloat16>::load(gp, g);
+  Pack8<__nv_bfloat16>::load(up, u);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) r[i] = silu_mul<__nv_bfloat16>(g[i] * f, u[i] * f);
+  Pack8<__nv_bfloat16>::store(out + (size_t)m * inter + (size_t)b * 8, r);
+}
+
 // table[staged[r][0]][:] = staged[r][1 : 1 + width] for r < n_rows: rows of a block table that changed on
 // the host, brought over inside the step's index buffer.
 __global__ void scatter_rows_kernel(int* __restrict__ table, const int* __restrict__ staged, int width, int table_rows) {
@@ -229,6 +257,23 @@ MLL_API int mll_cast(const void* in, int in_dtype, void* out, int out_dtype, lon
     MLL_LAUNCH((mll::cast_kernel<__nv_bfloat16, float>), (int)blocks, threads, 0, stream, (const __nv_bfloat16*)in, (float*)out, (size_t)n);
   else
     MLL_REQUIRE(false, "cast: unsupported dtype pair %d -> %d", in_dtype, out_dtype);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
+// bfloat16 gu [n_tokens, 2 inter] (halves: block 0; blocks of 8: block 8) computed from rows that lack their RMS
+// norm's factor 1 / sqrt(sum_p sumsq[m][p] / width + eps): out = silu(gate f) * (up f).
+MLL_API int mll_swiglu_rows(const void* gu, void* out, int n_tokens, int inter, int block, const float* sumsq, int partials,
+                            int stride, float eps, int width, cudaStream_t stream) {
+  MLL_REQUIRE(n_tokens >= 0 && n_tokens <= 65535 && inter > 0 && inter % 8 == 0 && (block == 0 || block == 8),
+              "swiglu_rows: bad sizes tokens=%d inter=%d block=%d", n_tokens, inter, block);
+  MLL_REQUIRE(sumsq && partials >= 1 && stride >= partials && eps >= 0.f && width > 0,
+              "swiglu_rows: partial sums: %d of stride %d", partials, stride);
+  MLL_REQUIRE(((uintptr_t)gu % 16 == 0) && ((uintptr_t)out % 16 == 0), "swiglu_rows: operands must be 16-byte aligned");
+  if (n_tokens == 0) return 0;
+  const int groups = inter / 8;
+  MLL_LAUNCH((mll::swiglu_rows_kernel), dim3((groups + 255) / 256, n_tokens), 256, 0, stream, (const __nv_bfloat16*)gu,
+             (__nv_bfloat16*)out, inter, block, mll::RowNormIn{sumsq, partials, stride, eps}, width);
   MLL_LAUNCH_CHECK();
   return 0;
 }

@@ -14,7 +14,7 @@ import torch
 from ..cache.paged import PAGE  # cache positions per page; the library's MLL_PAGE is checked against it on load
 from .build import KernelBuildError, load_library
 
-ABI_VERSION = 18
+ABI_VERSION = 19
 MAX_TOP_K = 1024
 
 
@@ -242,9 +242,11 @@ def linear_tc5_supported(rows: int, out_features: int, in_features: int, epilogu
 
 
 def linear_tc5(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-               epilogue: int = EPI_BF16, ranks: int = 0, row_norm: Optional[RowNorm] = None) -> None:
-    """As `linear_tma`, with the product on the fifth-generation tensor cores: tcgen05.mma reads
-    the TMA-filled stages from shared memory and accumulates in tensor memory."""
+               epilogue: int = EPI_BF16, ranks: int = 0, row_norm: Optional[RowNorm] = None,
+               residual: Optional[ResidualOut] = None) -> None:
+    """As `linear_small` (the residual epilogue included, here for up to 64 rows), with the product on the
+    fifth-generation tensor cores: tcgen05.mma reads the TMA-filled stages from shared memory and
+    accumulates in tensor memory.  Takes any N, any K that is a multiple of 8, at most 64 rows."""
     _need(x, "linear_tc5 x", torch.bfloat16, 2)
     _need(w, "linear_tc5 w", torch.bfloat16, 2)
     rows, k = x.shape
@@ -259,9 +261,23 @@ def linear_tc5(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], o
         _need(bias, "linear_tc5 bias", torch.float32, 1)
         if bias.shape[0] != n:
             raise KernelError("linear_tc5: bias length differs from the output width")
+    if (epilogue == EPI_RESID) != (residual is not None):
+        raise KernelError("linear_tc5: the residual epilogue and its outputs go together")
+    resid = next_w = out_sumsq = None
+    out_stride = 0
+    if residual is not None:
+        resid, next_w, out_sumsq = residual
+        _need(resid, "linear_tc5 resid", torch.float32, 2)
+        _need(next_w, "linear_tc5 next weight", torch.float32, 1)
+        _need(out_sumsq, "linear_tc5 sums of squares", torch.float32, 2)
+        if tuple(resid.shape) != (rows, n) or next_w.shape[0] != n or out_sumsq.shape[0] < rows:
+            raise KernelError(f"linear_tc5: resid {tuple(resid.shape)}, next weight {tuple(next_w.shape)}, sums "
+                              f"{tuple(out_sumsq.shape)} do not fit out {(rows, n)}")
+        out_stride = out_sumsq.shape[1]
     _check(lib().mll_linear_tc5_fused(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), ctypes.c_int(rows), ctypes.c_int(n),
                                       ctypes.c_int(k), ctypes.c_int(epilogue), ctypes.c_int(ranks),
-                                      *_row_norm_args(row_norm, rows, "linear_tc5"), _stream()), "linear_tc5")
+                                      *_row_norm_args(row_norm, rows, "linear_tc5"), _ptr(resid), _ptr(next_w),
+                                      _ptr(out_sumsq), ctypes.c_int(out_stride), _stream()), "linear_tc5")
 
 
 DEVICE_ERROR_BITS = ("the TMA linear kernel", "the tcgen05 linear kernel", "the tcgen05 prefill attention kernel",
@@ -287,20 +303,23 @@ def device_error_message(mask: int) -> str:
 
 
 TMA_MAX_ROWS = 8      # rows up to which tall matrices go to the TMA + mma.sync kernel (its batch tile is 8 rows)
-TC5_MAX_ROWS = 16     # rows up to which tall matrices go to the tcgen05 kernel (its batch tile is 16 rows)
+TC5_TALL_MAX_ROWS = 16  # rows up to which tall matrices go to the tcgen05 kernel (beyond: the library, which shares the
+                        # batch tile between the blocks of a cluster)
 DIRECT_MAX_ROWS = 16  # rows up to which the other matrices go to the direct kernel
+MID_MAX_ROWS = 64     # rows up to which the other matrices go to the tcgen05 kernel (32 or 64 batch columns per MMA)
 TALL = 16384          # output features from which a matrix counts as tall
 
 
 def small_linear_kind(rows: int, out_features: int, in_features: int, epilogue: int = EPI_BF16) -> str:
     """Which of this library's weight-streaming kernels takes the problem: "tc5", "tma", "direct" or "".
 
-    Measured on the 8B shapes (CUDA-graph timing, B200).  Tall matrices (gate/up, lm_head), where a
-    deep queue of TMA loads counts: up to 8 rows the kernel with mma.sync consumers (gate/up + SwiGLU
-    40.6 us, tcgen05 43.3), from 9 to 16 rows the tcgen05 kernel (43.6 us, the other 53.5 with its
-    second batch tile).  The 4096/6144-row projections, where a launch is short and a finer split
-    over the machine counts: the direct kernel up to 16 rows (it chooses its variant by rows and tiles).
-    Beyond that the library GEMM."""
+    Measured on B200 (CUDA-graph timing) on the shapes of the 8B, 7B and 1B Llama models.  Tall matrices
+    (gate/up, lm_head), where a deep queue of TMA loads counts: up to 8 rows the kernel with mma.sync
+    consumers (gate/up + SwiGLU 40.6 us, tcgen05 43.3), from 9 to 16 rows the tcgen05 kernel (43.6 us, the
+    other 53.5 with its second batch tile), beyond that the library GEMM.  The other projections, where a
+    launch is short and a fine split over the machine counts: the direct kernel up to 16 rows (it chooses
+    its variant by rows and tiles), the tcgen05 kernel with 32 or 64 batch columns from 17 to 64 rows
+    (split over K in clusters; the library's kernels for these shapes stream at 1.1 to 2.7 TB/s)."""
     if SMALL_LINEAR == "none":
         return ""
     if SMALL_LINEAR != "auto":  # a forced kind (tests, experiments)
@@ -309,25 +328,29 @@ def small_linear_kind(rows: int, out_features: int, in_features: int, epilogue: 
     if out_features >= TALL:
         if rows <= TMA_MAX_ROWS and linear_tma_supported(rows, out_features, in_features, epilogue):
             return "tma"
-        if rows <= TC5_MAX_ROWS and linear_tc5_supported(rows, out_features, in_features, epilogue):
+        if rows <= TC5_TALL_MAX_ROWS and linear_tc5_supported(rows, out_features, in_features, epilogue):
             return "tc5"
+        if rows > DIRECT_MAX_ROWS:
+            return ""
     if rows <= DIRECT_MAX_ROWS:
         if linear_small_supported(rows, out_features, in_features, epilogue):
             return "direct"
         if linear_tma_supported(rows, out_features, in_features, epilogue):
             return "tma"
+    if rows <= MID_MAX_ROWS and linear_tc5_supported(rows, out_features, in_features, epilogue):
+        return "tc5"
     return ""
 
 
 def small_linear(x, w, bias, out, epilogue: int = EPI_BF16, row_norm: Optional[RowNorm] = None,
                  residual: Optional[ResidualOut] = None) -> bool:
     """Run the product on the kernel that `small_linear_kind` names; False when there is none (then
-    nothing ran).  The residual epilogue exists in the direct kernel only."""
+    nothing ran).  The residual epilogue exists in the direct kernel and in the tcgen05 kernel."""
     kind = small_linear_kind(x.shape[0], w.shape[0], w.shape[1], EPI_BF16 if epilogue == EPI_RESID else epilogue)
-    if epilogue == EPI_RESID and kind != "direct":
+    if epilogue == EPI_RESID and kind not in ("direct", "tc5"):
         return False
     if kind == "tc5":
-        linear_tc5(x, w, bias, out, epilogue, 0, row_norm)
+        linear_tc5(x, w, bias, out, epilogue, 0, row_norm, residual)
     elif kind == "tma":
         linear_tma(x, w, bias, out, epilogue, 1 if x.shape[0] > 8 else 0, row_norm)
     elif kind == "direct":
@@ -337,8 +360,8 @@ def small_linear(x, w, bias, out, epilogue: int = EPI_BF16, row_norm: Optional[R
 
 def fused_norm_rows(rows: int) -> bool:
     """Whether products over `rows` rows may fold the norms around them in (the residual epilogue
-    exists in the direct kernel, which takes few rows)."""
-    return FUSE_NORM and 1 <= rows <= DIRECT_MAX_ROWS
+    exists in the kernels that take decode steps' row counts)."""
+    return FUSE_NORM and 1 <= rows <= MID_MAX_ROWS
 
 
 FUSE_NORM = True  # off: every norm is a kernel of its own
@@ -347,13 +370,24 @@ FUSE_NORM = True  # off: every norm is a kernel of its own
 SMALL_LINEAR = "auto"  # "auto", a forced kind ("tc5", "tma", "direct"), or "none" (library GEMM only)
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int) -> None:
-    """out[t, i] = silu(gate) * up; gate_up [T, 2I] holds halves (block 0) or blocks of `block`."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int, row_norm: Optional[RowNorm] = None,
+           width: int = 0) -> None:
+    """out[t, i] = silu(gate) * up; gate_up [T, 2I] holds halves (block 0) or blocks of `block`.
+    `row_norm` (bfloat16, I a multiple of 8): gate_up was computed from rows of `width` columns that lacked their
+    norm's factor; gate and up are multiplied by it first."""
     _need(gate_up, "swiglu gate_up", None, 2)
     _need(out, "swiglu out", gate_up.dtype, 2)
     tokens, inter = out.shape
     if gate_up.shape[0] != tokens or gate_up.shape[1] != 2 * inter:
         raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)} does not match out {tuple(out.shape)}")
+    if row_norm is not None:
+        if gate_up.dtype != torch.bfloat16 or inter % 8 or block not in (0, 8) or width <= 0:
+            raise KernelError("swiglu: rows without their norm's factor need bfloat16, I % 8 == 0 and the rows' width")
+        sumsq, partials, stride, eps = _row_norm_args(row_norm, tokens, "swiglu")
+        _check(lib().mll_swiglu_rows(_ptr(gate_up), _ptr(out), ctypes.c_int(tokens), ctypes.c_int(inter),
+                                     ctypes.c_int(block), sumsq, partials, stride, eps, ctypes.c_int(width), _stream()),
+               "swiglu_rows")
+        return
     _check(lib().mll_swiglu(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), ctypes.c_int(tokens),
                             ctypes.c_int(inter), ctypes.c_int(block), _stream()), "swiglu")
 

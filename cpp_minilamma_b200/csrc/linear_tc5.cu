@@ -1,4 +1,4 @@
-// y[M, N] = x[M, K] . W[N, K]^T for at most 16 rows: TMA -> shared memory -> tcgen05.mma -> TMEM.
+// y[M, N] = x[M, K] . W[N, K]^T for at most 64 rows: TMA -> shared memory -> tcgen05.mma -> TMEM.
 //
 // The fifth-generation tensor cores read both operands straight from shared memory and keep
 // the accumulator in tensor memory, so the block needs no fragment loads at all:
@@ -12,13 +12,22 @@
 //     frees the block's TMEM columns.  (One thread issuing every box or every MMA of a block
 //     caps the block's stream; two of each measured 1 % of a decode step.);
 //   * warps 0-3: after the last commits they read the two 128 x N float32 accumulators from
-//     TMEM (tcgen05.ld, one row per thread) and add them into shared memory.
-// "Swap-AB": the weights are the M operand, the batch is N, so a decode step with 1..16
-// sequences fills the 128-row MMA.  K is split over the blocks of a cluster; partial tiles
-// are summed in rank order through distributed shared memory (reproducible); the epilogue
-// (bias, SwiGLU on gate/up rows interleaved in blocks of 8, bfloat16 or float32 output) runs
-// on the full sum.  Rows and columns outside the matrices are zero-filled by TMA, so any N,
-// any M <= 16 and any K % 8 == 0 are taken.  No load uses cluster multicast.
+//     TMEM (tcgen05.ld, one row per thread) and add them into shared memory, batch row by batch
+//     row ([m][weight row]: neighbouring threads write neighbouring words).
+// "Swap-AB": the weights are the M operand, the batch is N, so a decode step with 1..64
+// sequences fills the 128-row MMA.  K is split over the blocks of a cluster; every block of the
+// cluster then owns a share of the batch rows, sums the partial tiles of all blocks for them in
+// rank order through distributed shared memory (reproducible) and runs the epilogue on them:
+// bias, SwiGLU on gate/up rows interleaved in blocks of 8, bfloat16 or float32 output, or the
+// residual epilogue (add to the float32 residual stream, write the new stream times the next norm's
+// weight with partial sums of squares per 16 columns).  Rows and columns outside the matrices are
+// zero-filled by TMA, so any N, any M <= 64 and any K % 8 == 0 are taken.  No load uses cluster multicast.
+//
+// The ring has an even number of stages for every batch width.  The two producers (and the two MMA
+// issuers) take the even and the odd k-blocks; with an even number of stages a stage is always
+// refilled by the producer that filled it before, which has seen that stage's previous phase
+// complete, so it can never wait on a barrier that is two phases behind (a parity wait cannot tell
+// those apart).  An earlier 32-column variant had five stages; that flaw was found by reading.
 //
 // Every mbarrier wait is bounded; on a timeout the thread raises an error flag (read with
 // mll_take_device_error) and leaves its loop, the block still reaches its barriers, frees its TMEM and exits.
@@ -37,7 +46,7 @@ __device__ int mll_tc5_error_flag = 0;
 
 namespace mll {
 
-enum : int { CEPI_BF16 = 0, CEPI_F32 = 1, CEPI_SWIGLU = 2 };
+enum : int { CEPI_BF16 = 0, CEPI_F32 = 1, CEPI_SWIGLU = 2, CEPI_RESID = 3 };
 constexpr int C_ROWS = 128;     // weight rows per block (the MMA's M)
 constexpr int C_KB = 64;        // k elements per stage: one 128-byte swizzle span
 constexpr int C_THREADS = 256;  // 4 epilogue warps, then producer A, MMA A, producer B, MMA B (even / odd k-blocks)
@@ -48,6 +57,10 @@ struct Tc5Args {
   void* out;
   int M, N, K, epilogue, blocks_per_rank;
   RowNormIn in;  // x still lacks its norm's factor (sumsq null: it does not)
+  float* resid;         // CEPI_RESID: float32 residual [M, N], updated in place
+  const float* next_w;  // CEPI_RESID: weight [N] of the norm that follows
+  float* out_sumsq;     // CEPI_RESID: [M, out_stride], entry [m][j] = sum of resid[m]^2 over columns 16 j .. 16 j + 15
+  int out_stride;
 };
 
 __device__ __forceinline__ unsigned c_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -113,7 +126,7 @@ struct Tc5Smem {
   static constexpr int W_BYTES = C_ROWS * C_KB * 2;  // 16384
   static constexpr int X_BYTES = NB * C_KB * 2;      // 2048 .. 8192
   static constexpr int STAGE = W_BYTES + X_BYTES;    // a multiple of 1024
-  static constexpr int STAGES = NB <= 16 ? 6 : (NB <= 32 ? 5 : 4);  // about 100 KB of ring: two blocks per multiprocessor
+  static constexpr int STAGES = NB <= 16 ? 6 : 4;  // even (see the header); 80 to 108 KB of ring: two blocks per multiprocessor
   static constexpr int RED_FLOATS = C_ROWS * NB;
   static constexpr int TMEM_COLS = 2 * NB < 32 ? 32 : 2 * NB;  // one accumulator per MMA issuer
   // the float32 tile that the epilogue works on reuses the ring once the last MMA is done
@@ -127,7 +140,7 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
   using L = Tc5Smem<NB>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  float* red = reinterpret_cast<float*>(base);  // [128][NB], over the ring: written only after the last MMA
+  float* red = reinterpret_cast<float*>(base);  // [NB][128], over the ring: written only after the last MMA
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(base + L::RING);  // full[S], empty[S], done
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * L::STAGES + 1);
   float* row_factor = reinterpret_cast<float*>(base + L::RING + 128);  // [NB]
@@ -141,6 +154,8 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
   }
   const int tile = blockIdx.x / ranks;
   const int n0 = tile * C_ROWS;
+  // the batch rows whose sums and epilogue this block owns
+  const int m_begin = rank * (NB / ranks), m_end = min(a.M, m_begin + NB / ranks);
   const int k_blocks = (a.K + C_KB - 1) / C_KB;
   const int first = rank * a.blocks_per_rank;
   const int count = max(0, min(k_blocks, first + a.blocks_per_rank) - first);
@@ -211,9 +226,9 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
 
   // epilogue warps: accumulator row (weight row) = TMEM lane, one row per thread
   if (warp < 4) {
-    if (a.in.sumsq && rank == 0) {  // while the products run: the rows' norm factors, for the epilogue
-      for (int m = warp; m < a.M; m += 8) {  // rows m and m + 4, their loads in flight together
-        const bool second = m + 4 < a.M;
+    if (a.in.sumsq) {  // while the products run: the norm factors of this block's rows, for the epilogue
+      for (int m = m_begin + warp; m < m_end; m += 8) {  // rows m and m + 4, their loads in flight together
+        const bool second = m + 4 < m_end;
         float f0, f1;
         row_norm_factors2(a.in.sumsq + (size_t)m * a.in.stride, a.in.sumsq + (size_t)(m + 4) * a.in.stride, second,
                           a.in.partials, a.K, a.in.eps, lane, f0, f1);
@@ -225,7 +240,7 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
     }
     const bool ok = c_mbar_wait(done_bar, 0);
     tc_fence_after();
-    float* row = red + (warp * 32 + lane) * NB;
+    float* row = red + warp * 32 + lane;  // this weight row's column of the [NB][128] tile
     if (ok && count > 0) {
 #pragma unroll
       for (int c = 0; c < NB; c += 16) {
@@ -242,11 +257,12 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
             : "r"(tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)(NB + c)));
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int j = 0; j < 16; ++j) row[c + j] = __uint_as_float(v[j]) + (count > 1 ? __uint_as_float(w[j]) : 0.f);
+        for (int j = 0; j < 16; ++j)
+          row[(c + j) * C_ROWS] = __uint_as_float(v[j]) + (count > 1 ? __uint_as_float(w[j]) : 0.f);
       }
     } else {
 #pragma unroll
-      for (int c = 0; c < NB; ++c) row[c] = 0.f;  // no k-block for this rank (or a timeout)
+      for (int c = 0; c < NB; ++c) row[c * C_ROWS] = 0.f;  // no k-block for this rank (or a timeout)
     }
   }
   tc_fence_before();
@@ -258,37 +274,58 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
   }
   if (CLUSTER) {
     cg::cluster_group cluster = cg::this_cluster();
-    cluster.sync();
-    if (rank == 0) {
-      for (int i = tid; i < L::RED_FLOATS; i += C_THREADS) {
-        float s = red[i];
-        for (int r = 1; r < ranks; ++r) s += *cluster.map_shared_rank(red + i, r);
-        red[i] = s;
-      }
+    cluster.sync();  // every block's partial tile is complete and visible
+    for (int i = m_begin * C_ROWS + tid; i < m_end * C_ROWS; i += C_THREADS) {
+      float part[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) part[r] = r < ranks ? *cluster.map_shared_rank(red + i, r) : 0.f;  // loads in flight together
+      float sum = part[0];
+#pragma unroll
+      for (int r = 1; r < 8; ++r) sum += part[r];  // rank order: the same result on every run
+      red[i] = sum;  // the peers read other batch rows of this block's tile, never these
     }
-    cluster.sync();
-    if (rank != 0) return;
     __syncthreads();
   }
 
-  // red[row][m] is y[m][n0 + row]
+  // red[m][row] is y[m][n0 + row]; neighbouring threads take neighbouring weight rows
+  const int span = max(0, m_end - m_begin);
   if (a.epilogue == CEPI_SWIGLU) {
     __nv_bfloat16* out = (__nv_bfloat16*)a.out;
     const int half = a.N >> 1;
-    for (int i = tid; i < (C_ROWS / 2) * NB; i += C_THREADS) {
-      const int m = i / (C_ROWS / 2), j = i % (C_ROWS / 2);
+    for (int i = tid; i < span * (C_ROWS / 2); i += C_THREADS) {
+      const int m = m_begin + i / (C_ROWS / 2), j = i % (C_ROWS / 2);
       const int row = (j >> 3) * 16 + (j & 7);  // gate row; its up row is 8 further
-      if (m < a.M && n0 + row + 8 < a.N) {
+      if (n0 + row + 8 < a.N) {
         const float f = a.in.sumsq ? row_factor[m] : 1.f;
-        const float gate = red[row * NB + m] * f, up = red[(row + 8) * NB + m] * f;
+        const float gate = red[m * C_ROWS + row] * f, up = red[m * C_ROWS + row + 8] * f;
         out[(size_t)m * half + (n0 >> 1) + j] = __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
       }
     }
+  } else if (a.epilogue == CEPI_RESID) {
+    // whole warps run the loop (its bound is a multiple of 32): 16 consecutive lanes hold 16 consecutive columns
+    __nv_bfloat16* out = (__nv_bfloat16*)a.out;
+    for (int i = tid; i < span * C_ROWS; i += C_THREADS) {
+      const int m = m_begin + i / C_ROWS, row = i % C_ROWS;
+      float now = 0.f;
+      if (n0 + row < a.N) {
+        float v = red[m * C_ROWS + row];
+        if (a.in.sumsq) v *= row_factor[m];
+        if (a.bias) v += a.bias[n0 + row];
+        const size_t at = (size_t)m * a.N + n0 + row;
+        now = a.resid[at] + v;
+        a.resid[at] = now;
+        out[at] = __float2bfloat16_rn(now * a.next_w[n0 + row]);
+      }
+      float sq = now * now;
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      if ((row & 15) == 0 && n0 + row < a.N) a.out_sumsq[(size_t)m * a.out_stride + ((n0 + row) >> 4)] = sq;
+    }
   } else {
-    for (int i = tid; i < C_ROWS * NB; i += C_THREADS) {
-      const int m = i / C_ROWS, row = i % C_ROWS;
-      if (m < a.M && n0 + row < a.N) {
-        float v = red[row * NB + m];
+    for (int i = tid; i < span * C_ROWS; i += C_THREADS) {
+      const int m = m_begin + i / C_ROWS, row = i % C_ROWS;
+      if (n0 + row < a.N) {
+        float v = red[m * C_ROWS + row];
         if (a.in.sumsq) v *= row_factor[m];
         if (a.bias) v += a.bias[n0 + row];
         if (a.epilogue == CEPI_F32)
@@ -298,6 +335,7 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constan
       }
     }
   }
+  if (CLUSTER) cg::this_cluster().sync();  // the peers have read this block's tile: its shared memory may go
   if (*(volatile int*)&mll_tc5_error_flag) {
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
   }
@@ -354,27 +392,29 @@ extern "C" int* mll_linear_tc5_error_address() {
   return address;
 }
 
-// At most 16 rows.  The kernel is written for 16, 32 or 64 batch columns, but one shape with 32
-// rows (6144 x 4096, clusters of 4) ended in "unspecified launch failure" and reading has not
-// shown why, while the same code passes its tests at 17, 33 and 64 rows on other shapes; until
-// the cause is known only the 16-column variant, which every decode step of the engine runs, is
-// offered.
+// Up to 64 rows: 16, 32 or 64 batch columns per MMA, chosen by the row count.
 MLL_API int mll_linear_tc5_supported(int M, int N, int K, int epilogue) {
-  if (M < 1 || M > 16 || N < 1 || K < 8 || K % 8 != 0) return 0;
+  if (M < 1 || M > 64 || N < 1 || K < 8 || K % 8 != 0) return 0;
   if (epilogue == mll::CEPI_SWIGLU && N % 16 != 0) return 0;
   return 1;
 }
 
-// Same contract as mll_linear_tma_fused.  ranks: cluster size along K (1, 2, 4 or 8), 0 = choose.
+// Same contract as mll_linear_small_fused (epilogue 3, the residual epilogue, included, here for up to 64
+// rows).  ranks: cluster size along K (1, 2, 4 or 8), 0 = choose.
 MLL_API int mll_linear_tc5_fused(const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
                                  int epilogue, int ranks, const float* in_sumsq, int in_partials, int in_stride,
-                                 float in_eps, cudaStream_t stream) {
+                                 float in_eps, float* resid, const float* next_w, float* out_sumsq, int out_stride,
+                                 cudaStream_t stream) {
   MLL_REQUIRE(!in_sumsq || (in_partials >= 1 && in_stride >= in_partials && in_eps >= 0.f),
               "linear_tc5: partial sums: %d of stride %d", in_partials, in_stride);
-  MLL_REQUIRE(mll_linear_tc5_supported(M, N, K, epilogue), "linear_tc5: unsupported sizes M=%d N=%d K=%d", M, N, K);
-  MLL_REQUIRE(epilogue >= 0 && epilogue <= 2, "linear_tc5: unknown epilogue %d", epilogue);
+  MLL_REQUIRE(epilogue >= 0 && epilogue <= 3, "linear_tc5: unknown epilogue %d", epilogue);
+  MLL_REQUIRE(mll_linear_tc5_supported(M, N, K, epilogue == mll::CEPI_RESID ? 0 : epilogue),
+              "linear_tc5: unsupported sizes M=%d N=%d K=%d", M, N, K);
   MLL_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "linear_tc5: operands must be 16-byte aligned");
   MLL_REQUIRE(epilogue != mll::CEPI_SWIGLU || bias == nullptr, "linear_tc5: the SwiGLU epilogue takes no bias");
+  if (epilogue == mll::CEPI_RESID)
+    MLL_REQUIRE(resid && next_w && out_sumsq && out_stride >= (N + 15) / 16,
+                "linear_tc5: the residual epilogue needs resid, next_w and out_sumsq with stride >= %d", (N + 15) / 16);
   const int tiles = (N + mll::C_ROWS - 1) / mll::C_ROWS;
   const int k_blocks = (K + mll::C_KB - 1) / mll::C_KB;
   if (ranks <= 0) {
@@ -385,16 +425,20 @@ MLL_API int mll_linear_tc5_fused(const void* x, const void* w, const float* bias
     while (ranks < 8 && tiles * ranks * 2 <= resident && k_blocks / (ranks * 2) >= 8) ranks *= 2;
   }
   MLL_REQUIRE(ranks == 1 || ranks == 2 || ranks == 4 || ranks == 8, "linear_tc5: cluster size %d", ranks);
-  const int nb = 16;
+  const int nb = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   CUtensorMap wmap, xmap;
   if (mll::tensor_map_bf16(w, N, K, mll::C_ROWS, &wmap) != 0) return -1;
   if (mll::tensor_map_bf16(x, M, K, nb, &xmap) != 0) return -1;
   mll::Tc5Args a{bias, out, M, N, K, epilogue, (k_blocks + ranks - 1) / ranks,
-                 mll::RowNormIn{in_sumsq, in_partials, in_stride, in_eps}};
-  return mll::launch_linear_tc5<16>(wmap, xmap, a, tiles, ranks, stream);
+                 mll::RowNormIn{in_sumsq, in_partials, in_stride, in_eps}, resid, next_w, out_sumsq, out_stride};
+  if (nb == 16) return mll::launch_linear_tc5<16>(wmap, xmap, a, tiles, ranks, stream);
+  if (nb == 32) return mll::launch_linear_tc5<32>(wmap, xmap, a, tiles, ranks, stream);
+  return mll::launch_linear_tc5<64>(wmap, xmap, a, tiles, ranks, stream);
 }
 
 MLL_API int mll_linear_tc5(const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
                            int epilogue, int ranks, cudaStream_t stream) {
-  return mll_linear_tc5_fused(x, w, bias, out, M, N, K, epilogue, ranks, nullptr, 0, 0, 0.f, stream);
+  MLL_REQUIRE(epilogue != mll::CEPI_RESID, "linear_tc5: the residual epilogue needs mll_linear_tc5_fused");
+  return mll_linear_tc5_fused(x, w, bias, out, M, N, K, epilogue, ranks, nullptr, 0, 0, 0.f, nullptr, nullptr, nullptr, 0,
+                              stream);
 }

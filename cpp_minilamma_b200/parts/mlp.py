@@ -73,6 +73,13 @@ class SwiGLUFeedForward(FeedForward):
             # few rows: one weight-streaming kernel whose epilogue applies the activation
             act = step.ws.buffer("act", (rows, self.inter), torch.bfloat16)
             K.small_linear(values, w, None, act, K.EPI_SWIGLU, row_norm)
+        elif (row_norm is not None and w.dtype == torch.bfloat16 and self.inter % 8 == 0
+              and not K.small_linear_kind(rows, 2 * self.inter, w.shape[1], K.EPI_BF16)):
+            # the library product cannot finish the norm in front of it: it runs on the rows as they are and
+            # the activation kernel multiplies gate and up by the rows' factors
+            gu = self.gate_up.forward(step, values, "gu")
+            act = step.ws.buffer("act", (rows, self.inter), torch.bfloat16)
+            K.swiglu(gu, act, self.block, row_norm, w.shape[1])
         else:
             gu = self.gate_up.forward(step, h, "gu")
             act = step.ws.buffer("act", (rows, self.inter), gu.dtype)

@@ -636,11 +636,12 @@ def test_linear_tma_refuses():
                      torch.zeros((2, 16), dtype=torch.bfloat16, device=DEV))
 
 
-@pytest.mark.parametrize("rows", [1, 3, 8, 13, 16])
+@pytest.mark.parametrize("rows", [1, 3, 8, 13, 16, 17, 32, 33, 50, 64])
 @pytest.mark.parametrize("n,k,ranks", [(16, 32, 1), (40, 64, 2), (4104, 4096, 0), (512, 14336, 8), (128, 4096, 4),
-                                        (100, 224, 1), (7, 8, 1), (257, 200, 2), (1000, 1096, 0), (6144, 4096, 0)])
+                                        (100, 224, 1), (7, 8, 1), (257, 200, 2), (1000, 1096, 0), (6144, 4096, 0),
+                                        (6144, 4096, 4), (3072, 2048, 8)])
 def test_linear_tc5(rows, n, k, ranks):
-    # the tcgen05 / TMEM kernel: same contract as the TMA kernel
+    # the tcgen05 / TMEM kernel: same contract as the TMA kernel, 16, 32 or 64 batch columns by the row count
     x = rnd((rows, k), torch.bfloat16, 50)
     w = rnd((n, k), torch.bfloat16, 51, 0.05)
     bias = rnd((n,), torch.float32, 52)
@@ -660,7 +661,7 @@ def test_linear_tc5(rows, n, k, ranks):
     assert K.take_device_error() == 0
 
 
-@pytest.mark.parametrize("rows", [1, 8, 13, 16])
+@pytest.mark.parametrize("rows", [1, 8, 13, 16, 17, 32, 40, 64])
 @pytest.mark.parametrize("inter,k,ranks", [(176, 64, 1), (1000, 4096, 0), (64, 14336, 8), (40, 72, 1)])
 def test_linear_tc5_swiglu(rows, inter, k, ranks):
     gate = rnd((inter, k), torch.bfloat16, 53, 0.05)
@@ -691,7 +692,7 @@ def _prenormed(rows, k, seed, eps):
     return stream, weight, values, K.RowNorm(sumsq.to(DEV), partials, eps), factor
 
 
-@pytest.mark.parametrize("rows", [1, 3, 8, 13, 16])
+@pytest.mark.parametrize("rows", [1, 3, 8, 13, 16, 17, 40, 64])
 @pytest.mark.parametrize("n,k", [(48, 64), (4104, 4096), (100, 224), (6144, 4096), (512, 8192)])
 @pytest.mark.parametrize("kind", ["direct", "tma", "tc5"])
 def test_linear_finishes_the_norm_before_it(rows, n, k, kind):
@@ -701,6 +702,8 @@ def test_linear_finishes_the_norm_before_it(rows, n, k, kind):
     w = rnd((n, k), torch.bfloat16, 62, 0.05)
     bias = rnd((n,), torch.float32, 63)
     run = {"direct": K.linear_small, "tma": K.linear_tma, "tc5": K.linear_tc5}[kind]
+    if kind == "direct" and not K.linear_small_supported(rows, n, k):
+        pytest.skip("the direct kernel does not take this shape")
     want = (as64(values) * factor) @ as64(w).T
     against_norm = pl.rms_norm(as64(stream), as64(weight), eps) @ as64(w).T
     np.testing.assert_allclose(want, against_norm, rtol=0, atol=8e-3 * np.abs(against_norm).max())
@@ -730,10 +733,15 @@ def test_linear_swiglu_finishes_the_norm_before_it(rows, kind):
     assert K.take_device_error() == 0
 
 
-@pytest.mark.parametrize("rows", [1, 3, 8, 13, 16])
-@pytest.mark.parametrize("n,k,ranks", [(48, 64, 1), (4096, 4096, 0), (100, 224, 1), (4096, 14336, 0), (520, 4096, 4)])
+@pytest.mark.parametrize("rows", [1, 3, 8, 13, 16, 17, 31, 32, 33, 64])
+@pytest.mark.parametrize("n,k,ranks", [(48, 64, 1), (4096, 4096, 0), (100, 224, 1), (4096, 14336, 0), (520, 4096, 4),
+                                        (2048, 8192, 8)])
 @pytest.mark.parametrize("normed_input", [False, True])
-def test_linear_small_adds_to_the_residual_and_starts_the_next_norm(rows, n, k, ranks, normed_input):
+@pytest.mark.parametrize("kind", ["direct", "tc5"])
+def test_linear_adds_to_the_residual_and_starts_the_next_norm(rows, n, k, ranks, normed_input, kind):
+    if kind == "direct" and rows > 16:
+        pytest.skip("the direct kernel's residual epilogue takes at most 16 rows")
+    run = {"direct": K.linear_small, "tc5": K.linear_tc5}[kind]
     eps = 1e-5
     if normed_input:
         _, _, x, row_norm, factor = _prenormed(rows, k, 70, eps)
@@ -747,8 +755,7 @@ def test_linear_small_adds_to_the_residual_and_starts_the_next_norm(rows, n, k, 
     resid_dev = resid.to(DEV)
     values = torch.full((rows, n), float("nan"), dtype=torch.bfloat16, device=DEV)
     sumsq = torch.full((rows, stride), float("nan"), dtype=torch.float32, device=DEV)
-    K.linear_small(x.to(DEV), w.to(DEV), None, values, K.EPI_RESID, ranks, row_norm,
-                   K.ResidualOut(resid_dev, next_w.to(DEV), sumsq))
+    run(x.to(DEV), w.to(DEV), None, values, K.EPI_RESID, ranks, row_norm, K.ResidualOut(resid_dev, next_w.to(DEV), sumsq))
     want = as64(resid) + (as64(x) * factor) @ as64(w).T
     np.testing.assert_allclose(as64(resid_dev), want, rtol=2e-5, atol=2e-5 * np.abs(want).max())
     np.testing.assert_allclose(as64(values), want * as64(next_w), rtol=8e-3, atol=1e-3)
@@ -762,6 +769,24 @@ def test_linear_small_adds_to_the_residual_and_starts_the_next_norm(rows, n, k, 
     factor_out = 1.0 / np.sqrt(as64(sumsq)[:, :tiles].sum(-1, keepdims=True) / n + eps)
     normed = pl.rms_norm(got, as64(next_w), eps)
     np.testing.assert_allclose(as64(values) * factor_out, normed, rtol=8e-3, atol=1e-3)
+    assert K.take_device_error() == 0
+
+
+@pytest.mark.parametrize("rows,inter,k,block", [(1, 176, 64, 8), (17, 14336, 4096, 8), (64, 8192, 2048, 8), (40, 200, 96, 0)])
+def test_swiglu_finishes_the_norm_before_the_product(rows, inter, k, block):
+    # gate/up computed by a product that could not apply the rows' norm factors: the activation kernel does
+    eps = 1e-5
+    _, _, values, row_norm, factor = _prenormed(rows, k, 90, eps)
+    gate = rnd((rows, inter), torch.bfloat16, 91, 2.0)   # stands for (x w_norm) . Wgate^T, not yet scaled
+    up = rnd((rows, inter), torch.bfloat16, 92, 2.0)
+    if block:
+        gu = torch.stack([gate.view(rows, inter // 8, 8), up.view(rows, inter // 8, 8)], dim=2).reshape(rows, 2 * inter)
+    else:
+        gu = torch.cat([gate, up], dim=1)
+    out = torch.full((rows, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    K.swiglu(gu.contiguous().to(DEV), out, block, row_norm, k)
+    want = pl.swiglu(as64(gate) * factor, as64(up) * factor)
+    np.testing.assert_allclose(as64(out), want, rtol=1e-2, atol=1e-2 * np.abs(want).max())
 
 
 def test_apply_row_norm():
