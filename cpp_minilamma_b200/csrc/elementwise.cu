@@ -58,6 +58,22 @@ __global__ void embedding_kernel(const int* __restrict__ tokens, const TableT* _
   for (int i = threadIdx.x; i < width; i += blockDim.x) out[i] = to_float(row[i]);
 }
 
+// the same for a bfloat16 table whose rows are multiples of 8 elements: 16-byte loads, one per thread and pass
+__global__ void embedding_bf16_vec8_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ table,
+                                           float* __restrict__ x, int width) {
+  const int t = blockIdx.x;
+  const uint4* row = reinterpret_cast<const uint4*>(table + (size_t)tokens[t] * width);
+  float4* out = reinterpret_cast<float4*>(x + (size_t)t * width);
+  for (int i = threadIdx.x; i < (width >> 3); i += blockDim.x) {
+    const uint4 raw = row[i];
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+    const float2 c = __bfloat1622float2(h[2]), d = __bfloat1622float2(h[3]);
+    out[2 * i] = make_float4(a.x, a.y, b.x, b.y);
+    out[2 * i + 1] = make_float4(c.x, c.y, d.x, d.y);
+  }
+}
+
 template <typename In, typename Out>
 __global__ void cast_kernel(const In* __restrict__ in, Out* __restrict__ out, size_t n) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -236,6 +252,9 @@ MLL_API int mll_embedding(const int* tokens, const void* table, int table_dtype,
   const int threads = width >= 1024 ? 256 : 128;
   if (table_dtype == MLL_F32)
     MLL_LAUNCH((mll::embedding_kernel<float>), n_tokens, threads, 0, stream, tokens, (const float*)table, x, width);
+  else if (table_dtype == MLL_BF16 && width % 8 == 0 && ((uintptr_t)table % 16 == 0) && ((uintptr_t)x % 16 == 0))
+    MLL_LAUNCH((mll::embedding_bf16_vec8_kernel), n_tokens, width >= 2048 ? 256 : 64, 0, stream, tokens,
+               (const __nv_bfloat16*)table, x, width);
   else if (table_dtype == MLL_BF16)
     MLL_LAUNCH((mll::embedding_kernel<__nv_bfloat16>), n_tokens, threads, 0, stream, tokens, (const __nv_bfloat16*)table, x, width);
   else

@@ -306,7 +306,6 @@ TMA_MAX_ROWS = 8      # rows up to which tall matrices go to the TMA + mma.sync 
 TC5_TALL_MAX_ROWS = 16  # rows up to which tall matrices go to the tcgen05 kernel (beyond: the library, which shares the
                         # batch tile between the blocks of a cluster)
 DIRECT_MAX_ROWS = 16  # rows up to which the other matrices go to the direct kernel
-MID_MAX_ROWS = 64     # rows up to which the other matrices go to the tcgen05 kernel (32 or 64 batch columns per MMA)
 TALL = 16384          # output features from which a matrix counts as tall
 
 
@@ -316,10 +315,13 @@ def small_linear_kind(rows: int, out_features: int, in_features: int, epilogue: 
     Measured on B200 (CUDA-graph timing) on the shapes of the 8B, 7B and 1B Llama models.  Tall matrices
     (gate/up, lm_head), where a deep queue of TMA loads counts: up to 8 rows the kernel with mma.sync
     consumers (gate/up + SwiGLU 40.6 us, tcgen05 43.3), from 9 to 16 rows the tcgen05 kernel (43.6 us, the
-    other 53.5 with its second batch tile), beyond that the library GEMM.  The other projections, where a
-    launch is short and a fine split over the machine counts: the direct kernel up to 16 rows (it chooses
-    its variant by rows and tiles), the tcgen05 kernel with 32 or 64 batch columns from 17 to 64 rows
-    (split over K in clusters; the library's kernels for these shapes stream at 1.1 to 2.7 TB/s)."""
+    other 53.5 with its second batch tile).  The other projections, where a launch is short and a fine
+    split over the machine counts: the direct kernel up to 16 rows (it chooses its variant by rows and
+    tiles).  From 17 rows on the library GEMM: the tcgen05 kernel takes up to 64 rows (32 or 64 batch
+    columns per MMA), but inside a CUDA graph the library's kernels are ahead on every shape tried
+    (64 rows, us, library / tcgen05: 8B q/k/v 11.8 / 16.2, o 9.9 / 13.1, down 24.9 / 26.5, gate/up 42.8 /
+    46.9; 1B q/k/v 5.9 / 9.6, o 5.7 / 9.1, down 13.2 / 14.5, gate/up 13.2 / 19.1), and in a batch-64 step
+    the three small products took 60.6 us a layer on it against 46.6 + two norm kernels on the library."""
     if SMALL_LINEAR == "none":
         return ""
     if SMALL_LINEAR != "auto":  # a forced kind (tests, experiments)
@@ -330,15 +332,11 @@ def small_linear_kind(rows: int, out_features: int, in_features: int, epilogue: 
             return "tma"
         if rows <= TC5_TALL_MAX_ROWS and linear_tc5_supported(rows, out_features, in_features, epilogue):
             return "tc5"
-        if rows > DIRECT_MAX_ROWS:
-            return ""
     if rows <= DIRECT_MAX_ROWS:
         if linear_small_supported(rows, out_features, in_features, epilogue):
             return "direct"
         if linear_tma_supported(rows, out_features, in_features, epilogue):
             return "tma"
-    if rows <= MID_MAX_ROWS and linear_tc5_supported(rows, out_features, in_features, epilogue):
-        return "tc5"
     return ""
 
 
@@ -361,7 +359,7 @@ def small_linear(x, w, bias, out, epilogue: int = EPI_BF16, row_norm: Optional[R
 def fused_norm_rows(rows: int) -> bool:
     """Whether products over `rows` rows may fold the norms around them in (the residual epilogue
     exists in the kernels that take decode steps' row counts)."""
-    return FUSE_NORM and 1 <= rows <= MID_MAX_ROWS
+    return FUSE_NORM and 1 <= rows <= (64 if SMALL_LINEAR == "tc5" else DIRECT_MAX_ROWS)
 
 
 FUSE_NORM = True  # off: every norm is a kernel of its own

@@ -41,10 +41,11 @@ def as64(t):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_embedding(dtype):
-    table = rnd((1000, 100), dtype, 1)
+@pytest.mark.parametrize("width", [100, 104, 4096])  # 104, 4096: the bfloat16 table's rows are read in 16-byte words
+def test_embedding(dtype, width):
+    table = rnd((1000, width), dtype, 1)
     tokens = torch.tensor([0, 999, 5, 5, 731], dtype=torch.int32)
-    out = torch.empty((5, 100), dtype=torch.float32, device=DEV)
+    out = torch.empty((5, width), dtype=torch.float32, device=DEV)
     K.embedding(tokens.to(DEV), table.to(DEV), out)
     np.testing.assert_array_equal(out.cpu().numpy(), pl.embedding(as64(table), tokens.numpy()).astype(np.float32))
 
@@ -452,18 +453,19 @@ def test_rope_cache_write(dtype, interleaved, hq, hk, d):
 
 
 # ------------------------------------------------------------------------------------ #
-def test_argmax_first_of_ties_and_status():
-    logits = rnd((6, 50257), torch.float32, 18)
-    logits[0, 100] = logits[0, 40000] = 9.0          # tie: the lower id wins (src/sampler.cc:31-41)
+@pytest.mark.parametrize("vocab", [1000, 50257, 128256])  # one block per row; a cluster per row, scalar and 16-byte loads
+def test_argmax_first_of_ties_and_status(vocab):
+    logits = rnd((6, vocab), torch.float32, 18)
+    logits[0, 100] = logits[0, vocab - 300] = 9.0    # tie, far apart: the lower id wins (src/sampler.cc:31-41)
     logits[1] = 0.0                                   # all equal: id 0
-    logits[2, 50256] = 12.0
+    logits[2, vocab - 1] = 12.0
     logits[3, 7] = float("nan")
     logits[4, 0] = 20.0
     tokens = torch.empty(6, dtype=torch.int32, device=DEV)
     status = torch.empty(6, dtype=torch.int32, device=DEV)
     K.argmax(logits.to(DEV), tokens, status)
     got = tokens.cpu().tolist()
-    assert got[0] == 100 and got[1] == 0 and got[2] == 50256 and got[4] == 0
+    assert got[0] == 100 and got[1] == 0 and got[2] == vocab - 1 and got[4] == 0
     assert got[5] == pl.greedy(logits[5].numpy())
     assert status.cpu().tolist() == [0, 0, 0, 1, 0, 0]
 

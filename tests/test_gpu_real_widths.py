@@ -192,6 +192,29 @@ def test_unequal_batches_with_decode_steps_of_1_to_40_rows(real, dtype):
     assert K.take_device_error() == 0
 
 
+def test_unequal_batches_with_every_product_on_the_tcgen05_kernel(real, monkeypatch):
+    """The engine sends decode steps of more than 16 rows to the library product (it is ahead there).  Forced
+    onto the tcgen05 kernel, the same steps run its 32- and 64-column variants, the residual epilogue at
+    17 and 40 rows and the norms folded in at every row count - inside a model, against the same oracle."""
+    folder, oracle = real
+    requests, _ = batched_requests()
+    monkeypatch.setattr(K, "SMALL_LINEAR", "tc5")
+    llm = load(folder, "bfloat16", max_seqs=40)
+    K.calls.clear()
+    norm_calls = []
+    real_norm = K.add_rmsnorm
+    monkeypatch.setattr(K, "add_rmsnorm", lambda *a, **kw: (norm_calls.append(a[3].shape[0]), real_norm(*a, **kw))[1])
+    got, decode_rows = replay_in_batches(llm, requests[:40], PROMPTS[:40], batch_size=40)
+    assert {40, 17, 16, 9, 8, 1} <= set(decode_rows), decode_rows
+    for i, tokens in enumerate(requests[:40]):
+        assert_close(got[i], oracle.logits(tokens, "bfloat16"), "bfloat16", f"real widths, tcgen05 forced, request {i}")
+    # decode steps (every norm call of 40 or fewer rows): only the first layer's input norm and the final norm are kernels
+    decode_norms = [rows for rows in norm_calls if rows <= 40]
+    assert len(decode_norms) == 2 * len(decode_rows), (len(decode_norms), len(decode_rows))
+    assert K.calls.get("linear_tc5", 0) >= len(decode_rows) * (4 * LAYERS + 1)
+    assert K.take_device_error() == 0
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_generation_under_graphs_with_run_ahead(real, dtype):
     """The same requests through the generation loop: decode steps replay captured graphs one step ahead
