@@ -20,8 +20,12 @@
 // O / l does not depend on the scale, so the result is exact all the same.  Two blocks fit a
 // multiprocessor (80 KB of shared memory, 256 columns of tensor memory each): one block's MMAs run
 // under the other's softmax.  Rows of the last page beyond the context are zeroed in shared memory
-// (P is zero there, but the cache may hold anything).  Tiles come as a list of 64-row entries; the
-// block of an entry that starts the second half of a 128-row tile returns at once.
+// (P is zero there, but the cache may hold anything).  Tiles come as a list of (sequence, first row)
+// entries, walked from the back (the caller puts the tiles that read the most keys last); an entry
+// whose first row is no multiple of 128 (a list made for 64-row tiles) makes its block return at
+// once - at a price: launched only to return, such blocks took the place of working ones for
+// microseconds each, 72 instead of 47 us for a 2,048-token prompt, so the caller passes a list of
+// 128-row tiles.
 //
 // Every mbarrier wait is bounded; a wait that runs out raises an error flag (read through
 // mll_take_device_error), makes the block's later waits return at once, the block stores nothing,
@@ -48,7 +52,7 @@ struct PrefillTc5Args {
   const int* seq_ctx;
   const int* seq_qstart;
   const int* seq_qlen;
-  const int* tile_seq;   // tiles of 64 rows; this kernel works on those that start a multiple of 128
+  const int* tile_seq;   // tiles of 128 rows (entries that do not start a multiple of 128 are skipped)
   const int* tile_row0;
   const int* block_table;
   __nv_bfloat16* out;    // [T, Hq * d]
@@ -140,6 +144,78 @@ __device__ __forceinline__ float a_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// 64 consecutive float32 columns of this thread's lane with one wait: both loads are in flight together
+__device__ __forceinline__ void a_tmem_ld64(unsigned addr, float* v) {
+  unsigned r[64];
+#pragma unroll
+  for (int half = 0; half < 2; ++half)
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[32 * half + 0]), "=r"(r[32 * half + 1]), "=r"(r[32 * half + 2]), "=r"(r[32 * half + 3]),
+          "=r"(r[32 * half + 4]), "=r"(r[32 * half + 5]), "=r"(r[32 * half + 6]), "=r"(r[32 * half + 7]),
+          "=r"(r[32 * half + 8]), "=r"(r[32 * half + 9]), "=r"(r[32 * half + 10]), "=r"(r[32 * half + 11]),
+          "=r"(r[32 * half + 12]), "=r"(r[32 * half + 13]), "=r"(r[32 * half + 14]), "=r"(r[32 * half + 15]),
+          "=r"(r[32 * half + 16]), "=r"(r[32 * half + 17]), "=r"(r[32 * half + 18]), "=r"(r[32 * half + 19]),
+          "=r"(r[32 * half + 20]), "=r"(r[32 * half + 21]), "=r"(r[32 * half + 22]), "=r"(r[32 * half + 23]),
+          "=r"(r[32 * half + 24]), "=r"(r[32 * half + 25]), "=r"(r[32 * half + 26]), "=r"(r[32 * half + 27]),
+          "=r"(r[32 * half + 28]), "=r"(r[32 * half + 29]), "=r"(r[32 * half + 30]), "=r"(r[32 * half + 31])
+        : "r"(addr + 32 * half));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
+// Two float32 values in one 64-bit register and the arithmetic that works on both at once (sm_100): the
+// softmax is bound by the instructions it issues and by the special-function unit (16 exponentials per
+// clock and multiprocessor), not by the tensor cores.
+typedef unsigned long long a_f32x2;
+__device__ __forceinline__ a_f32x2 a_pack2(float lo, float hi) {
+  a_f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void a_unpack2(a_f32x2 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ a_f32x2 a_fma2(a_f32x2 a, a_f32x2 b, a_f32x2 c) {
+  a_f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ a_f32x2 a_add2(a_f32x2 a, a_f32x2 b) {
+  a_f32x2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float a_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// 2^x for both halves of x on the FMA pipe: x = n + f with n = round(x) (the magic-number add leaves n in the
+// low mantissa bits of t), 2^f on [-0.5, 0.5] by a cubic whose relative error is below 7.5e-5 (P is rounded to
+// 8 bits of mantissa afterwards, and the same values go into the row's sum), and n added to the exponent bits.
+// x is clamped at -126 (a masked score is -infinity; 2^-126 is nothing against a row's largest term, which is 1
+// or more).  Every other pair of exponentials goes this way, the rest to the special-function unit, so that
+// both run side by side.
+__device__ __forceinline__ void a_exp2_pair_fma(a_f32x2 x, float& p0, float& p1) {
+  float x0, x1;
+  a_unpack2(x, x0, x1);
+  x = a_pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const a_f32x2 magic = a_pack2(12582912.f, 12582912.f), minus_magic = a_pack2(-12582912.f, -12582912.f);
+  const a_f32x2 t = a_add2(x, magic);
+  const a_f32x2 n = a_add2(t, minus_magic);
+  const a_f32x2 f = a_fma2(n, a_pack2(-1.f, -1.f), x);
+  a_f32x2 p = a_fma2(f, a_pack2(0.055171654f, 0.055171654f), a_pack2(0.24261113f, 0.24261113f));
+  p = a_fma2(p, f, a_pack2(0.69326097f, 0.69326097f));
+  p = a_fma2(p, f, a_pack2(0.99992806f, 0.99992806f));
+  float t0, t1, q0, q1;
+  a_unpack2(t, t0, t1);
+  a_unpack2(p, q0, q1);
+  p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
+  p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
+}
 
 // 32 consecutive 32-bit columns of this thread's lane, written from registers
 __device__ __forceinline__ void a_tmem_st32(unsigned addr, const unsigned* r) {
@@ -169,7 +245,16 @@ __device__ __forceinline__ void a_mbar_arrive(unsigned bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-constexpr int A_THREADS = 192;       // warps 0-3: one query row per thread; warp 4: TMA loads; warp 5: MMAs
+// Warps 0-3: one query row per thread; warp 4: TMA loads; warp 5: MMAs; warps 6 and 7 only fill the second
+// warpgroup.  Eight warps put two warps of every block on each of the multiprocessor's four schedulers, so a
+// new block fits as soon as one of the two resident blocks leaves.  With six warps of 168 registers it did
+// not: the schedulers' register files held exactly three such warps each, a block put two warps on two of
+// the schedulers and one on the others, and the next block's warps mostly fell on the wrong ones - the freed
+// place stayed empty until the other block had ended as well (a 2,048-token prompt: 62 us, of which the
+// longest block ran 47).  The block is launched with 128 registers per thread; the softmax warpgroup then
+// takes 168 (setmaxnreg) and the other warpgroup gives back all but 40.
+constexpr int A_THREADS = 256;
+constexpr int A_SOFTMAX_REGS = 168, A_OTHER_REGS = 40;
 constexpr float A_RESCALE_STEP = 8.f;  // the output is rescaled only when a row's maximum grows by more than 2^8
 
 template <int D>
@@ -247,6 +332,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
   a_fence_after();
   const unsigned tmem_base = *tmem_slot;
 
+  if (warp >= 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(A_OTHER_REGS));
   if (warp == 4) {
     // ---- loads: the query tile once, then key and value pages into a two-stage ring -------- //
     if (lane == 0) {
@@ -313,8 +399,9 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
         a_commit(bar(AB_V_EMPTY, st));
       }
     }
-  } else {
+  } else if (warp < 4) {
     // ---- softmax: thread tid owns query row tid = lane tid of tensor memory ---------------- //
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(A_SOFTMAX_REGS));
     const unsigned tmem_row = tmem_base + ((unsigned)(warp * 32) << 16);
     const int qpos = pos0 + tid;
     float m_used = -INFINITY, l_run = 0.f;  // the maximum that P and O are scaled by; the sum
@@ -323,8 +410,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
       wait(bar(AB_S_FULL, st), (i >> 1) & 1);
       a_fence_after();
       float s[MLL_PAGE];
-      a_tmem_ld32(tmem_row + st * MLL_PAGE, s);
-      a_tmem_ld32(tmem_row + st * MLL_PAGE + 32, s + 32);
+      a_tmem_ld64(tmem_row + st * MLL_PAGE, s);
       const int k0 = (p_first + i) * MLL_PAGE;
       const bool needs_mask = (k0 + MLL_PAGE - 1 > pos0) || a.window > 0 || rows < A_ROWS;
       if (needs_mask) {
@@ -337,11 +423,11 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < MLL_PAGE; c += 4) {
-        mx4[0] = fmaxf(mx4[0], s[c]);
-        mx4[1] = fmaxf(mx4[1], s[c + 1]);
-        mx4[2] = fmaxf(mx4[2], s[c + 2]);
-        mx4[3] = fmaxf(mx4[3], s[c + 3]);
+      for (int c = 0; c < MLL_PAGE; c += 8) {  // three-input maxima: half the instructions
+        mx4[0] = a_max3(mx4[0], s[c], s[c + 1]);
+        mx4[1] = a_max3(mx4[1], s[c + 2], s[c + 3]);
+        mx4[2] = a_max3(mx4[2], s[c + 4], s[c + 5]);
+        mx4[3] = a_max3(mx4[3], s[c + 6], s[c + 7]);
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;
       // P and O stay scaled by m_used while the row's maximum is within 2^8 of it: exact all the
@@ -363,16 +449,33 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
       }
       if (moved) m_used = mx;
       const float shift = m_used > -INFINITY ? m_used : 0.f;  // a fully masked row stays at zero weight
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      // p = 2^(s * scale - shift), two columns per instruction; the pairs alternate between the special-function
+      // unit and the FMA pipe
+      const a_f32x2 scale2 = a_pack2(a.scale_log2, a.scale_log2), shift2 = a_pack2(-shift, -shift);
+      a_f32x2 sum2[2] = {a_pack2(0.f, 0.f), a_pack2(0.f, 0.f)};
       unsigned packed[MLL_PAGE / 2];
 #pragma unroll
       for (int c = 0; c < MLL_PAGE; c += 2) {
-        const float p0 = a_exp2(fmaf(s[c], a.scale_log2, -shift)), p1 = a_exp2(fmaf(s[c + 1], a.scale_log2, -shift));
-        sum4[(c >> 1) & 3] += p0 + p1;
+        const a_f32x2 x = a_fma2(a_pack2(s[c], s[c + 1]), scale2, shift2);
+        float p0, p1;
+        if ((c >> 1) & 1) {
+          a_exp2_pair_fma(x, p0, p1);
+        } else {
+          float x0, x1;
+          a_unpack2(x, x0, x1);
+          p0 = a_exp2(x0);
+          p1 = a_exp2(x1);
+        }
+        sum2[(c >> 2) & 1] = a_add2(sum2[(c >> 2) & 1], a_pack2(p0, p1));
         __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
         packed[c >> 1] = *reinterpret_cast<unsigned*>(&pair);
       }
-      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      {
+        float s0, s1, s2, s3;
+        a_unpack2(sum2[0], s0, s1);
+        a_unpack2(sum2[1], s2, s3);
+        l_run += (s0 + s1) + (s2 + s3);
+      }
       a_tmem_st32(tmem_row + st * MLL_PAGE, packed);  // P over the first half of S
       const int valid = ctx - k0;  // positions of this page that the sequence has
       if (valid < MLL_PAGE) {      // only the sequence's last page: the rest of it may hold anything

@@ -14,7 +14,7 @@ import torch
 from ..cache.paged import PAGE  # cache positions per page; the library's MLL_PAGE is checked against it on load
 from .build import KernelBuildError, load_library
 
-ABI_VERSION = 19
+ABI_VERSION = 20
 MAX_TOP_K = 1024
 
 
@@ -624,8 +624,10 @@ PREFILL_TILE = 64  # query rows per entry of the work list that `attention_prefi
 
 def attention_prefill(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0,
                       block_table, out, n_tiles: int, n_heads: int, n_kv_heads: int, head_dim: int,
-                      window: int, scale: float) -> None:
-    """Tiles of up to 64 query tokens of sequences with unequal lengths over the paged cache."""
+                      window: int, scale: float, wide_tiles=None) -> None:
+    """Tiles of up to 64 query tokens of sequences with unequal lengths over the paged cache.
+    `wide_tiles`: (sequence, first row) int32 lists of the same rows in tiles of 128, which the tcgen05 kernel
+    works on; without them it walks the 64-row list and every other block finds nothing to do."""
     _check_attention(q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim)
     for name, t in (("seq_slot", seq_slot), ("seq_ctx", seq_ctx), ("seq_qstart", seq_qstart),
                     ("seq_qlen", seq_qlen), ("tile_seq", tile_seq), ("tile_row0", tile_row0)):
@@ -635,6 +637,13 @@ def attention_prefill(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_ql
         raise KernelError("attention prefill: tile lists shorter than the tile count")
     if (USE_TENSOR_CORE_PREFILL and USE_TCGEN05_PREFILL
             and lib().mll_attn_prefill_tc5_supported(dtype_code(q.dtype), head_dim)):
+        if wide_tiles is not None:
+            tile_seq, tile_row0 = wide_tiles
+            _need(tile_seq, "attention wide tile_seq", torch.int32, 1)
+            _need(tile_row0, "attention wide tile_row0", torch.int32, 1)
+            n_tiles = tile_seq.shape[0]
+            if tile_row0.shape[0] != n_tiles:
+                raise KernelError("attention prefill: the wide tile lists differ in length")
         _check(lib().mll_attn_prefill_tc5(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx),
                                           _ptr(seq_qstart), _ptr(seq_qlen), _ptr(tile_seq), _ptr(tile_row0),
                                           _ptr(block_table), _ptr(out), ctypes.c_int(q.shape[0]),

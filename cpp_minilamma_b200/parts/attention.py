@@ -98,18 +98,27 @@ class Attention(Mixer):
         return ("attention.prefill_tiles", PREFILL_TILE)  # every attention layer reads the same tile list
 
     def prepare_step(self, shape):
-        """The prefill kernels' work list: one tile of up to PREFILL_TILE query rows per entry, as
+        """The prefill kernels' work lists: one tile of up to PREFILL_TILE query rows per entry, as
         (sequence, first row within the sequence's new tokens), long contexts first so that the longest
-        tiles start first.  Steps of single tokens need none."""
+        tiles start first; and the same in tiles of twice as many rows, for the kernel that works on those
+        (a block per entry: no block is launched only to find that its rows belong to its neighbour).
+        Steps of single tokens need none."""
         if shape.all_decode:
             return {}
         order = sorted(range(shape.n_seqs), key=lambda i: -(shape.starts[i] + shape.lens[i]))
-        tile_seq, tile_row0 = [], []
+        lists = {"tile_seq": [], "tile_row0": []}
+        wide = []
         for i in order:
             for row0 in range(0, shape.lens[i], PREFILL_TILE):
-                tile_seq.append(i)
-                tile_row0.append(row0)
-        return {"tile_seq": tile_seq, "tile_row0": tile_row0}
+                lists["tile_seq"].append(i)
+                lists["tile_row0"].append(row0)
+            for row0 in range(0, shape.lens[i], 2 * PREFILL_TILE):
+                wide.append((shape.starts[i] + min(shape.lens[i], row0 + 2 * PREFILL_TILE), i, row0))
+        # that kernel walks its list from the back: the tiles that read the most keys come last here
+        wide.sort()
+        lists["wide_seq"] = [i for _, i, _ in wide]
+        lists["wide_row0"] = [row0 for _, _, row0 in wide]
+        return lists
 
     def capture_parameters(self, batch: int, max_positions: int):
         # a captured step serves every context length: the split count follows from the batch size alone
@@ -172,7 +181,8 @@ class Attention(Mixer):
                 tiles = step.meta[self.step_metadata_key()]
                 K.attention_prefill(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
                                     tiles["tile_seq"], tiles["tile_row0"], cache.block_table, out,
-                                    tiles["tile_seq"].shape[0], Hq, Hk, d, self.window, self.scale)
+                                    tiles["tile_seq"].shape[0], Hq, Hk, d, self.window, self.scale,
+                                    wide_tiles=(tiles["wide_seq"], tiles["wide_row0"]))
         if self.o_bias_t is None:
             return self.o.forward(step, out, "o", into=into)
         o = self.o.forward(step, out, "o")

@@ -349,10 +349,10 @@ def prefill_impl(request):
     K.USE_TCGEN05_PREFILL = True
 
 
-def _prefill_tiles(q_lens):
+def _prefill_tiles(q_lens, rows=64):
     tile_seq, tile_row0 = [], []
     for i, n in enumerate(q_lens):
-        for r in range(0, n, 64):
+        for r in range(0, n, rows):
             tile_seq.append(i)
             tile_row0.append(r)
     return tile_seq, tile_row0
@@ -360,12 +360,13 @@ def _prefill_tiles(q_lens):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("hq,hk,d", [(4, 2, 16), (6, 1, 32), (3, 3, 48), (10, 2, 80), (8, 2, 128), (4, 1, 256),
-                                      (6, 3, 64)])
+                                      (6, 3, 64), (3, 1, 128), (2, 2, 64)])
 @pytest.mark.parametrize("window", [0, 70])
 def test_attention_prefill(dtype, hq, hk, d, window, prefill_impl):
-    # sequences that start at 0 and sequences that continue an existing context
-    ctx = [200, 1, 65, 130, 64]
-    q_lens = [200, 1, 3, 66, 64]
+    # sequences that start at 0 and sequences that continue an existing context; tiles of 128 rows whose keys
+    # fill one, two, three and five pages
+    ctx = [200, 1, 65, 130, 64, 330, 449]
+    q_lens = [200, 1, 3, 66, 64, 129, 300]
     case = PagedCase(ctx, hk, d, dtype, seed=d + hq)
     total = sum(q_lens)
     q = rnd((total, hq, d), dtype, 14)
@@ -374,9 +375,11 @@ def test_attention_prefill(dtype, hq, hk, d, window, prefill_impl):
     tile_seq, tile_row0 = _prefill_tiles(q_lens)
     out = torch.empty((total, hq * d), dtype=dtype, device=DEV)
     i32 = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=DEV)
+    # with the list of 128-row tiles where the window is off (the tcgen05 kernel takes either list)
+    wide = None if window else tuple(i32(a) for a in _prefill_tiles(q_lens, 128))
     K.attention_prefill(q.reshape(total, hq * d).to(DEV), kc, vc, slots, ctx_t, i32(qstart), i32(q_lens),
                         i32(tile_seq), i32(tile_row0), table, out, len(tile_seq), hq, hk, d, window,
-                        1.0 / math.sqrt(d))
+                        1.0 / math.sqrt(d), wide_tiles=wide)
     got = as64(out).reshape(total, hq, d)
     for b, (c, n) in enumerate(zip(ctx, q_lens)):
         rows = slice(qstart[b], qstart[b] + n)
