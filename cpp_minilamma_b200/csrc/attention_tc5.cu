@@ -362,14 +362,23 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
     // ---- MMAs: S_{i+1} = Q K_{i+1}^T is issued before O += P_i V_i, so it runs under softmax i //
     if (lane == 0) {
       constexpr unsigned idesc_s = a_idesc(A_ROWS, MLL_PAGE, false), idesc_o = a_idesc(A_ROWS, D, true);
+      // The descriptors are built once; a step inside a tile only adds to the address field (16-byte units, 14
+      // bits: the tiles lie in the first 256 KB of shared memory, so the sum cannot carry out of it).  Built
+      // anew for every instruction they cost this thread some twenty dependent instructions per MMA, which it
+      // has to issue between those of two busy softmax warps on its scheduler: the MMAs then went out at 115 to
+      // 230 clocks apiece where the tensor cores take 48 (N = 64) or 64 (N = 128).
+      const unsigned long long q_desc = a_desc(q_s, 16);
+      const unsigned long long k_desc[2] = {a_desc(k_s, 16), a_desc(k_s + L::KV_BYTES, 16)};
+      const unsigned long long v_desc[2] = {a_desc(v_s, MLL_PAGE * 128), a_desc(v_s + L::KV_BYTES, MLL_PAGE * 128)};
       auto issue_s = [&](int i) {
-        const unsigned kt = k_s + (i & 1) * L::KV_BYTES;
+        const unsigned long long kd = k_desc[i & 1];
+        const unsigned d = tmem_base + (i & 1) * MLL_PAGE;
 #pragma unroll
         for (int b = 0; b < DB; ++b)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            a_umma(tmem_base + (i & 1) * MLL_PAGE, a_desc(q_s + b * (A_ROWS * 128) + k * 32, 16),
-                   a_desc(kt + b * (MLL_PAGE * 128) + k * 32, 16), idesc_s, (b > 0 || k > 0) ? 1u : 0u);
+            a_umma(d, q_desc + (unsigned long long)((b * (A_ROWS * 128) + k * 32) >> 4),
+                   kd + (unsigned long long)((b * (MLL_PAGE * 128) + k * 32) >> 4), idesc_s, (b > 0 || k > 0) ? 1u : 0u);
         a_commit(bar(AB_S_FULL, i & 1));
         a_commit(bar(AB_K_EMPTY, i & 1));
       };
@@ -390,10 +399,10 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
         wait(bar(AB_V_FULL, st), (i >> 1) & 1);
         a_fence_after();
         if (*abort_flag) break;
-        const unsigned vt = v_s + st * L::KV_BYTES;
+        const unsigned long long vd = v_desc[st];
 #pragma unroll
         for (int k = 0; k < 4; ++k)  // P: 16 keys = 8 packed columns per step
-          a_umma_ts(tmem_base + L::O_COL, tmem_base + st * MLL_PAGE + k * 8, a_desc(vt + k * (16 * 128), MLL_PAGE * 128),
+          a_umma_ts(tmem_base + L::O_COL, tmem_base + st * MLL_PAGE + k * 8, vd + (unsigned long long)((k * (16 * 128)) >> 4),
                     idesc_o, (i > 0 || k > 0) ? 1u : 0u);
         a_commit(bar(AB_PV_DONE, st));
         a_commit(bar(AB_V_EMPTY, st));
