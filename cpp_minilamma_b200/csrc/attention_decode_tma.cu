@@ -43,15 +43,7 @@ __device__ int mll_attn_decode_tma_error_flag = 0;
 namespace mll {
 
 constexpr int DT_STAGES = 3;
-// Four compute warps, the producer warp and three warps that only fill the second warpgroup: with eight warps
-// every block puts two warps on each of the multiprocessor's four schedulers, so that the place of a block that
-// has ended can be taken at once whatever the other resident block looks like (five warps of 168 registers left
-// one scheduler with two warps of a block and three with one; a new block whose pair fell on the wrong scheduler
-// had to wait for the other block to end as well).  Blocks start with 128 registers per thread; the compute
-// warpgroup then takes what it needs and the other gives back all but 64 (setmaxnreg; the code after the page
-// loop, which all warps run, has to fit into those).
-constexpr int DT_THREADS = 256;
-constexpr int DT_COMPUTE_REGS = 168, DT_OTHER_REGS = 64;
+constexpr int DT_THREADS = 160;  // four compute warps and the producer warp
 constexpr unsigned DT_SPIN_LIMIT = 4u << 20;
 
 template <int D>
@@ -173,7 +165,6 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     float o[NT][4];
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // rows g and g + 8, this warp's keys only
 
-    if (warp >= 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(DT_OTHER_REGS));
     if (warp == 4) {
       // ---- producer ---------------------------------------------------------------------------- //
       if (lane == 0 && n_pages > 0) {
@@ -194,9 +185,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
           }
         }
       }
-    } else if (warp < 4) {
+    } else {
       // ---- compute warps ----------------------------------------------------------------------- //
-      asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(DT_COMPUTE_REGS));
 #pragma unroll
       for (int n = 0; n < NT; ++n)
 #pragma unroll
