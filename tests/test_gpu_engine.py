@@ -150,6 +150,30 @@ def test_chunked_step_equals_whole(model_folders, dtype):
     assert_close(out[300:], ref_other[[69, 0]], dtype, "chunked short, want out of order")
 
 
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("D", "bfloat16"), ("D", "float32"), ("C", "bfloat16")])
+@pytest.mark.parametrize("length", [65, 66, 129])
+def test_chunk_edges_portions_of_one_and_two_tokens(model_folders, name, dtype, length):
+    # with chunks of 64 tokens a prompt of 65, 66 or 129 leaves a last portion of 1 or 2 tokens whose first
+    # position is the first row of a new page: alone it is a step of single tokens (the decode kernels, in D
+    # bfloat16 with rope and cache write fused into the attention), next to a longer neighbour a one-row tile
+    top = tc.TINY[name]["max_position_embeddings"]
+    if length > top:
+        pytest.skip("longer than the model's positions")
+    tokens = tc.random_tokens(name, length, 610 + length)
+    ref = plain_logits(folder := model_folders(name, dtype), tokens, dtype)
+    llm = ml.load(folder, dtype=dtype, max_tokens=4096, max_step_tokens=64)
+    slot, = llm.engine.acquire(1)
+    alone = llm.engine.step([StepEntry(slot, tokens, list(range(length)))]).cpu().numpy()
+    llm.engine.release(slot)
+    assert_close(alone, ref, dtype, f"{name} chunks of 64, {length} tokens alone")
+    other = tc.random_tokens(name, min(100, top), 611)
+    a, b = llm.engine.acquire(2)
+    out = llm.engine.step([StepEntry(a, other, [len(other) - 1]), StepEntry(b, tokens, list(range(length)))]).cpu().numpy()
+    assert_close(out[1:], ref, dtype, f"{name} chunks of 64, {length} tokens behind a neighbour")
+    assert_close(out[:1], plain_logits(folder, other, dtype)[-1:], dtype, "the neighbour")
+    llm.engine.cache.check()
+
+
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_greedy_generation_through_entry_point(model_folders, name, dtype):
     folder, llm = load(model_folders, name, dtype)

@@ -482,6 +482,15 @@ def test_toy_architecture_with_window_group_routing_and_other_encoding(tmp_path)
     out = llm.engine.step([StepEntry(a, tokens, list(range(300))), StepEntry(b, tokens[:7], [6])]).cpu().numpy()
     assert_close(out[:300], ref, "float32", "toy mix: whole")
     assert_close(out[300], mix_plain(weights, tokens[:7])[6], "float32", "toy mix: short neighbour")
+    llm.engine.release(a)
+    llm.engine.release(b)
+    # the same prompt cut into chunks of 64 tokens inside the engine: the window's edge (70 keys back) falls
+    # inside every portion but the first, and the windowed group hands pages back between the portions
+    chunked = ml.load(folder, dtype="float32", max_tokens=64 * 10, max_seqs=2, max_step_tokens=64)
+    slot, = chunked.engine.acquire(1)
+    out = chunked.engine.step([StepEntry(slot, tokens, list(range(300)))]).cpu().numpy()
+    assert_close(out, ref, "float32", "toy mix: whole, in chunks of 64")
+    chunked.engine.cache.check()
 
 
 # ------------------------------------------------------------------------------------ #

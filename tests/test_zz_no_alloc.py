@@ -5,10 +5,12 @@ Some programs that embed this library own all device memory themselves or run lo
 which cudaMalloc (which synchronises the device) is not acceptable; they can hand in their
 own inputs and outputs but not the scratch that the split decode kernel needs.  The entry
 point keeps that scratch in an array inside the library.  The test checks two calls in a
-row, with different data, against the ordinary entry point that takes caller scratch: the
+row, with different data, against the ordinary entry point that takes caller scratch (the
 array keeps the first call's contents, so a slot that the second call failed to overwrite
-would show.  The file sorts last so that a run stopping at the first failure has already
-run everything else.
+would show) and against the plain implementation, with and without context splits and with
+a window; and it checks the property the entry point exists for: the device's free memory
+is the same before and after a call.  The file sorts last so that a run stopping at the
+first failure has already run everything else.
 """
 import ctypes
 import math
@@ -16,6 +18,8 @@ import math
 import numpy as np
 import pytest
 import torch
+
+import plain_llama as pl
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -53,10 +57,23 @@ def _case(seed, dtype, ctx_lens, hq, hk, d):
                 ctx=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), table=table.to(DEV))
 
 
+def _plain(case, ctx_lens, hq, hk, d, window):
+    """The plain implementation on the same pages: one query at the last position of each sequence."""
+    rows = []
+    for b, c in enumerate(ctx_lens):
+        pages = case["table"][b, :(c + PAGE - 1) // PAGE].cpu().long()
+        k = case["k"].cpu().float()[pages].permute(0, 2, 1, 3).reshape(-1, hk, d)[:c].numpy().astype(np.float64)
+        v = case["v"].cpu().float()[pages].permute(0, 2, 1, 3).reshape(-1, hk, d)[:c].numpy().astype(np.float64)
+        q = case["q"][b].cpu().float().reshape(1, hq, d).numpy().astype(np.float64)
+        rows.append(pl.causal_attention(q, k, v, window=window or None, q_positions=[c - 1]).reshape(hq * d))
+    return np.stack(rows)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_two_calls_in_a_row_match_the_entry_point_with_caller_scratch(dtype):
+@pytest.mark.parametrize("splits,window", [(4, 0), (1, 0), (4, 70)])
+def test_two_calls_in_a_row_match_the_entry_point_with_caller_scratch(dtype, splits, window):
     lib = _library()
-    hq, hk, d, splits = 8, 2, 64, 4
+    hq, hk, d = 8, 2, 64
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     code = 0 if dtype == torch.float32 else 1
     tol = dict(rtol=2e-5, atol=2e-6) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1e-3)
@@ -65,19 +82,26 @@ def test_two_calls_in_a_row_match_the_entry_point_with_caller_scratch(dtype):
         n = len(ctx_lens)
         args = [c["q"].data_ptr(), c["k"].data_ptr(), c["v"].data_ptr(), c["slot"].data_ptr(), c["ctx"].data_ptr(),
                 c["table"].data_ptr()]
-        sizes = [code, n, hq, hk, d, c["table"].shape[1], splits, 0]
+        sizes = [code, n, hq, hk, d, c["table"].shape[1], splits, window]
         scale = ctypes.c_float(1.0 / math.sqrt(d))
         expected = torch.full((n, hq * d), float("nan"), dtype=dtype, device=DEV)
         scratch = torch.empty(n * hq * splits * (d + 2), dtype=torch.float32, device=DEV)
         rc = lib.mll_attn_decode(*args, scratch.data_ptr(), expected.data_ptr(), *sizes, scale, stream)
         assert rc == 0, lib.mll_last_error()
         got = torch.full((n, hq * d), float("nan"), dtype=dtype, device=DEV)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = lib.mll_attn_decode_no_alloc(*args, got.data_ptr(), *sizes, scale, stream)
         assert rc == 0, lib.mll_last_error()
         torch.cuda.synchronize()
+        if call == 1:  # the first call on a device looks the array's address up; after that nothing may move
+            assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the device's free memory"
         np.testing.assert_allclose(got.float().cpu().numpy(), expected.float().cpu().numpy(), **tol,
                                    err_msg=f"call {call}")
         assert torch.isfinite(got.float()).all()
+        plain_tol = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+        np.testing.assert_allclose(got.float().cpu().numpy(), _plain(c, ctx_lens, hq, hk, d, window), **plain_tol,
+                                   err_msg=f"call {call} against the plain implementation")
 
 
 def test_sizes_beyond_the_built_in_scratch_are_refused():
