@@ -19,7 +19,7 @@ struct DecodeMmaArgs {
   __nv_bfloat16* out;            // [B, Hq * d]
   int n_heads, n_kv_heads, max_blocks, n_splits, window;
   float scale;
-  int* counters;                 // optional [B, gridDim.y], zero between launches: the last split merges
+  int* counters;                 // optional [B, Hk x head chunks], zero between launches: the last split merges
   // fused variant: q, k and v of the step's token come straight from the projection's output;
   // the kernel rotates them and writes the new key and value row into the cache itself
   const __nv_bfloat16* qkv;      // [B, ld]: q heads, k heads, v heads
@@ -28,6 +28,9 @@ struct DecodeMmaArgs {
   __nv_bfloat16* k_write;        // the caches again, writable (null: this layer reads another layer's cache)
   __nv_bfloat16* v_write;
   int qkv_ld, interleaved;
+  // optional [B]: the sequences in the order their blocks should start (the TMA kernel; longest contexts first
+  // lets the short ones fill the end of the launch)
+  const int* seq_order;
 };
 
 __device__ __forceinline__ float2 unpack_bf162(unsigned r) {
@@ -70,13 +73,15 @@ __host__ __device__ inline int decode_splits_for(int pages, int offered) {
 }
 
 // Called by every thread of a block after it has written its split's partial result (float32
-// output rows, running maximum and sum) for heads h0 .. h0 + ng - 1 of sequence b.  The block that
+// output rows, running maximum and sum) for heads h0 .. h0 + ng - 1 of sequence b (item `item` of the
+// sequence's `items_per_seq` kv heads x head chunks).  The block that
 // arrives last for this (sequence, kv head, head chunk) merges the n_eff splits in use and writes
 // the output; the others return.  smem_f: at least 16 * n_eff + 20 floats that the block no longer
 // needs, its first word serving as a flag.  NTHREADS threads, all of which must call (it contains
 // block-wide barriers).
 template <int D, int NTHREADS>
-__device__ __forceinline__ void merge_decode_splits(const DecodeMmaArgs& a, int b, int h0, int ng, int n_eff,
+__device__ __forceinline__ void merge_decode_splits(const DecodeMmaArgs& a, int b, int item, int items_per_seq, int h0,
+                                                    int ng, int n_eff,
                                                     float* smem_f) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   volatile int* is_last_word = reinterpret_cast<volatile int*>(smem_f);
@@ -84,7 +89,7 @@ __device__ __forceinline__ void merge_decode_splits(const DecodeMmaArgs& a, int 
   __threadfence();  // this block's partial results are visible before its arrival is counted
   __syncthreads();
   if (tid == 0) {
-    int* counter = a.counters + (size_t)b * gridDim.y + blockIdx.y;
+    int* counter = a.counters + (size_t)b * items_per_seq + item;
     const int arrived = atomicAdd(counter, 1);
     const int last = arrived == n_eff - 1;
     if (last) *counter = 0;  // ready for the next launch

@@ -92,6 +92,11 @@ __device__ __forceinline__ void dt_tma_load_2d(unsigned dst, const CUtensorMap* 
 __device__ __forceinline__ unsigned dt_chunk_offset(int row, int chunk) {
   return (unsigned)((chunk >> 3) * (MLL_PAGE * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
+__device__ __forceinline__ float dt_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void dt_ldmatrix_x4(unsigned (&r)[4], unsigned addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -101,7 +106,215 @@ __device__ __forceinline__ void dt_ldmatrix_x4_trans(unsigned (&r)[4], unsigned 
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 
-// grid (B, Hk * head_chunks, n_splits); 160 threads.
+// The step's new key (rotated) and value of kv head `kvh` of sequence b, one pair of each per thread (tid < D / 2).
+template <int D>
+__device__ __forceinline__ void dt_fetch_new_row(const DecodeMmaArgs& a, int b, int kvh, int ctx, int tid,
+                                                 __nv_bfloat16& new_k0, __nv_bfloat16& new_k1, unsigned& new_v) {
+  const __nv_bfloat16* k_in = a.qkv + (size_t)b * a.qkv_ld + (size_t)(a.n_heads + kvh) * D;
+  const __nv_bfloat16* v_in = k_in + (size_t)a.n_kv_heads * D;
+  const int e0 = a.interleaved ? 2 * tid : tid, e1 = a.interleaved ? 2 * tid + 1 : tid + D / 2;
+  const float x0 = __bfloat162float(k_in[e0]), x1 = __bfloat162float(k_in[e1]);
+  new_v = *reinterpret_cast<const unsigned*>(v_in + 2 * tid);
+  float y0 = x0, y1 = x1;
+  if (a.cos_table != nullptr) {
+    const float c = a.cos_table[(size_t)(ctx - 1) * (D / 2) + tid], sv = a.sin_table[(size_t)(ctx - 1) * (D / 2) + tid];
+    y0 = x0 * c - x1 * sv;
+    y1 = x0 * sv + x1 * c;
+  }
+  new_k0 = __float2bfloat16_rn(y0);
+  new_k1 = __float2bfloat16_rn(y1);
+}
+
+// The query fragments (A operand of the score product) of heads h0 .. h0 + ng - 1 of sequence b: rows = heads,
+// zero beyond ng; the fused variant rotates them (the token's position is ctx - 1).
+template <int D, bool FUSED>
+__device__ __forceinline__ void dt_load_query(const DecodeMmaArgs& a, int b, int h0, int ng, int ctx, int g, int t,
+                                              unsigned (&qf)[D / 16][4]) {
+  constexpr int KSTEPS = D / 16;
+  const __nv_bfloat16* q0 = FUSED ? a.qkv + (size_t)b * a.qkv_ld + (size_t)h0 * D
+                                  : a.q + ((size_t)b * a.n_heads + h0) * D;
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+    const int col = ks * 16 + 2 * t;
+    qf[ks][0] = g < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + col) : 0u;
+    qf[ks][1] = g + 8 < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + col) : 0u;
+    qf[ks][2] = g < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + col + 8) : 0u;
+    qf[ks][3] = g + 8 < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + col + 8) : 0u;
+  }
+  if (FUSED && a.cos_table != nullptr && ctx > 0) {
+    // the token's position is ctx - 1 for every head; registers [2j] and [2j + 1] hold rows g and
+    // g + 8 at columns col + 8 j, col + 8 j + 1
+    const float* cs = a.cos_table + (size_t)(ctx - 1) * (D / 2);
+    const float* sn = a.sin_table + (size_t)(ctx - 1) * (D / 2);
+    if (a.interleaved) {  // pairs (2i, 2i + 1): both halves of a pair sit in one register
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int pair = ks * 8 + t + 4 * j;
+          const float c = cs[pair], sv = sn[pair];
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const float2 x = unpack_bf162(qf[ks][2 * j + r]);
+            qf[ks][2 * j + r] = pack_bf162(x.x * c - x.y * sv, x.x * sv + x.y * c);
+          }
+        }
+    } else {  // pairs (i, i + d/2): the partner sits in the same place of k-step ks + KSTEPS / 2
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS / 2; ++ks)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int i0 = ks * 16 + 2 * t + 8 * j;
+          const float c0 = cs[i0], s0 = sn[i0], c1 = cs[i0 + 1], s1 = sn[i0 + 1];
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const float2 lo = unpack_bf162(qf[ks][2 * j + r]), hi = unpack_bf162(qf[ks + KSTEPS / 2][2 * j + r]);
+            qf[ks][2 * j + r] = pack_bf162(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);
+            qf[ks + KSTEPS / 2][2 * j + r] = pack_bf162(lo.x * s0 + hi.x * c0, lo.y * s1 + hi.y * c1);
+          }
+        }
+    }
+  }
+}
+
+// One page (64 keys, in the ring stage at `stage`) for one compute warp: the warp's 16 keys against the (up to
+// 16) query heads, its running maximum and sum, and its [16 heads x head_dim] output.  p: the page's number in
+// the sequence.  On the sequence's last page the fused variant first puts the step's new key and value into the
+// stage and into the cache (the block that owns that page; the four compute warps meet once for it), and rows
+// beyond the context are masked (keys) and zeroed (values).
+template <int D, bool FUSED>
+__device__ __forceinline__ void dt_page_step(const DecodeMmaArgs& a, unsigned char* stage, int p, int ctx, int first_key,
+                                             int pages_total, bool owns_new_row, const int* table, int kvh,
+                                             __nv_bfloat16 new_k0, __nv_bfloat16 new_k1, unsigned new_v,
+                                             const unsigned (&qf)[D / 16][4], float (&o)[D / 8][4], float (&m_run)[2],
+                                             float (&l_run)[2]) {
+  constexpr int KSTEPS = D / 16, NT = D / 8;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, t = lane & 3;
+  const unsigned kt = dt_smem(stage), vt = kt + DecodeTmaSmem<D>::HALF;
+  if (p == pages_total - 1) {
+    if (FUSED && owns_new_row) {
+      // the step's token lies in this page: its key (rotated) and value replace whatever the cache held
+      const int row = (ctx - 1) % MLL_PAGE;
+      if (tid < D / 2) {
+        const size_t cache_row = (((size_t)table[p] * a.n_kv_heads + kvh) * MLL_PAGE + row) * D;
+        const int e0 = a.interleaved ? 2 * tid : tid, e1 = a.interleaved ? 2 * tid + 1 : tid + D / 2;
+        unsigned char* k_half = stage;
+        unsigned char* v_half = k_half + DecodeTmaSmem<D>::HALF;
+        *reinterpret_cast<__nv_bfloat16*>(k_half + dt_chunk_offset(row, e0 >> 3) + (e0 & 7) * 2) = new_k0;
+        *reinterpret_cast<__nv_bfloat16*>(k_half + dt_chunk_offset(row, e1 >> 3) + (e1 & 7) * 2) = new_k1;
+        a.k_write[cache_row + e0] = new_k0;
+        a.k_write[cache_row + e1] = new_k1;
+        *reinterpret_cast<unsigned*>(v_half + dt_chunk_offset(row, (2 * tid) >> 3) + ((2 * tid) & 7) * 2) = new_v;
+        *reinterpret_cast<unsigned*>(a.v_write + cache_row + 2 * tid) = new_v;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the compute warps only; once per block
+    }
+    const int valid = ctx - p * MLL_PAGE;  // positions of this page that the sequence has
+    if (valid < MLL_PAGE) {                // the rest of the page may hold anything: zero this warp's value rows
+      unsigned char* v_half = stage + DecodeTmaSmem<D>::HALF;
+      for (int idx = lane; idx < 16 * (D / 8); idx += 32) {
+        const int row = warp * 16 + idx / (D / 8), ch = idx % (D / 8);
+        if (row >= valid) *reinterpret_cast<uint4*>(v_half + dt_chunk_offset(row, ch)) = make_uint4(0, 0, 0, 0);
+      }
+      __syncwarp();
+    }
+  }
+
+  // Where this lane's ldmatrix rows lie in the swizzled tiles.  Chunk c of row r is stored at chunk c ^ (r & 7); the
+  // chunk a lane reads is an even number known at compile time plus one bit of the lane, so the lane's part is
+  // worked out once and the rest is one XOR with a constant (the tiles are 1,024-byte aligned).
+  const int k_row = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
+  const unsigned k_lane = kt + k_row * 128 + (((((lane >> 3) & 1) ^ k_row) & 7) << 4);
+  const int v_row = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+  const unsigned v_lane = vt + v_row * 128 + ((((lane >> 4) ^ v_row) & 7) << 4);
+
+  // scores of the 16 heads against this warp's 16 keys: two n-tiles of 8 keys; where registers allow (head_dim 64)
+  // even and odd k-steps go to accumulators of their own, which halves the chains of dependent MMAs
+  float s_acc[2][4], s_odd[2][4];
+#pragma unroll
+  for (int n = 0; n < 2; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s_acc[n][i] = s_odd[n][i] = 0.f;
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+    // matrices: (keys 0-7, dims 0-7), (keys 0-7, dims 8-15), (keys 8-15, dims 0-7), (keys 8-15, dims 8-15)
+    unsigned kb[4];
+    dt_ldmatrix_x4(kb, (k_lane ^ (unsigned)(((ks * 2) & 7) << 4)) + (ks >> 2) * DecodeTmaSmem<D>::BOX_BYTES);
+    if (D == 64 && (ks & 1)) {
+      mma_16816(s_odd[0], qf[ks], kb[0], kb[1]);
+      mma_16816(s_odd[1], qf[ks], kb[2], kb[3]);
+    } else {
+      mma_16816(s_acc[0], qf[ks], kb[0], kb[1]);
+      mma_16816(s_acc[1], qf[ks], kb[2], kb[3]);
+    }
+  }
+  // scale, mask (only a sequence's first and last page have keys to mask), the warp's row maxima
+  const bool edge = (p + 1) * MLL_PAGE > ctx || p * MLL_PAGE < first_key;
+  float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int n = 0; n < 2; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float v = (s_acc[n][i] + s_odd[n][i]) * a.scale;
+      if (edge) {
+        const int kpos = p * MLL_PAGE + warp * 16 + n * 8 + 2 * t + (i & 1);
+        if (!(kpos < ctx && kpos >= first_key)) v = -INFINITY;
+      }
+      s_acc[n][i] = v;
+      tile_max[i >> 1] = fmaxf(tile_max[i >> 1], v);
+    }
+  // exp(x - m) = 2^(x log2(e) - m log2(e)): one FMA and one ex2 per score.  A masked score is -inf and gives 0;
+  // while a row has seen no key at all its maximum is -inf, and 0 stands in for it so that nothing becomes NaN.
+  constexpr float LOG2E = 1.4426950408889634f;
+  float alpha[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+    tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+    const float m_new = fmaxf(m_run[r], tile_max[r]);
+    const float base = m_new > -INFINITY ? m_new * LOG2E : 0.f;
+    alpha[r] = m_new > -INFINITY ? dt_exp2((m_run[r] - m_new) * LOG2E) : 1.f;  // exactly 1 while the maximum stands
+    float sum = 0.f;
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const float pv = dt_exp2(fmaf(s_acc[n][2 * r + i], LOG2E, -base));
+        s_acc[n][2 * r + i] = pv;
+        sum += pv;
+      }
+    l_run[r] = l_run[r] * alpha[r] + sum;  // this thread's share of the row; the quad is summed after the loop
+    m_run[r] = m_new;
+  }
+  // the probabilities as the A fragment of a 16-key step: (row g, keys 2t..), (row g + 8, keys 2t..),
+  // (row g, keys 8 + 2t..), (row g + 8, keys 8 + 2t..)
+  unsigned pa[4];
+  pa[0] = pack_bf162(s_acc[0][0], s_acc[0][1]);
+  pa[1] = pack_bf162(s_acc[0][2], s_acc[0][3]);
+  pa[2] = pack_bf162(s_acc[1][0], s_acc[1][1]);
+  pa[3] = pack_bf162(s_acc[1][2], s_acc[1][3]);
+  // out = alpha * out + P[16 x 16] . V[this warp's 16 keys x head_dim]; after a sequence's first pages the maxima
+  // rarely move, and a warp none of whose rows moved leaves its output as it is
+  if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      o[n][0] *= alpha[0];
+      o[n][1] *= alpha[0];
+      o[n][2] *= alpha[1];
+      o[n][3] *= alpha[1];
+    }
+  }
+#pragma unroll
+  for (int n = 0; n < NT; n += 2) {
+    // transposed 8x8 tiles of V: (keys 0-7, cols n), (keys 8-15, cols n), (keys 0-7, cols n+1), (keys 8-15, cols n+1)
+    unsigned vb[4];
+    dt_ldmatrix_x4_trans(vb, (v_lane ^ (unsigned)((n & 7) << 4)) + (n >> 3) * DecodeTmaSmem<D>::BOX_BYTES);
+    mma_16816(o[n], pa, vb[0], vb[1]);
+    mma_16816(o[n + 1], pa, vb[2], vb[3]);
+  }
+}
+
+// grid (Hk * head_chunks, B, n_splits); 160 threads.
 template <int D, bool FUSED, bool CLUSTER>
 __global__ void __launch_bounds__(DT_THREADS, 2)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
@@ -120,8 +333,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
   const int g = lane >> 2, t = lane & 3;
   const int group = a.n_heads / a.n_kv_heads;
   const int chunks = (group + 15) / 16;
-  const int b = blockIdx.x;
-  const int kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks;
+  // sequences are the slower grid index, so blocks start in the order of `seq_order` (longest contexts first)
+  const int b = a.seq_order != nullptr ? a.seq_order[blockIdx.y] : blockIdx.y;
+  const int item = blockIdx.x;  // kv head x head chunk
+  const int kvh = item / chunks, chunk = item % chunks;
   const int split = blockIdx.z;
   const int ng = min(16, group - chunk * 16);
   const int h0 = kvh * group + chunk * 16;
@@ -198,177 +413,17 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
                                 pages_total - 1 < p_end;
       __nv_bfloat16 new_k0 = __float2bfloat16_rn(0.f), new_k1 = new_k0;
       unsigned new_v = 0;
-      if (owns_new_row && tid < D / 2) {
-        const __nv_bfloat16* k_in = a.qkv + (size_t)b * a.qkv_ld + (size_t)(a.n_heads + kvh) * D;
-        const __nv_bfloat16* v_in = k_in + (size_t)a.n_kv_heads * D;
-        const int e0 = a.interleaved ? 2 * tid : tid, e1 = a.interleaved ? 2 * tid + 1 : tid + D / 2;
-        const float x0 = __bfloat162float(k_in[e0]), x1 = __bfloat162float(k_in[e1]);
-        new_v = *reinterpret_cast<const unsigned*>(v_in + 2 * tid);
-        float y0 = x0, y1 = x1;
-        if (a.cos_table != nullptr) {
-          const float c = a.cos_table[(size_t)(ctx - 1) * (D / 2) + tid], sv = a.sin_table[(size_t)(ctx - 1) * (D / 2) + tid];
-          y0 = x0 * c - x1 * sv;
-          y1 = x0 * sv + x1 * c;
-        }
-        new_k0 = __float2bfloat16_rn(y0);
-        new_k1 = __float2bfloat16_rn(y1);
-      }
+      if (owns_new_row && tid < D / 2) dt_fetch_new_row<D>(a, b, kvh, ctx, tid, new_k0, new_k1, new_v);
 
-      // query fragments (A operand), rows = heads of this chunk, zero beyond ng
       unsigned qf[KSTEPS][4];
-      {
-        const __nv_bfloat16* q0 = FUSED ? a.qkv + (size_t)b * a.qkv_ld + (size_t)h0 * D
-                                        : a.q + ((size_t)b * a.n_heads + h0) * D;
-#pragma unroll
-        for (int ks = 0; ks < KSTEPS; ++ks) {
-          const int col = ks * 16 + 2 * t;
-          qf[ks][0] = g < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + col) : 0u;
-          qf[ks][1] = g + 8 < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + col) : 0u;
-          qf[ks][2] = g < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + col + 8) : 0u;
-          qf[ks][3] = g + 8 < ng ? *reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + col + 8) : 0u;
-        }
-        if (FUSED && a.cos_table != nullptr && ctx > 0) {
-          // the token's position is ctx - 1 for every head; registers [2j] and [2j + 1] hold rows g and
-          // g + 8 at columns col + 8 j, col + 8 j + 1
-          const float* cs = a.cos_table + (size_t)(ctx - 1) * (D / 2);
-          const float* sn = a.sin_table + (size_t)(ctx - 1) * (D / 2);
-          if (a.interleaved) {  // pairs (2i, 2i + 1): both halves of a pair sit in one register
-#pragma unroll
-            for (int ks = 0; ks < KSTEPS; ++ks)
-#pragma unroll
-              for (int j = 0; j < 2; ++j) {
-                const int pair = ks * 8 + t + 4 * j;
-                const float c = cs[pair], sv = sn[pair];
-#pragma unroll
-                for (int r = 0; r < 2; ++r) {
-                  const float2 x = unpack_bf162(qf[ks][2 * j + r]);
-                  qf[ks][2 * j + r] = pack_bf162(x.x * c - x.y * sv, x.x * sv + x.y * c);
-                }
-              }
-          } else {  // pairs (i, i + d/2): the partner sits in the same place of k-step ks + KSTEPS / 2
-#pragma unroll
-            for (int ks = 0; ks < KSTEPS / 2; ++ks)
-#pragma unroll
-              for (int j = 0; j < 2; ++j) {
-                const int i0 = ks * 16 + 2 * t + 8 * j;
-                const float c0 = cs[i0], s0 = sn[i0], c1 = cs[i0 + 1], s1 = sn[i0 + 1];
-#pragma unroll
-                for (int r = 0; r < 2; ++r) {
-                  const float2 lo = unpack_bf162(qf[ks][2 * j + r]), hi = unpack_bf162(qf[ks + KSTEPS / 2][2 * j + r]);
-                  qf[ks][2 * j + r] = pack_bf162(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);
-                  qf[ks + KSTEPS / 2][2 * j + r] = pack_bf162(lo.x * s0 + hi.x * c0, lo.y * s1 + hi.y * c1);
-                }
-              }
-          }
-        }
-      }
+      dt_load_query<D, FUSED>(a, b, h0, ng, ctx, g, t, qf);
 
       for (int it = 0; it < n_pages; ++it) {
         const int p = p_begin + it;
         const int st = it % DT_STAGES;
         dt_mbar_wait(full + 8 * st, (it / DT_STAGES) & 1, abort_flag);
-        const unsigned kt = ring + st * L::STAGE, vt = kt + L::HALF;
-        if (p == pages_total - 1) {
-          if (FUSED && owns_new_row) {
-            // the step's token lies in this page: its key (rotated) and value replace whatever the cache held
-            const int row = (ctx - 1) % MLL_PAGE;
-            if (tid < D / 2) {
-              const size_t cache_row = (((size_t)table[p] * a.n_kv_heads + kvh) * MLL_PAGE + row) * D;
-              const int e0 = a.interleaved ? 2 * tid : tid, e1 = a.interleaved ? 2 * tid + 1 : tid + D / 2;
-              unsigned char* k_half = smem_raw + st * L::STAGE;
-              unsigned char* v_half = k_half + L::HALF;
-              *reinterpret_cast<__nv_bfloat16*>(k_half + dt_chunk_offset(row, e0 >> 3) + (e0 & 7) * 2) = new_k0;
-              *reinterpret_cast<__nv_bfloat16*>(k_half + dt_chunk_offset(row, e1 >> 3) + (e1 & 7) * 2) = new_k1;
-              a.k_write[cache_row + e0] = new_k0;
-              a.k_write[cache_row + e1] = new_k1;
-              *reinterpret_cast<unsigned*>(v_half + dt_chunk_offset(row, (2 * tid) >> 3) + ((2 * tid) & 7) * 2) = new_v;
-              *reinterpret_cast<unsigned*>(a.v_write + cache_row + 2 * tid) = new_v;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");  // the compute warps only; once per block
-          }
-          const int valid = ctx - p * MLL_PAGE;  // positions of this page that the sequence has
-          if (valid < MLL_PAGE) {                // the rest of the page may hold anything: zero this warp's value rows
-            unsigned char* v_half = smem_raw + st * L::STAGE + L::HALF;
-            for (int idx = lane; idx < 16 * (D / 8); idx += 32) {
-              const int row = warp * 16 + idx / (D / 8), ch = idx % (D / 8);
-              if (row >= valid) *reinterpret_cast<uint4*>(v_half + dt_chunk_offset(row, ch)) = make_uint4(0, 0, 0, 0);
-            }
-            __syncwarp();
-          }
-        }
-
-        // scores of the 16 heads against this warp's 16 keys: two n-tiles of 8 keys
-        float s_acc[2][4];
-#pragma unroll
-        for (int n = 0; n < 2; ++n)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) s_acc[n][i] = 0.f;
-#pragma unroll
-        for (int ks = 0; ks < KSTEPS; ++ks) {
-          // matrices: (keys 0-7, dims 0-7), (keys 0-7, dims 8-15), (keys 8-15, dims 0-7), (keys 8-15, dims 8-15)
-          unsigned kb[4];
-          const int key = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
-          const int ch = ks * 2 + ((lane >> 3) & 1);
-          dt_ldmatrix_x4(kb, kt + dt_chunk_offset(key, ch));
-          mma_16816(s_acc[0], qf[ks], kb[0], kb[1]);
-          mma_16816(s_acc[1], qf[ks], kb[2], kb[3]);
-        }
-        // scale, mask, the warp's row maxima
-        float tile_max[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-        for (int n = 0; n < 2; ++n)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int kpos = p * MLL_PAGE + warp * 16 + n * 8 + 2 * t + (i & 1);
-            const bool ok = kpos < ctx && kpos >= first_key;
-            const float v = ok ? s_acc[n][i] * a.scale : -INFINITY;
-            s_acc[n][i] = v;
-            tile_max[i >> 1] = fmaxf(tile_max[i >> 1], v);
-          }
-        float alpha[2];
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
-          tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
-          const float m_new = fmaxf(m_run[r], tile_max[r]);
-          alpha[r] = m_new > -INFINITY ? __expf(m_run[r] - m_new) : 1.f;
-          float sum = 0.f;
-#pragma unroll
-          for (int n = 0; n < 2; ++n)
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-              const float pv = m_new > -INFINITY ? __expf(s_acc[n][2 * r + i] - m_new) : 0.f;
-              s_acc[n][2 * r + i] = pv;
-              sum += pv;
-            }
-          l_run[r] = l_run[r] * alpha[r] + sum;  // this thread's share of the row; the quad is summed after the loop
-          m_run[r] = m_new;
-        }
-        // the probabilities as the A fragment of a 16-key step: (row g, keys 2t..), (row g + 8, keys 2t..),
-        // (row g, keys 8 + 2t..), (row g + 8, keys 8 + 2t..)
-        unsigned pa[4];
-        pa[0] = pack_bf162(s_acc[0][0], s_acc[0][1]);
-        pa[1] = pack_bf162(s_acc[0][2], s_acc[0][3]);
-        pa[2] = pack_bf162(s_acc[1][0], s_acc[1][1]);
-        pa[3] = pack_bf162(s_acc[1][2], s_acc[1][3]);
-        // out = alpha * out + P[16 x 16] . V[this warp's 16 keys x head_dim]
-#pragma unroll
-        for (int n = 0; n < NT; n += 2) {
-          // transposed 8x8 tiles of V: (keys 0-7, cols n), (keys 8-15, cols n), (keys 0-7, cols n+1), (keys 8-15, cols n+1)
-          unsigned vb[4];
-          const int key = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
-          dt_ldmatrix_x4_trans(vb, vt + dt_chunk_offset(key, n + (lane >> 4)));
-          o[n][0] *= alpha[0];
-          o[n][1] *= alpha[0];
-          o[n][2] *= alpha[1];
-          o[n][3] *= alpha[1];
-          o[n + 1][0] *= alpha[0];
-          o[n + 1][1] *= alpha[0];
-          o[n + 1][2] *= alpha[1];
-          o[n + 1][3] *= alpha[1];
-          mma_16816(o[n], pa, vb[0], vb[1]);
-          mma_16816(o[n + 1], pa, vb[2], vb[3]);
-        }
+        dt_page_step<D, FUSED>(a, smem_raw + st * L::STAGE, p, ctx, first_key, pages_total, owns_new_row, table, kvh,
+                               new_k0, new_k1, new_v, qf, o, m_run, l_run);
         __syncwarp();
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty + 8 * st) : "memory");
       }
@@ -456,7 +511,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     }
   }
   if (n_eff == 1) return;
-  merge_decode_splits<D, DT_THREADS>(a, b, h0, ng, n_eff, merged_l + 16);
+  merge_decode_splits<D, DT_THREADS>(a, b, item, gridDim.x, h0, ng, n_eff, merged_l + 16);
 }
 
 // cluster: the splits of a group are the blocks of one thread-block cluster and merge through distributed
@@ -475,7 +530,7 @@ int launch_decode_tma_as(const CUtensorMap& kmap, const CUtensorMap& vmap, const
   }
   const int group = a.n_heads / a.n_kv_heads;
   cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(n_seqs, a.n_kv_heads * ((group + 15) / 16), a.n_splits);
+  config.gridDim = dim3(a.n_kv_heads * ((group + 15) / 16), n_seqs, a.n_splits);
   config.blockDim = dim3(DT_THREADS);
   config.dynamicSmemBytes = smem;
   config.stream = stream;
@@ -559,13 +614,14 @@ MLL_API int mll_attn_decode_tma_supported(int dtype, int head_dim) {
 // n_splits > 1, scratch and counters (int32, one per (sequence, kv head x head chunk), zero
 // before the first launch; left zero) are required: the last block of a group merges the splits.
 // cluster_merge != 0: with 2 to 16 splits the blocks of a group form a thread-block cluster and merge
-// through distributed shared memory instead (scratch and counters stay untouched).
+// through distributed shared memory instead (scratch and counters stay untouched).  seq_order: optional
+// permutation of 0 .. n_seqs - 1; the blocks of sequence seq_order[0] start first (give the longest first).
 MLL_API int mll_attn_decode_tma(const void* q, const void* qkv, int qkv_ld, const float* cos_table,
                                 const float* sin_table, int interleaved, int write_kv, void* k_cache, void* v_cache,
                                 long long n_pages, const int* seq_slot, const int* seq_ctx, const int* block_table,
                                 float* scratch, void* out, int n_seqs, int n_heads, int n_kv_heads, int head_dim,
                                 int max_blocks, int n_splits, int window, float scale, int* counters,
-                                int cluster_merge, cudaStream_t stream) {
+                                int cluster_merge, const int* seq_order, cudaStream_t stream) {
   MLL_REQUIRE(mll_attn_decode_tma_supported(MLL_BF16, head_dim), "attention decode (tma): head_dim %d", head_dim);
   MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention decode (tma): bad head counts");
   MLL_REQUIRE(n_seqs >= 0 && n_splits >= 1 && n_splits <= 65535, "attention decode (tma): bad batch or split count");
@@ -589,7 +645,7 @@ MLL_API int mll_attn_decode_tma(const void* q, const void* qkv, int qkv_ld, cons
                        (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, n_splits, window, scale, counters,
                        (const __nv_bfloat16*)qkv, fused ? cos_table : nullptr, fused ? sin_table : nullptr,
                        fused && write_kv ? (__nv_bfloat16*)k_cache : nullptr,
-                       fused && write_kv ? (__nv_bfloat16*)v_cache : nullptr, qkv_ld, interleaved};
+                       fused && write_kv ? (__nv_bfloat16*)v_cache : nullptr, qkv_ld, interleaved, seq_order};
   if (head_dim == 64)
     return fused ? mll::launch_decode_tma<64, true>(kmap, vmap, a, n_seqs, cluster_merge, stream)
                  : mll::launch_decode_tma<64, false>(kmap, vmap, a, n_seqs, cluster_merge, stream);

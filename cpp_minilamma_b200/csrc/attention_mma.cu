@@ -336,7 +336,7 @@ attn_decode_mma_kernel(DecodeMmaArgs a) {
   }
   if (n_eff == 1 || a.counters == nullptr) return;
 
-  merge_decode_splits<D, 128>(a, b, h0, ng, n_eff, reinterpret_cast<float*>(smem_raw));
+  merge_decode_splits<D, 128>(a, b, blockIdx.y, gridDim.y, h0, ng, n_eff, reinterpret_cast<float*>(smem_raw));
 }
 
 template <int D, int STAGES, bool FUSED>

@@ -14,7 +14,7 @@ import torch
 from ..cache.paged import PAGE  # cache positions per page; the library's MLL_PAGE is checked against it on load
 from .build import KernelBuildError, load_library
 
-ABI_VERSION = 20
+ABI_VERSION = 21
 MAX_TOP_K = 1024
 
 
@@ -496,9 +496,11 @@ USE_TCGEN05_PREFILL = True      # off: the mma.sync kernel takes the tensor-core
 
 def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch, out, n_seqs: int,
                      n_heads: int, n_kv_heads: int, head_dim: int, n_splits: int, window: int,
-                     scale: float, counters: Optional[torch.Tensor] = None) -> None:
+                     scale: float, counters: Optional[torch.Tensor] = None, order: Optional[torch.Tensor] = None) -> None:
     """One query token per sequence (q row i belongs to sequence i) over the paged cache.
-    bfloat16 with head_dim 64/128/256 runs on tensor cores, everything else on the general kernel."""
+    bfloat16 with head_dim 64/128/256 runs on tensor cores, everything else on the general kernel.
+    `order`: optional int32 permutation of the sequences, longest context first; the TMA-fed kernel starts its
+    blocks in that order so that short sequences fill the end of the launch (the others ignore it)."""
     _check_attention(q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim)
     _need(seq_slot, "attention seq_slot", torch.int32, 1)
     _need(seq_ctx, "attention seq_ctx", torch.int32, 1)
@@ -517,7 +519,7 @@ def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratc
             raise KernelError("attention decode: counters shorter than sequences x kv heads x head chunks")
     if q.dtype == torch.bfloat16 and _tma_decode(q, None, None, None, False, False, k_cache, v_cache, seq_slot, seq_ctx,
                                                 block_table, scratch, out, n_seqs, n_heads, n_kv_heads, head_dim,
-                                                n_splits, window, scale, counters):
+                                                n_splits, window, scale, counters, _order(order, n_seqs)):
         return
     if USE_TENSOR_CORE_DECODE and lib().mll_attn_decode_mma_supported(code, head_dim):
         _check(lib().mll_attn_decode_mma(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx),
@@ -545,8 +547,16 @@ USE_TMA_DECODE = True    # off: the cp.async / mma.sync decode kernel also takes
 USE_CLUSTER_MERGE = True  # off: the TMA decode kernel merges its context splits through global memory and counters
 
 
+def _order(order, n_seqs: int):
+    if order is not None:
+        _need(order, "attention order", torch.int32, 1)
+        if order.shape[0] < n_seqs:
+            raise KernelError("attention decode: the order is shorter than the batch")
+    return order
+
+
 def _tma_decode(q, qkv, cos, sin, interleaved, write_kv, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch, out,
-                n_seqs, n_heads, n_kv_heads, head_dim, n_splits, window, scale, counters) -> bool:
+                n_seqs, n_heads, n_kv_heads, head_dim, n_splits, window, scale, counters, order=None) -> bool:
     """Runs the TMA-fed decode kernel when it takes the problem (bfloat16, head_dim 64/128, arrival
     counters whenever the context is split); returns whether it did."""
     if not (USE_TMA_DECODE and USE_TENSOR_CORE_DECODE and lib().mll_attn_decode_tma_supported(dtype_code(out.dtype), head_dim)):
@@ -560,7 +570,7 @@ def _tma_decode(q, qkv, cos, sin, interleaved, write_kv, k_cache, v_cache, seq_s
                                      ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim),
                                      ctypes.c_int(block_table.shape[1]), ctypes.c_int(n_splits), ctypes.c_int(window),
                                      ctypes.c_float(scale), _ptr(counters if n_splits > 1 else None),
-                                     ctypes.c_int(int(USE_CLUSTER_MERGE)), _stream()),
+                                     ctypes.c_int(int(USE_CLUSTER_MERGE)), _ptr(order), _stream()),
            "attention_decode (TMA, cluster merge)" if USE_CLUSTER_MERGE and 2 <= n_splits <= 16
            else "attention_decode (TMA)")
     return True
@@ -574,7 +584,8 @@ def attention_decode_fused_supported(dtype: torch.dtype, head_dim: int) -> bool:
 
 def attention_decode_fused(qkv, cos, sin, interleaved: bool, write_kv: bool, k_cache, v_cache, seq_slot, seq_ctx,
                            block_table, scratch, out, n_seqs: int, n_heads: int, n_kv_heads: int, head_dim: int,
-                           n_splits: int, window: int, scale: float, counters: Optional[torch.Tensor] = None) -> None:
+                           n_splits: int, window: int, scale: float, counters: Optional[torch.Tensor] = None,
+                           order: Optional[torch.Tensor] = None) -> None:
     """Decode step: row i of qkv [B, (Hq + 2 Hk) d] is sequence i's new token at position seq_ctx[i] - 1.
     Rotates q and k (tables as for rope_cache_write, or None), writes k and v into the paged cache and
     attends over it, in one launch (bfloat16, head_dim 64/128/256)."""
@@ -606,7 +617,7 @@ def attention_decode_fused(qkv, cos, sin, interleaved: bool, write_kv: bool, k_c
         if counters.shape[0] < n_seqs * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16):
             raise KernelError("attention decode: counters shorter than sequences x kv heads x head chunks")
     if _tma_decode(None, qkv, cos, sin, interleaved, write_kv, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch,
-                   out, n_seqs, n_heads, n_kv_heads, head_dim, n_splits, window, scale, counters):
+                   out, n_seqs, n_heads, n_kv_heads, head_dim, n_splits, window, scale, counters, _order(order, n_seqs)):
         return
     _check(lib().mll_attn_decode_mma_fused(_ptr(qkv), ctypes.c_int(qkv.shape[1]), _ptr(cos), _ptr(sin),
                                            ctypes.c_int(int(interleaved)), ctypes.c_int(int(write_kv)), _ptr(k_cache),

@@ -95,16 +95,19 @@ class Attention(Mixer):
 
     # ---- step ------------------------------------------------------------- #
     def step_metadata_key(self):
-        return ("attention.prefill_tiles", PREFILL_TILE)  # every attention layer reads the same tile list
+        return ("attention.step_lists", PREFILL_TILE)  # every attention layer reads the same lists
 
     def prepare_step(self, shape):
         """The prefill kernels' work lists: one tile of up to PREFILL_TILE query rows per entry, as
         (sequence, first row within the sequence's new tokens), long contexts first so that the longest
         tiles start first; and the same in tiles of twice as many rows, for the kernel that works on those
         (a block per entry: no block is launched only to find that its rows belong to its neighbour).
-        Steps of single tokens need none."""
+        Steps of single tokens get the order in which the decode kernel starts its sequences instead: longest
+        context first, so that the short ones fill the end of the launch."""
         if shape.all_decode:
-            return {}
+            if shape.n_seqs < 2:
+                return {}
+            return {"decode_order": sorted(range(shape.n_seqs), key=lambda i: -(shape.starts[i] + shape.lens[i]))}
         order = sorted(range(shape.n_seqs), key=lambda i: -(shape.starts[i] + shape.lens[i]))
         lists = {"tile_seq": [], "tile_row0": []}
         wide = []
@@ -151,8 +154,9 @@ class Attention(Mixer):
         qkv = self.qkv.forward(step, h, "qkv")
         cos, sin = self.position.tables()
         out = step.ws.buffer("attn", (T, Hq * d), act)
-        splits, scratch, counters = 1, None, None
+        splits, scratch, counters, order = 1, None, None, None
         if step.all_decode:
+            order = step.meta.get(self.step_metadata_key(), {}).get("decode_order")
             fixed = step.fixed.get(self)
             splits = fixed["splits"] if fixed else self.decode_splits(step.n_seqs, step.max_ctx)
             # room for the most splits that this batch size can ever be given, from its first decode step on, so
@@ -168,7 +172,8 @@ class Attention(Mixer):
             # one launch: rotate q and k, write k and v into the cache, attend
             K.attention_decode_fused(qkv, cos, sin, self.position.interleaved, not self.reads_cache_only,
                                      cache.k, cache.v, step.seq_slot, step.seq_ctx, cache.block_table, scratch, out,
-                                     step.n_seqs, Hq, Hk, d, splits, self.window, self.scale, counters=counters)
+                                     step.n_seqs, Hq, Hk, d, splits, self.window, self.scale, counters=counters,
+                                     order=order)
         else:
             q = step.ws.buffer("q", (T, Hq * d), act)
             K.rope_cache_write(qkv, self.bias, cos, sin, step.tok_pos, step.tok_seq, step.seq_slot,
@@ -176,7 +181,8 @@ class Attention(Mixer):
                                self.position.interleaved, write_kv=not self.reads_cache_only)
             if step.all_decode:
                 K.attention_decode(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, cache.block_table, scratch, out,
-                                   step.n_seqs, Hq, Hk, d, splits, self.window, self.scale, counters=counters)
+                                   step.n_seqs, Hq, Hk, d, splits, self.window, self.scale, counters=counters,
+                                   order=order)
             else:
                 tiles = step.meta[self.step_metadata_key()]
                 K.attention_prefill(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,

@@ -338,6 +338,50 @@ def test_attention_decode_fused_with_rope_and_cache_write(hq, hk, d, interleaved
     np.testing.assert_allclose(as64(out), as64(out2), rtol=1.6e-2, atol=2.0 ** -8 * float(np.abs(v_new).max() + 4))
 
 
+@pytest.mark.parametrize("hq,hk,d", [(32, 8, 128), (16, 16, 64), (40, 2, 64)])
+@pytest.mark.parametrize("splits", [1, 3])
+@pytest.mark.parametrize("fused", [True, False])
+def test_attention_decode_in_a_given_order(hq, hk, d, splits, fused):
+    """The TMA-fed kernel starts the blocks of the sequences in the order it is given (longest first in the engine):
+    whatever the order, every sequence gets its own result, bit for bit the one of the plain order."""
+    dtype = torch.bfloat16
+    ctx = [1, 63, 64, 65, 700, 129, 2, 300]
+    B = len(ctx)
+    case = PagedCase(ctx, hk, d, dtype, seed=hq + d + 5)
+    qkv = rnd((B, (hq + 2 * hk) * d), dtype, 29)
+    kc, vc, slots, ctx_t, table_d = case.dev()
+    scratch = torch.empty(max(1, K.attention_decode_scratch_floats(B, hq, d, splits)), dtype=torch.float32, device=DEV)
+    counters = torch.zeros(B * hk * (-(-(hq // hk) // 16)), dtype=torch.int32, device=DEV)
+    outs = []
+    for order in (None, sorted(range(B), key=lambda i: -ctx[i]), [3, 0, 7, 1, 6, 2, 5, 4]):
+        order_t = None if order is None else torch.tensor(order, dtype=torch.int32, device=DEV)
+        out = torch.full((B, hq * d), float("nan"), dtype=dtype, device=DEV)
+        k2, v2 = kc.clone(), vc.clone()
+        if fused:
+            K.attention_decode_fused(qkv.to(DEV), None, None, False, True, k2, v2, slots, ctx_t, table_d, scratch, out,
+                                     B, hq, hk, d, splits, 0, 1.0 / math.sqrt(d), counters=counters, order=order_t)
+        else:
+            K.attention_decode(qkv[:, :hq * d].contiguous().to(DEV), k2, v2, slots, ctx_t, table_d, scratch, out,
+                               B, hq, hk, d, splits, 0, 1.0 / math.sqrt(d), counters=counters, order=order_t)
+        assert int(counters.abs().sum()) == 0 and K.take_device_error() == 0
+        outs.append(out)
+    x = as64(qkv)
+    for b, c in enumerate(ctx):
+        k_all, v_all = as64(case.k[b]).copy(), as64(case.v[b]).copy()
+        if fused:   # the step's own key and value take the last place
+            k_all[c - 1] = x[b, hq * d:(hq + hk) * d].reshape(hk, d)
+            v_all[c - 1] = x[b, (hq + hk) * d:].reshape(hk, d)
+        ref = pl.causal_attention(x[b:b + 1, :hq * d].reshape(1, hq, d), k_all, v_all, q_positions=[c - 1])
+        np.testing.assert_allclose(as64(outs[0][b]).reshape(hq, d), ref[0], **attention_tol(dtype, "tensor_core", v_all),
+                                   err_msg=f"seq {b} ctx {c}")
+    same = lambda a, b: torch.equal(a.view(torch.int16), b.view(torch.int16))
+    assert same(outs[0], outs[1]) and same(outs[0], outs[2])
+    with pytest.raises(K.KernelError):
+        K.attention_decode(qkv[:, :hq * d].contiguous().to(DEV), kc, vc, slots, ctx_t, table_d, scratch, outs[0], B, hq, hk, d,
+                           splits, 0, 1.0 / math.sqrt(d), counters=counters,
+                           order=torch.zeros(B - 1, dtype=torch.int32, device=DEV))
+
+
 @pytest.fixture(params=["tcgen05", "tensor_core", "general"])
 def prefill_impl(request):
     """tcgen05: the TMA/tensor-memory kernel (head sizes 64 and 128, else the next one);
