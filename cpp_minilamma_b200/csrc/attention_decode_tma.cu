@@ -44,7 +44,7 @@ namespace mll {
 
 constexpr int DT_STAGES = 3;
 constexpr int DT_THREADS = 160;  // four compute warps and the producer warp
-constexpr unsigned DT_SPIN_LIMIT = 4u << 20;
+constexpr long long DT_WAIT_CLOCKS = 2ll << 30;
 
 template <int D>
 struct DecodeTmaSmem {
@@ -60,23 +60,23 @@ struct DecodeTmaSmem {
 };
 
 __device__ __forceinline__ unsigned dt_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ bool dt_mbar_test(unsigned bar, unsigned parity) {
+// One try: the hardware parks the thread until the phase completes or a time limit of its own runs out (a spin
+// on test_wait would spend the multiprocessor's issue slots, which the other block's warps can use).
+__device__ __forceinline__ bool dt_mbar_try(unsigned bar, unsigned parity) {
   unsigned done;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(done) : "r"(bar), "r"(parity) : "memory");
   return done != 0;
 }
 __device__ __forceinline__ void dt_mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag) {
   if (*abort_flag) return;
-  for (unsigned spin = 0; spin < DT_SPIN_LIMIT; ++spin) {
-    if (dt_mbar_test(bar, parity)) return;
-    if (spin > 64) {
-      __nanosleep(32);
-      if ((spin & 255) == 0 && *abort_flag) return;
-    }
+  if (dt_mbar_try(bar, parity)) return;
+  const long long began = clock64();
+  while (clock64() - began < DT_WAIT_CLOCKS) {  // about a second: a load that has not come by then never will
+    if (dt_mbar_try(bar, parity) || *abort_flag) return;
   }
   *abort_flag = 1;
   atomicExch(&mll_attn_decode_tma_error_flag, 1);

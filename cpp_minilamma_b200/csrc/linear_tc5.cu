@@ -50,7 +50,7 @@ enum : int { CEPI_BF16 = 0, CEPI_F32 = 1, CEPI_SWIGLU = 2, CEPI_RESID = 3 };
 constexpr int C_ROWS = 128;     // weight rows per block (the MMA's M)
 constexpr int C_KB = 64;        // k elements per stage: one 128-byte swizzle span
 constexpr int C_THREADS = 256;  // 4 epilogue warps, then producer A, MMA A, producer B, MMA B (even / odd k-blocks)
-constexpr unsigned C_SPIN_LIMIT = 4u << 20;
+constexpr long long C_WAIT_CLOCKS = 2ll << 30;  // clocks a wait may take
 
 struct Tc5Args {
   const float* bias;
@@ -74,15 +74,18 @@ __device__ __forceinline__ bool c_mbar_test(unsigned bar, unsigned parity) {
   unsigned done;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(done) : "r"(bar), "r"(parity) : "memory");
   return done != 0;
 }
 __device__ __forceinline__ bool c_mbar_wait(unsigned bar, unsigned parity) {
-  for (unsigned spin = 0; spin < C_SPIN_LIMIT; ++spin) {
+  // each try parks the thread until the phase completes or a time limit of the hardware's own runs out (a spin
+  // on test_wait spends issue slots that the other warps of the multiprocessor can use); about a second in all
+  if (c_mbar_test(bar, parity)) return true;
+  const long long began = clock64();
+  while (clock64() - began < C_WAIT_CLOCKS) {
     if (c_mbar_test(bar, parity)) return true;
-    if (spin > 64) __nanosleep(40);
   }
   atomicExch(&mll_tc5_error_flag, 1);
   return false;
