@@ -45,7 +45,7 @@ __device__ int mll_attn_tc5_error_flag = 0;
 namespace mll {
 
 constexpr int A_ROWS = 128;  // query rows per block (the MMA's M)
-constexpr unsigned A_SPIN_LIMIT = 4u << 20;
+constexpr long long A_WAIT_CLOCKS = 2ll << 30;  // clocks a wait may take (about a second)
 
 struct PrefillTc5Args {
   const int* seq_slot;
@@ -71,15 +71,16 @@ __device__ __forceinline__ bool a_mbar_test(unsigned bar, unsigned parity) {
   unsigned done;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(done) : "r"(bar), "r"(parity) : "memory");
   return done != 0;
 }
 __device__ __forceinline__ bool a_mbar_wait(unsigned bar, unsigned parity) {
-  for (unsigned spin = 0; spin < A_SPIN_LIMIT; ++spin) {
+  if (a_mbar_test(bar, parity)) return true;
+  const long long began = clock64();
+  while (clock64() - began < A_WAIT_CLOCKS) {
     if (a_mbar_test(bar, parity)) return true;
-    if (spin > 256) __nanosleep(32);
   }
   atomicExch(&mll_attn_tc5_error_flag, 1);
   return false;
