@@ -246,45 +246,66 @@ __device__ __forceinline__ void a_mbar_arrive(unsigned bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-// Warps 0-3: one query row per thread; warp 4: TMA loads; warp 5: MMAs; warps 6 and 7 only fill the second
-// warpgroup.  Eight warps put two warps of every block on each of the multiprocessor's four schedulers, so a
-// new block fits as soon as one of the two resident blocks leaves.  With six warps of 168 registers it did
-// not: the schedulers' register files held exactly three such warps each, a block put two warps on two of
-// the schedulers and one on the others, and the next block's warps mostly fell on the wrong ones - the freed
-// place stayed empty until the other block had ended as well (a 2,048-token prompt: 62 us, of which the
-// longest block ran 47).  The block is launched with 128 registers per thread; the softmax warpgroup then
-// takes 168 (setmaxnreg) and the other warpgroup gives back all but 40.
-constexpr int A_THREADS = 256;
+// One block works on TILES (1 or 2) query tiles of 128 rows: the same rows of TILES neighbouring heads, which
+// share their kv head and so every key and value page.
+//
+// One tile a block: warps 0-3: one query row per thread; warp 4: TMA loads; warp 5: MMAs; warps 6 and 7 only
+// fill the second warpgroup.  Eight warps put two warps of every block on each of the multiprocessor's four
+// schedulers, so a new block fits as soon as one of the two resident blocks leaves.  With six warps of 168
+// registers it did not: the schedulers' register files held exactly three such warps each, a block put two
+// warps on two of the schedulers and one on the others, and the next block's warps mostly fell on the wrong
+// ones - the freed place stayed empty until the other block had ended as well (a 2,048-token prompt: 62 us,
+// of which the longest block ran 47).  The block is launched with 128 registers per thread; the softmax
+// warpgroup then takes 168 (setmaxnreg) and the other warpgroup gives back all but 40.
+//
+// Two tiles a block (an even number of query heads per kv head): warps 0-3 and 4-7 are the softmax of tile 0
+// and tile 1, warp 8 loads, warp 9 issues the MMAs of both tiles, warps 10 and 11 fill the third warpgroup
+// (twelve warps of 168 registers: the whole register file, no setmaxnreg).  One block a multiprocessor, all
+// 512 columns of tensor memory, a key/value ring of four stages.  Two blocks of one tile each have two
+// threads issuing MMAs into one tensor pipe: an MMA is accepted only when the pipe has room, so each thread
+// waits out the other's MMAs too, and a clock trace showed the MMA thread's loop (12 MMAs a page, 1,700 clocks
+// of issuing for 640 clocks of work, plus its waits) to be the block's period, 2,300 clocks a page, with the
+// softmax warps idle half of the time.  One thread issuing for both tiles waits for nobody, and each key and
+// value page is loaded once for two tiles.
 constexpr int A_SOFTMAX_REGS = 168, A_OTHER_REGS = 40;
 constexpr float A_RESCALE_STEP = 8.f;  // the output is rescaled only when a row's maximum grows by more than 2^8
 
-template <int D>
+template <int D, int TILES>
 struct PrefillTc5Smem {
-  static constexpr int Q_BYTES = A_ROWS * D * 2;       // D / 64 boxes of [128 rows x 128 bytes]
+  static constexpr int THREADS = TILES == 1 ? 256 : 384;
+  static constexpr int KV_STAGES = TILES == 1 ? 2 : 4;
+  static constexpr int Q_BYTES = A_ROWS * D * 2;       // D / 64 boxes of [128 rows x 128 bytes], per tile
   static constexpr int KV_BYTES = MLL_PAGE * D * 2;    // D / 64 boxes of [64 rows x 128 bytes]
-  static constexpr int Q_OFF = 0, K_OFF = Q_BYTES, V_OFF = K_OFF + 2 * KV_BYTES;
-  static constexpr int BAR_OFF = V_OFF + 2 * KV_BYTES;
-  // Two blocks per multiprocessor (their tensor memory: 2 x 256 columns); never three: the request
+  static constexpr int Q_OFF = 0, K_OFF = TILES * Q_BYTES, V_OFF = K_OFF + KV_STAGES * KV_BYTES;
+  static constexpr int BAR_OFF = V_OFF + KV_STAGES * KV_BYTES;
+  // One tile: two blocks per multiprocessor (their tensor memory: 2 x 256 columns); never three: the request
   // is padded above a third of the shared memory.  The kernel checks that its dynamic shared
   // memory starts on a 1024-byte boundary (the swizzle's period) and refuses otherwise.
-  static constexpr size_t USED = (size_t)BAR_OFF + 256;
-  static constexpr size_t BYTES = USED > 80 * 1024 ? USED : 80 * 1024;
-  static constexpr int TMEM_COLS = 256;                // S / P: 2 x 64, O: up to 128
+  static constexpr size_t USED = (size_t)BAR_OFF + 512;
+  static constexpr size_t BYTES = (TILES == 1 && USED < 80 * 1024) ? 80 * 1024 : USED;
+  static constexpr int TILE_COLS = 256;                // per tile: S / P: 2 x 64, O: up to 128
+  static constexpr int TMEM_COLS = TILES * TILE_COLS;
   static constexpr int O_COL = 128;
+  // barrier slots: the queries; keys and values full / empty per ring stage; per tile and S buffer: S full,
+  // P ready, P V done
+  static constexpr int AB_Q = 0, AB_K_FULL = 1, AB_V_FULL = AB_K_FULL + KV_STAGES, AB_K_EMPTY = AB_V_FULL + KV_STAGES,
+                       AB_V_EMPTY = AB_K_EMPTY + KV_STAGES, AB_S_FULL = AB_V_EMPTY + KV_STAGES,
+                       AB_P_READY = AB_S_FULL + 2 * TILES, AB_PV_DONE = AB_P_READY + 2 * TILES,
+                       AB_COUNT = AB_PV_DONE + 2 * TILES;
+  static_assert(AB_COUNT * 8 + 16 <= 512, "the barriers must fit behind the tiles");
 };
 
-// barrier slots
-enum : int { AB_Q = 0, AB_K_FULL = 1, AB_V_FULL = 3, AB_K_EMPTY = 5, AB_V_EMPTY = 7, AB_S_FULL = 9, AB_P_READY = 11,
-             AB_PV_DONE = 13, AB_COUNT = 15 };
-
-template <int D>
-__global__ void __launch_bounds__(A_THREADS, 2)
+template <int D, int TILES>
+__global__ void __launch_bounds__(PrefillTc5Smem<D, TILES>::THREADS, TILES == 1 ? 2 : 1)
 attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                         const __grid_constant__ CUtensorMap vmap, PrefillTc5Args a) {
-  using L = PrefillTc5Smem<D>;
+  using L = PrefillTc5Smem<D, TILES>;
   constexpr int DB = D / 64;  // 64-column boxes per row of Q, K or V
+  constexpr int KS = L::KV_STAGES;
+  constexpr int LOAD_WARP = 4 * TILES, MMA_WARP = 4 * TILES + 1, PV_WARP = 4 * TILES + 2;
   // later tiles of a sequence see more keys: they go first, so that the short ones fill the tail
-  const int tile = (gridDim.x - 1 - blockIdx.x) / a.n_heads;   // all heads of a tile are neighbours
+  const int head_blocks = a.n_heads / TILES;
+  const int tile = (gridDim.x - 1 - blockIdx.x) / head_blocks;   // all heads of a tile are neighbours
   const int row0 = a.tile_row0[tile];
   if (row0 % A_ROWS != 0) return;  // the second half of a 128-row tile
 
@@ -295,8 +316,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
     return;
   }
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(base + L::BAR_OFF);
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + AB_COUNT);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + AB_COUNT) + 1;
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + L::AB_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + L::AB_COUNT) + 1;
   const unsigned q_s = a_smem(base + L::Q_OFF), k_s = a_smem(base + L::K_OFF), v_s = a_smem(base + L::V_OFF);
   auto bar = [&](int slot, int index) { return a_smem(bars + slot + index); };
   // a wait that gives up makes every later wait of the block return at once
@@ -307,8 +328,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int seq = a.tile_seq[tile];
-  const int h = blockIdx.x % a.n_heads;
-  const int kvh = h / (a.n_heads / a.n_kv_heads);
+  const int h0 = (blockIdx.x % head_blocks) * TILES;   // the block's first head
+  const int kvh = h0 / (a.n_heads / a.n_kv_heads);
   const int ctx = a.seq_ctx[seq], qlen = a.seq_qlen[seq], qstart = a.seq_qstart[seq];
   const int rows = min(A_ROWS, qlen - row0);
   const int pos0 = ctx - qlen + row0;
@@ -318,12 +339,12 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
   const int n_pages = p_last - p_first + 1;
 
   if (tid == 0) {
-    for (int i = 0; i < AB_COUNT; ++i)
-      a_mbar_init(a_smem(bars + i), (i == AB_P_READY || i == AB_P_READY + 1) ? A_ROWS : 1);
+    for (int i = 0; i < L::AB_COUNT; ++i)
+      a_mbar_init(a_smem(bars + i), (i >= L::AB_P_READY && i < L::AB_PV_DONE) ? A_ROWS : 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) {
+  if (warp == MMA_WARP) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(a_smem(tmem_slot)),
                  "r"((unsigned)L::TMEM_COLS));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
@@ -333,101 +354,124 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
   a_fence_after();
   const unsigned tmem_base = *tmem_slot;
 
-  if (warp >= 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(A_OTHER_REGS));
-  if (warp == 4) {
-    // ---- loads: the query tile once, then key and value pages into a two-stage ring -------- //
+  if (TILES == 1 && warp >= 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(A_OTHER_REGS));
+  if (warp == LOAD_WARP) {
+    // ---- loads: the query tiles once, then key and value pages into the ring ---------------- //
     if (lane == 0) {
-      a_mbar_expect_tx(bar(AB_Q, 0), L::Q_BYTES);
+      a_mbar_expect_tx(bar(L::AB_Q, 0), TILES * L::Q_BYTES);
 #pragma unroll
-      for (int b = 0; b < DB; ++b)
-        a_tma_load_2d(q_s + b * (A_ROWS * 128), &qmap, h * D + b * 64, qstart + row0, bar(AB_Q, 0));
+      for (int t = 0; t < TILES; ++t)
+#pragma unroll
+        for (int b = 0; b < DB; ++b)
+          a_tma_load_2d(q_s + t * L::Q_BYTES + b * (A_ROWS * 128), &qmap, (h0 + t) * D + b * 64, qstart + row0,
+                        bar(L::AB_Q, 0));
       int page = table[p_first];
       for (int i = 0; i < n_pages && !*abort_flag; ++i) {
-        const int st = i & 1;
-        const unsigned parity = ((i >> 1) & 1) ^ 1;  // the stage's previous use (none for the first two pages)
+        const int st = i % KS;
+        const unsigned parity = ((i / KS) & 1) ^ 1;  // the stage's previous use (none in the first round)
         const int row = (page * a.n_kv_heads + kvh) * MLL_PAGE;
         if (i + 1 < n_pages) page = table[p_first + i + 1];  // looked up while this page's loads fly
-        wait(bar(AB_K_EMPTY, st), parity);
-        a_mbar_expect_tx(bar(AB_K_FULL, st), L::KV_BYTES);
+        wait(bar(L::AB_K_EMPTY, st), parity);
+        a_mbar_expect_tx(bar(L::AB_K_FULL, st), L::KV_BYTES);
 #pragma unroll
         for (int b = 0; b < DB; ++b)
-          a_tma_load_2d(k_s + st * L::KV_BYTES + b * (MLL_PAGE * 128), &kmap, b * 64, row, bar(AB_K_FULL, st));
-        wait(bar(AB_V_EMPTY, st), parity);
-        a_mbar_expect_tx(bar(AB_V_FULL, st), L::KV_BYTES);
+          a_tma_load_2d(k_s + st * L::KV_BYTES + b * (MLL_PAGE * 128), &kmap, b * 64, row, bar(L::AB_K_FULL, st));
+        wait(bar(L::AB_V_EMPTY, st), parity);
+        a_mbar_expect_tx(bar(L::AB_V_FULL, st), L::KV_BYTES);
 #pragma unroll
         for (int b = 0; b < DB; ++b)
-          a_tma_load_2d(v_s + st * L::KV_BYTES + b * (MLL_PAGE * 128), &vmap, b * 64, row, bar(AB_V_FULL, st));
+          a_tma_load_2d(v_s + st * L::KV_BYTES + b * (MLL_PAGE * 128), &vmap, b * 64, row, bar(L::AB_V_FULL, st));
       }
     }
-  } else if (warp == 5) {
-    // ---- MMAs: S_{i+1} = Q K_{i+1}^T is issued before O += P_i V_i, so it runs under softmax i //
+  } else if (warp == MMA_WARP) {
+    // ---- S = Q K^T, one thread.  S_i goes into buffer i % 2, which held P_{i-2}: it waits for that page's P V.
     if (lane == 0) {
-      constexpr unsigned idesc_s = a_idesc(A_ROWS, MLL_PAGE, false), idesc_o = a_idesc(A_ROWS, D, true);
+      constexpr unsigned idesc_s = a_idesc(A_ROWS, MLL_PAGE, false);
       // The descriptors are built once; a step inside a tile only adds to the address field (16-byte units, 14
       // bits: the tiles lie in the first 256 KB of shared memory, so the sum cannot carry out of it).  Built
-      // anew for every instruction they cost this thread some twenty dependent instructions per MMA, which it
-      // has to issue between those of two busy softmax warps on its scheduler: the MMAs then went out at 115 to
-      // 230 clocks apiece where the tensor cores take 48 (N = 64) or 64 (N = 128).
-      const unsigned long long q_desc = a_desc(q_s, 16);
-      const unsigned long long k_desc[2] = {a_desc(k_s, 16), a_desc(k_s + L::KV_BYTES, 16)};
-      const unsigned long long v_desc[2] = {a_desc(v_s, MLL_PAGE * 128), a_desc(v_s + L::KV_BYTES, MLL_PAGE * 128)};
-      auto issue_s = [&](int i) {
-        const unsigned long long kd = k_desc[i & 1];
-        const unsigned d = tmem_base + (i & 1) * MLL_PAGE;
+      // anew for every instruction they cost this thread some twenty dependent instructions per MMA.
+      unsigned long long q_desc[TILES], k_desc[KS];
 #pragma unroll
-        for (int b = 0; b < DB; ++b)
+      for (int t = 0; t < TILES; ++t) q_desc[t] = a_desc(q_s + t * L::Q_BYTES, 16);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            a_umma(d, q_desc + (unsigned long long)((b * (A_ROWS * 128) + k * 32) >> 4),
-                   kd + (unsigned long long)((b * (MLL_PAGE * 128) + k * 32) >> 4), idesc_s, (b > 0 || k > 0) ? 1u : 0u);
-        a_commit(bar(AB_S_FULL, i & 1));
-        a_commit(bar(AB_K_EMPTY, i & 1));
-      };
-      wait(bar(AB_Q, 0), 0);
-      wait(bar(AB_K_FULL, 0), 0);
-      a_fence_after();
-      if (!*abort_flag) issue_s(0);
+      for (int s = 0; s < KS; ++s) k_desc[s] = a_desc(k_s + s * L::KV_BYTES, 16);
+      wait(bar(L::AB_Q, 0), 0);
       for (int i = 0; i < n_pages && !*abort_flag; ++i) {
-        const int st = i & 1;
-        if (i + 1 < n_pages) {
-          // S[(i + 1) % 2] held P of page i - 1: the MMAs of one thread run in order, and that
-          // page's P V was issued before
-          wait(bar(AB_K_FULL, st ^ 1), ((i + 1) >> 1) & 1);
-          a_fence_after();
-          if (!*abort_flag) issue_s(i + 1);
-        }
-        wait(bar(AB_P_READY, st), (i >> 1) & 1);
-        wait(bar(AB_V_FULL, st), (i >> 1) & 1);
-        a_fence_after();
-        if (*abort_flag) break;
-        const unsigned long long vd = v_desc[st];
+        const int sb = i & 1, st = i % KS;
+        unsigned long long kd = k_desc[0];
 #pragma unroll
-        for (int k = 0; k < 4; ++k)  // P: 16 keys = 8 packed columns per step
-          a_umma_ts(tmem_base + L::O_COL, tmem_base + st * MLL_PAGE + k * 8, vd + (unsigned long long)((k * (16 * 128)) >> 4),
-                    idesc_o, (i > 0 || k > 0) ? 1u : 0u);
-        a_commit(bar(AB_PV_DONE, st));
-        a_commit(bar(AB_V_EMPTY, st));
+        for (int s = 1; s < KS; ++s)
+          if (st == s) kd = k_desc[s];
+        wait(bar(L::AB_K_FULL, st), (i / KS) & 1);
+#pragma unroll
+        for (int t = 0; t < TILES; ++t) {
+          if (i >= 2) wait(bar(L::AB_PV_DONE, 2 * t + sb), ((i - 2) >> 1) & 1);  // P_{i-2} has been read
+          a_fence_after();
+          if (*abort_flag) break;
+          const unsigned d = tmem_base + t * L::TILE_COLS + sb * MLL_PAGE;
+#pragma unroll
+          for (int b = 0; b < DB; ++b)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              a_umma(d, q_desc[t] + (unsigned long long)((b * (A_ROWS * 128) + k * 32) >> 4),
+                     kd + (unsigned long long)((b * (MLL_PAGE * 128) + k * 32) >> 4), idesc_s, (b > 0 || k > 0) ? 1u : 0u);
+          a_commit(bar(L::AB_S_FULL, 2 * t + sb));
+        }
+        if (*abort_flag) break;
+        a_commit(bar(L::AB_K_EMPTY, st));
       }
     }
-  } else if (warp < 4) {
-    // ---- softmax: thread tid owns query row tid = lane tid of tensor memory ---------------- //
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(A_SOFTMAX_REGS));
-    const unsigned tmem_row = tmem_base + ((unsigned)(warp * 32) << 16);
-    const int qpos = pos0 + tid;
+  } else if (warp == PV_WARP) {
+    // ---- O += P V, a thread of its own: with one thread for both products a page's MMAs went out one behind
+    // the other (75 clocks apiece for S, 135 for P V, and a hundred for every wait, even one that is over),
+    // 2,400 to 3,000 clocks a page of which the tensor cores worked 640, and the softmax warps waited
+    if (lane == 0) {
+      constexpr unsigned idesc_o = a_idesc(A_ROWS, D, true);
+      unsigned long long v_desc[KS];
+#pragma unroll
+      for (int s = 0; s < KS; ++s) v_desc[s] = a_desc(v_s + s * L::KV_BYTES, MLL_PAGE * 128);
+      for (int i = 0; i < n_pages && !*abort_flag; ++i) {
+        const int sb = i & 1, st = i % KS;
+        unsigned long long vd = v_desc[0];
+#pragma unroll
+        for (int s = 1; s < KS; ++s)
+          if (st == s) vd = v_desc[s];
+        wait(bar(L::AB_V_FULL, st), (i / KS) & 1);
+#pragma unroll
+        for (int t = 0; t < TILES; ++t) {
+          wait(bar(L::AB_P_READY, 2 * t + sb), (i >> 1) & 1);
+          a_fence_after();
+          if (*abort_flag) break;
+#pragma unroll
+          for (int k = 0; k < 4; ++k)  // P: 16 keys = 8 packed columns per step
+            a_umma_ts(tmem_base + t * L::TILE_COLS + L::O_COL, tmem_base + t * L::TILE_COLS + sb * MLL_PAGE + k * 8,
+                      vd + (unsigned long long)((k * (16 * 128)) >> 4), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+          a_commit(bar(L::AB_PV_DONE, 2 * t + sb));
+        }
+        if (*abort_flag) break;
+        a_commit(bar(L::AB_V_EMPTY, st));
+      }
+    }
+  } else if (warp < 4 * TILES) {
+    // ---- softmax: thread r of tile t owns query row r = lane r of tensor memory ---------------- //
+    if (TILES == 1) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(A_SOFTMAX_REGS));
+    const int t = warp >> 2, r = tid & (A_ROWS - 1);
+    const unsigned tmem_row = tmem_base + t * L::TILE_COLS + ((unsigned)((warp & 3) * 32) << 16);
+    const int qpos = pos0 + r;
     float m_used = -INFINITY, l_run = 0.f;  // the maximum that P and O are scaled by; the sum
     for (int i = 0; i < n_pages; ++i) {
-      const int st = i & 1;
-      wait(bar(AB_S_FULL, st), (i >> 1) & 1);
+      const int sb = i & 1, st = i % KS;
+      wait(bar(L::AB_S_FULL, 2 * t + sb), (i >> 1) & 1);
       a_fence_after();
       float s[MLL_PAGE];
-      a_tmem_ld64(tmem_row + st * MLL_PAGE, s);
+      a_tmem_ld64(tmem_row + sb * MLL_PAGE, s);
       const int k0 = (p_first + i) * MLL_PAGE;
       const bool needs_mask = (k0 + MLL_PAGE - 1 > pos0) || a.window > 0 || rows < A_ROWS;
       if (needs_mask) {
 #pragma unroll
         for (int c = 0; c < MLL_PAGE; ++c) {
           const int kpos = k0 + c;
-          const bool keep = tid < rows && kpos <= qpos && (a.window <= 0 || kpos > qpos - a.window);
+          const bool keep = r < rows && kpos <= qpos && (a.window <= 0 || kpos > qpos - a.window);
           s[c] = keep ? s[c] : -INFINITY;
         }
       }
@@ -445,15 +489,15 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
       const bool moved = mx > m_used + A_RESCALE_STEP || (m_used == -INFINITY && mx > -INFINITY);
       if (i > 0 && __any_sync(0xffffffffu, moved)) {
         const float alpha = moved ? a_exp2(m_used - mx) : 1.f;
-        wait(bar(AB_PV_DONE, st ^ 1), ((i - 1) >> 1) & 1);  // O holds every page before this one
+        wait(bar(L::AB_PV_DONE, 2 * t + (sb ^ 1)), ((i - 1) >> 1) & 1);  // O holds every page before this one
         a_fence_after();
 #pragma unroll
         for (int c = 0; c < D; c += 32) {
-          float t[32];
-          a_tmem_ld32(tmem_row + L::O_COL + c, t);
+          float o[32];
+          a_tmem_ld32(tmem_row + L::O_COL + c, o);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) t[j] *= alpha;
-          a_tmem_st32(tmem_row + L::O_COL + c, reinterpret_cast<const unsigned*>(t));
+          for (int j = 0; j < 32; ++j) o[j] *= alpha;
+          a_tmem_st32(tmem_row + L::O_COL + c, reinterpret_cast<const unsigned*>(o));
         }
         l_run *= alpha;
       }
@@ -486,41 +530,42 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
         a_unpack2(sum2[1], s2, s3);
         l_run += (s0 + s1) + (s2 + s3);
       }
-      a_tmem_st32(tmem_row + st * MLL_PAGE, packed);  // P over the first half of S
+      a_tmem_st32(tmem_row + sb * MLL_PAGE, packed);  // P over the first half of S
       const int valid = ctx - k0;  // positions of this page that the sequence has
-      if (valid < MLL_PAGE) {      // only the sequence's last page: the rest of it may hold anything
-        wait(bar(AB_V_FULL, st), (i >> 1) & 1);
+      if (valid < MLL_PAGE && t == 0) {  // only the sequence's last page: the rest of it may hold anything
+        // (the first tile's threads do it: the MMA thread has waited for their P before it issues any P V)
+        wait(bar(L::AB_V_FULL, st), (i / KS) & 1);
         unsigned char* vt = base + L::V_OFF + st * L::KV_BYTES;
         const int n_chunks = (MLL_PAGE - valid) * 8;  // 16-byte chunks per box
         for (int b = 0; b < DB; ++b)
-          for (int c = tid; c < n_chunks; c += A_ROWS)
+          for (int c = r; c < n_chunks; c += A_ROWS)
             *reinterpret_cast<uint4*>(vt + b * (MLL_PAGE * 128) + valid * 128 + c * 16) = make_uint4(0, 0, 0, 0);
         a_fence_async_smem();
       }
       a_tmem_wait_st();
       a_fence_before();
-      a_mbar_arrive(bar(AB_P_READY, st));
+      a_mbar_arrive(bar(L::AB_P_READY, 2 * t + sb));
     }
     // the output row: O / l
-    wait(bar(AB_PV_DONE, (n_pages - 1) & 1), ((n_pages - 1) >> 1) & 1);
+    wait(bar(L::AB_PV_DONE, 2 * t + ((n_pages - 1) & 1)), ((n_pages - 1) >> 1) & 1);
     a_fence_after();
     {
       // tcgen05.ld is a warp-wide instruction: every thread of the warp reads its lane, and only the
       // threads that own a row of the sequence store
-      const bool store = !*abort_flag && tid < rows;
+      const bool store = !*abort_flag && r < rows;
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* dst = a.out + ((size_t)qstart + row0 + (store ? tid : 0)) * a.n_heads * D + (size_t)h * D;
+      __nv_bfloat16* dst = a.out + ((size_t)qstart + row0 + (store ? r : 0)) * a.n_heads * D + (size_t)(h0 + t) * D;
 #pragma unroll
       for (int c = 0; c < D; c += 32) {
-        float t[32];
-        a_tmem_ld32(tmem_row + L::O_COL + c, t);
+        float o[32];
+        a_tmem_ld32(tmem_row + L::O_COL + c, o);
         if (store) {
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
             uint4 w;
             __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&w);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) hp[e] = __floats2bfloat162_rn(t[j + 2 * e] * inv, t[j + 2 * e + 1] * inv);
+            for (int e = 0; e < 4; ++e) hp[e] = __floats2bfloat162_rn(o[j + 2 * e] * inv, o[j + 2 * e + 1] * inv);
             *reinterpret_cast<uint4*>(dst + c + j) = w;
           }
         }
@@ -534,24 +579,25 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
   }
   __syncthreads();
-  if (warp == 5) {
+  if (warp == MMA_WARP) {
     a_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)L::TMEM_COLS));
   }
 }
 
-template <int D>
+template <int D, int TILES>
 int launch_prefill_tc5(const CUtensorMap& qmap, const CUtensorMap& kmap, const CUtensorMap& vmap,
                        const PrefillTc5Args& a, int n_tiles, cudaStream_t stream) {
-  const size_t smem = PrefillTc5Smem<D>::BYTES;
-  auto kernel = attn_prefill_tc5_kernel<D>;
+  using L = PrefillTc5Smem<D, TILES>;
+  const size_t smem = L::BYTES;
+  auto kernel = attn_prefill_tc5_kernel<D, TILES>;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (err != cudaSuccess) {
     mll_set_error("attention prefill (tcgen05): cannot reserve %zu bytes of shared memory: %s", smem,
                   cudaGetErrorString(err));
     return (int)err;
   }
-  MLL_LAUNCH((kernel), dim3((unsigned)(n_tiles * a.n_heads)), A_THREADS, smem, stream, qmap, kmap, vmap, a);
+  MLL_LAUNCH((kernel), dim3((unsigned)(n_tiles * (a.n_heads / TILES))), L::THREADS, smem, stream, qmap, kmap, vmap, a);
   MLL_LAUNCH_CHECK();
   return 0;
 }
@@ -568,6 +614,10 @@ extern "C" int* mll_attn_tc5_error_address() {
   }
   return address;
 }
+
+// Tests and measurements switch the two-tile blocks off to reach the one-tile kernel at every shape.
+static int mll_prefill_tc5_pairs = 1;
+MLL_API void mll_attn_prefill_tc5_set_pairs(int on) { mll_prefill_tc5_pairs = on != 0; }
 
 MLL_API int mll_attn_prefill_tc5_supported(int dtype, int head_dim) {
   return dtype == MLL_BF16 && (head_dim == 64 || head_dim == 128);
@@ -595,6 +645,11 @@ MLL_API int mll_attn_prefill_tc5(const void* q, const void* k_cache, const void*
   if (mll::tensor_map_bf16(v_cache, n_pages * n_kv_heads * MLL_PAGE, head_dim, MLL_PAGE, &vmap) != 0) return -1;
   mll::PrefillTc5Args a{seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0, block_table,
                         (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, window, scale * 1.4426950408889634f};
-  if (head_dim == 64) return mll::launch_prefill_tc5<64>(qmap, kmap, vmap, a, n_tiles, stream);
-  return mll::launch_prefill_tc5<128>(qmap, kmap, vmap, a, n_tiles, stream);
+  // two tiles a block where two neighbouring heads share a kv head
+  const bool pairs = (n_heads / n_kv_heads) % 2 == 0 && mll_prefill_tc5_pairs;
+  if (head_dim == 64)
+    return pairs ? mll::launch_prefill_tc5<64, 2>(qmap, kmap, vmap, a, n_tiles, stream)
+                 : mll::launch_prefill_tc5<64, 1>(qmap, kmap, vmap, a, n_tiles, stream);
+  return pairs ? mll::launch_prefill_tc5<128, 2>(qmap, kmap, vmap, a, n_tiles, stream)
+               : mll::launch_prefill_tc5<128, 1>(qmap, kmap, vmap, a, n_tiles, stream);
 }
