@@ -1,7 +1,7 @@
 // Causal attention of many query tokens over the paged cache on the fifth-generation tensor
 // cores: TMA -> shared memory -> tcgen05.mma -> tensor memory (bfloat16, head_dim 64 or 128).
 //
-// One block owns 128 query rows of one head.  Its six warps:
+// One block owns 128 query rows of one head.  Its warps:
 //   * warps 0-3, the softmax: thread i owns query row i, which is lane i of tensor memory, so the
 //     softmax needs no exchange between threads.  Per page of 64 keys a thread reads its row of S
 //     (tcgen05.ld), masks it where the page meets the diagonal, the window's edge or the end of the
@@ -9,12 +9,16 @@
 //     half of the S columns as packed bfloat16 (tcgen05.st);
 //   * warp 4, one thread: TMA loads with the 128-byte swizzle - the query tile once, then the key and
 //     the value pages (64 positions each) into a two-stage ring guarded by full / empty mbarriers;
-//   * warp 5, one thread: the MMAs.  S = Q K^T (M = 128 rows, N = 64 keys, both operands K-major) goes
-//     into one of two 64-column buffers of tensor memory, and the product of page i + 1 is issued
-//     before O += P_i V_i, so that it runs under the softmax of page i.  P V takes P as the
-//     tensor-memory A operand and the value page as it lies in the cache ([position][dim], MN-major)
-//     as B; O stays in tensor memory (64 or 128 further columns).  The warp also allocates and frees
-//     the block's 256 columns.
+//   * warp 5, one thread: S = Q K^T (M = 128 rows, N = 64 keys, both operands K-major) into one of two
+//     64-column buffers of tensor memory; S_i is issued as soon as page i's keys are there and the buffer's
+//     last user, O += P_{i-2} V_{i-2}, is done, so it runs under the softmax of page i - 1.  The warp also
+//     allocates and frees the block's 256 columns;
+//   * warp 6, one thread: O += P_i V_i, with P as the tensor-memory A operand and the value page as it lies
+//     in the cache ([position][dim], MN-major) as B; O stays in tensor memory (64 or 128 further columns).
+//     The two products have a thread each because a tcgen05.mma is accepted only when the tensor pipe has
+//     room and a wait costs about a hundred clocks even when it is over: one thread for both sent a page's
+//     twelve MMAs out one behind the other with its waits in between, 2,300 clocks a page of which the tensor
+//     cores worked 640, and the softmax warps waited (742 us for 8,192 tokens; 535 us with two threads).
 // O and P are scaled by a maximum that follows the row's true maximum only in steps of 2^8: O in
 // tensor memory is rescaled when a row's maximum has grown by more than that, which is rare, and
 // O / l does not depend on the scale, so the result is exact all the same.  Two blocks fit a
@@ -246,11 +250,8 @@ __device__ __forceinline__ void a_mbar_arrive(unsigned bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-// One block works on TILES (1 or 2) query tiles of 128 rows: the same rows of TILES neighbouring heads, which
-// share their kv head and so every key and value page.
-//
-// One tile a block: warps 0-3: one query row per thread; warp 4: TMA loads; warp 5: MMAs; warps 6 and 7 only
-// fill the second warpgroup.  Eight warps put two warps of every block on each of the multiprocessor's four
+// Warps 0-3: one query row per thread; warp 4: TMA loads; warp 5: the S MMAs; warp 6: the P V MMAs; warp 7 only
+// fills the second warpgroup.  Eight warps put two warps of every block on each of the multiprocessor's four
 // schedulers, so a new block fits as soon as one of the two resident blocks leaves.  With six warps of 168
 // registers it did not: the schedulers' register files held exactly three such warps each, a block put two
 // warps on two of the schedulers and one on the others, and the next block's warps mostly fell on the wrong
@@ -258,54 +259,47 @@ __device__ __forceinline__ void a_mbar_arrive(unsigned bar) {
 // of which the longest block ran 47).  The block is launched with 128 registers per thread; the softmax
 // warpgroup then takes 168 (setmaxnreg) and the other warpgroup gives back all but 40.
 //
-// Two tiles a block (an even number of query heads per kv head): warps 0-3 and 4-7 are the softmax of tile 0
-// and tile 1, warp 8 loads, warp 9 issues the MMAs of both tiles, warps 10 and 11 fill the third warpgroup
-// (twelve warps of 168 registers: the whole register file, no setmaxnreg).  One block a multiprocessor, all
-// 512 columns of tensor memory, a key/value ring of four stages.  Two blocks of one tile each have two
-// threads issuing MMAs into one tensor pipe: an MMA is accepted only when the pipe has room, so each thread
-// waits out the other's MMAs too, and a clock trace showed the MMA thread's loop (12 MMAs a page, 1,700 clocks
-// of issuing for 640 clocks of work, plus its waits) to be the block's period, 2,300 clocks a page, with the
-// softmax warps idle half of the time.  One thread issuing for both tiles waits for nobody, and each key and
-// value page is loaded once for two tiles.
+// Tried and taken out again: blocks of two tiles (the same rows of two heads that share a kv head: eight softmax
+// warps, one block a multiprocessor, all 512 columns of tensor memory, a four-stage key/value ring, each page
+// loaded once for both tiles).  877 against 1,027 TFLOP/s at 8,192 tokens: what bounds the kernel is the chain
+// softmax -> P V -> S -> softmax of each S buffer (3,500 clocks for two pages, a quarter of it hand-overs), and
+// two blocks of one tile have the same number of chains but two threads for each product.
 constexpr int A_SOFTMAX_REGS = 168, A_OTHER_REGS = 40;
 constexpr float A_RESCALE_STEP = 8.f;  // the output is rescaled only when a row's maximum grows by more than 2^8
 
-template <int D, int TILES>
+template <int D>
 struct PrefillTc5Smem {
-  static constexpr int THREADS = TILES == 1 ? 256 : 384;
-  static constexpr int KV_STAGES = TILES == 1 ? 2 : 4;
-  static constexpr int Q_BYTES = A_ROWS * D * 2;       // D / 64 boxes of [128 rows x 128 bytes], per tile
+  static constexpr int THREADS = 256;
+  static constexpr int KV_STAGES = 2;
+  static constexpr int Q_BYTES = A_ROWS * D * 2;       // D / 64 boxes of [128 rows x 128 bytes]
   static constexpr int KV_BYTES = MLL_PAGE * D * 2;    // D / 64 boxes of [64 rows x 128 bytes]
-  static constexpr int Q_OFF = 0, K_OFF = TILES * Q_BYTES, V_OFF = K_OFF + KV_STAGES * KV_BYTES;
+  static constexpr int Q_OFF = 0, K_OFF = Q_BYTES, V_OFF = K_OFF + KV_STAGES * KV_BYTES;
   static constexpr int BAR_OFF = V_OFF + KV_STAGES * KV_BYTES;
-  // One tile: two blocks per multiprocessor (their tensor memory: 2 x 256 columns); never three: the request
+  // Two blocks per multiprocessor (their tensor memory: 2 x 256 columns); never three: the request
   // is padded above a third of the shared memory.  The kernel checks that its dynamic shared
   // memory starts on a 1024-byte boundary (the swizzle's period) and refuses otherwise.
   static constexpr size_t USED = (size_t)BAR_OFF + 512;
-  static constexpr size_t BYTES = (TILES == 1 && USED < 80 * 1024) ? 80 * 1024 : USED;
-  static constexpr int TILE_COLS = 256;                // per tile: S / P: 2 x 64, O: up to 128
-  static constexpr int TMEM_COLS = TILES * TILE_COLS;
+  static constexpr size_t BYTES = USED < 80 * 1024 ? 80 * 1024 : USED;
+  static constexpr int TMEM_COLS = 256;                // S / P: 2 x 64, O: up to 128
   static constexpr int O_COL = 128;
-  // barrier slots: the queries; keys and values full / empty per ring stage; per tile and S buffer: S full,
-  // P ready, P V done
+  // barrier slots: the queries; keys and values full / empty per ring stage; per S buffer: S full, P ready,
+  // P V done
   static constexpr int AB_Q = 0, AB_K_FULL = 1, AB_V_FULL = AB_K_FULL + KV_STAGES, AB_K_EMPTY = AB_V_FULL + KV_STAGES,
                        AB_V_EMPTY = AB_K_EMPTY + KV_STAGES, AB_S_FULL = AB_V_EMPTY + KV_STAGES,
-                       AB_P_READY = AB_S_FULL + 2 * TILES, AB_PV_DONE = AB_P_READY + 2 * TILES,
-                       AB_COUNT = AB_PV_DONE + 2 * TILES;
+                       AB_P_READY = AB_S_FULL + 2, AB_PV_DONE = AB_P_READY + 2, AB_COUNT = AB_PV_DONE + 2;
   static_assert(AB_COUNT * 8 + 16 <= 512, "the barriers must fit behind the tiles");
 };
 
-template <int D, int TILES>
-__global__ void __launch_bounds__(PrefillTc5Smem<D, TILES>::THREADS, TILES == 1 ? 2 : 1)
+template <int D>
+__global__ void __launch_bounds__(PrefillTc5Smem<D>::THREADS, 2)
 attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                         const __grid_constant__ CUtensorMap vmap, PrefillTc5Args a) {
-  using L = PrefillTc5Smem<D, TILES>;
+  using L = PrefillTc5Smem<D>;
   constexpr int DB = D / 64;  // 64-column boxes per row of Q, K or V
   constexpr int KS = L::KV_STAGES;
-  constexpr int LOAD_WARP = 4 * TILES, MMA_WARP = 4 * TILES + 1, PV_WARP = 4 * TILES + 2;
+  constexpr int LOAD_WARP = 4, MMA_WARP = 5, PV_WARP = 6;
   // later tiles of a sequence see more keys: they go first, so that the short ones fill the tail
-  const int head_blocks = a.n_heads / TILES;
-  const int tile = (gridDim.x - 1 - blockIdx.x) / head_blocks;   // all heads of a tile are neighbours
+  const int tile = (gridDim.x - 1 - blockIdx.x) / a.n_heads;   // all heads of a tile are neighbours
   const int row0 = a.tile_row0[tile];
   if (row0 % A_ROWS != 0) return;  // the second half of a 128-row tile
 
@@ -328,8 +322,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int seq = a.tile_seq[tile];
-  const int h0 = (blockIdx.x % head_blocks) * TILES;   // the block's first head
-  const int kvh = h0 / (a.n_heads / a.n_kv_heads);
+  const int h = blockIdx.x % a.n_heads;
+  const int kvh = h / (a.n_heads / a.n_kv_heads);
   const int ctx = a.seq_ctx[seq], qlen = a.seq_qlen[seq], qstart = a.seq_qstart[seq];
   const int rows = min(A_ROWS, qlen - row0);
   const int pos0 = ctx - qlen + row0;
@@ -354,17 +348,14 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
   a_fence_after();
   const unsigned tmem_base = *tmem_slot;
 
-  if (TILES == 1 && warp >= 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(A_OTHER_REGS));
+  if (warp >= 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(A_OTHER_REGS));
   if (warp == LOAD_WARP) {
-    // ---- loads: the query tiles once, then key and value pages into the ring ---------------- //
+    // ---- loads: the query tile once, then key and value pages into the ring ----------------- //
     if (lane == 0) {
-      a_mbar_expect_tx(bar(L::AB_Q, 0), TILES * L::Q_BYTES);
+      a_mbar_expect_tx(bar(L::AB_Q, 0), L::Q_BYTES);
 #pragma unroll
-      for (int t = 0; t < TILES; ++t)
-#pragma unroll
-        for (int b = 0; b < DB; ++b)
-          a_tma_load_2d(q_s + t * L::Q_BYTES + b * (A_ROWS * 128), &qmap, (h0 + t) * D + b * 64, qstart + row0,
-                        bar(L::AB_Q, 0));
+      for (int b = 0; b < DB; ++b)
+        a_tma_load_2d(q_s + b * (A_ROWS * 128), &qmap, h * D + b * 64, qstart + row0, bar(L::AB_Q, 0));
       int page = table[p_first];
       for (int i = 0; i < n_pages && !*abort_flag; ++i) {
         const int st = i % KS;
@@ -390,9 +381,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
       // The descriptors are built once; a step inside a tile only adds to the address field (16-byte units, 14
       // bits: the tiles lie in the first 256 KB of shared memory, so the sum cannot carry out of it).  Built
       // anew for every instruction they cost this thread some twenty dependent instructions per MMA.
-      unsigned long long q_desc[TILES], k_desc[KS];
-#pragma unroll
-      for (int t = 0; t < TILES; ++t) q_desc[t] = a_desc(q_s + t * L::Q_BYTES, 16);
+      const unsigned long long q_desc = a_desc(q_s, 16);
+      unsigned long long k_desc[KS];
 #pragma unroll
       for (int s = 0; s < KS; ++s) k_desc[s] = a_desc(k_s + s * L::KV_BYTES, 16);
       wait(bar(L::AB_Q, 0), 0);
@@ -403,21 +393,17 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
         for (int s = 1; s < KS; ++s)
           if (st == s) kd = k_desc[s];
         wait(bar(L::AB_K_FULL, st), (i / KS) & 1);
-#pragma unroll
-        for (int t = 0; t < TILES; ++t) {
-          if (i >= 2) wait(bar(L::AB_PV_DONE, 2 * t + sb), ((i - 2) >> 1) & 1);  // P_{i-2} has been read
-          a_fence_after();
-          if (*abort_flag) break;
-          const unsigned d = tmem_base + t * L::TILE_COLS + sb * MLL_PAGE;
-#pragma unroll
-          for (int b = 0; b < DB; ++b)
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-              a_umma(d, q_desc[t] + (unsigned long long)((b * (A_ROWS * 128) + k * 32) >> 4),
-                     kd + (unsigned long long)((b * (MLL_PAGE * 128) + k * 32) >> 4), idesc_s, (b > 0 || k > 0) ? 1u : 0u);
-          a_commit(bar(L::AB_S_FULL, 2 * t + sb));
-        }
+        if (i >= 2) wait(bar(L::AB_PV_DONE, sb), ((i - 2) >> 1) & 1);  // P_{i-2} has been read
+        a_fence_after();
         if (*abort_flag) break;
+        const unsigned d = tmem_base + sb * MLL_PAGE;
+#pragma unroll
+        for (int b = 0; b < DB; ++b)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            a_umma(d, q_desc + (unsigned long long)((b * (A_ROWS * 128) + k * 32) >> 4),
+                   kd + (unsigned long long)((b * (MLL_PAGE * 128) + k * 32) >> 4), idesc_s, (b > 0 || k > 0) ? 1u : 0u);
+        a_commit(bar(L::AB_S_FULL, sb));
         a_commit(bar(L::AB_K_EMPTY, st));
       }
     }
@@ -437,31 +423,27 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
         for (int s = 1; s < KS; ++s)
           if (st == s) vd = v_desc[s];
         wait(bar(L::AB_V_FULL, st), (i / KS) & 1);
-#pragma unroll
-        for (int t = 0; t < TILES; ++t) {
-          wait(bar(L::AB_P_READY, 2 * t + sb), (i >> 1) & 1);
-          a_fence_after();
-          if (*abort_flag) break;
-#pragma unroll
-          for (int k = 0; k < 4; ++k)  // P: 16 keys = 8 packed columns per step
-            a_umma_ts(tmem_base + t * L::TILE_COLS + L::O_COL, tmem_base + t * L::TILE_COLS + sb * MLL_PAGE + k * 8,
-                      vd + (unsigned long long)((k * (16 * 128)) >> 4), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
-          a_commit(bar(L::AB_PV_DONE, 2 * t + sb));
-        }
+        wait(bar(L::AB_P_READY, sb), (i >> 1) & 1);
+        a_fence_after();
         if (*abort_flag) break;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)  // P: 16 keys = 8 packed columns per step
+          a_umma_ts(tmem_base + L::O_COL, tmem_base + sb * MLL_PAGE + k * 8, vd + (unsigned long long)((k * (16 * 128)) >> 4),
+                    idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+        a_commit(bar(L::AB_PV_DONE, sb));
         a_commit(bar(L::AB_V_EMPTY, st));
       }
     }
-  } else if (warp < 4 * TILES) {
-    // ---- softmax: thread r of tile t owns query row r = lane r of tensor memory ---------------- //
-    if (TILES == 1) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(A_SOFTMAX_REGS));
-    const int t = warp >> 2, r = tid & (A_ROWS - 1);
-    const unsigned tmem_row = tmem_base + t * L::TILE_COLS + ((unsigned)((warp & 3) * 32) << 16);
+  } else if (warp < 4) {
+    // ---- softmax: thread r owns query row r = lane r of tensor memory ------------------------- //
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(A_SOFTMAX_REGS));
+    const int r = tid;
+    const unsigned tmem_row = tmem_base + ((unsigned)(warp * 32) << 16);
     const int qpos = pos0 + r;
     float m_used = -INFINITY, l_run = 0.f;  // the maximum that P and O are scaled by; the sum
     for (int i = 0; i < n_pages; ++i) {
       const int sb = i & 1, st = i % KS;
-      wait(bar(L::AB_S_FULL, 2 * t + sb), (i >> 1) & 1);
+      wait(bar(L::AB_S_FULL, sb), (i >> 1) & 1);
       a_fence_after();
       float s[MLL_PAGE];
       a_tmem_ld64(tmem_row + sb * MLL_PAGE, s);
@@ -489,7 +471,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
       const bool moved = mx > m_used + A_RESCALE_STEP || (m_used == -INFINITY && mx > -INFINITY);
       if (i > 0 && __any_sync(0xffffffffu, moved)) {
         const float alpha = moved ? a_exp2(m_used - mx) : 1.f;
-        wait(bar(L::AB_PV_DONE, 2 * t + (sb ^ 1)), ((i - 1) >> 1) & 1);  // O holds every page before this one
+        wait(bar(L::AB_PV_DONE, sb ^ 1), ((i - 1) >> 1) & 1);  // O holds every page before this one
         a_fence_after();
 #pragma unroll
         for (int c = 0; c < D; c += 32) {
@@ -532,8 +514,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
       }
       a_tmem_st32(tmem_row + sb * MLL_PAGE, packed);  // P over the first half of S
       const int valid = ctx - k0;  // positions of this page that the sequence has
-      if (valid < MLL_PAGE && t == 0) {  // only the sequence's last page: the rest of it may hold anything
-        // (the first tile's threads do it: the MMA thread has waited for their P before it issues any P V)
+      if (valid < MLL_PAGE) {      // only the sequence's last page: the rest of it may hold anything
         wait(bar(L::AB_V_FULL, st), (i / KS) & 1);
         unsigned char* vt = base + L::V_OFF + st * L::KV_BYTES;
         const int n_chunks = (MLL_PAGE - valid) * 8;  // 16-byte chunks per box
@@ -544,17 +525,17 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
       }
       a_tmem_wait_st();
       a_fence_before();
-      a_mbar_arrive(bar(L::AB_P_READY, 2 * t + sb));
+      a_mbar_arrive(bar(L::AB_P_READY, sb));
     }
     // the output row: O / l
-    wait(bar(L::AB_PV_DONE, 2 * t + ((n_pages - 1) & 1)), ((n_pages - 1) >> 1) & 1);
+    wait(bar(L::AB_PV_DONE, (n_pages - 1) & 1), ((n_pages - 1) >> 1) & 1);
     a_fence_after();
     {
       // tcgen05.ld is a warp-wide instruction: every thread of the warp reads its lane, and only the
       // threads that own a row of the sequence store
       const bool store = !*abort_flag && r < rows;
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* dst = a.out + ((size_t)qstart + row0 + (store ? r : 0)) * a.n_heads * D + (size_t)(h0 + t) * D;
+      __nv_bfloat16* dst = a.out + ((size_t)qstart + row0 + (store ? r : 0)) * a.n_heads * D + (size_t)h * D;
 #pragma unroll
       for (int c = 0; c < D; c += 32) {
         float o[32];
@@ -585,19 +566,19 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
   }
 }
 
-template <int D, int TILES>
+template <int D>
 int launch_prefill_tc5(const CUtensorMap& qmap, const CUtensorMap& kmap, const CUtensorMap& vmap,
                        const PrefillTc5Args& a, int n_tiles, cudaStream_t stream) {
-  using L = PrefillTc5Smem<D, TILES>;
+  using L = PrefillTc5Smem<D>;
   const size_t smem = L::BYTES;
-  auto kernel = attn_prefill_tc5_kernel<D, TILES>;
+  auto kernel = attn_prefill_tc5_kernel<D>;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (err != cudaSuccess) {
     mll_set_error("attention prefill (tcgen05): cannot reserve %zu bytes of shared memory: %s", smem,
                   cudaGetErrorString(err));
     return (int)err;
   }
-  MLL_LAUNCH((kernel), dim3((unsigned)(n_tiles * (a.n_heads / TILES))), L::THREADS, smem, stream, qmap, kmap, vmap, a);
+  MLL_LAUNCH((kernel), dim3((unsigned)(n_tiles * a.n_heads)), L::THREADS, smem, stream, qmap, kmap, vmap, a);
   MLL_LAUNCH_CHECK();
   return 0;
 }
@@ -614,10 +595,6 @@ extern "C" int* mll_attn_tc5_error_address() {
   }
   return address;
 }
-
-// Tests and measurements switch the two-tile blocks off to reach the one-tile kernel at every shape.
-static int mll_prefill_tc5_pairs = 1;
-MLL_API void mll_attn_prefill_tc5_set_pairs(int on) { mll_prefill_tc5_pairs = on != 0; }
 
 MLL_API int mll_attn_prefill_tc5_supported(int dtype, int head_dim) {
   return dtype == MLL_BF16 && (head_dim == 64 || head_dim == 128);
@@ -645,11 +622,6 @@ MLL_API int mll_attn_prefill_tc5(const void* q, const void* k_cache, const void*
   if (mll::tensor_map_bf16(v_cache, n_pages * n_kv_heads * MLL_PAGE, head_dim, MLL_PAGE, &vmap) != 0) return -1;
   mll::PrefillTc5Args a{seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0, block_table,
                         (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, window, scale * 1.4426950408889634f};
-  // two tiles a block where two neighbouring heads share a kv head
-  const bool pairs = (n_heads / n_kv_heads) % 2 == 0 && mll_prefill_tc5_pairs;
-  if (head_dim == 64)
-    return pairs ? mll::launch_prefill_tc5<64, 2>(qmap, kmap, vmap, a, n_tiles, stream)
-                 : mll::launch_prefill_tc5<64, 1>(qmap, kmap, vmap, a, n_tiles, stream);
-  return pairs ? mll::launch_prefill_tc5<128, 2>(qmap, kmap, vmap, a, n_tiles, stream)
-               : mll::launch_prefill_tc5<128, 1>(qmap, kmap, vmap, a, n_tiles, stream);
+  if (head_dim == 64) return mll::launch_prefill_tc5<64>(qmap, kmap, vmap, a, n_tiles, stream);
+  return mll::launch_prefill_tc5<128>(qmap, kmap, vmap, a, n_tiles, stream);
 }

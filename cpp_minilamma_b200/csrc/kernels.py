@@ -14,7 +14,7 @@ import torch
 from ..cache.paged import PAGE  # cache positions per page; the library's MLL_PAGE is checked against it on load
 from .build import KernelBuildError, load_library
 
-ABI_VERSION = 22
+ABI_VERSION = 23
 MAX_TOP_K = 1024
 
 
@@ -492,7 +492,6 @@ def attention_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_
 USE_TENSOR_CORE_DECODE = True  # tests switch these off to reach the general kernels at every size
 USE_TENSOR_CORE_PREFILL = True
 USE_TCGEN05_PREFILL = True      # off: the mma.sync kernel takes the tensor-core prefill
-USE_TCGEN05_PAIRS = True        # off: the tcgen05 prefill kernel never gives a block two heads' tiles
 
 
 def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch, out, n_seqs: int,
@@ -656,7 +655,6 @@ def attention_prefill(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_ql
             n_tiles = tile_seq.shape[0]
             if tile_row0.shape[0] != n_tiles:
                 raise KernelError("attention prefill: the wide tile lists differ in length")
-        lib().mll_attn_prefill_tc5_set_pairs(ctypes.c_int(int(USE_TCGEN05_PAIRS)))
         _check(lib().mll_attn_prefill_tc5(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx),
                                           _ptr(seq_qstart), _ptr(seq_qlen), _ptr(tile_seq), _ptr(tile_row0),
                                           _ptr(block_table), _ptr(out), ctypes.c_int(q.shape[0]),

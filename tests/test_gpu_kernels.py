@@ -382,18 +382,15 @@ def test_attention_decode_in_a_given_order(hq, hk, d, splits, fused):
                            order=torch.zeros(B - 1, dtype=torch.int32, device=DEV))
 
 
-@pytest.fixture(params=["tcgen05", "tcgen05_one_tile", "tensor_core", "general"])
+@pytest.fixture(params=["tcgen05", "tensor_core", "general"])
 def prefill_impl(request):
-    """tcgen05: the TMA/tensor-memory kernel (head sizes 64 and 128, else the next one), which gives a block
-    the tiles of two heads where the head counts allow, or (second variant) always one; tensor_core: the mma.sync
-    kernel; general: the kernel for every size and dtype."""
+    """tcgen05: the TMA/tensor-memory kernel (head sizes 64 and 128, else the next one);
+    tensor_core: the mma.sync kernel; general: the kernel for every size and dtype."""
     K.USE_TENSOR_CORE_PREFILL = request.param != "general"
-    K.USE_TCGEN05_PREFILL = request.param.startswith("tcgen05")
-    K.USE_TCGEN05_PAIRS = request.param == "tcgen05"
+    K.USE_TCGEN05_PREFILL = request.param == "tcgen05"
     yield "general" if request.param == "general" else "tensor_core"
     K.USE_TENSOR_CORE_PREFILL = True
     K.USE_TCGEN05_PREFILL = True
-    K.USE_TCGEN05_PAIRS = True
 
 
 def _prefill_tiles(q_lens, rows=64):
