@@ -334,7 +334,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
 
   if (tid == 0) {
     for (int i = 0; i < L::AB_COUNT; ++i)
-      a_mbar_init(a_smem(bars + i), (i >= L::AB_P_READY && i < L::AB_PV_DONE) ? A_ROWS : 1);
+      a_mbar_init(a_smem(bars + i), (i >= L::AB_P_READY && i < L::AB_PV_DONE) ? 4 : 1);  // P ready: one arrival a softmax warp
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -525,7 +525,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
       }
       a_tmem_wait_st();
       a_fence_before();
-      a_mbar_arrive(bar(L::AB_P_READY, sb));
+      __syncwarp();  // one arrival a warp: 128 arrivals on one barrier are 128 shared-memory atomics in a row
+      if (lane == 0) a_mbar_arrive(bar(L::AB_P_READY, sb));
     }
     // the output row: O / l
     wait(bar(L::AB_PV_DONE, (n_pages - 1) & 1), ((n_pages - 1) >> 1) & 1);
