@@ -8,10 +8,12 @@
 //     tile, keeps the running maximum and sum in float32 (base 2), and writes P back over the first
 //     half of the S columns as packed bfloat16 (tcgen05.st);
 //   * warp 4, one thread: TMA loads with the 128-byte swizzle - the query tile once, then the key and
-//     the value pages (64 positions each) into a two-stage ring guarded by full / empty mbarriers;
+//     the value pages (64 positions each) into a ring of two stages (three at head size 64) guarded by
+//     full / empty mbarriers;
 //   * warp 5, one thread: S = Q K^T (M = 128 rows, N = 64 keys, both operands K-major) into one of two
-//     64-column buffers of tensor memory; S_i is issued as soon as page i's keys are there and the buffer's
-//     last user, O += P_{i-2} V_{i-2}, is done, so it runs under the softmax of page i - 1.  The warp also
+//     64-column buffers of tensor memory (three at head size 64, where O takes half the columns); S_i is issued
+//     as soon as page i's keys are there and the buffer's last user, the P V of two (three) pages before, is
+//     done, so it runs under the softmax of the pages between.  The warp also
 //     allocates and frees the block's 256 columns;
 //   * warp 6, one thread: O += P_i V_i, with P as the tensor-memory A operand and the value page as it lies
 //     in the cache ([position][dim], MN-major) as B; O stays in tensor memory (64 or 128 further columns).
@@ -270,7 +272,7 @@ constexpr float A_RESCALE_STEP = 8.f;  // the output is rescaled only when a row
 template <int D>
 struct PrefillTc5Smem {
   static constexpr int THREADS = 256;
-  static constexpr int KV_STAGES = 2;
+  static constexpr int KV_STAGES = D == 64 ? 3 : 2;   // as many key/value stages as S buffers (80 KB a block either way)
   static constexpr int Q_BYTES = A_ROWS * D * 2;       // D / 64 boxes of [128 rows x 128 bytes]
   static constexpr int KV_BYTES = MLL_PAGE * D * 2;    // D / 64 boxes of [64 rows x 128 bytes]
   static constexpr int Q_OFF = 0, K_OFF = Q_BYTES, V_OFF = K_OFF + KV_STAGES * KV_BYTES;
@@ -280,13 +282,19 @@ struct PrefillTc5Smem {
   // memory starts on a 1024-byte boundary (the swizzle's period) and refuses otherwise.
   static constexpr size_t USED = (size_t)BAR_OFF + 512;
   static constexpr size_t BYTES = USED < 80 * 1024 ? 80 * 1024 : USED;
-  static constexpr int TMEM_COLS = 256;                // S / P: 2 x 64, O: up to 128
-  static constexpr int O_COL = 128;
+  // Tensor memory, 256 columns a block: S / P buffers of 64 columns, then O (D columns).  Head size 128 leaves room
+  // for two S buffers, head size 64 for three: the chain softmax -> P V -> S -> softmax that bounds a block's pace
+  // then runs over three pages instead of two.
+  static constexpr int S_BUFS = D == 64 ? 3 : 2;
+  static constexpr int TMEM_COLS = 256;
+  static constexpr int O_COL = S_BUFS * MLL_PAGE;
+  static_assert(O_COL + D <= TMEM_COLS, "S buffers and O must fit the block's columns");
   // barrier slots: the queries; keys and values full / empty per ring stage; per S buffer: S full, P ready,
   // P V done
   static constexpr int AB_Q = 0, AB_K_FULL = 1, AB_V_FULL = AB_K_FULL + KV_STAGES, AB_K_EMPTY = AB_V_FULL + KV_STAGES,
                        AB_V_EMPTY = AB_K_EMPTY + KV_STAGES, AB_S_FULL = AB_V_EMPTY + KV_STAGES,
-                       AB_P_READY = AB_S_FULL + 2, AB_PV_DONE = AB_P_READY + 2, AB_COUNT = AB_PV_DONE + 2;
+                       AB_P_READY = AB_S_FULL + S_BUFS, AB_PV_DONE = AB_P_READY + S_BUFS,
+                       AB_COUNT = AB_PV_DONE + S_BUFS;
   static_assert(AB_COUNT * 8 + 16 <= 512, "the barriers must fit behind the tiles");
 };
 
@@ -296,7 +304,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
                         const __grid_constant__ CUtensorMap vmap, PrefillTc5Args a) {
   using L = PrefillTc5Smem<D>;
   constexpr int DB = D / 64;  // 64-column boxes per row of Q, K or V
-  constexpr int KS = L::KV_STAGES;
+  constexpr int KS = L::KV_STAGES, SB = L::S_BUFS;
   constexpr int LOAD_WARP = 4, MMA_WARP = 5, PV_WARP = 6;
   // later tiles of a sequence see more keys: they go first, so that the short ones fill the tail
   const int tile = (gridDim.x - 1 - blockIdx.x) / a.n_heads;   // all heads of a tile are neighbours
@@ -375,7 +383,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
       }
     }
   } else if (warp == MMA_WARP) {
-    // ---- S = Q K^T, one thread.  S_i goes into buffer i % 2, which held P_{i-2}: it waits for that page's P V.
+    // ---- S = Q K^T, one thread.  S_i goes into buffer i % SB, which held P_{i-SB}: it waits for that page's P V.
     if (lane == 0) {
       constexpr unsigned idesc_s = a_idesc(A_ROWS, MLL_PAGE, false);
       // The descriptors are built once; a step inside a tile only adds to the address field (16-byte units, 14
@@ -387,13 +395,13 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
       for (int s = 0; s < KS; ++s) k_desc[s] = a_desc(k_s + s * L::KV_BYTES, 16);
       wait(bar(L::AB_Q, 0), 0);
       for (int i = 0; i < n_pages && !*abort_flag; ++i) {
-        const int sb = i & 1, st = i % KS;
+        const int sb = i % SB, st = i % KS;
         unsigned long long kd = k_desc[0];
 #pragma unroll
         for (int s = 1; s < KS; ++s)
           if (st == s) kd = k_desc[s];
         wait(bar(L::AB_K_FULL, st), (i / KS) & 1);
-        if (i >= 2) wait(bar(L::AB_PV_DONE, sb), ((i - 2) >> 1) & 1);  // P_{i-2} has been read
+        if (i >= SB) wait(bar(L::AB_PV_DONE, sb), ((i - SB) / SB) & 1);  // the buffer's P, of page i - SB, has been read
         a_fence_after();
         if (*abort_flag) break;
         const unsigned d = tmem_base + sb * MLL_PAGE;
@@ -417,13 +425,13 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
 #pragma unroll
       for (int s = 0; s < KS; ++s) v_desc[s] = a_desc(v_s + s * L::KV_BYTES, MLL_PAGE * 128);
       for (int i = 0; i < n_pages && !*abort_flag; ++i) {
-        const int sb = i & 1, st = i % KS;
+        const int sb = i % SB, st = i % KS;
         unsigned long long vd = v_desc[0];
 #pragma unroll
         for (int s = 1; s < KS; ++s)
           if (st == s) vd = v_desc[s];
         wait(bar(L::AB_V_FULL, st), (i / KS) & 1);
-        wait(bar(L::AB_P_READY, sb), (i >> 1) & 1);
+        wait(bar(L::AB_P_READY, sb), (i / SB) & 1);
         a_fence_after();
         if (*abort_flag) break;
 #pragma unroll
@@ -442,8 +450,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
     const int qpos = pos0 + r;
     float m_used = -INFINITY, l_run = 0.f;  // the maximum that P and O are scaled by; the sum
     for (int i = 0; i < n_pages; ++i) {
-      const int sb = i & 1, st = i % KS;
-      wait(bar(L::AB_S_FULL, sb), (i >> 1) & 1);
+      const int sb = i % SB, st = i % KS;
+      wait(bar(L::AB_S_FULL, sb), (i / SB) & 1);
       a_fence_after();
       float s[MLL_PAGE];
       a_tmem_ld64(tmem_row + sb * MLL_PAGE, s);
@@ -471,7 +479,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
       const bool moved = mx > m_used + A_RESCALE_STEP || (m_used == -INFINITY && mx > -INFINITY);
       if (i > 0 && __any_sync(0xffffffffu, moved)) {
         const float alpha = moved ? a_exp2(m_used - mx) : 1.f;
-        wait(bar(L::AB_PV_DONE, sb ^ 1), ((i - 1) >> 1) & 1);  // O holds every page before this one
+        wait(bar(L::AB_PV_DONE, (i - 1) % SB), ((i - 1) / SB) & 1);  // O holds every page before this one
         a_fence_after();
 #pragma unroll
         for (int c = 0; c < D; c += 32) {
@@ -529,7 +537,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
       if (lane == 0) a_mbar_arrive(bar(L::AB_P_READY, sb));
     }
     // the output row: O / l
-    wait(bar(L::AB_PV_DONE, (n_pages - 1) & 1), ((n_pages - 1) >> 1) & 1);
+    wait(bar(L::AB_PV_DONE, (n_pages - 1) % SB), ((n_pages - 1) / SB) & 1);
     a_fence_after();
     {
       // tcgen05.ld is a warp-wide instruction: every thread of the warp reads its lane, and only the
