@@ -8,8 +8,8 @@ prompts (uniform in [128, 2048)) on a cache sized for 4096 tokens each; `value` 
 tokens per second measured with CUDA events around K steps after W warm-up steps (the loop of
 K steps is repeated and the median repeat reported).  Before anything is timed the bfloat16
 engine's tokens are compared with a float32 run at the same layer widths (`checked`).  The
-same line carries: `e2e` (the same metric through `LLM.generate`, token ids in host lists
-in and out), `prefill` (one 2,048-token prompt), `roofline` (bytes a decode step must
+same line carries: `e2e` (the same metric through one `LLM.generate` call, token ids in host lists
+in and out, the last K of its W + K decode steps on the host clock), `prefill` (one 2,048-token prompt), `roofline` (bytes a decode step must
 read / its time, against the measured HBM copy bandwidth), `points` (decode at batch 1
 and 64, with their fractions of the HBM peak) and `workloads` (the Llama-2-7B shape at batch
 16 and the Llama-3.2-1B shape at batch 64, each with its own bytes and fraction).  Weights are
@@ -311,12 +311,21 @@ def time_workload(name, peaks, warmup, layers=None):
     return out
 
 
-def time_e2e(llm, batch, steps, seed):
-    """Decoded tokens per second through LLM.generate: host token lists in, host lists out."""
+def time_e2e(llm, batch, steps, warmup, seed):
+    """Decoded tokens per second through LLM.generate, host token lists in, host lists out: one call that
+    generates warmup + steps + 1 tokens per prompt; the host clock is read as each step's tokens arrive, and the
+    last `steps` decode steps count (the `warmup` steps before them are the warm-up, as for the device-timed
+    figure).  Also returned: the rate of the first `steps` decode steps, which follow the prompt step into the
+    power cap and run slower."""
     prompts = prompts_for(batch, llm.config.vocab_size, seed)
     stats = {}
-    llm.generate(prompts, max_new_tokens=steps + 1, ignore_eos=True, stats=stats)
-    return stats
+    llm.generate(prompts, max_new_tokens=warmup + steps + 1, ignore_eos=True, stats=stats)
+    stamps = stats["step_stamps"]  # [0]: the prompt step's tokens, [k]: decode step k's
+    if len(stamps) < warmup + steps + 1:
+        raise RuntimeError(f"the generation made {len(stamps) - 1} decode steps, {warmup + steps} were asked for")
+    timed = stamps[warmup + steps] - stamps[warmup]
+    first = stamps[steps] - stamps[0]
+    return batch * steps / timed, batch * steps / first
 
 
 def time_prefill(llm, tokens, reps, warmup, seed, pause=0.0):
@@ -441,8 +450,7 @@ def main():
     value = BATCH * 1000.0 / ms
     achieved = decode_bytes(llm, live_tokens) / (ms * 1e-3) / 1e9
 
-    stats = time_e2e(llm, BATCH, steps, seed=2)
-    e2e_value = BATCH * stats["decode_steps"] / stats["decode_s"]
+    e2e_value, e2e_after_prompt = time_e2e(llm, BATCH, steps, warmup, seed=2)
     meta_ints = 10 * BATCH  # the captured step's ten index arrays; block-table rows ride along when a page is crossed
 
     prefill_hot_ms = time_prefill(llm, PREFILL_TOKENS, reps=5, warmup=1, seed=3)
@@ -471,7 +479,8 @@ def main():
                    "peaks": peaks["source"], "repeats": len(all_ms), "reported": "median repeat of `steps` steps"},
         "clocks": clocks,
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": 4 * meta_ints,
-                "d2h_bytes_per_step": 4 * 2 * 64},
+                "d2h_bytes_per_step": 4 * 2 * 64, "warmup_steps": warmup,
+                "first_steps_after_prompt": round(e2e_after_prompt, 1)},
         "gpu_launches": int(round(launches * steps)),
         "prefill": {"value": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PREFILL_TOKENS,
                     "ms": round(prefill_ms, 3),

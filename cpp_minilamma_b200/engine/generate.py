@@ -182,6 +182,8 @@ def _run_batch(backend, requests, prompts, budgets, stops, results, stats=None) 
                 decode_began = time.perf_counter()
                 if stats is not None:
                     stats["prefill_s"] = stats.get("prefill_s", 0.0) + decode_began - began
+            if stats is not None:  # when each step's tokens reached the host: the prompt step first
+                stats.setdefault("step_stamps", []).append(time.perf_counter())
             before = order
             order = apply(order, sampled)
             step += 1
@@ -190,6 +192,8 @@ def _run_batch(backend, requests, prompts, budgets, stops, results, stats=None) 
                     ticket = spec
                     continue
                 by_request = dict(zip(before, backend.collect(spec)))  # rows of ended sequences are dropped
+                if stats is not None:
+                    stats["step_stamps"].append(time.perf_counter())
                 if not order:
                     break
                 order = apply(order, [by_request[r] for r in order])
