@@ -40,7 +40,7 @@ constexpr int T_ROWS = 64;     // weight rows per block
 constexpr int T_KB = 64;       // k elements per stage (128 bytes: one swizzle span)
 constexpr int T_STAGES = 3;
 constexpr int T_THREADS = 160; // four consumer warps and one producer warp
-constexpr unsigned T_SPIN_LIMIT = 4u << 20;
+constexpr long long T_WAIT_CLOCKS = 2ll << 30;  // clocks a wait may take
 
 struct TmaLinearArgs {
   const float* bias;  // optional [N]
@@ -64,16 +64,19 @@ __device__ __forceinline__ bool mbar_test(unsigned bar, unsigned parity) {
   unsigned done;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(done) : "r"(bar), "r"(parity) : "memory");
   return done != 0;
 }
 // Bounded wait; false (and the error flag raised) when the phase never completes.
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
-  for (unsigned spin = 0; spin < T_SPIN_LIMIT; ++spin) {
+  // each try parks the thread until the phase completes or a time limit of the hardware's own runs out (a spin
+  // on test_wait spends issue slots and power while the block waits for memory); about a second in all
+  if (mbar_test(bar, parity)) return true;
+  const long long began = clock64();
+  while (clock64() - began < T_WAIT_CLOCKS) {
     if (mbar_test(bar, parity)) return true;
-    if (spin > 64) __nanosleep(40);
   }
   atomicExch(&mll_device_error_flag, 1);
   return false;
