@@ -89,7 +89,8 @@ def generate(backend: Backend, prompts: Sequence[Sequence[int]], max_new_tokens,
     "prompt + n-predict exceeds context window", app/backend_cli.cc:146-148) unless
     `clip` shortens it (its legacy bench clips, app/main.cc:170).  `stats`, when given,
     receives wall-clock seconds and counts of the prompt steps and of the decode steps
-    (sampling included, as the caller sees them).
+    (sampling included, as the caller sees them), and `step_stamps`, the host time at which
+    each step's tokens arrived (the prompt step's first).
     """
     n_requests = len(prompts)
     if isinstance(max_new_tokens, int):

@@ -187,3 +187,19 @@ def test_step_ahead_rows_of_a_stopped_sequence_are_dropped():
     assert fed_to_0 == [[1], [10], [99]]
     fed_to_1 = [tokens for step in backend.log for r, tokens, _, _ in step if r == 1]
     assert fed_to_1 == [[2], [20], [21], [22], [23]]
+
+
+@pytest.mark.parametrize("backend_kind", [Scripted, ScriptedAhead])
+def test_statistics_count_steps_and_stamp_each_step(backend_kind):
+    """`stats` counts the prompt step and the decode steps and carries one host time per step whose tokens
+    reached the host (the prompt step first): what the bench reads its end-to-end figure from."""
+    scripts = {0: [10, 11, 12, 13, 14, 15], 1: [20, 21, 22, 23, 24, 25]}
+    backend = backend_kind(scripts)
+    stats = {}
+    out = generate(backend, [[1, 2, 3], [4]], 6, stats=stats)
+    assert [c.tokens for c in out] == [scripts[0], scripts[1]]
+    assert stats["prefill_steps"] == 1 and stats["prefill_tokens"] == 4
+    assert stats["decode_steps"] == 5 and stats["decode_tokens"] == 10
+    stamps = stats["step_stamps"]
+    assert len(stamps) == 6 and all(b >= a for a, b in zip(stamps, stamps[1:]))
+    assert stats["decode_s"] >= stamps[-1] - stamps[0] >= 0.0
