@@ -409,9 +409,14 @@ MLL_API int mll_linear_tma_fused(const void* x, const void* w, const float* bias
   const int tiles = (N + mll::T_ROWS - 1) / mll::T_ROWS;
   const int k_blocks = (K + mll::T_KB - 1) / mll::T_KB;
   if (ranks <= 0) {
-    // as many blocks as can be resident together (7 per multiprocessor), each with >= 8 k-blocks
+    // As many blocks as can be resident together (7 per multiprocessor), each with at least 32 k-blocks (2,048
+    // columns) once every multiprocessor has a block, 8 before that.  (With 8 everywhere the 16384 x 2048 gate/up
+    // product of a 2,048-wide model got clusters of 4 with 512 columns a block: 20.5 us in a graph against 15.0
+    // without any split; 28672 x 4096 keeps its clusters of 2: 41.3 against 42.5 us.)
     ranks = 1;
-    while (ranks < 8 && tiles * ranks * 2 <= mll_sm_count() * 7 && k_blocks / (ranks * 2) >= 8) ranks *= 2;
+    while (ranks < 8 && tiles * ranks * 2 <= mll_sm_count() * 7 &&
+           k_blocks / (ranks * 2) >= (tiles * ranks * 2 <= mll_sm_count() ? 8 : 32))
+      ranks *= 2;
   }
   MLL_REQUIRE(ranks == 1 || ranks == 2 || ranks == 4 || ranks == 8, "linear_tma: cluster size %d", ranks);
   const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
