@@ -302,7 +302,7 @@ def device_error_message(mask: int) -> str:
             + "; the step's results are not valid")
 
 
-TMA_MAX_ROWS = 8      # rows up to which tall matrices go to the TMA + mma.sync kernel (its batch tile is 8 rows)
+TMA_MAX_ROWS = 8      # rows up to which tall matrices go to the direct kernel, or the TMA + mma.sync kernel (one batch tile of 8 rows)
 TC5_TALL_MAX_ROWS = 16  # rows up to which tall matrices go to the tcgen05 kernel (beyond: the library, which shares the
                         # batch tile between the blocks of a cluster)
 DIRECT_MAX_ROWS = 16  # rows up to which the other matrices go to the direct kernel
@@ -313,11 +313,12 @@ def small_linear_kind(rows: int, out_features: int, in_features: int, epilogue: 
     """Which of this library's weight-streaming kernels takes the problem: "tc5", "tma", "direct" or "".
 
     Measured on B200 (CUDA-graph timing) on the shapes of the 8B, 7B and 1B Llama models.  Tall matrices
-    (gate/up, lm_head), where a deep queue of TMA loads counts: up to 8 rows the kernel with mma.sync
-    consumers (gate/up + SwiGLU 40.6 us, tcgen05 43.3), from 9 to 16 rows the tcgen05 kernel (43.6 us, the
-    other 53.5 with its second batch tile).  The other projections, where a launch is short and a fine
-    split over the machine counts: the direct kernel up to 16 rows (it chooses its variant by rows and
-    tiles).  From 17 rows on the library GEMM: the tcgen05 kernel takes up to 64 rows (32 or 64 batch
+    (gate/up, lm_head) up to 8 rows: the direct kernel, as it stands since it got its register targets and eight
+    warps a block (us at 8 rows, direct / TMA + mma.sync / tcgen05: 8B gate/up + SwiGLU 38.7 / 41.5 / 42.6, lm_head
+    154.7 / 159.5 / 161.5; 7B 31.1 / 32.3 / 33.0 and 42.5 / 46.3 / 46.2; 1B 13.3 / 15.2 / 16.1 and 78.3 / 80.4 /
+    83.0; the TMA kernel stays for widths the direct kernel does not take); from 9 to 16 rows the tcgen05 kernel
+    (8B gate/up 43.0 against 45.3 direct and 54.5 TMA with their second batch tile).  The other projections: the
+    direct kernel up to 16 rows (it chooses its variant by rows and tiles).  From 17 rows on the library GEMM: the tcgen05 kernel takes up to 64 rows (32 or 64 batch
     columns per MMA), but inside a CUDA graph the library's kernels are ahead on every shape tried
     (64 rows, us, library / tcgen05: 8B q/k/v 11.8 / 16.2, o 9.9 / 13.1, down 24.9 / 26.5, gate/up 42.8 /
     46.9; 1B q/k/v 5.9 / 9.6, o 5.7 / 9.1, down 13.2 / 14.5, gate/up 13.2 / 19.1), and in a batch-64 step
@@ -328,8 +329,11 @@ def small_linear_kind(rows: int, out_features: int, in_features: int, epilogue: 
         supported = {"tc5": linear_tc5_supported, "tma": linear_tma_supported, "direct": linear_small_supported}
         return SMALL_LINEAR if rows <= 64 and supported[SMALL_LINEAR](rows, out_features, in_features, epilogue) else ""
     if out_features >= TALL:
-        if rows <= TMA_MAX_ROWS and linear_tma_supported(rows, out_features, in_features, epilogue):
-            return "tma"
+        if rows <= TMA_MAX_ROWS:  # one batch tile of 8 rows in either kernel
+            if linear_small_supported(rows, out_features, in_features, epilogue):
+                return "direct"
+            if linear_tma_supported(rows, out_features, in_features, epilogue):
+                return "tma"
         if rows <= TC5_TALL_MAX_ROWS and linear_tc5_supported(rows, out_features, in_features, epilogue):
             return "tc5"
     if rows <= DIRECT_MAX_ROWS:

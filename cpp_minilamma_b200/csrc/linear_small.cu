@@ -105,6 +105,38 @@ linear_small_kernel(LinearArgs a) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
 
+  // At most 16 rows and 8 warps: warp m works out the norm factors of rows m and m + 8 now, before its loop.  The partial sums lie
+  // in the L2 cache, so this is one cache latency (0.5 us); the warp first asks the L2 cache for the weights of its
+  // first round of loads, which come from HBM and take longer, so nothing is lost.  (That request alone, without
+  // a factor to wait for, helps products of many tiles and long rows by up to 1 us and costs the short one-wave
+  // ones as much: it is made only here.)  Worked out after the loop, as
+  // the wider cases still do, the factor cost every block that latency at its end, with nothing to hide it: with
+  // the 1,792 blocks of a 28672-row gate/up product 5 us of 43 at 8 rows.
+  constexpr bool EARLY_FACTORS = NT <= 2 && LS_WARPS == 8;  // at most 16 rows: warp m has rows m and m + 8
+  const bool early = EARLY_FACTORS && a.in.sumsq != nullptr && rank == 0;
+  if (early && warp < a.M) {
+#pragma unroll
+    for (int u = 0; u < LS_UNROLL; ++u)
+      if (first + u < last) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(wa + (size_t)(first + u) * 32));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(wb + (size_t)(first + u) * 32));
+      }
+    if (NT == 1) {
+      const float f = row_norm_factor<32>(a.in.sumsq + (size_t)warp * a.in.stride, a.in.partials, a.K, a.in.eps, lane,
+                                          0xffffffffu);
+      if (lane == 0) row_factor[warp] = f;
+    } else {
+      const bool second = warp + LS_WARPS < a.M;
+      float f0, f1;
+      row_norm_factors2(a.in.sumsq + (size_t)warp * a.in.stride, a.in.sumsq + (size_t)(warp + LS_WARPS) * a.in.stride,
+                        second, a.in.partials, a.K, a.in.eps, lane, f0, f1);
+      if (lane == 0) {
+        row_factor[warp] = f0;
+        if (second) row_factor[warp + LS_WARPS] = f1;
+      }
+    }
+  }
+
   int c = first;
   for (; c + LS_UNROLL <= last; c += LS_UNROLL) {
     uint4 fa[LS_UNROLL], fb[LS_UNROLL];
@@ -171,7 +203,8 @@ linear_small_kernel(LinearArgs a) {
     // the rows' norm factors, from partial sums that lie in the L2 cache: plain loads here, at the end, cost
     // 0.6 us (q/k/v of the 8B shape); fetching them into shared memory during the main loop cost 1.5 us,
     // through the share of the L1 cache that the buffer takes from the activations
-    if (NT == 1) {  // at most 8 rows: one per warp of the 8-warp variants (the two-row form cost them 0.4 us)
+    if (early) {  // done before the loop
+    } else if (NT == 1) {  // at most 8 rows: one per warp of the 8-warp variants (the two-row form cost them 0.4 us)
       for (int m = warp; m < a.M; m += LS_WARPS) {
         const float f = row_norm_factor<32>(a.in.sumsq + (size_t)m * a.in.stride, a.in.partials, a.K, a.in.eps, lane,
                                             0xffffffffu);

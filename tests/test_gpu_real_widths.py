@@ -1,8 +1,9 @@
 """The engine at the layer widths of a real model, against the plain implementation.
 
-The tiny configurations never reach the schedule that a model of real size runs: tall
-matrices (gate/up with the fused activation, the head) on the TMA and tcgen05 weight-streaming
-kernels, the other products on the direct kernel with the norms folded in, 32/8 heads of 128
+The tiny configurations never reach the schedule that a model of real size runs: every product
+of a small decode step on the weight-streaming kernels with the norms folded in (the direct kernel
+up to 8 rows, the tall matrices - gate/up with the fused activation, the head - on the tcgen05
+kernel from 9 to 16 rows, and the TMA kernel where it is forced), 32/8 heads of 128
 in the tcgen05 prefill attention and the cluster-merged decode attention, decode steps of
 more than 16 rows on the library product.  Here the layers have the widths of Llama-3.1-8B
 (hidden 4096, 32 query / 8 key-value heads of 128, intermediate 14336, llama3 rope scaling
@@ -115,10 +116,9 @@ def test_last_32_one_by_one(real, dtype):
         llm.engine.release(slot)
         assert_close(np.concatenate(rows), oracle.logits(tokens, dtype), dtype, f"real widths last-32 len {length}")
     if dtype == "bfloat16":
-        # one row: gate/up and the head stream through the TMA kernel, q/k/v, o and down through the direct
-        # kernel, and the 200-token context is split over a cluster
-        assert K.calls.get("linear_tma", 0) >= 64 * (LAYERS + 1), K.calls
-        assert K.calls.get("linear_small", 0) >= 64 * 3 * LAYERS, K.calls
+        # one row: every product, the tall gate/up and head too, streams through the direct kernel, and the
+        # 200-token context is split over a cluster
+        assert K.calls.get("linear_small", 0) >= 64 * (4 * LAYERS + 1), K.calls
         assert K.calls.get("attention_decode (TMA, cluster merge)", 0) >= 32 * LAYERS, K.calls
     assert K.take_device_error() == 0
 
@@ -187,7 +187,7 @@ def test_unequal_batches_with_decode_steps_of_1_to_40_rows(real, dtype):
         assert_close(got[i], oracle.logits(tokens, dtype), dtype, f"real widths batched request {i}")
     assert llm.engine.cache.n_free_slots == llm.engine.cache.n_slots
     if dtype == "bfloat16":
-        for kind in ("linear_tma", "linear_tc5", "linear_small", "attention_prefill (tcgen05)"):
+        for kind in ("linear_tc5", "linear_small", "attention_prefill (tcgen05)"):
             assert K.calls.get(kind, 0) > 0, (kind, K.calls)
     assert K.take_device_error() == 0
 
@@ -212,6 +212,23 @@ def test_unequal_batches_with_every_product_on_the_tcgen05_kernel(real, monkeypa
     decode_norms = [rows for rows in norm_calls if rows <= 40]
     assert len(decode_norms) == 2 * len(decode_rows), (len(decode_norms), len(decode_rows))
     assert K.calls.get("linear_tc5", 0) >= len(decode_rows) * (4 * LAYERS + 1)
+    assert K.take_device_error() == 0
+
+
+def test_unequal_batches_with_the_small_steps_on_the_tma_kernel(real, monkeypatch):
+    """The engine prefers the direct kernel up to 8 rows; the TMA + mma.sync kernel is what takes a width the direct
+    kernel does not.  Forced onto it, the decode steps of up to 64 rows run its one to eight batch tiles with the
+    norm folded in and the fused activation - inside a model, against the same oracle."""
+    folder, oracle = real
+    requests, _ = batched_requests()
+    monkeypatch.setattr(K, "SMALL_LINEAR", "tma")
+    llm = load(folder, "bfloat16", max_seqs=40)
+    K.calls.clear()
+    got, decode_rows = replay_in_batches(llm, requests[:40], PROMPTS[:40], batch_size=40)
+    assert {40, 17, 16, 9, 8, 1} <= set(decode_rows), decode_rows
+    for i, tokens in enumerate(requests[:40]):
+        assert_close(got[i], oracle.logits(tokens, "bfloat16"), "bfloat16", f"real widths, TMA kernel forced, request {i}")
+    assert K.calls.get("linear_tma", 0) >= len(decode_rows) * 2 * LAYERS, K.calls
     assert K.take_device_error() == 0
 
 
