@@ -137,6 +137,19 @@ linear_small_kernel(LinearArgs a) {
     }
   }
 
+  // The residual epilogue of the 8-warp variants has one element per thread (16 weight rows x up to 16 batch rows):
+  // the thread asks for its residual value and the next norm's weight now, so that the block's end does not wait
+  // a memory latency for them.
+  constexpr bool EARLY_RESID = NT <= 2 && LS_WARPS == 8;
+  float resid_early = 0.f, next_w_early = 0.f;
+  if (EARLY_RESID && a.epilogue == EPI_RESID && rank == 0 && threadIdx.x < 16 * 8 * NT) {
+    const int m = threadIdx.x >> 4, r = threadIdx.x & 15;
+    if (m < a.M && n0 + r < a.N) {
+      resid_early = a.resid[(size_t)m * a.N + n0 + r];
+      next_w_early = a.next_w[n0 + r];
+    }
+  }
+
   int c = first;
   for (; c + LS_UNROLL <= last; c += LS_UNROLL) {
     uint4 fa[LS_UNROLL], fb[LS_UNROLL];
@@ -248,9 +261,9 @@ linear_small_kernel(LinearArgs a) {
         if (a.in.sumsq) v *= row_factor[m];
         if (a.bias) v += a.bias[n0 + r];
         const size_t at = (size_t)m * a.N + n0 + r;
-        now = a.resid[at] + v;
+        now = (EARLY_RESID ? resid_early : a.resid[at]) + v;  // EARLY_RESID: i is threadIdx.x, one round of this loop
         a.resid[at] = now;
-        out[at] = __float2bfloat16_rn(now * a.next_w[n0 + r]);
+        out[at] = __float2bfloat16_rn(now * (EARLY_RESID ? next_w_early : a.next_w[n0 + r]));
       }
       float sq = now * now;
 #pragma unroll
