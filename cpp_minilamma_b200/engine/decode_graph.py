@@ -47,6 +47,7 @@ class _Captured:
         self.dev = torch.zeros(size, dtype=torch.int32, device=engine.device)
         self.copied = torch.cuda.Event()
         self.graph = None
+        self.generation = -1  # the workspace's generation when the graph was captured
         self.failures = 0  # captures that did not go through (the step then ran eagerly)
         self.launches = 0
         h = self.host.numpy()[:_FIELDS * batch].reshape(_FIELDS, batch)
@@ -118,9 +119,7 @@ class DecodeGraphs:
         starts = [engine.cache.seq_len[s] for s in slots]
         engine.cache.reserve([(s, 1) for s in slots])
         updates = engine.cache.take_table_updates()
-        if self._generation != engine.ws.generation:  # a workspace buffer moved: old graphs point at freed memory
-            self._captured.clear()
-            self._generation = engine.ws.generation
+        self._forget_stale_graphs()  # a prompt step or another engine call may have moved a workspace buffer
         key = (batch, params.is_greedy, params.temperature, params.top_k, params.seed)
         cap = self._captured.get(key)
         fresh = cap is None
@@ -173,22 +172,39 @@ class DecodeGraphs:
                 return self.sampler.ticket(batch)
             cap.launches = K.launches - before
             K.launches = before
-            if self._generation != engine.ws.generation:
-                # the capture itself grew the workspace: its addresses are stale, run eagerly and try again later
-                self._generation = engine.ws.generation
-                self._captured.pop(key, None)
+            if self._forget_stale_graphs():
+                # the capture itself grew the workspace: its addresses are stale (and so are those of every
+                # other batch size's graph), run eagerly and try again later
                 self._body(cap, params)
+                self._forget_stale_graphs()
                 return self.sampler.ticket(batch)
             cap.graph = graph
+            cap.generation = engine.ws.generation
         if cap.graph is not None:
+            if cap.generation != engine.ws.generation:
+                raise RuntimeError("decode graphs: a captured step outlived the workspace buffers it was captured with")
             cap.graph.replay()
             K.launches += cap.launches
             self.replays += 1
         else:
             self._body(cap, params)
-            if self._generation != engine.ws.generation:
-                self._generation = engine.ws.generation
+            # an eager step of a new batch size may have grown buffers that the graphs of other batch sizes
+            # were captured with; this one has no graph yet and keeps its index buffers
+            self._forget_stale_graphs(keep=key)
         return self.sampler.ticket(batch)
+
+    def _forget_stale_graphs(self, keep=None) -> bool:
+        """Drop every captured step if a workspace buffer has moved since the last look (a graph replays the
+        addresses it was captured with, and the old buffer is freed); True if one had.  `keep`: a key whose
+        entry has no graph yet and stays."""
+        if self._generation == self.engine.ws.generation:
+            return False
+        self._generation = self.engine.ws.generation
+        kept = self._captured.get(keep) if keep is not None else None
+        self._captured.clear()
+        if kept is not None and kept.graph is None:
+            self._captured[keep] = kept
+        return True
 
     def _body(self, cap: _Captured, params: SamplingParams) -> None:
         logits = self.engine.model.forward(cap.state, self.engine.cache, cap.state.tokens, cap.state.want_rows)

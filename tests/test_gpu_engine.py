@@ -425,6 +425,33 @@ def test_long_generation_crosses_pages_under_graphs_and_run_ahead(model_folders,
     llm.engine.cache.check()
 
 
+@pytest.mark.parametrize("name,dtype", [("D", "bfloat16"), ("B", "bfloat16"), ("C", "float32")])
+def test_graphs_of_a_small_batch_survive_a_larger_batch_in_between(model_folders, name, dtype):
+    """A batch of 2, then a batch of 5, then the batch of 2 again on one engine whose prompt steps are cut
+    into portions of 64 tokens.  No portion of the larger batch's prompts holds more sequences than the
+    smaller batch had, so the first buffers to grow are those of the larger batch's first decode step, and
+    the smaller batch's captured step was recorded with them; it must not be replayed with the old
+    addresses.  Same tokens as an engine without graphs, and no captured step is older than the workspace."""
+    from cpp_minilamma_b200 import EngineBackend, SamplingParams
+    from cpp_minilamma_b200.engine.generate import generate
+    folder, llm = load(model_folders, name, dtype, max_seqs=5, max_step_tokens=64)
+    _, plain_llm = load(model_folders, name, dtype, max_seqs=5, max_step_tokens=64)
+    two = [tc.random_tokens(name, n, 950 + n) for n in (70, 67)]
+    five = [tc.random_tokens(name, n, 960 + n) for n in (66, 70, 65, 72, 68)]
+    graphs = llm.engine.shared_decode_graphs()
+    generations = []
+    for round_, prompts in enumerate((two, five, two, five, two)):
+        got = generate(EngineBackend(llm.engine, SamplingParams()), prompts, 12, set())
+        ref = generate(EngineBackend(plain_llm.engine, SamplingParams(), use_graphs=False), prompts, 12, set())
+        assert [c.tokens for c in got] == [c.tokens for c in ref], f"{name} {dtype}: batch {round_} of {len(prompts)}"
+        for cap in graphs._captured.values():
+            assert cap.graph is None or cap.generation == llm.engine.ws.generation
+        generations.append(llm.engine.ws.generation)
+    assert generations[1] > generations[0], "the larger batch grew no buffer: the test does not reach its case"
+    assert graphs.replays > 0
+    llm.engine.cache.check()
+
+
 @pytest.mark.parametrize("name", ["B", "D"])
 def test_decode_with_norms_folded_into_products_and_apart(model_folders, name, monkeypatch):
     # decode steps of few rows fold every norm but the first and the last into the products around it;
