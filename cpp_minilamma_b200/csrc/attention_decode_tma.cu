@@ -551,11 +551,12 @@ int launch_decode_tma_as(const CUtensorMap& kmap, const CUtensorMap& vmap, const
   return 0;
 }
 
-// Whether a cluster of `n_splits` of these blocks can be resident (asked once per kernel and size).
+// How many clusters of `n_splits` of these blocks the device holds at once (0: such a cluster cannot be
+// launched); asked once per kernel and size.
 template <int D, bool FUSED>
-bool decode_cluster_fits(int n_splits) {
-  static int known[17] = {0};  // 0 unknown, 1 fits, 2 does not
-  if (n_splits < 2 || n_splits > 16) return false;
+int decode_clusters_resident(int n_splits) {
+  static int known[17] = {0};  // 0 unknown, -1 none, else the count
+  if (n_splits < 2 || n_splits > 16) return 0;
   if (known[n_splits] == 0) {
     auto kernel = attn_decode_tma_kernel<D, FUSED, true>;
     const size_t smem = DecodeTmaSmem<D>::BYTES;
@@ -578,15 +579,15 @@ bool decode_cluster_fits(int n_splits) {
       err = cudaOccupancyMaxActiveClusters(&clusters, kernel, &config);
     }
     if (err != cudaSuccess) cudaGetLastError();  // not an error of the caller's: the other merge is used
-    known[n_splits] = (err == cudaSuccess && clusters >= 1) ? 1 : 2;
+    known[n_splits] = (err == cudaSuccess && clusters >= 1) ? clusters : -1;
   }
-  return known[n_splits] == 1;
+  return max(known[n_splits], 0);
 }
 
 template <int D, bool FUSED>
 int launch_decode_tma(const CUtensorMap& kmap, const CUtensorMap& vmap, const DecodeMmaArgs& a, int n_seqs,
                       int cluster_merge, cudaStream_t stream) {
-  if (cluster_merge && decode_cluster_fits<D, FUSED>(a.n_splits))
+  if (cluster_merge && decode_clusters_resident<D, FUSED>(a.n_splits) >= 1)
     return launch_decode_tma_as<D, FUSED, true>(kmap, vmap, a, n_seqs, stream);
   return launch_decode_tma_as<D, FUSED, false>(kmap, vmap, a, n_seqs, stream);
 }
@@ -606,6 +607,16 @@ extern "C" int* mll_attn_decode_tma_error_address() {
 
 MLL_API int mll_attn_decode_tma_supported(int dtype, int head_dim) {
   return dtype == MLL_BF16 && (head_dim == 64 || head_dim == 128);
+}
+
+// Clusters of `n_splits` blocks of the (fused) kernel for this head size that the device holds at once; 0 if
+// such a cluster cannot be launched or the head size is not taken.
+MLL_API int mll_attn_decode_tma_resident_clusters(int head_dim, int fused, int n_splits) {
+  if (head_dim == 64)
+    return fused ? mll::decode_clusters_resident<64, true>(n_splits) : mll::decode_clusters_resident<64, false>(n_splits);
+  if (head_dim == 128)
+    return fused ? mll::decode_clusters_resident<128, true>(n_splits) : mll::decode_clusters_resident<128, false>(n_splits);
+  return 0;
 }
 
 // One query token per sequence over the paged cache (bfloat16, head_dim 64 or 128).  Either q [B, Hq d]

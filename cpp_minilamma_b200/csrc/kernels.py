@@ -14,7 +14,7 @@ import torch
 from ..cache.paged import PAGE  # cache positions per page; the library's MLL_PAGE is checked against it on load
 from .build import KernelBuildError, load_library
 
-ABI_VERSION = 23
+ABI_VERSION = 24
 MAX_TOP_K = 1024
 
 
@@ -578,6 +578,26 @@ def _tma_decode(q, qkv, cos, sin, interleaved, write_kv, k_cache, v_cache, seq_s
            "attention_decode (TMA, cluster merge)" if USE_CLUSTER_MERGE and 2 <= n_splits <= 16
            else "attention_decode (TMA)")
     return True
+
+
+_cluster_capacity = {}
+
+
+def attention_decode_cluster_capacity(dtype: torch.dtype, head_dim: int, fused: bool):
+    """capacity[s], s = 0 .. 16: how many clusters of s blocks of the TMA decode kernel the device holds at once
+    (0: no such cluster), or None when that kernel or its cluster merge is not what runs for this dtype and
+    head size.  A launch with more clusters than that runs in two waves; measured on B200 at 8 kv heads of
+    128, contexts of 128 .. 2,048: 3 sequences with 12 splits (24 clusters, 21 fit) 14.2 us, with 10 splits
+    8.8 us; 4 sequences 9 / 8 splits 14.4 / 9.1 us; 5 sequences 7 / 6 splits 15.1 / 9.9 us."""
+    if not (USE_TMA_DECODE and USE_TENSOR_CORE_DECODE and USE_CLUSTER_MERGE and dtype == torch.bfloat16
+            and lib().mll_attn_decode_tma_supported(dtype_code(dtype), head_dim)):
+        return None
+    key = (head_dim, bool(fused))
+    if key not in _cluster_capacity:
+        _cluster_capacity[key] = (0, 0) + tuple(
+            int(lib().mll_attn_decode_tma_resident_clusters(ctypes.c_int(head_dim), ctypes.c_int(int(fused)), ctypes.c_int(s)))
+            for s in range(2, 17))
+    return _cluster_capacity[key]
 
 
 def attention_decode_fused_supported(dtype: torch.dtype, head_dim: int) -> bool:

@@ -140,7 +140,17 @@ class Attention(Mixer):
         # The tensor-core kernel applies the same rule to each sequence's own length (a short
         # sequence uses fewer of the offered splits), so a launch captured for the longest
         # context serves the short ones at their own split count.
-        return max(1, min(self.target_blocks // blocks, pages, max(16, pages // 16)))
+        by_length = min(pages, max(16, pages // 16))
+        splits = max(1, min(self.target_blocks // blocks, by_length))
+        # Up to 16 splits the TMA kernel's blocks of one (sequence, kv head) form a cluster, and fewer clusters
+        # of s blocks are resident together than 2 x multiprocessors / s blocks are (a cluster stays inside
+        # one group of multiprocessors): the most splits whose clusters are all resident at once.
+        capacity = K.attention_decode_cluster_capacity(self.ctx.act_dtype, self.head_dim, self.bias is None)
+        if capacity is not None and by_length >= 2:
+            fit = [s for s in range(2, min(16, by_length) + 1) if blocks <= capacity[s]]
+            if fit:
+                return fit[-1]
+        return splits
 
     takes_prenormed = True  # the q/k/v product may read rows whose norm it finishes itself
     adds_residual = True    # the output product may add to the residual stream and prepare the next norm
