@@ -22,9 +22,9 @@ from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent
 SOURCES = ["elementwise.cu", "norm.cu", "rope_cache.cu", "attention.cu", "sampling.cu",
-           "linear_small.cu", "linear_tma.cu", "linear_tc5.cu", "attention_mma.cu", "attention_tc5.cu",
-           "attention_decode_tma.cu", "device_error.cu"]
-HEADERS = ["common.cuh", "no_alloc.h", "tensor_map.h", "attention_decode.cuh", "device_error.h"]
+           "linear_small.cu", "linear_tma.cu", "linear_tc5.cu", "attention_mma.cu", "attention_mma_odd.cu",
+           "attention_mma_prefill.cu", "attention_tc5.cu", "attention_decode_tma.cu", "device_error.cu"]
+HEADERS = ["common.cuh", "no_alloc.h", "tensor_map.h", "attention_decode.cuh", "attention_mma.cuh", "device_error.h"]
 LIB_NAME = "libmll_kernels.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

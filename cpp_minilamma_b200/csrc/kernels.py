@@ -14,7 +14,7 @@ import torch
 from ..cache.paged import PAGE  # cache positions per page; the library's MLL_PAGE is checked against it on load
 from .build import KernelBuildError, load_library
 
-ABI_VERSION = 24
+ABI_VERSION = 25
 MAX_TOP_K = 1024
 
 
@@ -502,7 +502,7 @@ def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratc
                      n_heads: int, n_kv_heads: int, head_dim: int, n_splits: int, window: int,
                      scale: float, counters: Optional[torch.Tensor] = None, order: Optional[torch.Tensor] = None) -> None:
     """One query token per sequence (q row i belongs to sequence i) over the paged cache.
-    bfloat16 with head_dim 64/128/256 runs on tensor cores, everything else on the general kernel.
+    bfloat16 runs on tensor cores (head sizes 16 .. 256 in steps of 16), float32 on the general kernel.
     `order`: optional int32 permutation of the sequences, longest context first; the TMA-fed kernel starts its
     blocks in that order so that short sequences fill the end of the launch (the others ignore it)."""
     _check_attention(q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim)
@@ -612,7 +612,7 @@ def attention_decode_fused(qkv, cos, sin, interleaved: bool, write_kv: bool, k_c
                            order: Optional[torch.Tensor] = None) -> None:
     """Decode step: row i of qkv [B, (Hq + 2 Hk) d] is sequence i's new token at position seq_ctx[i] - 1.
     Rotates q and k (tables as for rope_cache_write, or None), writes k and v into the paged cache and
-    attends over it, in one launch (bfloat16, head_dim 64/128/256)."""
+    attends over it, in one launch (bfloat16, head sizes 16 .. 256 in steps of 16)."""
     _need(qkv, "attention qkv", torch.bfloat16, 2)
     _need(out, "attention out", torch.bfloat16, 2)
     _need(k_cache, "attention k_cache", torch.bfloat16, 4)

@@ -166,7 +166,7 @@ class PagedCase:
 def decode_impl(request):
     """bfloat16 decode attention has two tensor-core kernels: the TMA-fed one (head sizes 64/128,
     needs arrival counters when the context is split; it merges the splits inside a thread-block
-    cluster, or - second variant - through global memory) and the cp.async one (64/128/256); the
+    cluster, or - second variant - through global memory) and the cp.async one (16 .. 256 in steps of 16); the
     general kernel must stay right at those sizes too."""
     K.USE_TENSOR_CORE_DECODE = request.param != "general"
     K.USE_TMA_DECODE = request.param.startswith("tma")
@@ -454,6 +454,37 @@ def test_attention_prefill_far_key_stands_out(dtype, prefill_impl):
     np.testing.assert_allclose(got[far:], 7.0, rtol=1e-2, atol=1e-2)   # every query from `far` on sees it
     ref = pl.causal_attention(as64(q), as64(case.k[0]), as64(case.v[0]))
     np.testing.assert_allclose(got, ref, **attention_tol(dtype, prefill_impl, as64(case.v[0])))
+
+
+EVERY_HEAD_SIZE = [(4, 2, 16), (6, 1, 32), (3, 3, 48), (16, 16, 64), (10, 2, 80), (6, 2, 96), (4, 4, 112), (32, 8, 128),
+                   (3, 1, 144), (8, 2, 160), (34, 2, 176), (6, 3, 192), (4, 2, 208), (2, 2, 224), (5, 1, 240), (8, 1, 256)]
+
+
+@pytest.mark.parametrize("hq,hk,d", EVERY_HEAD_SIZE)
+@pytest.mark.parametrize("splits", [1, 3])
+def test_attention_decode_on_tensor_cores_at_every_head_size(hq, hk, d, splits, monkeypatch):
+    """The cp.async / mma.sync decode kernel takes head sizes 16 .. 256 in steps of 16: a warp owns whole
+    8-column tiles of the output, and where the head's tiles do not divide by four the last warps own fewer
+    (34 heads on 2 kv heads: two chunks of 16 heads and one of 1)."""
+    monkeypatch.setattr(K, "USE_TMA_DECODE", False)
+    test_attention_decode(torch.bfloat16, hq, hk, d, splits, "tensor_core")
+
+
+@pytest.mark.parametrize("hq,hk,d", EVERY_HEAD_SIZE)
+@pytest.mark.parametrize("interleaved", [True, False])
+def test_attention_decode_fused_at_every_head_size(hq, hk, d, interleaved, monkeypatch):
+    """The fused launch rotates the queries in their fragment registers; with pairs (i, i + d/2) the partner
+    of a column lies d/2 further, which is a whole number of 16-column steps only when d is a multiple of 32."""
+    test_attention_decode_fused_with_rope_and_cache_write(hq, hk, d, interleaved, 3, 0, True, False, monkeypatch)
+    test_attention_decode_fused_with_rope_and_cache_write(hq, hk, d, interleaved, 2, 70, True, False, monkeypatch)
+
+
+@pytest.mark.parametrize("hq,hk,d", EVERY_HEAD_SIZE)
+@pytest.mark.parametrize("window", [0, 70])
+def test_attention_prefill_on_tensor_cores_at_every_head_size(hq, hk, d, window, monkeypatch):
+    """The mma.sync prefill kernel at head sizes 16 .. 256 (fewer blocks per multiprocessor above 128)."""
+    monkeypatch.setattr(K, "USE_TCGEN05_PREFILL", False)
+    test_attention_prefill(torch.bfloat16, hq, hk, d, window, "tensor_core")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
