@@ -1,4 +1,5 @@
-// Sampling on the device: greedy, temperature and top-k, one block per logits row.
+// Sampling on the device: greedy, temperature and top-k, one block per logits row, or a cluster of eight for a
+// large vocabulary.
 //
 // Rules of the reference's CPU sampler (src/sampler.cc):
 //   * greedy returns the first index of the maximum (:31-41);
@@ -419,6 +420,393 @@ sample_top_k_kernel(const float* __restrict__ logits, int vocab, int top_k, floa
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------- //
+// Sampling over a large vocabulary: the eight blocks of a thread-block cluster share one row.  Every
+// thread keeps VPT consecutive logits of the row in registers (block r the r-th eighth, thread t of it
+// the t-th run of VPT), so the row is read from memory once, and whatever runs over the candidates in
+// id order (the cumulative weights, the lowest ids among equal logits) is a scan over threads and then
+// over blocks.  One block per row (above) reads its 128,256 logits several times with 4-byte or
+// scattered loads: 60 us (temperature) and 190 us (top-k) a decode step at eight rows; these take a tenth.
+// ---------------------------------------------------------------------------------------------------- //
+constexpr int SC_CLUSTER = 8;
+constexpr int SC_THREADS = 512;
+
+__device__ __forceinline__ int block_exclusive_scan_int(int v, int* scratch, int* total) {
+  // scratch: 33 ints; fixed order
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int n = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += n;
+  }
+  __syncthreads();
+  if (lane == 31) scratch[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    const int w = lane < (int)(blockDim.x >> 5) ? scratch[lane] : 0;
+    int wi = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, wi, o);
+      if (lane >= o) wi += n;
+    }
+    scratch[lane] = wi - w;
+    if (lane == 31) scratch[32] = wi;
+  }
+  __syncthreads();
+  *total = scratch[32];
+  return scratch[warp] + incl - v;
+}
+
+// The thread's VPT logits of row `row` (ids first .. first + VPT - 1, those at or beyond `end` read as -inf);
+// returns whether one of them is not finite.
+template <int VPT>
+__device__ __forceinline__ bool load_run(const float* __restrict__ row, int first, int end, bool vector_ok, float (&v)[VPT]) {
+  bool nonfinite = false;
+  if (vector_ok && first + VPT <= end) {
+#pragma unroll
+    for (int j = 0; j < VPT; j += 4) {
+      const float4 x = *reinterpret_cast<const float4*>(row + first + j);
+      v[j] = x.x;
+      v[j + 1] = x.y;
+      v[j + 2] = x.z;
+      v[j + 3] = x.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) v[j] = first + j < end ? row[first + j] : -INFINITY;
+  }
+#pragma unroll
+  for (int j = 0; j < VPT; ++j)
+    if (first + j < end && !isfinite(v[j])) nonfinite = true;
+  return nonfinite;
+}
+
+// How a row is cut: block `rank` takes ids [begin, end), a multiple of four of them.
+__device__ __forceinline__ void cluster_slice(int vocab, int rank, int& begin, int& end) {
+  const int per = ((vocab + SC_CLUSTER * 4 - 1) / (SC_CLUSTER * 4)) * 4;
+  begin = min(vocab, rank * per);
+  end = min(vocab, begin + per);
+}
+
+// Temperature sampling over the whole vocabulary, candidates in id order (the rule of sample_temperature_kernel).
+// Every block takes its weights relative to its own maximum; after one cluster barrier each block knows all
+// eight (maximum, sum) pairs and with them the row's maximum, the total and the sum before its own share.  The
+// thread whose run holds the threshold reports its token to block 0 (the lowest id wins), which writes it out
+// after the second barrier.
+template <int VPT>
+__global__ void __cluster_dims__(SC_CLUSTER, 1, 1) __launch_bounds__(SC_THREADS, (VPT <= 16 ? 2 : 1))
+sample_temperature_cluster_kernel(const float* __restrict__ logits, int vocab, float temperature,
+                                  unsigned long long seed, const int* __restrict__ request,
+                                  const int* __restrict__ step, int* __restrict__ tokens, int* __restrict__ status,
+                                  MllDeviceErrorWords errors) {
+  __shared__ float fscratch[33];
+  __shared__ int iscratch[32];
+  __shared__ float blk_max, blk_total;
+  __shared__ int cl_pick, cl_bad;  // block 0's are the cluster's
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
+  const int row_index = blockIdx.y, tid = threadIdx.x;
+  const float* row = logits + (size_t)row_index * vocab;
+  int begin, end;
+  cluster_slice(vocab, rank, begin, end);
+  const int first = begin + tid * VPT;
+  float v[VPT];
+  const bool nonfinite = load_run<VPT>(row, first, end, vocab % 4 == 0 && ((uintptr_t)logits & 15) == 0, v);
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) mx = fmaxf(mx, v[j]);
+  mx = block_max(mx, fscratch);
+  const int any_bad = __syncthreads_or(nonfinite ? 1 : 0);
+  const float inv_t = 1.f / temperature;
+  float mine = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    v[j] = (first + j < end && v[j] > -INFINITY) ? expf((v[j] - mx) * inv_t) : 0.f;  // the weights, from here on
+    mine += v[j];
+  }
+  float total;
+  const float before = block_exclusive_scan(mine, fscratch, &total);
+  if (tid == 0) {
+    blk_max = mx;
+    blk_total = total;
+    cl_pick = 0x7fffffff;
+    cl_bad = 0;
+  }
+  cluster.sync();  // every block's maximum and sum stand
+  float row_max = -INFINITY;
+#pragma unroll
+  for (int r = 0; r < SC_CLUSTER; ++r) row_max = fmaxf(row_max, *cluster.map_shared_rank(&blk_max, r));
+  float base = 0.f, grand = 0.f, scale = 0.f;
+#pragma unroll
+  for (int r = 0; r < SC_CLUSTER; ++r) {
+    const float m = *cluster.map_shared_rank(&blk_max, r);
+    const float f = m > -INFINITY ? expf((m - row_max) * inv_t) : 0.f;  // block r's weights relative to the row's maximum
+    const float t = *cluster.map_shared_rank(&blk_total, r) * f;
+    if (r < rank) base += t;
+    if (r == rank) scale = f;
+    grand += t;
+  }
+  const float u = uniform01(seed, request[row_index], step[row_index]);
+  const float threshold = u * grand;
+  const int owner = block_min_int((first < end && threshold <= base + (before + mine) * scale) ? tid : 0x7fffffff, iscratch);
+  if (tid == owner) {
+    float cum = base + before * scale;
+    int pick = min(end, first + VPT) - 1;
+    bool found = false;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      cum += v[j] * scale;
+      if (!found && first + j < end && threshold <= cum) {
+        pick = first + j;
+        found = true;
+      }
+    }
+    atomicMin(cluster.map_shared_rank(&cl_pick, 0), pick);  // ids rise with the rank: the first block that holds it wins
+  }
+  if (tid == 0 && any_bad) atomicOr(cluster.map_shared_rank(&cl_bad, 0), 1);
+  cluster.sync();  // the candidates and flags are in block 0's shared memory
+  if (rank == 0 && tid == 0) {
+    tokens[row_index] = cl_pick == 0x7fffffff ? vocab - 1 : cl_pick;
+    status[row_index] = cl_bad | (row_index == 0 ? take_error_bits(errors) : 0);
+  }
+}
+
+constexpr int SC_BITS0 = 11, SC_BITS1 = 11, SC_BITS2 = 10;  // radix digits of the three selection passes
+constexpr int SC_BINS = 1 << SC_BITS0;
+constexpr int SC_CAND = 1024;
+
+// Top-k (k <= 1024) then temperature sampling over the kept candidates in descending order, equal logits by
+// lower id (the rule of sample_top_k_kernel).  The k-th largest key is narrowed down by a radix selection over the
+// registers, 11, 11 and 10 bits at a time; after each pass every block sums the eight histograms through
+// distributed shared memory and finds the digit for itself (two histogram buffers in turn, so one cluster barrier
+// a pass).  As soon as no more than 1,024 keys are left at or above the digit's lower bound - with a few dozen
+// kept out of 128,256 that is after the first pass - they all go to block 0, which sorts them and draws among the
+// first k.  Only when more than 1,024 keys tie with the k-th does the exact rule need the counts of every block.
+template <int VPT>
+__global__ void __cluster_dims__(SC_CLUSTER, 1, 1) __launch_bounds__(SC_THREADS, (VPT <= 16 ? 2 : 1))
+sample_top_k_cluster_kernel(const float* __restrict__ logits, int vocab, int top_k, float temperature,
+                            unsigned long long seed, const int* __restrict__ request, const int* __restrict__ step,
+                            int* __restrict__ tokens, int* __restrict__ status, MllDeviceErrorWords errors) {
+  __shared__ unsigned long long cand[SC_CAND];  // used in block 0
+  __shared__ int hist[2][SC_BINS];
+  __shared__ float fscratch[33];
+  __shared__ int iscratch[33];
+  __shared__ unsigned sel_prefix;
+  __shared__ int sel_remaining, sel_at_or_above;
+  __shared__ int blk_greater, blk_equal;
+  __shared__ int cl_count, cl_bad;              // block 0's are the cluster's
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
+  const int row_index = blockIdx.y, tid = threadIdx.x;
+  const float* row = logits + (size_t)row_index * vocab;
+  int begin, end;
+  cluster_slice(vocab, rank, begin, end);
+  const int first = begin + tid * VPT;
+  unsigned key[VPT];
+  int any_bad;
+  {
+    float v[VPT];
+    const bool nonfinite = load_run<VPT>(row, first, end, vocab % 4 == 0 && ((uintptr_t)logits & 15) == 0, v);
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) key[j] = order_key(v[j]);
+    any_bad = __syncthreads_or(nonfinite ? 1 : 0);
+  }
+  for (int i = tid; i < SC_CAND; i += SC_THREADS) cand[i] = 0ull;
+  if (tid == 0) {
+    cl_count = 0;
+    cl_bad = 0;
+  }
+  unsigned prefix = 0;       // the digits of the k-th key found so far
+  int remaining = top_k;     // its rank among the keys that share them
+  int at_or_above = vocab;   // keys at or above the lower bound that the digits give
+  int passes = 0;
+  for (; passes < 3 && at_or_above > SC_CAND; ++passes) {
+    const int bits = passes == 0 ? SC_BITS0 : passes == 1 ? SC_BITS1 : SC_BITS2;
+    const int shift = passes == 0 ? SC_BITS1 + SC_BITS2 : passes == 1 ? SC_BITS2 : 0;
+    const int bins = 1 << bits;
+    const unsigned mask = passes == 0 ? 0u : (0xffffffffu << (shift + bits));
+    int* mine_hist = hist[passes & 1];  // the peers read pass p's buffer before they arrive at pass p + 1's barrier
+    for (int i = tid; i < bins; i += SC_THREADS) mine_hist[i] = 0;
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < VPT; ++j)
+      if (first + j < end && (key[j] & mask) == prefix) atomicAdd(&mine_hist[(key[j] >> shift) & (unsigned)(bins - 1)], 1);
+    cluster.sync();  // every block's histogram stands (block-wide barrier included)
+    // thread t sums bins[bins - 1 - per t - i], i < per, over the blocks: a scan over the threads then counts from the top
+    const int per = bins / SC_THREADS;
+    int c[SC_BINS / SC_THREADS];
+    int mine = 0;
+#pragma unroll
+    for (int i = 0; i < SC_BINS / SC_THREADS; ++i) {
+      c[i] = 0;
+      if (i < per) {
+        const int bin = bins - 1 - (tid * per + i);
+#pragma unroll
+        for (int r = 0; r < SC_CLUSTER; ++r) c[i] += cluster.map_shared_rank(mine_hist, r)[bin];
+      }
+      mine += c[i];
+    }
+    int total;
+    int above = block_exclusive_scan_int(mine, iscratch, &total);
+    if (above < remaining && remaining <= above + mine) {  // exactly one thread: the k-th key falls into its bins
+#pragma unroll
+      for (int i = 0; i < SC_BINS / SC_THREADS; ++i) {
+        if (i < per && above < remaining) {
+          const int bin = bins - 1 - (tid * per + i);
+          if (remaining <= above + c[i]) {
+            sel_prefix = prefix | ((unsigned)bin << shift);
+            sel_remaining = remaining - above;
+            sel_at_or_above = (top_k - remaining) + above + c[i];
+            above = remaining;  // done
+          } else {
+            above += c[i];
+          }
+        }
+      }
+    }
+    __syncthreads();
+    prefix = sel_prefix;
+    remaining = sel_remaining;
+    at_or_above = sel_at_or_above;
+  }
+  unsigned long long* out = cluster.map_shared_rank(cand, 0);
+  int n_cand;
+  if (at_or_above <= SC_CAND) {
+    // every key at or above the lower bound: the order in which they arrive does not matter, block 0 sorts them
+    n_cand = at_or_above;
+    int n = 0;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) n += first + j < end && key[j] >= prefix;
+    if (n > 0) {
+      int at = atomicAdd(cluster.map_shared_rank(&cl_count, 0), n);
+#pragma unroll
+      for (int j = 0; j < VPT; ++j)
+        if (first + j < end && key[j] >= prefix)
+          out[at++] = ((unsigned long long)key[j] << 32) | (unsigned)(0xffffffffu - (unsigned)(first + j));
+    }
+  } else {
+    // more than 1,024 keys equal to the k-th (all three passes are done: prefix is that key): the greater ones
+    // and, of the equal ones, those with the lowest ids
+    n_cand = top_k;
+    const unsigned kth = prefix;
+    const int need_equal = remaining;
+    int n_greater = 0, n_equal = 0;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j)
+      if (first + j < end) {
+        n_greater += key[j] > kth;
+        n_equal += key[j] == kth;
+      }
+    int total_g, total_e;
+    int pos_g = block_exclusive_scan_int(n_greater, iscratch, &total_g);
+    int pos_e = block_exclusive_scan_int(n_equal, iscratch, &total_e);
+    if (tid == 0) {
+      blk_greater = total_g;
+      blk_equal = total_e;
+    }
+    cluster.sync();  // every block's counts stand (the branch is the same for the whole cluster)
+    int all_greater = 0;
+#pragma unroll
+    for (int r = 0; r < SC_CLUSTER; ++r) {
+      const int g = *cluster.map_shared_rank(&blk_greater, r), e = *cluster.map_shared_rank(&blk_equal, r);
+      if (r < rank) {
+        pos_g += g;
+        pos_e += e;
+      }
+      all_greater += g;
+    }
+#pragma unroll
+    for (int j = 0; j < VPT; ++j)
+      if (first + j < end) {
+        const unsigned long long packed = ((unsigned long long)key[j] << 32) | (unsigned)(0xffffffffu - (unsigned)(first + j));
+        if (key[j] > kth) {
+          out[pos_g++] = packed;
+        } else if (key[j] == kth) {
+          if (pos_e < need_equal) out[all_greater + pos_e] = packed;
+          ++pos_e;
+        }
+      }
+  }
+  if (tid == 0 && any_bad) atomicOr(cluster.map_shared_rank(&cl_bad, 0), 1);
+  cluster.sync();  // the candidates are in block 0's shared memory; the peers are done
+  if (rank != 0) return;
+
+  // bitonic sort of the first `width` entries, descending; unused entries are 0 and sink to the end
+  int width = 2;
+  while (width < n_cand) width <<= 1;
+  for (int size = 2; size <= width; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int i = tid; i < width; i += SC_THREADS) {
+        const int partner = i ^ stride;
+        if (partner > i) {
+          const unsigned long long x = cand[i], y = cand[partner];
+          const bool descending = (i & size) == 0;
+          if (descending ? x < y : x > y) {
+            cand[i] = y;
+            cand[partner] = x;
+          }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  const int kept = top_k;  // the first k of the sorted candidates
+  const float mx = key_value((unsigned)(cand[0] >> 32));
+  const float inv_t = 1.f / temperature;
+  // thread t holds entries 2 t and 2 t + 1 of the sorted list
+  const float w0 = 2 * tid < kept ? expf((key_value((unsigned)(cand[2 * tid] >> 32)) - mx) * inv_t) : 0.f;
+  const float w1 = 2 * tid + 1 < kept ? expf((key_value((unsigned)(cand[2 * tid + 1] >> 32)) - mx) * inv_t) : 0.f;
+  float total;
+  const float before = block_exclusive_scan(w0 + w1, fscratch, &total);
+  const float u = uniform01(seed, request[row_index], step[row_index]);
+  const float threshold = u * total;
+  int mine = 0x7fffffff;
+  if (2 * tid < kept && threshold <= before + w0) mine = 2 * tid;
+  else if (2 * tid + 1 < kept && threshold <= before + w0 + w1) mine = 2 * tid + 1;
+  const int pick = block_min_int(mine, iscratch);
+  if (tid == 0) {
+    const int at = pick == 0x7fffffff ? kept - 1 : pick;
+    tokens[row_index] = (int)(0xffffffffu - (unsigned)(cand[at] & 0xffffffffull));
+    status[row_index] = cl_bad | (row_index == 0 ? take_error_bits(errors) : 0);
+  }
+}
+
+// How many of a kernel's clusters of SC_CLUSTER blocks the device holds at once (0 if the query fails).
+template <typename Kernel>
+int sample_clusters_resident(Kernel kernel) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(SC_CLUSTER, 1);
+  config.blockDim = dim3(SC_THREADS);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = SC_CLUSTER;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return clusters;
+}
+
+template <int VPT>
+void launch_sample_cluster(const float* logits, int n_rows, int vocab, float temperature, int top_k,
+                           unsigned long long seed, const int* request, const int* step, int* tokens, int* status,
+                           const MllDeviceErrorWords& errors, cudaStream_t stream) {
+  if (top_k == 0)
+    MLL_LAUNCH((sample_temperature_cluster_kernel<VPT>), dim3(SC_CLUSTER, n_rows), SC_THREADS, 0, stream, logits, vocab,
+               temperature, seed, request, step, tokens, status, errors);
+  else
+    MLL_LAUNCH((sample_top_k_cluster_kernel<VPT>), dim3(SC_CLUSTER, n_rows), SC_THREADS, 0, stream, logits, vocab, top_k,
+               temperature, seed, request, step, tokens, status, errors);
+}
+
 }  // namespace mll
 
 // logits: float32 [n_rows, vocab]; tokens, status: int32 [n_rows].
@@ -437,6 +825,21 @@ MLL_API int mll_argmax(const float* logits, int n_rows, int vocab, int* tokens, 
   return 0;
 }
 
+// Clusters (one per row) of the large-vocabulary sampling kernel for this vocabulary that are resident at once:
+// top_k == 0 the temperature kernel, else the top-k kernel; 0 where the one-block kernels run.
+MLL_API int mll_sample_resident_rows(int vocab, int top_k) {
+  const long long per_thread = ((long long)vocab + mll::SC_CLUSTER * mll::SC_THREADS - 1) / (mll::SC_CLUSTER * mll::SC_THREADS);
+  if (vocab < 8192 || per_thread > 60) return 0;
+  if (per_thread <= 14)
+    return top_k == 0 ? mll::sample_clusters_resident(mll::sample_temperature_cluster_kernel<16>)
+                      : mll::sample_clusters_resident(mll::sample_top_k_cluster_kernel<16>);
+  if (per_thread <= 30)
+    return top_k == 0 ? mll::sample_clusters_resident(mll::sample_temperature_cluster_kernel<32>)
+                      : mll::sample_clusters_resident(mll::sample_top_k_cluster_kernel<32>);
+  return top_k == 0 ? mll::sample_clusters_resident(mll::sample_temperature_cluster_kernel<64>)
+                    : mll::sample_clusters_resident(mll::sample_top_k_cluster_kernel<64>);
+}
+
 // temperature > 0; top_k == 0 samples from the whole vocabulary, 2 <= top_k <= 1024 from the
 // k largest logits.  request/step: int32 [n_rows] random-number counters.
 MLL_API int mll_sample(const float* logits, int n_rows, int vocab, float temperature, int top_k,
@@ -451,10 +854,20 @@ MLL_API int mll_sample(const float* logits, int n_rows, int vocab, float tempera
   if (n_rows == 0) return 0;
   MllDeviceErrorWords errors;
   mll_device_error_words(&errors);
-  if (top_k == 0)
+  const long long per_thread = ((long long)vocab + mll::SC_CLUSTER * mll::SC_THREADS - 1) / (mll::SC_CLUSTER * mll::SC_THREADS);
+  if (vocab >= 8192 && n_rows <= 65535 && per_thread <= 60) {
+    // a cluster per row, the row in registers (a block's share is rounded up to a multiple of four: 60, not 64)
+    if (per_thread <= 14)
+      mll::launch_sample_cluster<16>(logits, n_rows, vocab, temperature, top_k, seed, request, step, tokens, status, errors, stream);
+    else if (per_thread <= 30)
+      mll::launch_sample_cluster<32>(logits, n_rows, vocab, temperature, top_k, seed, request, step, tokens, status, errors, stream);
+    else
+      mll::launch_sample_cluster<64>(logits, n_rows, vocab, temperature, top_k, seed, request, step, tokens, status, errors, stream);
+  } else if (top_k == 0) {
     MLL_LAUNCH((mll::sample_temperature_kernel), n_rows, mll::SAMPLE_THREADS, 0, stream, logits, vocab, temperature, seed, request, step, tokens, status, errors);
-  else
+  } else {
     MLL_LAUNCH((mll::sample_top_k_kernel), n_rows, mll::SAMPLE_THREADS, 0, stream, logits, vocab, top_k, temperature, seed, request, step, tokens, status, errors);
+  }
   MLL_LAUNCH_CHECK();
   return 0;
 }
