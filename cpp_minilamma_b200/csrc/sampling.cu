@@ -774,6 +774,17 @@ sample_top_k_cluster_kernel(const float* __restrict__ logits, int vocab, int top
   }
 }
 
+// Logits a thread of the cluster kernels keeps for a vocabulary (16, 32 or 64: a block's share of the row, a
+// multiple of four, spread over its threads), or 0 where the one-block kernels run (small or huge vocabularies).
+inline int sample_cluster_run(int vocab) {
+  if (vocab < 8192) return 0;
+  const long long share = (((long long)vocab + SC_CLUSTER * 4 - 1) / (SC_CLUSTER * 4)) * 4;
+  if (share <= 16ll * SC_THREADS) return 16;
+  if (share <= 32ll * SC_THREADS) return 32;
+  if (share <= 64ll * SC_THREADS) return 64;
+  return 0;
+}
+
 // How many of a kernel's clusters of SC_CLUSTER blocks the device holds at once (0 if the query fails).
 template <typename Kernel>
 int sample_clusters_resident(Kernel kernel) {
@@ -828,12 +839,12 @@ MLL_API int mll_argmax(const float* logits, int n_rows, int vocab, int* tokens, 
 // Clusters (one per row) of the large-vocabulary sampling kernel for this vocabulary that are resident at once:
 // top_k == 0 the temperature kernel, else the top-k kernel; 0 where the one-block kernels run.
 MLL_API int mll_sample_resident_rows(int vocab, int top_k) {
-  const long long per_thread = ((long long)vocab + mll::SC_CLUSTER * mll::SC_THREADS - 1) / (mll::SC_CLUSTER * mll::SC_THREADS);
-  if (vocab < 8192 || per_thread > 60) return 0;
-  if (per_thread <= 14)
+  const int run = mll::sample_cluster_run(vocab);
+  if (run == 0) return 0;
+  if (run == 16)
     return top_k == 0 ? mll::sample_clusters_resident(mll::sample_temperature_cluster_kernel<16>)
                       : mll::sample_clusters_resident(mll::sample_top_k_cluster_kernel<16>);
-  if (per_thread <= 30)
+  if (run == 32)
     return top_k == 0 ? mll::sample_clusters_resident(mll::sample_temperature_cluster_kernel<32>)
                       : mll::sample_clusters_resident(mll::sample_top_k_cluster_kernel<32>);
   return top_k == 0 ? mll::sample_clusters_resident(mll::sample_temperature_cluster_kernel<64>)
@@ -854,12 +865,12 @@ MLL_API int mll_sample(const float* logits, int n_rows, int vocab, float tempera
   if (n_rows == 0) return 0;
   MllDeviceErrorWords errors;
   mll_device_error_words(&errors);
-  const long long per_thread = ((long long)vocab + mll::SC_CLUSTER * mll::SC_THREADS - 1) / (mll::SC_CLUSTER * mll::SC_THREADS);
-  if (vocab >= 8192 && n_rows <= 65535 && per_thread <= 60) {
-    // a cluster per row, the row in registers (a block's share is rounded up to a multiple of four: 60, not 64)
-    if (per_thread <= 14)
+  const int run = n_rows <= 65535 ? mll::sample_cluster_run(vocab) : 0;
+  if (run != 0) {
+    // a cluster per row, the row in registers
+    if (run == 16)
       mll::launch_sample_cluster<16>(logits, n_rows, vocab, temperature, top_k, seed, request, step, tokens, status, errors, stream);
-    else if (per_thread <= 30)
+    else if (run == 32)
       mll::launch_sample_cluster<32>(logits, n_rows, vocab, temperature, top_k, seed, request, step, tokens, status, errors, stream);
     else
       mll::launch_sample_cluster<64>(logits, n_rows, vocab, temperature, top_k, seed, request, step, tokens, status, errors, stream);
