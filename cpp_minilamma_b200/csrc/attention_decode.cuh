@@ -31,6 +31,12 @@ struct DecodeMmaArgs {
   // optional [B]: the sequences in the order their blocks should start (the TMA kernel; longest contexts first
   // lets the short ones fill the end of the launch)
   const int* seq_order;
+  // optional [work_pairs]: the launch as a list of (sequence, split) pairs in the order their blocks should start
+  // (the TMA kernel without clusters; the grid's second index runs over it).  Entry: sequence | split << 16 |
+  // splits of that sequence << 24, or -1 for an unused place.  A sequence then has the number of splits the
+  // entry says (at most n_splits, which stays the stride of the partial results), long sequences more than
+  // short ones.
+  const int* work;
 };
 
 __device__ __forceinline__ float2 unpack_bf162(unsigned r) {

@@ -333,11 +333,15 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
   const int g = lane >> 2, t = lane & 3;
   const int group = a.n_heads / a.n_kv_heads;
   const int chunks = (group + 15) / 16;
-  // sequences are the slower grid index, so blocks start in the order of `seq_order` (longest contexts first)
-  const int b = a.seq_order != nullptr ? a.seq_order[blockIdx.y] : blockIdx.y;
+  // sequences are the slower grid index, so blocks start in the order of `seq_order` (longest contexts first);
+  // with a work list the slower index runs over its (sequence, split) pairs instead
+  const int entry = !CLUSTER && a.work != nullptr ? a.work[blockIdx.y] : 0;
+  if (entry < 0) return;  // an unused place of the list (the same for the whole block)
+  const bool listed = !CLUSTER && a.work != nullptr;
+  const int b = listed ? (entry & 0xffff) : a.seq_order != nullptr ? a.seq_order[blockIdx.y] : blockIdx.y;
   const int item = blockIdx.x;  // kv head x head chunk
   const int kvh = item / chunks, chunk = item % chunks;
-  const int split = blockIdx.z;
+  const int split = listed ? ((entry >> 16) & 0xff) : blockIdx.z;
   const int ng = min(16, group - chunk * 16);
   const int h0 = kvh * group + chunk * 16;
 
@@ -346,7 +350,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
   const int pages_total = (ctx + MLL_PAGE - 1) / MLL_PAGE;
   const int first_page = first_key / MLL_PAGE;
   // a sequence uses as many of the offered splits as its own length pays for (attention_decode.cuh)
-  const int n_eff = decode_splits_for(pages_total - first_page, a.n_splits);
+  // ... or as many as its entry of the work list says
+  const int n_eff = listed ? min(entry >> 24, max(1, pages_total - first_page))
+                           : decode_splits_for(pages_total - first_page, a.n_splits);
   const bool misplaced = (ring & 1023u) != 0;  // cannot hold swizzled tiles: report, and do no work (uniform for the block)
   if (misplaced && tid == 0) atomicExch(&mll_attn_decode_tma_error_flag, 2);
   // splits beyond the sequence's own count have no work; in a cluster they still meet the others at its barriers
@@ -530,7 +536,8 @@ int launch_decode_tma_as(const CUtensorMap& kmap, const CUtensorMap& vmap, const
   }
   const int group = a.n_heads / a.n_kv_heads;
   cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(a.n_kv_heads * ((group + 15) / 16), n_seqs, a.n_splits);
+  // with a work list: one block per (item, pair); n_seqs is then the length of the list
+  config.gridDim = dim3(a.n_kv_heads * ((group + 15) / 16), n_seqs, !CLUSTER && a.work != nullptr ? 1 : a.n_splits);
   config.blockDim = dim3(DT_THREADS);
   config.dynamicSmemBytes = smem;
   config.stream = stream;
@@ -587,7 +594,7 @@ int decode_clusters_resident(int n_splits) {
 template <int D, bool FUSED>
 int launch_decode_tma(const CUtensorMap& kmap, const CUtensorMap& vmap, const DecodeMmaArgs& a, int n_seqs,
                       int cluster_merge, cudaStream_t stream) {
-  if (cluster_merge && decode_clusters_resident<D, FUSED>(a.n_splits) >= 1)
+  if (cluster_merge && a.work == nullptr && decode_clusters_resident<D, FUSED>(a.n_splits) >= 1)
     return launch_decode_tma_as<D, FUSED, true>(kmap, vmap, a, n_seqs, stream);
   return launch_decode_tma_as<D, FUSED, false>(kmap, vmap, a, n_seqs, stream);
 }
@@ -627,15 +634,21 @@ MLL_API int mll_attn_decode_tma_resident_clusters(int head_dim, int fused, int n
 // cluster_merge != 0: with 2 to 16 splits the blocks of a group form a thread-block cluster and merge
 // through distributed shared memory instead (scratch and counters stay untouched).  seq_order: optional
 // permutation of 0 .. n_seqs - 1; the blocks of sequence seq_order[0] start first (give the longest first).
+// work: optional list of work_pairs (sequence, split) entries (attention_decode.cuh) that replaces the grid over
+// sequences and splits, so that sequences of one launch have different numbers of splits; n_splits is then the
+// most any sequence has, and no cluster is formed.
 MLL_API int mll_attn_decode_tma(const void* q, const void* qkv, int qkv_ld, const float* cos_table,
                                 const float* sin_table, int interleaved, int write_kv, void* k_cache, void* v_cache,
                                 long long n_pages, const int* seq_slot, const int* seq_ctx, const int* block_table,
                                 float* scratch, void* out, int n_seqs, int n_heads, int n_kv_heads, int head_dim,
                                 int max_blocks, int n_splits, int window, float scale, int* counters,
-                                int cluster_merge, const int* seq_order, cudaStream_t stream) {
+                                int cluster_merge, const int* seq_order, const int* work, int work_pairs,
+                                cudaStream_t stream) {
   MLL_REQUIRE(mll_attn_decode_tma_supported(MLL_BF16, head_dim), "attention decode (tma): head_dim %d", head_dim);
   MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention decode (tma): bad head counts");
   MLL_REQUIRE(n_seqs >= 0 && n_splits >= 1 && n_splits <= 65535, "attention decode (tma): bad batch or split count");
+  MLL_REQUIRE(work == nullptr || (work_pairs >= n_seqs && work_pairs <= 65535 && n_seqs <= 65535 && n_splits <= 127),
+              "attention decode (tma): a work list of %d pairs for %d sequences and up to %d splits", work_pairs, n_seqs, n_splits);
   MLL_REQUIRE(n_splits == 1 || (scratch != nullptr && counters != nullptr),
               "attention decode (tma): %d splits need scratch memory and arrival counters", n_splits);
   MLL_REQUIRE(q != nullptr || qkv != nullptr, "attention decode (tma): neither q nor qkv");
@@ -656,10 +669,11 @@ MLL_API int mll_attn_decode_tma(const void* q, const void* qkv, int qkv_ld, cons
                        (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, n_splits, window, scale, counters,
                        (const __nv_bfloat16*)qkv, fused ? cos_table : nullptr, fused ? sin_table : nullptr,
                        fused && write_kv ? (__nv_bfloat16*)k_cache : nullptr,
-                       fused && write_kv ? (__nv_bfloat16*)v_cache : nullptr, qkv_ld, interleaved, seq_order};
+                       fused && write_kv ? (__nv_bfloat16*)v_cache : nullptr, qkv_ld, interleaved, seq_order, work};
+  const int rows = work != nullptr ? work_pairs : n_seqs;  // the grid's second index
   if (head_dim == 64)
-    return fused ? mll::launch_decode_tma<64, true>(kmap, vmap, a, n_seqs, cluster_merge, stream)
-                 : mll::launch_decode_tma<64, false>(kmap, vmap, a, n_seqs, cluster_merge, stream);
-  return fused ? mll::launch_decode_tma<128, true>(kmap, vmap, a, n_seqs, cluster_merge, stream)
-               : mll::launch_decode_tma<128, false>(kmap, vmap, a, n_seqs, cluster_merge, stream);
+    return fused ? mll::launch_decode_tma<64, true>(kmap, vmap, a, rows, cluster_merge, stream)
+                 : mll::launch_decode_tma<64, false>(kmap, vmap, a, rows, cluster_merge, stream);
+  return fused ? mll::launch_decode_tma<128, true>(kmap, vmap, a, rows, cluster_merge, stream)
+               : mll::launch_decode_tma<128, false>(kmap, vmap, a, rows, cluster_merge, stream);
 }

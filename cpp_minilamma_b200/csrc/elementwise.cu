@@ -21,7 +21,7 @@ MLL_API const char* mll_last_error() { return g_error; }
 thread_local cudaError_t mll_launch_status = cudaSuccess;
 
 // Identifies the build; the Python side checks it after loading the library.
-MLL_API int mll_abi_version() { return 25; }
+MLL_API int mll_abi_version() { return 26; }
 
 // Cache positions per page, for the Python side to check against its own constant.
 MLL_API int mll_page() { return MLL_PAGE; }

@@ -14,7 +14,7 @@ import torch
 from ..cache.paged import PAGE  # cache positions per page; the library's MLL_PAGE is checked against it on load
 from .build import KernelBuildError, load_library
 
-ABI_VERSION = 25
+ABI_VERSION = 26
 MAX_TOP_K = 1024
 
 
@@ -500,7 +500,8 @@ USE_TCGEN05_PREFILL = True      # off: the mma.sync kernel takes the tensor-core
 
 def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch, out, n_seqs: int,
                      n_heads: int, n_kv_heads: int, head_dim: int, n_splits: int, window: int,
-                     scale: float, counters: Optional[torch.Tensor] = None, order: Optional[torch.Tensor] = None) -> None:
+                     scale: float, counters: Optional[torch.Tensor] = None, order: Optional[torch.Tensor] = None,
+                     work: Optional[torch.Tensor] = None) -> None:
     """One query token per sequence (q row i belongs to sequence i) over the paged cache.
     bfloat16 runs on tensor cores (head sizes 16 .. 256 in steps of 16), float32 on the general kernel.
     `order`: optional int32 permutation of the sequences, longest context first; the TMA-fed kernel starts its
@@ -523,8 +524,10 @@ def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratc
             raise KernelError("attention decode: counters shorter than sequences x kv heads x head chunks")
     if q.dtype == torch.bfloat16 and _tma_decode(q, None, None, None, False, False, k_cache, v_cache, seq_slot, seq_ctx,
                                                 block_table, scratch, out, n_seqs, n_heads, n_kv_heads, head_dim,
-                                                n_splits, window, scale, counters, _order(order, n_seqs)):
+                                                n_splits, window, scale, counters, _order(order, n_seqs), work):
         return
+    if work is not None:
+        raise KernelError("attention decode: a work list was given, but the kernel that takes one does not run here")
     if USE_TENSOR_CORE_DECODE and lib().mll_attn_decode_mma_supported(code, head_dim):
         _check(lib().mll_attn_decode_mma(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx),
                                          _ptr(block_table), _ptr(scratch), _ptr(out), ctypes.c_int(n_seqs),
@@ -559,14 +562,33 @@ def _order(order, n_seqs: int):
     return order
 
 
+WORK_LIST_MAX_SPLITS = 32  # splits a sequence of a work list can have (the stride of the partial results)
+
+
+def decode_work_entry(sequence: int, split: int, n_splits: int) -> int:
+    """One place of a decode work list: block `split` of the `n_splits` that `sequence` is cut into."""
+    return sequence | (split << 16) | (n_splits << 24)
+
+
+def _work(work, n_seqs: int, n_splits: int):
+    if work is not None:
+        _need(work, "attention work list", torch.int32, 1)
+        if work.shape[0] < n_seqs or work.shape[0] > 65535 or n_seqs > 65535:
+            raise KernelError(f"attention decode: a work list of {work.shape[0]} places for {n_seqs} sequences")
+        if n_splits > 127:
+            raise KernelError("attention decode: a work list takes at most 127 splits a sequence")
+    return work
+
+
 def _tma_decode(q, qkv, cos, sin, interleaved, write_kv, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch, out,
-                n_seqs, n_heads, n_kv_heads, head_dim, n_splits, window, scale, counters, order=None) -> bool:
+                n_seqs, n_heads, n_kv_heads, head_dim, n_splits, window, scale, counters, order=None, work=None) -> bool:
     """Runs the TMA-fed decode kernel when it takes the problem (bfloat16, head_dim 64/128, arrival
     counters whenever the context is split); returns whether it did."""
     if not (USE_TMA_DECODE and USE_TENSOR_CORE_DECODE and lib().mll_attn_decode_tma_supported(dtype_code(out.dtype), head_dim)):
         return False
     if n_splits > 1 and counters is None:
         return False
+    work = _work(work, n_seqs, n_splits)
     _check(lib().mll_attn_decode_tma(_ptr(q), _ptr(qkv), ctypes.c_int(qkv.shape[1] if qkv is not None else 0),
                                      _ptr(cos), _ptr(sin), ctypes.c_int(int(interleaved)), ctypes.c_int(int(write_kv)),
                                      _ptr(k_cache), _ptr(v_cache), ctypes.c_longlong(k_cache.shape[0]), _ptr(seq_slot),
@@ -574,8 +596,10 @@ def _tma_decode(q, qkv, cos, sin, interleaved, write_kv, k_cache, v_cache, seq_s
                                      ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim),
                                      ctypes.c_int(block_table.shape[1]), ctypes.c_int(n_splits), ctypes.c_int(window),
                                      ctypes.c_float(scale), _ptr(counters if n_splits > 1 else None),
-                                     ctypes.c_int(int(USE_CLUSTER_MERGE)), _ptr(order), _stream()),
-           "attention_decode (TMA, cluster merge)" if USE_CLUSTER_MERGE and 2 <= n_splits <= 16
+                                     ctypes.c_int(int(USE_CLUSTER_MERGE)), _ptr(order), _ptr(work),
+                                     ctypes.c_int(work.shape[0] if work is not None else 0), _stream()),
+           "attention_decode (TMA, work list)" if work is not None
+           else "attention_decode (TMA, cluster merge)" if USE_CLUSTER_MERGE and 2 <= n_splits <= 16
            else "attention_decode (TMA)")
     return True
 
@@ -609,10 +633,12 @@ def attention_decode_fused_supported(dtype: torch.dtype, head_dim: int) -> bool:
 def attention_decode_fused(qkv, cos, sin, interleaved: bool, write_kv: bool, k_cache, v_cache, seq_slot, seq_ctx,
                            block_table, scratch, out, n_seqs: int, n_heads: int, n_kv_heads: int, head_dim: int,
                            n_splits: int, window: int, scale: float, counters: Optional[torch.Tensor] = None,
-                           order: Optional[torch.Tensor] = None) -> None:
+                           order: Optional[torch.Tensor] = None, work: Optional[torch.Tensor] = None) -> None:
     """Decode step: row i of qkv [B, (Hq + 2 Hk) d] is sequence i's new token at position seq_ctx[i] - 1.
     Rotates q and k (tables as for rope_cache_write, or None), writes k and v into the paged cache and
-    attends over it, in one launch (bfloat16, head sizes 16 .. 256 in steps of 16)."""
+    attends over it, in one launch (bfloat16, head sizes 16 .. 256 in steps of 16).
+    `work`: int32 list of `decode_work_entry` places (-1: unused) that gives every sequence its own number of
+    splits, long ones more than short ones; n_splits is then the most any has (the TMA-fed kernel only)."""
     _need(qkv, "attention qkv", torch.bfloat16, 2)
     _need(out, "attention out", torch.bfloat16, 2)
     _need(k_cache, "attention k_cache", torch.bfloat16, 4)
@@ -641,8 +667,10 @@ def attention_decode_fused(qkv, cos, sin, interleaved: bool, write_kv: bool, k_c
         if counters.shape[0] < n_seqs * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16):
             raise KernelError("attention decode: counters shorter than sequences x kv heads x head chunks")
     if _tma_decode(None, qkv, cos, sin, interleaved, write_kv, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch,
-                   out, n_seqs, n_heads, n_kv_heads, head_dim, n_splits, window, scale, counters, _order(order, n_seqs)):
+                   out, n_seqs, n_heads, n_kv_heads, head_dim, n_splits, window, scale, counters, _order(order, n_seqs), work):
         return
+    if work is not None:
+        raise KernelError("attention decode: a work list was given, but the kernel that takes one does not run here")
     _check(lib().mll_attn_decode_mma_fused(_ptr(qkv), ctypes.c_int(qkv.shape[1]), _ptr(cos), _ptr(sin),
                                            ctypes.c_int(int(interleaved)), ctypes.c_int(int(write_kv)), _ptr(k_cache),
                                            _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx), _ptr(block_table),

@@ -120,10 +120,13 @@ class DecodeGraphs:
         engine.cache.reserve([(s, 1) for s in slots])
         updates = engine.cache.take_table_updates()
         self._forget_stale_graphs()  # a prompt step or another engine call may have moved a workspace buffer
-        key = (batch, params.is_greedy, params.temperature, params.top_k, params.seed)
+        shape = StepShape(list(slots), starts, [1] * batch)
+        # parts that launch differently for different kinds of steps (a batch with one very long sequence, say)
+        # have a captured step for each kind
+        variants = tuple(part.step_variant(shape) for part in engine.providers.values())
+        key = (batch, params.is_greedy, params.temperature, params.top_k, params.seed, variants)
         cap = self._captured.get(key)
         fresh = cap is None
-        shape = StepShape(list(slots), starts, [1] * batch)
         if fresh:
             cap = self._captured[key] = _Captured(engine, batch, shape)
         else:

@@ -34,6 +34,7 @@ class Attention(Mixer):
     """
 
     capturable = True
+    work_list_min_pages = 16  # a piece of a cut sequence is no shorter than this many pages (decode_work_list)
 
     def __init__(self, params, ctx: BuildContext):
         super().__init__(params, ctx)
@@ -95,7 +96,8 @@ class Attention(Mixer):
 
     # ---- step ------------------------------------------------------------- #
     def step_metadata_key(self):
-        return ("attention.step_lists", PREFILL_TILE)  # every attention layer reads the same lists
+        # attention layers of one shape read the same lists
+        return ("attention.step_lists", PREFILL_TILE, self.n_heads, self.n_kv_heads, self.head_dim, self.window)
 
     def prepare_step(self, shape):
         """The prefill kernels' work lists: one tile of up to PREFILL_TILE query rows per entry, as
@@ -107,6 +109,9 @@ class Attention(Mixer):
         if shape.all_decode:
             if shape.n_seqs < 2:
                 return {}
+            work = self.decode_work_list(shape)
+            if work is not None:
+                return {"decode_work": work}
             return {"decode_order": sorted(range(shape.n_seqs), key=lambda i: -(shape.starts[i] + shape.lens[i]))}
         order = sorted(range(shape.n_seqs), key=lambda i: -(shape.starts[i] + shape.lens[i]))
         lists = {"tile_seq": [], "tile_row0": []}
@@ -122,6 +127,63 @@ class Attention(Mixer):
         lists["wide_seq"] = [i for _, i, _ in wide]
         lists["wide_row0"] = [row0 for _, _, row0 in wide]
         return lists
+
+    def _decode_pages(self, shape):
+        """Pages of keys that each sequence's decode step reads."""
+        pages = []
+        for start, length in zip(shape.starts, shape.lens):
+            ctx = start + length
+            first = max(0, ctx - self.window) // K.PAGE if self.window > 0 else 0
+            pages.append(max(1, -(-ctx // K.PAGE) - first))
+        return pages
+
+    def step_variant(self, shape):
+        """"list" for a decode step that runs from a list of (sequence, split) pairs (decode_work_list)."""
+        return "list" if shape.all_decode and shape.n_seqs >= 2 and self._wants_work_list(shape) else None
+
+    def _wants_work_list(self, shape) -> bool:
+        n = shape.n_seqs
+        capacity = K.attention_decode_cluster_capacity(self.ctx.act_dtype, self.head_dim, self.bias is None)
+        if capacity is None or n > 32767:
+            return False  # the kernel that takes such a list does not run
+        splits = self.decode_splits(n, self.ctx.max_positions)
+        if splits == 1:
+            return True   # too many sequences for a split of each: only a list can cut the long ones
+        # A smaller batch gives every sequence the same number of splits inside a cluster, which is the faster
+        # merge when the lengths are alike.  When the longest sequence's share is more than one and a half times
+        # what an even share of the device would read (or the shortest piece worth cutting), the list wins:
+        # 8 sequences of which one has 32,768 tokens take 77 us in clusters of 4 and 45 us in clusters of 8.
+        pages = self._decode_pages(shape)
+        group = self.n_heads // self.n_kv_heads
+        items = self.n_kv_heads * (-(-group // 16))
+        even = max(self.work_list_min_pages, -(-sum(pages) * items // (2 * capacity[2])))
+        return 2 * max(pages) > 3 * even * splits
+
+    def decode_work_list(self, shape):
+        """For a batch so large that a split of every sequence would not fit the device (decode_splits gives 1),
+        or one whose longest sequence is far longer than the rest: the launch as a list of (sequence, split)
+        pairs, as many places as sequences and again as many (at least 32) for cuts.  Sequences much longer
+        than the rest are cut - one of 32,768 tokens among 63 of a thousand kept its block busy for 280 us while
+        the others' took 45 - into pieces of about the length that an even share of the device would read,
+        none shorter than 16 pages; the pairs start longest first.  None where the step does not want a list."""
+        if not self._wants_work_list(shape):
+            return None
+        n = shape.n_seqs
+        capacity = K.attention_decode_cluster_capacity(self.ctx.act_dtype, self.head_dim, self.bias is None)
+        group = self.n_heads // self.n_kv_heads
+        items = self.n_kv_heads * (-(-group // 16))
+        pages = self._decode_pages(shape)
+        extra = max(n, 32)
+        resident = 2 * capacity[2]  # blocks that the device holds at once
+        per_split = max(self.work_list_min_pages, -(-5 * sum(pages) * items // (4 * resident)))
+        while True:
+            cuts = [min(K.WORK_LIST_MAX_SPLITS, -(-p // per_split)) for p in pages]
+            if sum(cuts) - n <= extra:
+                break
+            per_split = -(-5 * per_split // 4)
+        pairs = sorted(((-(-pages[i] // cuts[i]), -i, s) for i in range(n) for s in range(cuts[i])), reverse=True)
+        work = [K.decode_work_entry(-i, s, cuts[-i]) for _, i, s in pairs]
+        return work + [-1] * (n + extra - len(work))
 
     def capture_parameters(self, batch: int, max_positions: int):
         # a captured step serves every context length: the split count follows from the batch size alone
@@ -146,10 +208,9 @@ class Attention(Mixer):
         # of s blocks are resident together than 2 x multiprocessors / s blocks are (a cluster stays inside
         # one group of multiprocessors): the most splits whose clusters are all resident at once.
         capacity = K.attention_decode_cluster_capacity(self.ctx.act_dtype, self.head_dim, self.bias is None)
-        if capacity is not None and by_length >= 2:
+        if capacity is not None:
             fit = [s for s in range(2, min(16, by_length) + 1) if blocks <= capacity[s]]
-            if fit:
-                return fit[-1]
+            return fit[-1] if fit else 1
         return splits
 
     takes_prenormed = True  # the q/k/v product may read rows whose norm it finishes itself
@@ -164,14 +225,17 @@ class Attention(Mixer):
         qkv = self.qkv.forward(step, h, "qkv")
         cos, sin = self.position.tables()
         out = step.ws.buffer("attn", (T, Hq * d), act)
-        splits, scratch, counters, order = 1, None, None, None
+        splits, scratch, counters, order, work = 1, None, None, None, None
         if step.all_decode:
-            order = step.meta.get(self.step_metadata_key(), {}).get("decode_order")
+            lists = step.meta.get(self.step_metadata_key(), {})
+            order, work = lists.get("decode_order"), lists.get("decode_work")
             fixed = step.fixed.get(self)
             splits = fixed["splits"] if fixed else self.decode_splits(step.n_seqs, step.max_ctx)
             # room for the most splits that this batch size can ever be given, from its first decode step on, so
             # that no buffer appears or grows (an allocation in the middle of a generation) when the contexts do
             most = max(splits, self.decode_splits(step.n_seqs, self.ctx.max_positions))
+            if work is not None:  # every sequence has the number of splits its places of the list say
+                splits = most = K.WORK_LIST_MAX_SPLITS
             if most > 1:
                 scratch = step.ws.buffer(
                     "attn.scratch", (K.attention_decode_scratch_floats(step.n_seqs, Hq, d, most),), torch.float32)
@@ -183,7 +247,7 @@ class Attention(Mixer):
             K.attention_decode_fused(qkv, cos, sin, self.position.interleaved, not self.reads_cache_only,
                                      cache.k, cache.v, step.seq_slot, step.seq_ctx, cache.block_table, scratch, out,
                                      step.n_seqs, Hq, Hk, d, splits, self.window, self.scale, counters=counters,
-                                     order=order)
+                                     order=order, work=work)
         else:
             q = step.ws.buffer("q", (T, Hq * d), act)
             K.rope_cache_write(qkv, self.bias, cos, sin, step.tok_pos, step.tok_seq, step.seq_slot,
@@ -192,7 +256,7 @@ class Attention(Mixer):
             if step.all_decode:
                 K.attention_decode(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, cache.block_table, scratch, out,
                                    step.n_seqs, Hq, Hk, d, splits, self.window, self.scale, counters=counters,
-                                   order=order)
+                                   order=order, work=work)
             else:
                 tiles = step.meta[self.step_metadata_key()]
                 K.attention_prefill(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,

@@ -234,6 +234,12 @@ class Part:
         the number of sequences alone (such steps are replayed from a captured graph)."""
         return {}
 
+    def step_variant(self, shape: "StepShape"):
+        """None, or a hashable value when the part launches differently for different kinds of steps of one
+        batch size (a list of other length from `prepare_step`, another kernel).  Captured decode steps are
+        kept per (batch size, variants of all parts): the part sees only steps of one variant in each."""
+        return None
+
     def capture_parameters(self, batch: int, max_positions: int) -> Dict[str, int]:
         """Launch parameters that must not change between replays of a captured decode step of `batch`
         sequences (a captured graph serves every context length).  The part finds them in

@@ -452,6 +452,49 @@ def test_graphs_of_a_small_batch_survive_a_larger_batch_in_between(model_folders
     llm.engine.cache.check()
 
 
+@pytest.mark.parametrize("graphs", [True, False])
+@pytest.mark.parametrize("room,prompts,extra", [
+    ((0, 0, 4, 2, 2, 1, 1, 1, 1), [300, 5, 70, 2, 129], [70, 40, 70, 12, 55]),  # no split of every sequence fits
+    ((0, 0, 8, 4, 2, 1, 1, 1, 1), [5, 300, 70], [40, 70, 70]),                  # two splits each fit, one is far longer
+])
+def test_decode_batch_with_one_long_sequence_cut_by_the_work_list(model_folders, monkeypatch, graphs, room, prompts, extra):
+    """A batch too large for a split of every sequence, or one whose longest sequence is far longer than the
+    rest, runs its decode attention from a list of (sequence, split) pairs in which only the long sequences
+    are cut.  The device is made to look small (room for a few clusters of two) and the shortest piece one
+    page, so that the tiny model reaches that path: one request of 300 tokens beside short ones, decoded for
+    70 steps (the long one crosses a page, the short ones end earlier, so that the batch shrinks and the kind of
+    step changes), eagerly and under graph replay, against the plain implementation."""
+    from cpp_minilamma_b200.csrc import kernels as K
+    from cpp_minilamma_b200.parts.attention import Attention
+    real = K.attention_decode_cluster_capacity
+    monkeypatch.setattr(K, "attention_decode_cluster_capacity",
+                        lambda *a: None if real(*a) is None else tuple(room) + (0,) * 8)
+    monkeypatch.setattr(Attention, "work_list_min_pages", 1)
+    name, dtype = "D", "bfloat16"
+    folder, llm = load(model_folders, name, dtype, max_seqs=5)
+    requests = [tc.random_tokens(name, p + e, 970 + i) for i, (p, e) in enumerate(zip(prompts, extra))]
+    K.calls.clear()
+    if graphs:
+        from cpp_minilamma_b200 import EngineBackend, SamplingParams
+        from cpp_minilamma_b200.engine.generate import generate
+        got = generate(EngineBackend(llm.engine, SamplingParams()), [r[:p] for r, p in zip(requests, prompts)], extra, set())
+        for prompt_len, request, completion in zip(prompts, requests, got):
+            ref = plain_logits(folder, request[:prompt_len] + completion.tokens, dtype)
+            for i, token in enumerate(completion.tokens):
+                row = ref[prompt_len - 1 + i]
+                best = int(np.argmax(row))
+                assert token == best or row[best] - row[token] <= 0.04 * np.abs(row).max(), f"token {i}: {token} vs {best}"
+    else:
+        got = _batched_replay(llm, requests, prompts, batch_size=5)
+        for i, tokens in enumerate(requests):
+            assert_close(got[i], plain_logits(folder, tokens, dtype), dtype, f"request {i}")
+    assert K.calls.get("attention_decode (TMA, work list)", 0) > 0, K.calls
+    if len(prompts) == 3:  # once the long request is alone or the lengths are alike, the clusters are back
+        assert K.calls.get("attention_decode (TMA, cluster merge)", 0) > 0 or not graphs, K.calls
+    assert K.take_device_error() == 0
+    llm.engine.cache.check()
+
+
 @pytest.mark.parametrize("name", ["B", "D"])
 def test_decode_with_norms_folded_into_products_and_apart(model_folders, name, monkeypatch):
     # decode steps of few rows fold every norm but the first and the last into the products around it;

@@ -382,6 +382,61 @@ def test_attention_decode_in_a_given_order(hq, hk, d, splits, fused):
                            order=torch.zeros(B - 1, dtype=torch.int32, device=DEV))
 
 
+@pytest.mark.parametrize("hq,hk,d", [(32, 8, 128), (16, 16, 64), (40, 2, 64)])
+@pytest.mark.parametrize("fused", [True, False])
+@pytest.mark.parametrize("window", [0, 200])
+def test_attention_decode_from_a_work_list(hq, hk, d, fused, window):
+    """The TMA-fed kernel's launch as a list of (sequence, split) pairs: a sequence of 2,000 keys in 12 blocks and
+    one of 700 in 3 beside short ones in one block each, the pairs in any order with unused places between
+    them; every sequence against the plain reference, and twice over so that the counters are seen to come
+    back as zeros."""
+    dtype = torch.bfloat16
+    ctx = [1, 63, 2000, 65, 700, 129, 2, 300]
+    cuts = [1, 1, 12, 1, 3, 2, 1, 1] if not window else [1, 1, 4, 1, 2, 1, 1, 2]  # never more than a sequence has pages to read
+    B = len(ctx)
+    case = PagedCase(ctx, hk, d, dtype, seed=hq + d + 6)
+    qkv = rnd((B, (hq + 2 * hk) * d), dtype, 31)
+    kc, vc, slots, ctx_t, table_d = case.dev()
+    most = K.WORK_LIST_MAX_SPLITS
+    scratch = torch.empty(K.attention_decode_scratch_floats(B, hq, d, most), dtype=torch.float32, device=DEV)
+    counters = torch.zeros(B * hk * (-(-(hq // hk) // 16)), dtype=torch.int32, device=DEV)
+    pairs = [K.decode_work_entry(i, s, cuts[i]) for i in range(B) for s in range(cuts[i])]
+    shuffled = list(np.random.RandomState(3).permutation(pairs))
+    lists = [pairs + [-1] * 5, [-1, -1] + shuffled[:7] + [-1] + shuffled[7:] + [-1]]
+    outs = []
+    for work in lists:
+        for _ in range(2):
+            out = torch.full((B, hq * d), float("nan"), dtype=dtype, device=DEV)
+            k2, v2 = kc.clone(), vc.clone()
+            work_t = torch.tensor([int(w) for w in work], dtype=torch.int32, device=DEV)
+            if fused:
+                K.attention_decode_fused(qkv.to(DEV), None, None, False, True, k2, v2, slots, ctx_t, table_d, scratch, out,
+                                         B, hq, hk, d, most, window, 1.0 / math.sqrt(d), counters=counters, work=work_t)
+            else:
+                K.attention_decode(qkv[:, :hq * d].contiguous().to(DEV), k2, v2, slots, ctx_t, table_d, scratch, out,
+                                   B, hq, hk, d, most, window, 1.0 / math.sqrt(d), counters=counters, work=work_t)
+            assert int(counters.abs().sum()) == 0 and K.take_device_error() == 0
+            assert K.calls.get("attention_decode (TMA, work list)", 0) > 0
+            outs.append(out)
+    x = as64(qkv)
+    for b, c in enumerate(ctx):
+        k_all, v_all = as64(case.k[b]).copy(), as64(case.v[b]).copy()
+        if fused:   # the step's own key and value take the last place
+            k_all[c - 1] = x[b, hq * d:(hq + hk) * d].reshape(hk, d)
+            v_all[c - 1] = x[b, (hq + hk) * d:].reshape(hk, d)
+        ref = pl.causal_attention(x[b:b + 1, :hq * d].reshape(1, hq, d), k_all, v_all, q_positions=[c - 1],
+                                  window=window or None)
+        np.testing.assert_allclose(as64(outs[0][b]).reshape(hq, d), ref[0],
+                                   **attention_tol(dtype, "tensor_core", v_all[max(0, c - window) if window else 0:]),
+                                   err_msg=f"seq {b} ctx {c}")
+    same = lambda a, b: torch.equal(a.view(torch.int16), b.view(torch.int16))
+    assert all(same(outs[0], o) for o in outs[1:])  # the order of the pairs changes no bit
+    with pytest.raises(K.KernelError, match="work list"):
+        K.attention_decode(qkv[:, :hq * d].contiguous().to(DEV), kc, vc, slots, ctx_t, table_d, scratch, outs[0], B, hq, hk, d,
+                           most, 0, 1.0 / math.sqrt(d), counters=counters,
+                           work=torch.zeros(B - 1, dtype=torch.int32, device=DEV))
+
+
 @pytest.fixture(params=["tcgen05", "tensor_core", "general"])
 def prefill_impl(request):
     """tcgen05: the TMA/tensor-memory kernel (head sizes 64 and 128, else the next one);
