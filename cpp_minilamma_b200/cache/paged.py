@@ -13,6 +13,8 @@
 * **State** is per-slot storage of fixed size for mixers that keep a running state
   instead of (or beside) keys and values: `state[name] [slots, *shape]`, float32, zeroed
   when the slot is handed out.
+* One **padding slot** beyond the slots that are handed out, with a page and a state row of its own,
+  stands in for the spare rows of a decode step whose batch size was rounded up.
 
 The reference keeps one contiguous cache per sequence, `[layers, max_seq_len, kv_heads,
 head_dim]` float32 (src/kvcache.cc:16-54, src/cuda_kvcache.cc:116-179), and a `Context`
@@ -107,11 +109,13 @@ class CacheGroup:
         self.entries = list(entries)
         self.pool = PagePool(n_pages)
         self.max_blocks = max_blocks
-        shape = (len(entries), n_pages, need.n_kv_heads, PAGE, need.head_dim)
+        # one page and one block-table row beyond those that are handed out: the padding slot's (SequenceCache.pad_slot)
+        shape = (len(entries), n_pages + 1, need.n_kv_heads, PAGE, need.head_dim)
         self.k = torch.empty(shape, dtype=dtype, device=device)
         self.v = torch.empty(shape, dtype=dtype, device=device)
-        self.table_host = np.full((n_slots, max_blocks), -1, dtype=np.int32)
-        self.table_dev = torch.full((n_slots, max_blocks), -1, dtype=torch.int32, device=device)
+        self.table_host = np.full((n_slots + 1, max_blocks), -1, dtype=np.int32)
+        self.table_host[n_slots, 0] = n_pages
+        self.table_dev = torch.from_numpy(self.table_host.copy()).to(device)
         self._dirty: set = set()
         # pages of each slot by block index (None once a window let go of it)
         self.pages: List[List[Optional[int]]] = [[] for _ in range(n_slots)]
@@ -204,7 +208,7 @@ class SequenceCache:
                 by_need.setdefault(need.kv, []).append(entry)
             if need.state is not None:
                 self.state[entry] = {
-                    name: torch.zeros((self.n_slots, *shape), dtype=torch.float32, device=device)
+                    name: torch.zeros((self.n_slots + 1, *shape), dtype=torch.float32, device=device)
                     for name, shape in need.state.tensors}
         for need, entries in by_need.items():
             g = len(self.groups)
@@ -214,6 +218,10 @@ class SequenceCache:
         for entry, source in self._entry_source.items():
             if source in self._entry_source:
                 raise CacheError(f"entry {entry} reads entry {source}, which itself owns no cache")
+        # The padding slot: never handed out.  A captured decode step of a rounded-up batch size fills its
+        # spare rows with it (one token at position 0 of a page of its own, which those rows write and read);
+        # what they compute is thrown away.
+        self.pad_slot = self.n_slots
         self._free_slots: List[int] = list(range(self.n_slots - 1, -1, -1))
         self._live = [False] * self.n_slots
         self.seq_len = [0] * self.n_slots

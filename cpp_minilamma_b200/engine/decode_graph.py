@@ -26,6 +26,18 @@ from .step import Engine, StepState
 _FIELDS = 10  # tokens, tok_pos, tok_seq, seq_slot, seq_ctx, seq_qstart, seq_qlen, want, rng request, rng step
 
 
+def decode_bucket(batch: int) -> int:
+    """The batch size a decode step of `batch` sequences is captured and replayed at.  Up to 16 its own (the
+    kernels differ from row to row there); beyond, the next multiple of 8 (to 64), 16 (to 128) or 32, the spare
+    rows filled with the cache's padding slot.  A batch whose sequences end one after the other then replays a
+    handful of graphs instead of capturing one for every size on its way down: 64 requests that end three steps
+    apart took 3.3 ms a step the first time and 1.95 ms later, against 1.33 ms for a batch that stays whole."""
+    if batch <= 16:
+        return batch
+    unit = 8 if batch <= 64 else 16 if batch <= 128 else 32
+    return -(-batch // unit) * unit
+
+
 class _Captured:
     """The fixed-address buffers of one captured step: the ten index arrays of `batch` integers each, then
     the index arrays that parts prepare for decode steps (sizes fixed by the batch size), then room for the
@@ -111,7 +123,7 @@ class DecodeGraphs:
         step before it has seen them."""
         from ..csrc import kernels as K
         engine = self.engine
-        batch = len(slots)
+        n_live = len(slots)
         vocab = engine.vocab_size
         for t in tokens or ():
             if not 0 <= t < vocab:
@@ -120,6 +132,17 @@ class DecodeGraphs:
         engine.cache.reserve([(s, 1) for s in slots])
         updates = engine.cache.take_table_updates()
         self._forget_stale_graphs()  # a prompt step or another engine call may have moved a workspace buffer
+        # the step runs at a rounded-up batch size; its spare rows are one-token sequences in the padding slot
+        batch = decode_bucket(n_live)
+        if batch > self.sampler.rows:
+            batch = n_live
+        spare = batch - n_live
+        slots = list(slots) + [engine.cache.pad_slot] * spare
+        starts = starts + [0] * spare
+        requests = list(requests) + [0] * spare
+        steps = list(steps) + [0] * spare
+        if tokens is not None:
+            tokens = list(tokens) + [0] * spare
         shape = StepShape(list(slots), starts, [1] * batch)
         # parts that launch differently for different kinds of steps (a batch with one very long sequence, say)
         # have a captured step for each kind
@@ -172,7 +195,7 @@ class DecodeGraphs:
                 K.launches = before
                 torch.cuda.synchronize()
                 self._body(cap, params)
-                return self.sampler.ticket(batch)
+                return self.sampler.ticket(n_live)
             cap.launches = K.launches - before
             K.launches = before
             if self._forget_stale_graphs():
@@ -180,7 +203,7 @@ class DecodeGraphs:
                 # other batch size's graph), run eagerly and try again later
                 self._body(cap, params)
                 self._forget_stale_graphs()
-                return self.sampler.ticket(batch)
+                return self.sampler.ticket(n_live)
             cap.graph = graph
             cap.generation = engine.ws.generation
         if cap.graph is not None:
@@ -194,7 +217,7 @@ class DecodeGraphs:
             # an eager step of a new batch size may have grown buffers that the graphs of other batch sizes
             # were captured with; this one has no graph yet and keeps its index buffers
             self._forget_stale_graphs(keep=key)
-        return self.sampler.ticket(batch)
+        return self.sampler.ticket(n_live)
 
     def _forget_stale_graphs(self, keep=None) -> bool:
         """Drop every captured step if a workspace buffer has moved since the last look (a graph replays the

@@ -221,7 +221,8 @@ class Engine:
     def shared_sampler(self):
         if getattr(self, "_sampler", None) is None:
             from ..sampling.sampler import DeviceSampler
-            self._sampler = DeviceSampler(self.device, max(self.cache.n_slots, 64))
+            from .decode_graph import decode_bucket
+            self._sampler = DeviceSampler(self.device, max(decode_bucket(self.cache.n_slots), 64))
         return self._sampler
 
     def shared_decode_graphs(self):

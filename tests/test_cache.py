@@ -80,8 +80,12 @@ def test_block_tables_and_views():
     cache.flush()
     group = cache.groups[0]
     assert len(cache.groups) == 1 and group.entries == [0, 1]           # equal needs share a group
-    assert group.k.shape == (2, 8, 2, PAGE, 16)
+    assert group.k.shape == (2, 8 + 1, 2, PAGE, 16)                      # 8 pages to hand out and the padding slot's
     table = group.table_dev
+    assert table.shape[0] == cache.n_slots + 1 and cache.pad_slot == cache.n_slots
+    assert int(table[cache.pad_slot, 0]) == 8 and int(table[cache.pad_slot, 1]) == -1
+    with pytest.raises(CacheError):
+        cache.reserve([(cache.pad_slot, 1)])                            # never handed out, never grown
     pages_a = [int(p) for p in table[a, :2]]
     assert pages_a == group.pages[a] and int(table[a, 2]) == -1
     assert not set(pages_a) & {int(table[b, 0])}
@@ -110,7 +114,7 @@ def test_groups_with_different_needs_have_storage_of_their_own():
     full, window = cache.groups
     assert full.entries == [0] and window.entries == [1]
     assert cache.view(2).k.data_ptr() == cache.view(0).k.data_ptr() and not cache.view(2).owns_kv
-    assert cache.view(3).k is None and cache.view(3).state["sum"].shape == (cache.n_slots, 8)
+    assert cache.view(3).k is None and cache.view(3).state["sum"].shape == (cache.n_slots + 1, 8)  # and the padding slot
     s, = cache.acquire(1)
     cache.reserve([(s, 3 * PAGE)])
     assert window.pool.n_free == full.pool.n_free == 13
