@@ -70,6 +70,7 @@ class EngineBackend(Backend):
     def submit(self, entries, requests, steps):
         """Enqueue a step and its sampling; `collect` brings the token ids to the host."""
         self.steps += 1
+        self._rows = {e.slot: i for i, e in enumerate(entries)}  # where each slot's sampled token will lie
         if self.graphs is not None and all(len(e.tokens) == 1 for e in entries):
             return self.graphs.submit([e.slot for e in entries], [e.tokens[0] for e in entries], self.params,
                                       requests, steps)
@@ -81,13 +82,19 @@ class EngineBackend(Backend):
                                           on_device=(self.engine.extras["rng_request"], self.engine.extras["rng_step"]))
 
     def submit_ahead(self, slots, requests, steps):
-        """Enqueue one more token for `slots`, which must be the slots of the previous `submit` in
-        the same order: that step's sampled tokens are taken on the device, before the host has
-        collected them.  Returns None when this backend cannot run ahead (no captured decode)."""
+        """Enqueue one more token for `slots`, all of which the previous `submit` or `submit_ahead` must
+        have had (it may have had more: sequences that end with it): that step's sampled tokens are taken
+        on the device, before the host has collected them.  Returns None when this backend cannot run
+        ahead (no captured decode)."""
         if self.graphs is None:
             return None
+        rows = getattr(self, "_rows", {})
+        if any(s not in rows for s in slots):
+            raise ValueError("submit_ahead: a slot that the step before did not have")
+        source_rows = [rows[s] for s in slots]
         self.steps += 1
-        return self.graphs.submit(list(slots), None, self.params, requests, steps)
+        self._rows = {s: i for i, s in enumerate(slots)}
+        return self.graphs.submit(list(slots), None, self.params, requests, steps, source_rows=source_rows)
 
     def collect(self, ticket):
         from .csrc.kernels import DeviceKernelError

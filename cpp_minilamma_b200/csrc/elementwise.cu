@@ -21,7 +21,7 @@ MLL_API const char* mll_last_error() { return g_error; }
 thread_local cudaError_t mll_launch_status = cudaSuccess;
 
 // Identifies the build; the Python side checks it after loading the library.
-MLL_API int mll_abi_version() { return 26; }
+MLL_API int mll_abi_version() { return 27; }
 
 // Cache positions per page, for the Python side to check against its own constant.
 MLL_API int mll_page() { return MLL_PAGE; }
@@ -218,7 +218,25 @@ __global__ void scatter_rows_kernel(int* __restrict__ table, const int* __restri
   for (int i = threadIdx.x; i < width; i += blockDim.x) table[(size_t)target * width + i] = row[1 + i];
 }
 
+// dst[i] = src[index[i]] for i < n; an index outside [0, n_src) gives 0.
+__global__ void gather_int32_kernel(int* __restrict__ dst, const int* __restrict__ src, const int* __restrict__ index, int n,
+                                    int n_src) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int at = index[i];
+  dst[i] = at >= 0 && at < n_src ? src[at] : 0;
+}
+
 }  // namespace mll
+
+// dst: int32 [n]; src: int32 [n_src]; index: int32 [n].  dst and src must not overlap.
+MLL_API int mll_gather_int32(int* dst, const int* src, const int* index, int n, int n_src, cudaStream_t stream) {
+  MLL_REQUIRE(n >= 0 && n_src > 0, "gather_int32: bad sizes n=%d n_src=%d", n, n_src);
+  if (n == 0) return 0;
+  MLL_LAUNCH((mll::gather_int32_kernel), (n + 127) / 128, 128, 0, stream, dst, src, index, n, n_src);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
 
 // table: int32 [table_rows, width]; staged: int32 [n_rows, 1 + width], column 0 the row of `table` to replace.
 MLL_API int mll_scatter_rows(int* table, const int* staged, int n_rows, int width, int table_rows, cudaStream_t stream) {

@@ -14,7 +14,7 @@ import torch
 from ..cache.paged import PAGE  # cache positions per page; the library's MLL_PAGE is checked against it on load
 from .build import KernelBuildError, load_library
 
-ABI_VERSION = 26
+ABI_VERSION = 27
 MAX_TOP_K = 1024
 
 
@@ -131,6 +131,17 @@ def scatter_rows(table: torch.Tensor, staged: torch.Tensor, n_rows: int) -> None
         raise KernelError("scatter_rows: staged rows shorter than the count says")
     _check(lib().mll_scatter_rows(_ptr(table), _ptr(staged), ctypes.c_int(n_rows), ctypes.c_int(table.shape[1]),
                                   ctypes.c_int(table.shape[0]), _stream()), "scatter_rows")
+
+
+def gather_int32(dst: torch.Tensor, src: torch.Tensor, index: torch.Tensor, n: int) -> None:
+    """dst[i] = src[index[i]] for i < n (int32; an index outside src gives 0): the tokens that a step sampled,
+    brought into the order of the next step's rows on the device."""
+    for name, t in (("dst", dst), ("src", src), ("index", index)):
+        _need(t, f"gather_int32 {name}", torch.int32, 1)
+    if dst.shape[0] < n or index.shape[0] < n:
+        raise KernelError("gather_int32: dst or index shorter than the count says")
+    _check(lib().mll_gather_int32(_ptr(dst), _ptr(src), _ptr(index), ctypes.c_int(n), ctypes.c_int(src.shape[0]),
+                                  _stream()), "gather_int32")
 
 
 EPI_BF16, EPI_F32, EPI_SWIGLU, EPI_RESID = 0, 1, 2, 3

@@ -23,7 +23,7 @@ from ..parts.base import StepShape
 from ..sampling.sampler import DeviceSampler, SamplingParams
 from .step import Engine, StepState
 
-_FIELDS = 10  # tokens, tok_pos, tok_seq, seq_slot, seq_ctx, seq_qstart, seq_qlen, want, rng request, rng step
+_FIELDS = 11  # tokens, tok_pos, tok_seq, seq_slot, seq_ctx, seq_qstart, seq_qlen, want, rng request, rng step, source row
 
 
 def decode_bucket(batch: int) -> int:
@@ -80,6 +80,7 @@ class _Captured:
             if fixed:
                 self.state.fixed[part] = fixed
         self.rng_request, self.rng_step = d[8], d[9]
+        self.source_rows = d[10]  # for a step fed on the device: the row of the previous step that sampled each input
 
     def refresh_meta(self, shape: StepShape) -> None:
         """The parts' index arrays for this step, into their fixed places."""
@@ -114,13 +115,13 @@ class DecodeGraphs:
         return self.sampler.collect(self.submit(slots, tokens, params, requests, steps))
 
     def submit(self, slots: Sequence[int], tokens: Optional[Sequence[int]], params: SamplingParams,
-               requests: Sequence[int], steps: Sequence[int]):
+               requests: Sequence[int], steps: Sequence[int], source_rows: Optional[Sequence[int]] = None):
         """Enqueue one token for each slot: reserve, refresh the index buffer, run (eagerly the
         first time, then from the graph), sample; returns the sampler's ticket for the token ids.
 
-        `tokens` None: the inputs are the tokens that the previous step sampled for the same
-        slots in the same order; they are taken on the device, so the host can enqueue this
-        step before it has seen them."""
+        `tokens` None: the inputs are the tokens that the previous step sampled; slot i takes the one of
+        that step's row `source_rows[i]` (default: row i).  They are taken on the device, so the host can
+        enqueue this step before it has seen them."""
         from ..csrc import kernels as K
         engine = self.engine
         n_live = len(slots)
@@ -128,6 +129,12 @@ class DecodeGraphs:
         for t in tokens or ():
             if not 0 <= t < vocab:
                 raise ValueError(f"token {t} outside the vocabulary [0, {vocab})")
+        if tokens is None:
+            if source_rows is None:
+                source_rows = list(range(n_live))
+            if len(source_rows) != n_live or any(not 0 <= r < self.sampler.rows for r in source_rows):
+                raise ValueError("a step fed on the device needs, for each slot, the row of the previous step that sampled its token")
+            source_rows = list(source_rows)
         starts = [engine.cache.seq_len[s] for s in slots]
         engine.cache.reserve([(s, 1) for s in slots])
         updates = engine.cache.take_table_updates()
@@ -159,6 +166,8 @@ class DecodeGraphs:
         f[0], f[1], f[3] = (tokens if tokens is not None else 0), starts, slots
         f[4] = np.asarray(starts, dtype=np.int32) + 1
         f[8], f[9] = requests, steps
+        if source_rows is not None:
+            f[10] = source_rows + [0] * spare
         if cap.meta_layout:
             cap.refresh_meta(shape)
         used = cap.updates_at
@@ -178,8 +187,8 @@ class DecodeGraphs:
         cap.copied.record()
         for group, region, n_rows in staged:
             K.scatter_rows(group.table_dev, region, n_rows)
-        if tokens is None:
-            cap.state.tokens.copy_(self.sampler.out[:batch])  # device to device, after the index buffer's copy
+        if tokens is None:  # on the device, after the index buffer's copy: the previous step's tokens in this step's order
+            K.gather_int32(cap.state.tokens, self.sampler.out[:self.sampler.rows], cap.source_rows, batch)
         if cap.graph is None and not fresh and cap.failures < 3:
             before = K.launches
             graph = torch.cuda.CUDAGraph()

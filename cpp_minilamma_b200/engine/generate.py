@@ -131,9 +131,9 @@ def _run_batch(backend, requests, prompts, budgets, stops, results, stats=None) 
 
     A backend that has `submit`, `submit_ahead` and `collect` is kept one step ahead: while
     the host looks at the tokens of step t, step t + 1 (fed on the device with those same
-    tokens) is already running.  The step ahead is enqueued only when no sequence can end by
-    length at step t; if one ends by a stop token, the step ahead has computed a row for it
-    that is dropped, and the others' rows are used."""
+    tokens) is already running.  The step ahead holds the sequences that cannot end by length
+    at step t (those that do are known beforehand and left out); if one of them ends by a stop
+    token, the step ahead has computed a row for it that is dropped, and the others' rows are used."""
     slots = backend.acquire(len(requests))
     live = dict(zip(requests, slots))  # request -> slot, in request order
     submit = getattr(backend, "submit", None)
@@ -173,11 +173,13 @@ def _run_batch(backend, requests, prompts, budgets, stops, results, stats=None) 
         ticket = submit(entries, order, [0] * len(order)) if submit else None
         decode_began = None
         while True:
-            spec = None
-            if ahead is not None and all(len(results[r].tokens) + 1 < budgets[r] for r in order):
-                spec = ahead([live[r] for r in order], order, [step + 1] * len(order))
-                if spec is not None:
-                    count("decode", len(order))
+            spec, spec_order = None, None
+            if ahead is not None:
+                spec_order = [r for r in order if len(results[r].tokens) + 1 < budgets[r]]  # the others end with this step
+                if spec_order:
+                    spec = ahead([live[r] for r in spec_order], spec_order, [step + 1] * len(spec_order))
+                    if spec is not None:
+                        count("decode", len(spec_order))
             sampled = backend.collect(ticket) if submit else backend.step_and_sample(entries, order, [step] * len(order))
             if decode_began is None:
                 decode_began = time.perf_counter()
@@ -185,14 +187,13 @@ def _run_batch(backend, requests, prompts, budgets, stops, results, stats=None) 
                     stats["prefill_s"] = stats.get("prefill_s", 0.0) + decode_began - began
             if stats is not None:  # when each step's tokens reached the host: the prompt step first
                 stats.setdefault("step_stamps", []).append(time.perf_counter())
-            before = order
             order = apply(order, sampled)
             step += 1
             if spec is not None:
-                if order == before:   # nobody ended: the step ahead is the next step
+                if order == spec_order:   # nobody ended by a stop token: the step ahead is the next step
                     ticket = spec
                     continue
-                by_request = dict(zip(before, backend.collect(spec)))  # rows of ended sequences are dropped
+                by_request = dict(zip(spec_order, backend.collect(spec)))  # rows of ended sequences are dropped
                 if stats is not None:
                     stats["step_stamps"].append(time.perf_counter())
                 if not order:

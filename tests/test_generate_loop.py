@@ -141,10 +141,11 @@ class ScriptedAhead(Scripted):
 
     def submit_ahead(self, slots, requests, steps):
         from cpp_minilamma_b200 import StepEntry
-        assert self.last_step is not None and list(slots) == self.last_step[0], "not the previous step's slots, in order"
+        assert self.last_step is not None and set(slots) <= set(self.last_step[0]), "a slot the previous step did not have"
         assert len(self.pending) == 1, "a step ahead goes out while exactly one step is uncollected"
         self.ahead_calls += 1
-        return self.submit([StepEntry(s, [t], [0]) for s, t in zip(slots, self.last_step[1])], requests, steps)
+        sampled = dict(zip(*self.last_step))  # "on the device": by slot, whatever the order
+        return self.submit([StepEntry(s, [sampled[s]], [0]) for s in slots], requests, steps)
 
     def collect(self, ticket):
         return self.pending.pop(0)
@@ -173,8 +174,27 @@ def test_running_one_step_ahead_changes_no_result(case):
         for r, tokens, _, s in step:
             if s > 0:
                 assert tokens == [case["scripts"][r][s - 1]]
-    # a step ahead is never sent when a sequence could end by length at the step before it
-    assert ahead.ahead_calls > 0 or all(n <= 2 for n in ([case["budget"]] * 3 if isinstance(case["budget"], int) else case["budget"]))
+    # a sequence that ends by length is in no step after its last: it is fed one token fewer than it keeps
+    budgets = [case["budget"]] * len(case["prompts"]) if isinstance(case["budget"], int) else case["budget"]
+    for r, completion in enumerate(b):
+        if completion.finish_reason == "length" and budgets[r] > 0:
+            fed = sum(1 for step in ahead.log for rr, _, _, s in step if rr == r and s > 0)
+            assert fed == budgets[r] - 1, (r, fed)
+    assert ahead.ahead_calls > 0 or all(n <= 2 for n in budgets)
+
+
+def test_step_ahead_leaves_out_the_sequences_that_end_by_length():
+    """Which sequences end by length with a step is known before its tokens are: the step ahead goes out without
+    them, so a batch whose requests have different budgets stays one step ahead all the way."""
+    scripts = {0: [10, 11, 12, 13, 14, 15], 1: [20, 21, 22, 23, 24, 25], 2: [30, 31, 32, 33, 34, 35]}
+    backend = ScriptedAhead(scripts)
+    out = generate(backend, [[1], [2, 2], [3]], [6, 3, 4])
+    assert [c.tokens for c in out] == [scripts[0], scripts[1][:3], scripts[2][:4]]
+    assert all(c.finish_reason == "length" for c in out)
+    sizes = [len(step) for step in backend.log]
+    assert sizes == [3, 3, 3, 2, 1, 1]           # the prompt step, then the batch as it shrinks
+    assert backend.ahead_calls == 5               # every decode step went out ahead of the host
+    assert not backend.held and not backend.pending
 
 
 def test_step_ahead_rows_of_a_stopped_sequence_are_dropped():

@@ -93,12 +93,22 @@ def test_a_decode_step_allocates_nothing_and_copies_one_buffer_each_way(model_fo
     assert crossed, "no sequence crossed a page: the block-table rows were never sent"
     if use_graphs:
         assert backend.graphs.replays >= 8
-        # a step ahead of the host takes its tokens on the device: one more copy, device to device
+        # a step ahead of the host takes its tokens on the device (a gather kernel, by the previous step's rows):
+        # no further copy; it may leave out sequences that ended with the step before
+        from cpp_minilamma_b200.csrc import kernels as K
         backend.submit([StepEntry(s, [t], [0]) for s, t in zip(slots, last)], requests, [12] * 3)
+        gathers = K.calls.get("gather_int32", 0)
         with Traffic() as traffic:
             ticket = backend.submit_ahead(slots, requests, [13] * 3)
-        assert traffic.allocations == 0 and len(traffic.copies["h2d"]) == 1 and traffic.copies["d2d"] == [3]
+        assert traffic.allocations == 0 and len(traffic.copies["h2d"]) == 1 and traffic.copies["d2d"] == []
+        assert K.calls.get("gather_int32", 0) == gathers + 1
         backend.collect(ticket)
+        with Traffic() as traffic:
+            ticket = backend.submit_ahead([slots[2], slots[0]], [2, 0], [14] * 2)
+        assert len(traffic.copies["h2d"]) == 1 and traffic.copies["d2d"] == []
+        assert len(backend.collect(ticket)) == 2
+        with pytest.raises(ValueError, match="did not have"):
+            backend.submit_ahead([slots[1]], [1], [15])
     for s in slots:
         backend.release(s)
     llm.engine.cache.check()
