@@ -132,18 +132,23 @@ def _run_batch(backend, requests, prompts, budgets, stops, results, stats=None) 
     A backend that has `submit`, `submit_ahead` and `collect` is kept one step ahead: while
     the host looks at the tokens of step t, step t + 1 (fed on the device with those same
     tokens) is already running.  The step ahead holds the sequences that cannot end by length
-    at step t (those that do are known beforehand and left out); if one of them ends by a stop
-    token, the step ahead has computed a row for it that is dropped, and the others' rows are used."""
+    at step t (those that do are known beforehand and left out).  If one of them ends by a
+    stop token at step t, the step ahead has a row for it all the same; that row is dropped when
+    the step is collected, and the step after it goes out without the sequence - the device never
+    waits for the host."""
     slots = backend.acquire(len(requests))
     live = dict(zip(requests, slots))  # request -> slot, in request order
     submit = getattr(backend, "submit", None)
     ahead = getattr(backend, "submit_ahead", None) if submit is not None else None
     last = {}
 
-    def apply(order, sampled):
-        """Take one sampled token per request of `order`; returns the requests that go on."""
+    def apply(rows, sampled):
+        """Take one sampled token per request of `rows` that is still live (a row of a sequence that has
+        ended since the step was sent is dropped); returns the requests that go on."""
         goes_on = []
-        for r, token in zip(order, sampled):
+        for r, token in zip(rows, sampled):
+            if r not in live:
+                continue
             done = None
             if token in stops:
                 done = "stop"
@@ -165,47 +170,41 @@ def _run_batch(backend, requests, prompts, budgets, stops, results, stats=None) 
             stats[kind + "_tokens"] = stats.get(kind + "_tokens", 0) + n_tokens
 
     try:
-        order = list(live)
-        entries = [StepEntry(live[r], list(prompts[r]), [len(prompts[r]) - 1]) for r in order]
+        rows = list(live)  # the requests of the step in flight, in the order of its rows
+        entries = [StepEntry(live[r], list(prompts[r]), [len(prompts[r]) - 1]) for r in rows]
         began = time.perf_counter()
         step = 0
         count("prefill", sum(len(e.tokens) for e in entries))
-        ticket = submit(entries, order, [0] * len(order)) if submit else None
+        ticket = submit(entries, rows, [0] * len(rows)) if submit else None
         decode_began = None
         while True:
-            spec, spec_order = None, None
+            spec, spec_rows = None, None
             if ahead is not None:
-                spec_order = [r for r in order if len(results[r].tokens) + 1 < budgets[r]]  # the others end with this step
-                if spec_order:
-                    spec = ahead([live[r] for r in spec_order], spec_order, [step + 1] * len(spec_order))
+                # who goes on whatever this step samples, unless it is a stop token: the others end with this step
+                spec_rows = [r for r in rows if r in live and len(results[r].tokens) + 1 < budgets[r]]
+                if spec_rows:
+                    spec = ahead([live[r] for r in spec_rows], spec_rows, [step + 1] * len(spec_rows))
                     if spec is not None:
-                        count("decode", len(spec_order))
-            sampled = backend.collect(ticket) if submit else backend.step_and_sample(entries, order, [step] * len(order))
+                        count("decode", len(spec_rows))
+            sampled = backend.collect(ticket) if submit else backend.step_and_sample(entries, rows, [step] * len(rows))
             if decode_began is None:
                 decode_began = time.perf_counter()
                 if stats is not None:
                     stats["prefill_s"] = stats.get("prefill_s", 0.0) + decode_began - began
             if stats is not None:  # when each step's tokens reached the host: the prompt step first
                 stats.setdefault("step_stamps", []).append(time.perf_counter())
-            order = apply(order, sampled)
+            goes_on = apply(rows, sampled)
             step += 1
-            if spec is not None:
-                if order == spec_order:   # nobody ended by a stop token: the step ahead is the next step
-                    ticket = spec
-                    continue
-                by_request = dict(zip(spec_order, backend.collect(spec)))  # rows of ended sequences are dropped
-                if stats is not None:
-                    stats["step_stamps"].append(time.perf_counter())
-                if not order:
-                    break
-                order = apply(order, [by_request[r] for r in order])
-                step += 1
-            if not order:
+            if spec is not None:  # the step ahead is the next step; rows of sequences that just stopped are dropped then
+                ticket, rows = spec, spec_rows
+                continue
+            if not goes_on:
                 break
-            entries = [StepEntry(live[r], [last[r]], [0]) for r in order]
-            count("decode", len(order))
+            rows = goes_on
+            entries = [StepEntry(live[r], [last[r]], [0]) for r in rows]
+            count("decode", len(rows))
             if submit:
-                ticket = submit(entries, order, [step] * len(order))
+                ticket = submit(entries, rows, [step] * len(rows))
         if stats is not None and decode_began is not None:
             # everything after the prompt step: decode steps, sampling, host bookkeeping
             stats["decode_s"] = stats.get("decode_s", 0.0) + time.perf_counter() - decode_began

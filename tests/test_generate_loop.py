@@ -207,6 +207,8 @@ def test_step_ahead_rows_of_a_stopped_sequence_are_dropped():
     assert fed_to_0 == [[1], [10], [99]]
     fed_to_1 = [tokens for step in backend.log for r, tokens, _, _ in step if r == 1]
     assert fed_to_1 == [[2], [20], [21], [22], [23]]
+    # the stop cost no step sent from the host's side of the tokens: only the prompt step was not a step ahead
+    assert len(backend.log) - backend.ahead_calls == 1
 
 
 @pytest.mark.parametrize("backend_kind", [Scripted, ScriptedAhead])
