@@ -451,7 +451,11 @@ def main():
     achieved = decode_bytes(llm, live_tokens) / (ms * 1e-3) / 1e9
 
     e2e_value, e2e_after_prompt = time_e2e(llm, BATCH, steps, warmup, seed=2)
-    meta_ints = 10 * BATCH  # the captured step's ten index arrays; block-table rows ride along when a page is crossed
+    # what a replayed decode step copies to the device: the captured step's index arrays and the parts' own lists
+    # (counted from the buffer the engine copies; block-table rows ride along when a page is crossed)
+    captured = [cap for key, cap in llm.engine.shared_decode_graphs()._captured.items() if key[0] == BATCH and cap.graph is not None]
+    meta_ints = captured[0].updates_at if captured else 11 * BATCH
+    d2h_ints = 2 * llm.engine.shared_sampler().rows  # the sampler's token ids and status words
 
     prefill_hot_ms = time_prefill(llm, PREFILL_TOKENS, reps=5, warmup=1, seed=3)
     flops = prefill_flops(cfg, PREFILL_TOKENS)
@@ -479,7 +483,7 @@ def main():
                    "peaks": peaks["source"], "repeats": len(all_ms), "reported": "median repeat of `steps` steps"},
         "clocks": clocks,
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": 4 * meta_ints,
-                "d2h_bytes_per_step": 4 * 2 * 64, "warmup_steps": warmup,
+                "d2h_bytes_per_step": 4 * d2h_ints, "warmup_steps": warmup,
                 "first_steps_after_prompt": round(e2e_after_prompt, 1)},
         "gpu_launches": int(round(launches * steps)),
         "prefill": {"value": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PREFILL_TOKENS,
