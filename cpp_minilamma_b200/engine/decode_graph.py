@@ -3,7 +3,8 @@
 A decode step launches a few hundred small kernels; launched one by one from Python the
 host, not the GPU, sets the pace.  `DecodeGraphs` captures the whole step - every layer,
 the final norm, the head and the sampling kernel - once per (batch size, sampling
-parameters) and replays it.  What changes from step to step (token ids, positions, slots,
+parameters, kind of step that a part may name) and replays it; above 16 sequences the batch
+size is rounded up and the spare rows run in the cache's padding slot.  What changes from step to step (token ids, positions, slots,
 context lengths, random-number counters) lives in one small int32 buffer at a fixed
 address that is refreshed with a single host-to-device copy before each replay; block
 tables are updated by the cache outside the graph.  The first step of a new batch size
