@@ -497,7 +497,7 @@ __device__ __forceinline__ void cluster_slice(int vocab, int rank, int& begin, i
 // thread whose run holds the threshold reports its token to block 0 (the lowest id wins), which writes it out
 // after the second barrier.
 template <int VPT>
-__global__ void __cluster_dims__(SC_CLUSTER, 1, 1) __launch_bounds__(SC_THREADS, (VPT <= 16 ? 2 : 1))
+__global__ void __cluster_dims__(SC_CLUSTER, 1, 1) __launch_bounds__(SC_THREADS, (VPT <= 32 ? 2 : 1))
 sample_temperature_cluster_kernel(const float* __restrict__ logits, int vocab, float temperature,
                                   unsigned long long seed, const int* __restrict__ request,
                                   const int* __restrict__ step, int* __restrict__ tokens, int* __restrict__ status,
@@ -586,7 +586,7 @@ constexpr int SC_CAND = 1024;
 // kept out of 128,256 that is after the first pass - they all go to block 0, which sorts them and draws among the
 // first k.  Only when more than 1,024 keys tie with the k-th does the exact rule need the counts of every block.
 template <int VPT>
-__global__ void __cluster_dims__(SC_CLUSTER, 1, 1) __launch_bounds__(SC_THREADS, (VPT <= 16 ? 2 : 1))
+__global__ void __cluster_dims__(SC_CLUSTER, 1, 1) __launch_bounds__(SC_THREADS, (VPT <= 32 ? 2 : 1))
 sample_top_k_cluster_kernel(const float* __restrict__ logits, int vocab, int top_k, float temperature,
                             unsigned long long seed, const int* __restrict__ request, const int* __restrict__ step,
                             int* __restrict__ tokens, int* __restrict__ status, MllDeviceErrorWords errors) {
