@@ -96,3 +96,90 @@ def test_trace_run_reports_a_full_cache(model_folders, tmp_path):
          "--out", str(tmp_path / "o"), "--max-tokens", "64"],
         input=json.dumps(steps[0]) + "\n", capture_output=True, text=True, timeout=600)
     assert proc.returncode != 0 and "free" in proc.stderr
+
+
+def random_trace(name, rng):
+    """Batches of 1 to 20 requests that start together with unequal prompts and go on one token each, the
+    shorter ones ending earlier; up to two batches live at once, their steps interleaved (a live request is not in
+    every step); places wanted: none, the last, all, or a few in any order.  Returns (steps, expectation, requests,
+    the most tokens held at once, each request's count rounded up to 64), expectation[step] = [(id, positions)]."""
+    top, vocab = tc.TINY[name]["max_position_embeddings"], tc.TINY[name]["vocab_size"]
+    steps, expect, requests, held, batches = [], {}, {}, {}, []
+    peak, made, n_batches = 0, 0, int(rng.randint(2, 6))
+
+    def add(entries, rows, end):
+        nonlocal peak
+        peak = max(peak, sum(-(-n // 64) * 64 for n in held.values()))
+        steps.append({"step": len(steps), "entries": entries, "end": end})
+        if rows:
+            expect[len(steps) - 1] = rows
+        for i in end:
+            del held[i]
+
+    while made < n_batches or batches:
+        if made < n_batches and len(batches) < 2 and (not batches or rng.rand() < 0.3):
+            ids = [f"r{made}_{i}" for i in range(int(rng.choice([1, 2, 3, 5, 8, 13, 20])))]
+            fed, total = {}, {}
+            entries, rows = [], []
+            for i in ids:
+                prompt = int(min(top - 2, rng.choice([1, 2, 7, 31, 63, 64, 65, 100, 129, 200])))
+                total[i] = min(top, prompt + int(rng.choice([0, 1, 2, 5, 17, 40])))
+                fed[i] = min(prompt, total[i])
+                requests[i] = [int(t) for t in rng.randint(0, vocab, size=total[i])]
+                kind = rng.randint(4)
+                want = ([], [fed[i] - 1], list(range(fed[i])), [int(x) for x in rng.randint(0, fed[i], size=3)])[kind]
+                entries.append({"id": i, "tokens": requests[i][:fed[i]], "want": want})
+                if want:
+                    rows.append((i, want))
+                held[i] = fed[i]
+            add(entries, rows, [i for i in ids if fed[i] == total[i]])
+            alive = [i for i in ids if fed[i] < total[i]]
+            if alive:
+                batches.append({"ids": alive, "fed": fed, "total": total})
+            made += 1
+            continue
+        batch = batches[int(rng.randint(len(batches)))]
+        entries, rows = [], []
+        for i in batch["ids"]:
+            want = [0] if rng.rand() < 0.8 else []
+            entries.append({"id": i, "tokens": [requests[i][batch["fed"][i]]], "want": want})
+            if want:
+                rows.append((i, [batch["fed"][i]]))
+            batch["fed"][i] += 1
+            held[i] = batch["fed"][i]
+        end = [i for i in batch["ids"] if batch["fed"][i] == batch["total"][i]]
+        add(entries, rows, end)
+        batch["ids"] = [i for i in batch["ids"] if i not in end]
+        if not batch["ids"]:
+            batches.remove(batch)
+    return steps, expect, requests, peak
+
+
+@pytest.mark.parametrize("name,dtype,seed", [("D", "bfloat16", 4), ("B", "float32", 5), ("C", "bfloat16", 3), ("A", "float32", 1)])
+def test_random_traces_with_the_cache_sized_to_the_token(model_folders, tmp_path, name, dtype, seed):
+    """A trace drawn from a seed, the steps sent one at a time (the next only after `done <step>`), and
+    --max-tokens exactly what the trace holds at its fullest."""
+    folder = model_folders(name, dtype)
+    steps, expect, requests, peak = random_trace(name, np.random.RandomState(seed))
+    out = tmp_path / "out"
+    proc = subprocess.Popen(
+        [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype, "--out", str(out),
+         "--max-tokens", str(peak)], stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    try:
+        for s in steps:
+            proc.stdin.write(json.dumps(s) + "\n")
+            proc.stdin.flush()
+            line = proc.stdout.readline().strip()
+            assert line == f"done {s['step']}", (line, proc.stderr.read()[-2000:] if proc.poll() is not None else "")
+        proc.stdin.close()
+        assert proc.wait(timeout=120) == 0
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+    vocab = tc.TINY[name]["vocab_size"]
+    refs = {i: plain_logits(folder, tokens, dtype) for i, tokens in requests.items()}
+    assert sorted(int(f[:-4]) for f in os.listdir(out)) == sorted(expect)   # a step that wants nothing writes nothing
+    for step, rows in expect.items():
+        got = np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(-1, vocab)
+        want = np.concatenate([refs[i][positions] for i, positions in rows])
+        assert_close(got, want, dtype, f"{name} {dtype} seed {seed} step {step}")
