@@ -369,7 +369,7 @@ def profile_region(args):
     import cpp_minilamma_b200 as ml
     from cpp_minilamma_b200 import StepEntry
     cfg = shape_config(args.shape, args.layers or 4)
-    context = SHAPES[args.shape]["context"]
+    context = max(SHAPES[args.shape]["context"], args.context + 64)  # room for a longer --context than the workload's
     llm = ml.random_model(cfg, seed=0, dtype="bfloat16", max_tokens=(args.batch + 1) * context, max_positions=context,
                           max_seqs=args.batch + 2, max_step_tokens=8192)
     rng = np.random.RandomState(0)
