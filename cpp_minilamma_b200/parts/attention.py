@@ -150,14 +150,16 @@ class Attention(Mixer):
         if splits == 1:
             return True   # too many sequences for a split of each: only a list can cut the long ones
         # A smaller batch gives every sequence the same number of splits inside a cluster, which is the faster
-        # merge when the lengths are alike.  When the longest sequence's share is more than one and a half times
-        # what an even share of the device would read (or the shortest piece worth cutting), the list wins:
-        # 8 sequences of which one has 32,768 tokens take 77 us in clusters of 4 and 45 us in clusters of 8.
+        # merge when the lengths are alike, and still when they are spread (4 sequences of 1,024 to 16,384 tokens:
+        # 1.04 ms a step of 8 layers in clusters of 8, 1.09 to 1.20 from the list, whose cut sequences merge
+        # through global memory).  When the longest sequence's share is more than three times what an even share
+        # of the device would read (or the shortest piece worth cutting), the list wins: 8 sequences of which one
+        # has 32,768 tokens 1.25 against 1.58 ms, 16 sequences 1.29 against 2.06.
         pages = self._decode_pages(shape)
         group = self.n_heads // self.n_kv_heads
         items = self.n_kv_heads * (-(-group // 16))
         even = max(self.work_list_min_pages, -(-sum(pages) * items // (2 * capacity[2])))
-        return 2 * max(pages) > 3 * even * splits
+        return max(pages) > 3 * even * splits
 
     def decode_work_list(self, shape):
         """For a batch so large that a split of every sequence would not fit the device (decode_splits gives 1),

@@ -491,13 +491,13 @@ def test_batches_above_16_run_at_rounded_up_sizes_with_padding_rows(model_folder
 @pytest.mark.parametrize("graphs", [True, False])
 @pytest.mark.parametrize("room,prompts,extra", [
     ((0, 0, 4, 2, 2, 1, 1, 1, 1), [300, 5, 70, 2, 129], [70, 40, 70, 12, 55]),  # no split of every sequence fits
-    ((0, 0, 8, 4, 2, 1, 1, 1, 1), [5, 300, 70], [40, 70, 70]),                  # two splits each fit, one is far longer
+    ((0, 0, 10, 5, 2, 1, 1, 1, 1), [5, 430, 70], [40, 70, 70]),                 # two splits each fit, one is far longer
 ])
 def test_decode_batch_with_one_long_sequence_cut_by_the_work_list(model_folders, monkeypatch, graphs, room, prompts, extra):
     """A batch too large for a split of every sequence, or one whose longest sequence is far longer than the
     rest, runs its decode attention from a list of (sequence, split) pairs in which only the long sequences
     are cut.  The device is made to look small (room for a few clusters of two) and the shortest piece one
-    page, so that the tiny model reaches that path: one request of 300 tokens beside short ones, decoded for
+    page, so that the tiny model reaches that path: one request of 300 or 430 tokens beside short ones, decoded for
     70 steps (the long one crosses a page, the short ones end earlier, so that the batch shrinks and the kind of
     step changes), eagerly and under graph replay, against the plain implementation."""
     from cpp_minilamma_b200.csrc import kernels as K
